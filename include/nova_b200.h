@@ -1,0 +1,233 @@
+/*
+ * nova_b200.h — C ABI of libnova_b200, the B200 (sm_100a) execution backend for
+ * the Nova compiler's matmul hot path.
+ *
+ * The Nova reference lowers nova.matmul / nova.linear / linalg.matmul /
+ * linalg.batch_matmul (+ fused bias / ReLU / GELU consumers) to device code it
+ * generates itself.  This library replaces everything below the point where
+ * those ops reach code generation: a lowering pass rewrites each contraction
+ * (and the row-wise ops next to it) into ONE call through this header.  The
+ * reference already calls C runtimes from compiled IR in exactly this style —
+ * plain `llvm.call`s to externs declared by getOrDeclareFunc
+ * (lib/Transforms/FixGpuLaunch.cpp:17-33), with device pointers taken from
+ * memref-descriptor field 1 (:245-246) and a stream handle (:99-104).
+ *
+ * Conventions
+ *  - every function returns a nova_b200_status (0 == OK); nothing throws,
+ *    aborts or exits;  nova_b200_last_error_string() describes the last failure
+ *    on the calling thread.
+ *  - pointers named *_dev are device pointers on the current CUDA device; the
+ *    library never allocates user-visible outputs.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls
+ *    only enqueue work, they do not synchronise (the *_host helpers do).
+ *  - there is no CPU fallback: without a usable sm_100 device every compute
+ *    entry point fails with NOVA_B200_ERR_NO_DEVICE.
+ */
+#ifndef NOVA_B200_H_
+#define NOVA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* the library is built with -fvisibility=hidden; everything declared here is exported */
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define NOVA_B200_ABI_VERSION 1
+
+typedef enum nova_b200_status {
+  NOVA_B200_OK = 0,
+  NOVA_B200_ERR_INVALID_ARG = 1,    /* null pointer, negative extent, bad enum                      */
+  NOVA_B200_ERR_LAYOUT = 2,         /* stride / pitch combination the kernels cannot express        */
+  NOVA_B200_ERR_UNSUPPORTED = 3,    /* valid request with no kernel (e.g. f64)                      */
+  NOVA_B200_ERR_CUDA = 4,           /* a CUDA runtime / driver call failed                          */
+  NOVA_B200_ERR_NO_DEVICE = 5,      /* no CUDA device, or not compute capability 10.x               */
+  NOVA_B200_ERR_DEVICE_TIMEOUT = 6, /* a bounded in-kernel wait gave up (see nova_b200_device_status) */
+  NOVA_B200_ERR_TOO_LARGE = 7       /* extent exceeds a documented limit                            */
+} nova_b200_status;
+
+typedef enum nova_b200_dtype {
+  NOVA_B200_F32 = 0,
+  NOVA_B200_F16 = 1,
+  NOVA_B200_BF16 = 2,
+  NOVA_B200_I16 = 3, /* index types for gather; i16 is zero-extended like the reference */
+  NOVA_B200_I32 = 4,
+  NOVA_B200_I64 = 5
+} nova_b200_dtype;
+
+/* Fused consumers of the contraction, as classified by the reference's isEpilogue
+ * (lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1876-1895). */
+typedef enum nova_b200_act {
+  NOVA_B200_ACT_NONE = 0,
+  NOVA_B200_ACT_RELU = 1,      /* nova.relu -> arith.maximumf(x, 0)  (NovaToLinalg.cpp:1053-1084)           */
+  NOVA_B200_ACT_GELU_TANH = 2  /* nova.gelu, tanh form (NovaToLinalgGeneric.cpp:1277-1337)                 */
+} nova_b200_act;
+
+/* What the accumulator starts from.  FuseMatmulBias (lib/Transforms/FuseMatmulBias.cpp:95-193)
+ * turns `fill(0) + matmul + add` into a matmul whose outs IS the (broadcast) bias or a full
+ * residual tensor; a matmul whose outs is a live tensor reads C itself
+ * (readingExistingAccBuffer, NovaKernelConfig.cpp:386-397). */
+typedef enum nova_b200_acc_init {
+  NOVA_B200_INIT_ZERO = 0,
+  NOVA_B200_INIT_BIAS_ROW = 1,      /* bias[N], broadcast along rows                         */
+  NOVA_B200_INIT_RESIDUAL_FULL = 2, /* residual[batch, M, N] (own pitch and batch stride)     */
+  NOVA_B200_INIT_FROM_C = 3         /* C holds the initial accumulator and is overwritten     */
+} nova_b200_acc_init;
+
+typedef enum nova_b200_f32_mode {
+  NOVA_B200_TF32X3 = 0, /* hi/lo split, three tensor-core products: rel. error ~1e-6 (default)            */
+  NOVA_B200_TF32X1 = 1  /* single TF32 product, what the reference's own GPU path computes
+                           (NVIDIATargetUtils.cpp:58-65)                                                  */
+} nova_b200_f32_mode;
+
+/* One (batched) contraction  C[b] = act( init[b] + op(A[b]) * op(B[b]) ).
+ *
+ * Replaces, per call: linalg.matmul / linalg.batch_matmul as emitted by NovaMatmulOpLowering
+ * (include/Compiler/Translation/NovaToLinalg/NovaToLinalg.cpp:874-1050), the rank-2/3 forms of
+ * NovaLinearOpLowering (NovaToLinalgGeneric.cpp:1623-1823) including its batch-shared weight
+ * (batch_stride_b == 0, :1726-1753), linalg.matmul_transpose_a (NovaToLinalg.cpp:824-872, trans_a),
+ * the bias-as-accumulator form of FuseMatmulBias and the trailing GELU / ReLU generic.
+ *
+ * Layout: all tensors row-major with unit inner stride; ld* are row pitches in ELEMENTS,
+ * batch strides are in elements (0 = the same matrix for every batch).  With trans_a the buffer
+ * holds A as [K, M] (lda >= M); with trans_b it holds B as [N, K] (ldb >= K).  Accumulation is
+ * always fp32.  Ragged M/N/K need no padding.  Operands whose base or pitch is not a multiple of
+ * 16 bytes are read through a non-TMA loader instead of being repacked (see nova_b200_gemm_plan). */
+typedef struct nova_b200_gemm_args {
+  uint32_t struct_size; /* = sizeof(nova_b200_gemm_args), for ABI evolution */
+  int32_t dtype_ab;     /* NOVA_B200_F32 / F16 / BF16: element type of A and B */
+  int32_t dtype_c;      /* element type of C, bias and residual */
+  int32_t trans_a;
+  int32_t trans_b;
+  int32_t act;          /* nova_b200_act */
+  int32_t init;         /* nova_b200_acc_init */
+  int32_t f32_mode;     /* nova_b200_f32_mode, used when dtype_ab == F32 */
+  int64_t batch, M, N, K;
+  const void* A;
+  const void* B;
+  void* C;
+  const void* bias;     /* [N], dtype_c; used when init == BIAS_ROW */
+  const void* residual; /* used when init == RESIDUAL_FULL */
+  int64_t lda, ldb, ldc, ldr;
+  int64_t batch_stride_a, batch_stride_b, batch_stride_c, batch_stride_r;
+} nova_b200_gemm_args;
+
+/* How a call will be executed; filled by nova_b200_gemm_plan without launching anything. */
+typedef struct nova_b200_gemm_plan_info {
+  int32_t loader_a;     /* 0 = TMA, 1 = predicated ld.global loader (unaligned base or pitch) */
+  int32_t loader_b;
+  int32_t store_c;      /* 0 = 16-byte vector stores, 1 = element stores (unaligned C pitch)   */
+  int32_t block_m, block_n, block_k;
+  int32_t stages;
+  int32_t grid;         /* persistent CTAs launched */
+  int64_t tiles;        /* output tiles over all batches */
+  int64_t scratch_bytes;/* device scratch the call uses (hi/lo split of f32 operands), else 0 */
+} nova_b200_gemm_plan_info;
+
+/* Binds the calling thread's current device (or `device` >= 0) : checks compute capability 10.x,
+ * resolves the tensor-map encoder, allocates the 4-byte device status word.  Idempotent.
+ * Counterpart in the reference: none explicit — mgpuModuleLoad does this implicitly
+ * (lib/Transforms/LLVMGPU/Passes.cpp:482-483). */
+int32_t nova_b200_init(int32_t device);
+/* Frees per-device state (scratch pool, status words).  Safe to call without init. */
+int32_t nova_b200_shutdown(void);
+const char* nova_b200_last_error_string(void);
+int32_t nova_b200_abi_version(void);
+
+/* The contraction; device pointers; enqueues on `stream`. */
+int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream);
+/* Validation + kernel selection only (no launch); usable without a GPU. */
+int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
+/* Same contraction with HOST pointers for A, B, C, bias, residual: stages them through
+ * library-owned device buffers (H2D, kernel, D2H) and synchronises before returning.  This is the
+ * form the reference's host harnesses use (driver.cpp:22-40: host descriptors in, result out). */
+int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args);
+
+/* y = act(x), n elements, standalone nova.gelu / nova.relu (NovaToLinalgGeneric.cpp:1277-1337,
+ * NovaToLinalg.cpp:1053-1084) for graphs where the activation is not adjacent to a contraction. */
+int32_t nova_b200_activation(const void* x_dev, void* y_dev, int64_t n, int32_t dtype, int32_t act, void* stream);
+
+/* out[r, c] = a[r, c] + b[c]  (b_is_full == 0)  or  a[r, c] + b[r, c]: nova.add with a row-broadcast
+ * operand (NovaToLinalg.cpp:115-194; the `[1,10]` bias of ltest/test_cpu.mlir). */
+int32_t nova_b200_add_rowbcast(const void* a_dev, const void* b_dev, void* out_dev, int64_t rows, int64_t cols,
+                               int32_t b_is_full, int32_t dtype, void* stream);
+
+/* nova.layer_norm over the last dim of x[rows, D] (NovaLayerNormPattern,
+ * NovaToLinalgGeneric.cpp:1997-2126): y = (x - mean) * rsqrt(var + 1e-5) * gamma + beta with
+ * var = E[x^2] - mean^2; also returns the RAW row sum (not the mean) and rstd, as the reference does
+ * (:2121-2123).  Statistics are computed in fp32; mean_sum / rstd have dtype `dtype`. Either may be NULL. */
+int32_t nova_b200_layer_norm(const void* x_dev, const void* gamma_dev, const void* beta_dev, void* y_dev,
+                             void* mean_sum_dev, void* rstd_dev, int64_t rows, int64_t D, int32_t dtype,
+                             void* stream);
+
+/* nova.softmax along the last dim of x[rows, D] (NovaSoftmaxForwardPattern,
+ * NovaToLinalgGeneric.cpp:1427-1534): e = exp(x - max), out = e * (1 / max(sum e, 1e-7)). */
+int32_t nova_b200_softmax(const void* x_dev, void* y_dev, int64_t rows, int64_t D, int32_t dtype, void* stream);
+
+/* nova.gather (NovaGatherOpLowering, NovaToLinalgGeneric.cpp:2372-2472) on the canonical view
+ * in[pre, axis_len, post], idx[n_idx] (or idx[pre, n_idx] when batched_idx != 0) -> out[pre, n_idx, post].
+ * Bit-exact row copies.  Indices < 32 bits wide are zero-extended (:2446-2449).  Out-of-range
+ * indices produce zero rows and are counted in *bad_count_dev (int64, may be NULL). */
+int32_t nova_b200_gather(const void* in_dev, const void* idx_dev, void* out_dev, int64_t pre, int64_t axis_len,
+                         int64_t post, int64_t n_idx, int32_t idx_dtype, int32_t batched_idx, int32_t elem_bytes,
+                         int64_t* bad_count_dev, void* stream);
+
+/* Reads (and clears) the device-side status word of the current device: 0 when every bounded wait
+ * inside the kernels completed; otherwise a code naming the wait that gave up.  Synchronises the device. */
+int32_t nova_b200_device_status(uint32_t* code_out);
+
+/* ---- memref-descriptor entry points ------------------------------------------------------------
+ * The outer boundary of the reference is `_mlir_ciface_<fn>(MemRef* result, MemRef* in0, ...)` with
+ * descriptors {allocated, aligned, offset, sizes[R], strides[R]} (driver.cpp:9-15,
+ * robust_driver.cpp:9-23; expanded 7-scalar form in test/wrapper.c:15-24).  The lowering pass emits
+ * `func.call`s with llvm.emit_c_interface to the functions below, so they take that struct as-is.
+ * `aligned + offset` is the first element; strides are in elements; the inner stride must be 1
+ * (or the two inner dims swapped, which selects trans_a / trans_b).  Buffers may be device or
+ * host memory (detected per pointer); host buffers are staged like nova_b200_gemm_host. */
+typedef struct nova_b200_memref2d {
+  void* allocated;
+  void* aligned;
+  int64_t offset;
+  int64_t sizes[2];
+  int64_t strides[2];
+} nova_b200_memref2d;
+
+typedef struct nova_b200_memref3d {
+  void* allocated;
+  void* aligned;
+  int64_t offset;
+  int64_t sizes[3];
+  int64_t strides[3];
+} nova_b200_memref3d;
+
+typedef struct nova_b200_memref1d {
+  void* allocated;
+  void* aligned;
+  int64_t offset;
+  int64_t sizes[1];
+  int64_t strides[1];
+} nova_b200_memref1d;
+
+/* C = A * B (linalg.matmul, NovaToLinalg.cpp:1028-1048).  dtype is the element type of all three
+ * (f32 / f16 / bf16 with fp32 accumulation).  Returns a status as well as writing C. */
+int32_t _mlir_ciface_nova_b200_matmul(nova_b200_memref2d* C, nova_b200_memref2d* A, nova_b200_memref2d* B,
+                                      int32_t dtype);
+/* C[b] = A[b] * B[b] (linalg.batch_matmul, NovaToLinalg.cpp:1039-1043); ab_dtype inputs, c_dtype output. */
+int32_t _mlir_ciface_nova_b200_batch_matmul(nova_b200_memref3d* C, nova_b200_memref3d* A, nova_b200_memref3d* B,
+                                            int32_t ab_dtype, int32_t c_dtype);
+/* Y = act(X * W + bias) (nova.linear rank 2, NovaToLinalgGeneric.cpp:1623-1823, + optional activation). */
+int32_t _mlir_ciface_nova_b200_linear(nova_b200_memref2d* Y, nova_b200_memref2d* X, nova_b200_memref2d* W,
+                                      nova_b200_memref1d* bias, int32_t dtype, int32_t act);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOVA_B200_H_ */

@@ -1,0 +1,476 @@
+// The contraction kernel of libnova_b200: a persistent, warp-specialised sm_100a GEMM.
+//
+//   warp 0      TMA producer: one lane streams 128-byte-swizzled operand boxes into a
+//               kStages-deep shared-memory ring (mbarrier full/empty pairs).
+//   warp 1      owns tensor memory (alloc/dealloc) and issues tcgen05.mma from one lane;
+//               tcgen05.commit releases ring stages and publishes finished accumulators.
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (TMEM lane == output row),
+//               add bias / residual, apply ReLU / GELU, cast, store.  Two accumulator
+//               buffers in TMEM let the epilogue of tile i overlap the mainloop of tile i+1.
+//   warps 6..9  (only launched when an operand cannot use TMA) predicated ld.global
+//               loader for operands whose base or pitch is not a multiple of 16 bytes.
+//
+// One CTA per SM; tiles are handed out round-robin in a grouped raster order so that
+// the CTAs of one wave share A row-panels and B column-panels in L2.
+//
+// Ragged extents need no padded copies: TMA zero-fills out-of-bounds box elements
+// (zeros add nothing along K) and the epilogue predicates its stores on row < M, col < N.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx_sm100.cuh"
+#include "runtime.h"
+
+namespace nova {
+
+static constexpr int kBlockM = 128;          // UMMA M (cta_group::1): TMEM lane i holds output row i
+static constexpr int kSwizzleBytes = 128;    // operand rows in shared memory are 128 bytes
+static constexpr int kNumEpilogueWarps = 4;
+static constexpr int kNumLoaderWarps = 4;
+static constexpr int kFirstEpilogueWarp = 2;
+static constexpr int kFirstLoaderWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
+static constexpr int kThreadsTma = 32 * kFirstLoaderWarp;                      // 192
+static constexpr int kThreadsWithLoader = 32 * (kFirstLoaderWarp + kNumLoaderWarps);  // 320
+
+struct GemmKernelParams {
+  int32_t M, N, K, batch;
+  int32_t m_blocks, n_blocks, k_blocks;
+  int32_t group_m;    // raster: tiles walk group_m row-blocks of one column-block before the next column
+  int32_t tiles;      // batch * m_blocks * n_blocks
+  int32_t a_batch_mul, b_batch_mul;  // 0 when the operand is shared by every batch, else 1
+  uint32_t idesc;     // tcgen05 instruction descriptor
+  uint32_t a_desc_hi, b_desc_hi;      // shared-memory matrix descriptor, bits 32..63
+  uint32_t a_desc_lbo, b_desc_lbo;    // leading-byte-offset field, already shifted into bits 16..29
+  uint32_t a_kstep, b_kstep;          // bytes the descriptor start address advances per UMMA K step
+  int32_t loader_a, loader_b;         // 0 = TMA, 1 = ld.global loader warps
+  // raw operand views for the ld.global loader
+  const void* A; const void* B;
+  int64_t lda, ldb, stride_a, stride_b;
+  // epilogue
+  void* C;
+  const void* bias;
+  const void* residual;
+  int64_t ldc, stride_c, ldr, stride_r;
+  int32_t act, init, out_dtype, vec_store;
+  uint32_t* status;
+};
+
+// kOpTerms: operand copies per stage (2 = hi and lo halves of the 3xTF32 split, else 1)
+template <int kBlockN, int kOpTerms, int kStages>
+struct GemmSmemLayout {
+  static constexpr int kATile = kBlockM * kSwizzleBytes;  // one operand term of A per stage
+  static constexpr int kBTile = kBlockN * kSwizzleBytes;
+  static constexpr int kStageBytes = kOpTerms * (kATile + kBTile);
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]; then tmem base + abort flag
+  static constexpr int kNumBarriers = 2 * kStages + 4;
+  static constexpr int kBarrierOffset = kRingBytes;
+  static constexpr int kMiscOffset = kBarrierOffset + 8 * kNumBarriers;
+  static constexpr int kTotalBytes = kMiscOffset + 16;
+  static constexpr int kDynamicBytes = kTotalBytes + 1024;  // slack to align the ring to 1024 bytes
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_field, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | static_cast<uint64_t>(lbo_field | ((addr >> 4) & 0x3fffu));
+}
+
+struct TileCoord {
+  int32_t batch, m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmKernelParams& p, int32_t tile) {
+  const int32_t per_batch = p.m_blocks * p.n_blocks;
+  TileCoord t;
+  t.batch = tile / per_batch;
+  const int32_t r = tile - t.batch * per_batch;
+  const int32_t group_tiles = p.group_m * p.n_blocks;
+  const int32_t g = r / group_tiles;
+  const int32_t first_m = g * p.group_m;
+  const int32_t gm = min(p.group_m, p.m_blocks - first_m);
+  const int32_t rr = r - g * group_tiles;
+  t.n_blk = rr / gm;
+  t.m_blk = first_m + (rr - t.n_blk * gm);
+  return t;
+}
+
+// ---------------------------------------------------------------- epilogue math
+
+__device__ __forceinline__ float gelu_tanh_f32(float x) {
+  // 0.5*x*(1+tanh(u)) == x / (1 + exp(-2u)),  u = 0.79788456*(x + 0.044715*x^3)
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x, x * x, x);
+  return __fdividef(x, 1.0f + __expf(-2.0f * u));
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// One thread finishes 32 consecutive columns of one output row.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_row_chunk(const GemmKernelParams& p, const uint32_t (&acc)[32], int32_t batch,
+                                                   int32_t row, int32_t col0) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
+  const int32_t ncols = min(32, p.N - col0);
+  OutT* crow = reinterpret_cast<OutT*>(p.C) + static_cast<int64_t>(batch) * p.stride_c +
+               static_cast<int64_t>(row) * p.ldc + col0;
+  if (p.init == NOVA_B200_INIT_BIAS_ROW) {
+    const OutT* b = reinterpret_cast<const OutT*>(p.bias) + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += to_f32<OutT>(__ldg(b + j));
+  } else if (p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_FROM_C) {
+    const OutT* r = p.init == NOVA_B200_INIT_FROM_C
+                        ? crow
+                        : reinterpret_cast<const OutT*>(p.residual) + static_cast<int64_t>(batch) * p.stride_r +
+                              static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += to_f32<OutT>(r[j]);
+  }
+  if (p.act == NOVA_B200_ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+  } else if (p.act == NOVA_B200_ACT_GELU_TANH) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f32(v[j]);
+  }
+  constexpr int kPerVec = 16 / static_cast<int>(sizeof(OutT));
+  if (p.vec_store && ncols == 32) {
+#pragma unroll
+    for (int j = 0; j < 32; j += kPerVec) {
+      union { uint4 u; OutT e[kPerVec]; } pk;
+#pragma unroll
+      for (int e = 0; e < kPerVec; ++e) pk.e[e] = from_f32<OutT>(v[j + e]);
+      *reinterpret_cast<uint4*>(crow + j) = pk.u;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) crow[j] = from_f32<OutT>(v[j]);
+  }
+}
+
+// ---------------------------------------------------------------- the kernel
+//
+// kElemBytes : 2 (f16 / bf16, kind::f16) or 4 (f32 read as tf32, kind::tf32)
+// kTerms     : 1, or 3 for the hi/lo split (operand term 0 = hi, 1 = lo; products lo*hi + hi*lo + hi*hi)
+// kAMn/kBMn  : operand is MN-major in global memory (A stored [K,M]; B stored [K,N]) instead of K-major
+template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages>
+__global__ void __launch_bounds__(kThreadsWithLoader, 1)
+nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
+                       const __grid_constant__ CUtensorMap tmap_b0, const __grid_constant__ CUtensorMap tmap_b1,
+                       const GemmKernelParams p) {
+  constexpr int kOpTerms = kTerms == 3 ? 2 : 1;
+  using L = GemmSmemLayout<kBlockN, kOpTerms, kStages>;
+  constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;  // 64 (16-bit) or 32 (tf32): BLOCK_K and MN chunk
+  constexpr int kBlockK = kElemsPerRow;
+  constexpr int kUmmaK = 32 / kElemBytes;
+  constexpr int kKSteps = kBlockK / kUmmaK;  // 4
+  constexpr uint32_t kTmemCols = 2 * kBlockN < 32 ? 32 : 2 * kBlockN;
+  static_assert(kBlockN % 32 == 0 && kBlockN >= 32 && kBlockN <= 256, "UMMA N / epilogue chunking");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::kBarrierOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool use_loader = (p.loader_a | p.loader_b) != 0;
+
+  if (threadIdx.x == 0) {
+    // arrivals per phase on a full barrier: the producer's expect_tx arrive, plus one per loader warp
+    const uint32_t full_count = 1u + (use_loader ? kNumLoaderWarps : 0u);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), full_count);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), kNumEpilogueWarps * 32);
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ============================================================ TMA producer
+    if (lane == 0) {
+      if (!p.loader_a) { tma_prefetch_desc(&tmap_a0); if (kOpTerms == 2) tma_prefetch_desc(&tmap_a1); }
+      if (!p.loader_b) { tma_prefetch_desc(&tmap_b0); if (kOpTerms == 2) tma_prefetch_desc(&tmap_b1); }
+      uint32_t expect = 0;
+      if (!p.loader_a) expect += kOpTerms * L::kATile;
+      if (!p.loader_b) expect += kOpTerms * L::kBTile;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile(p, tile);
+        const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
+        const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kStatusProducerEmptyWait)) { ok = false; break; }
+          const uint32_t stage = smem_base + s * L::kStageBytes;
+          const uint32_t bar = full_bar(s);
+          mbar_arrive_expect_tx(bar, expect);
+          const int k0 = kb * kBlockK;
+#pragma unroll
+          for (int term = 0; term < kOpTerms; ++term) {
+            if (!p.loader_a) {
+              const CUtensorMap* ma = term == 0 ? &tmap_a0 : &tmap_a1;
+              const uint32_t dst = stage + term * L::kATile;
+              if (!kAMn) {
+                tma_load_3d(dst, ma, bar, k0, m0, za);  // box {BLOCK_K, 128 rows}
+              } else {
+#pragma unroll
+                for (int c = 0; c < kBlockM / kElemsPerRow; ++c)  // box {chunk of M, BLOCK_K rows}
+                  tma_load_3d(dst + c * (kBlockK * kSwizzleBytes), ma, bar, m0 + c * kElemsPerRow, k0, za);
+              }
+            }
+            if (!p.loader_b) {
+              const CUtensorMap* mb = term == 0 ? &tmap_b0 : &tmap_b1;
+              const uint32_t dst = stage + kOpTerms * L::kATile + term * L::kBTile;
+              if (!kBMn) {
+                tma_load_3d(dst, mb, bar, k0, n0, zb);  // box {BLOCK_K, kBlockN rows}
+              } else {
+#pragma unroll
+                for (int c = 0; c < kBlockN / kElemsPerRow; ++c)  // box {chunk of N, BLOCK_K rows}
+                  tma_load_3d(dst + c * (kBlockK * kSwizzleBytes), mb, bar, n0 + c * kElemsPerRow, k0, zb);
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kStatusMmaTmemEmptyWait)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kStatusMmaFullWait)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_stage = smem_base + s * L::kStageBytes;
+          const uint32_t b_stage = a_stage + kOpTerms * L::kATile;
+#pragma unroll
+          for (int k = 0; k < kKSteps; ++k) {
+            const uint32_t first = (kb | k) == 0 ? 0u : 1u;
+            const uint64_t a_hi = make_smem_desc(a_stage + k * p.a_kstep, p.a_desc_lbo, p.a_desc_hi);
+            const uint64_t b_hi = make_smem_desc(b_stage + k * p.b_kstep, p.b_desc_lbo, p.b_desc_hi);
+            if (kElemBytes == 2) {
+              umma_f16(d_tmem, a_hi, b_hi, p.idesc, first);
+            } else if (kTerms == 1) {
+              umma_tf32(d_tmem, a_hi, b_hi, p.idesc, first);
+            } else {
+              const uint64_t a_lo = make_smem_desc(a_stage + L::kATile + k * p.a_kstep, p.a_desc_lbo, p.a_desc_hi);
+              const uint64_t b_lo = make_smem_desc(b_stage + L::kBTile + k * p.b_kstep, p.b_desc_lbo, p.b_desc_hi);
+              umma_tf32(d_tmem, a_lo, b_hi, p.idesc, first);  // small terms first
+              umma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
+              umma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+            }
+          }
+          umma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(tmem_full_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else if (warp < kFirstLoaderWarp) {
+    // ============================================================ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t tile_iter = 0;
+    for (int32_t tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tile_iter) {
+      const TileCoord t = decode_tile(p, tile);
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      if (!mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag, p.status, kStatusEpilogueTmemFullWait)) break;
+      tc_fence_after_sync();
+      const int32_t row = t.m_blk * kBlockM + q * 32 + lane;
+      const int32_t n0 = t.n_blk * kBlockN;
+      const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kBlockN / 32; ++c) {
+        const int32_t col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+          if (p.out_dtype == NOVA_B200_BF16) epilogue_row_chunk<__nv_bfloat16>(p, r, t.batch, row, col0);
+          else if (p.out_dtype == NOVA_B200_F16) epilogue_row_chunk<__half>(p, r, t.batch, row, col0);
+          else epilogue_row_chunk<float>(p, r, t.batch, row, col0);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tmem_empty_bar(acc));
+    }
+  } else {
+    // ============================================================ ld.global loader (operands TMA cannot address)
+    // Each stage's operand tile is written exactly as TMA would write it: 128-byte rows whose
+    // 16-byte chunks are XOR-swizzled with (row & 7); out-of-range elements are zero.
+    const int lw = warp - kFirstLoaderWarp;       // 0..3
+    const int lt = lw * 32 + lane;                // 0..127
+    uint32_t it = 0;
+    bool ok = true;
+    for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(p, tile);
+      const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kStatusLoaderEmptyWait)) { ok = false; break; }
+        uint8_t* stage = smem_gen + s * L::kStageBytes;
+        const int k0 = kb * kBlockK;
+#pragma unroll
+        for (int op = 0; op < 2; ++op) {
+          if (op == 0 ? !p.loader_a : !p.loader_b) continue;
+          const bool mn = op == 0 ? kAMn : kBMn;
+          const int rows_mn = op == 0 ? kBlockM : kBlockN;  // extent of the tile along M (or N)
+          const int mn0 = op == 0 ? m0 : n0;
+          const int mn_limit = op == 0 ? p.M : p.N;
+          const int64_t ld = op == 0 ? p.lda : p.ldb;
+          const uint8_t* gbase = reinterpret_cast<const uint8_t*>(op == 0 ? p.A : p.B) +
+                                 static_cast<int64_t>(t.batch) * (op == 0 ? p.a_batch_mul * p.stride_a
+                                                                          : p.b_batch_mul * p.stride_b) * kElemBytes;
+          uint8_t* dst = stage + (op == 0 ? 0 : kOpTerms * L::kATile);
+          // smem row r (128 B): K-major -> r indexes M/N, 128 B span BLOCK_K elements of K
+          //                     MN-major -> rows are grouped per chunk of kElemsPerRow M/N elements:
+          //                                 row = chunk * BLOCK_K + k, 128 B span the chunk
+          const int total_rows = mn ? (rows_mn / kElemsPerRow) * kBlockK : rows_mn;
+          constexpr int kChunks = kSwizzleBytes / 16;  // 16-byte chunks per row
+          for (int idx = lt; idx < total_rows * kChunks; idx += kNumLoaderWarps * 32) {
+            const int r = idx / kChunks, ch = idx % kChunks;
+            int64_t outer;  // index along the pitched (outer) global dimension
+            int inner0;     // first index along the contiguous global dimension
+            int outer_limit, inner_limit;
+            if (!mn) { outer = mn0 + r; inner0 = k0 + ch * (16 / kElemBytes); outer_limit = mn_limit; inner_limit = p.K; }
+            else {
+              const int chunk = r / kBlockK, kk = r % kBlockK;
+              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + ch * (16 / kElemBytes);
+              outer_limit = p.K; inner_limit = mn_limit;
+            }
+            union { uint4 u; uint16_t h[8]; uint32_t w[4]; } v;
+            v.u = make_uint4(0u, 0u, 0u, 0u);
+            if (outer < outer_limit) {
+              const uint8_t* src = gbase + (outer * ld + inner0) * kElemBytes;
+              if (kElemBytes == 2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (inner0 + e < inner_limit) v.h[e] = __ldg(reinterpret_cast<const uint16_t*>(src) + e);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (inner0 + e < inner_limit) v.w[e] = __ldg(reinterpret_cast<const uint32_t*>(src) + e);
+              }
+            }
+            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + ((ch ^ (r & 7)) << 4)) = v.u;
+          }
+        }
+        fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u && threadIdx.x == 0) {
+    // a wait gave up: let this CTA's in-flight bulk copies land before its shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- helper kernels
+
+// hi = x rounded to tf32 (round-to-nearest), lo = x - hi (exact in fp32); written to compact
+// [batch, rows, ld_out] buffers whose pitch is a multiple of 16 bytes whatever the input pitch was.
+__global__ void nova_split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                       int64_t rows_total, int32_t rows_per_batch, int32_t cols, int64_t ld_in,
+                                       int64_t stride_in, int32_t ld_out) {
+  const int64_t n = rows_total * ld_out;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / ld_out;
+    const int32_t c = static_cast<int32_t>(i - r * ld_out);
+    float h = 0.0f, l = 0.0f;
+    if (c < cols) {
+      const int64_t b = r / rows_per_batch;
+      const int64_t rr = r - b * rows_per_batch;
+      const float v = x[b * stride_in + rr * ld_in + c];
+      uint32_t hb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v));
+      h = __uint_as_float(hb);
+      l = v - h;
+    }
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// C = act(init) for K == 0 (an empty contraction leaves the accumulator at its initial value).
+template <typename OutT>
+__global__ void nova_gemm_k0_kernel(GemmKernelParams p) {
+  const int64_t per_batch = static_cast<int64_t>(p.M) * p.N;
+  const int64_t n = per_batch * p.batch;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = i / per_batch;
+    const int64_t r = (i - b * per_batch) / p.N;
+    const int64_t c = i - b * per_batch - r * p.N;
+    OutT* dst = reinterpret_cast<OutT*>(p.C) + b * p.stride_c + r * p.ldc + c;
+    float v = 0.0f;
+    if (p.init == NOVA_B200_INIT_BIAS_ROW) v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.bias)[c]);
+    else if (p.init == NOVA_B200_INIT_RESIDUAL_FULL)
+      v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.residual)[b * p.stride_r + r * p.ldr + c]);
+    else if (p.init == NOVA_B200_INIT_FROM_C) v = to_f32<OutT>(*dst);
+    if (p.act == NOVA_B200_ACT_RELU) v = fmaxf(v, 0.0f);
+    else if (p.act == NOVA_B200_ACT_GELU_TANH) v = gelu_tanh_f32(v);
+    *dst = from_f32<OutT>(v);
+  }
+}
+
+}  // namespace nova

@@ -1,0 +1,294 @@
+// Host side of the contraction: argument validation, kernel selection ("plan"),
+// tensor-map encoding and launch.  See gemm_kernel.cuh for the device code.
+#include <cstdlib>
+#include <cstring>
+
+#include "gemm_kernel.cuh"
+
+namespace nova {
+namespace {
+
+struct Plan {
+  nova_b200_gemm_plan_info info{};
+  int elem_bytes = 2;
+  int terms = 1;
+  bool a_mn = false, b_mn = false;
+  int out_bytes = 2;
+  bool k_zero = false;
+  bool empty = false;
+};
+
+constexpr int64_t kMaxExtent = (1ll << 31) - 1;
+
+int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count) {
+  if (!a) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: args is null");
+  if (a->struct_size != sizeof(nova_b200_gemm_args))
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: struct_size does not match this library's nova_b200_gemm_args");
+  if (a->dtype_ab != NOVA_B200_F32 && a->dtype_ab != NOVA_B200_F16 && a->dtype_ab != NOVA_B200_BF16)
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: dtype_ab must be f32, f16 or bf16");
+  if (!is_float_dtype(a->dtype_c)) return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: dtype_c must be f32, f16 or bf16");
+  if (a->act < NOVA_B200_ACT_NONE || a->act > NOVA_B200_ACT_GELU_TANH)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown activation");
+  if (a->init < NOVA_B200_INIT_ZERO || a->init > NOVA_B200_INIT_FROM_C)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown accumulator init");
+  if (a->f32_mode != NOVA_B200_TF32X3 && a->f32_mode != NOVA_B200_TF32X1)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown f32_mode");
+  if (a->batch < 0 || a->M < 0 || a->N < 0 || a->K < 0)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: negative extent");
+  if (a->batch > kMaxExtent || a->M > kMaxExtent || a->N > kMaxExtent || a->K > kMaxExtent)
+    return fail(NOVA_B200_ERR_TOO_LARGE, "gemm: extent exceeds 2^31-1");
+  plan->empty = a->batch == 0 || a->M == 0 || a->N == 0;
+  plan->k_zero = a->K == 0;
+  plan->elem_bytes = dtype_bytes(a->dtype_ab);
+  plan->out_bytes = dtype_bytes(a->dtype_c);
+  plan->a_mn = a->trans_a != 0;  // A stored [K, M]: M is the contiguous (MN-major) dimension
+  plan->b_mn = a->trans_b == 0;  // B stored [K, N]: N is the contiguous (MN-major) dimension
+  if (plan->empty) return NOVA_B200_OK;
+
+  if (!a->C) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: C is null");
+  if (!plan->k_zero && (!a->A || !a->B)) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: A or B is null");
+  if (a->init == NOVA_B200_INIT_BIAS_ROW && !a->bias) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: bias is null");
+  if (a->init == NOVA_B200_INIT_RESIDUAL_FULL && !a->residual)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: residual is null");
+  const int64_t a_inner = a->trans_a ? a->M : a->K;
+  const int64_t b_inner = a->trans_b ? a->K : a->N;
+  if (!plan->k_zero && (a->lda < a_inner || a->ldb < b_inner))
+    return fail(NOVA_B200_ERR_LAYOUT, "gemm: lda/ldb smaller than the contiguous extent");
+  if (a->ldc < a->N) return fail(NOVA_B200_ERR_LAYOUT, "gemm: ldc smaller than N");
+  if (a->init == NOVA_B200_INIT_RESIDUAL_FULL && a->ldr < a->N)
+    return fail(NOVA_B200_ERR_LAYOUT, "gemm: ldr smaller than N");
+  if (a->batch_stride_a < 0 || a->batch_stride_b < 0 || a->batch_stride_c < 0 || a->batch_stride_r < 0)
+    return fail(NOVA_B200_ERR_LAYOUT, "gemm: negative batch stride");
+  if (a->batch > 1 && a->batch_stride_c < a->M * a->ldc && a->batch_stride_c != 0)
+    return fail(NOVA_B200_ERR_LAYOUT, "gemm: batch_stride_c makes output batches overlap");
+  if (a->batch > 1 && a->batch_stride_c == 0)
+    return fail(NOVA_B200_ERR_LAYOUT, "gemm: output cannot be shared across batches");
+
+  nova_b200_gemm_plan_info& pi = plan->info;
+  const int es = plan->elem_bytes;
+  auto tma_ok = [&](const void* base, int64_t ld, int64_t bstride) {
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
+    if ((ld * es) % 16 != 0) return false;
+    if (a->batch > 1 && bstride != 0 && (bstride * es) % 16 != 0) return false;
+    if (static_cast<unsigned long long>(ld) * es >= (1ull << 40)) return false;
+    if (static_cast<unsigned long long>(bstride) * es >= (1ull << 40)) return false;
+    return true;
+  };
+  plan->terms = (a->dtype_ab == NOVA_B200_F32 && a->f32_mode == NOVA_B200_TF32X3) ? 3 : 1;
+  if (plan->terms == 3) {
+    pi.loader_a = pi.loader_b = 0;  // operands are re-laid out by the hi/lo split into aligned scratch
+    const int64_t a_rows = a->trans_a ? a->K : a->M, a_cols = a->trans_a ? a->M : a->K;
+    const int64_t b_rows = a->trans_b ? a->N : a->K, b_cols = a->trans_b ? a->K : a->N;
+    const int64_t a_b = a->batch_stride_a == 0 ? 1 : a->batch, b_b = a->batch_stride_b == 0 ? 1 : a->batch;
+    pi.scratch_bytes = 2 * 4 * (a_b * a_rows * ((a_cols + 3) & ~3ll) + b_b * b_rows * ((b_cols + 3) & ~3ll));
+  } else {
+    pi.loader_a = tma_ok(a->A, a->lda, a->batch_stride_a) ? 0 : 1;
+    pi.loader_b = tma_ok(a->B, a->ldb, a->batch_stride_b) ? 0 : 1;
+    pi.scratch_bytes = 0;
+  }
+  const int osz = plan->out_bytes;
+  const bool c_vec = reinterpret_cast<uintptr_t>(a->C) % 16 == 0 && (a->ldc * osz) % 16 == 0 &&
+                     (a->batch <= 1 || (a->batch_stride_c * osz) % 16 == 0);
+  pi.store_c = c_vec ? 0 : 1;
+
+  pi.block_m = kBlockM;
+  pi.block_k = kSwizzleBytes / es;
+  const int64_t m_blocks = (a->M + kBlockM - 1) / kBlockM;
+  // 256-wide tiles halve the A re-reads and use the whole of tensor memory; fall back to 128 when
+  // the problem would not even fill one wave of SMs with them.
+  int block_n = 256;
+  if (plan->terms == 3) block_n = 128;
+  else if (a->N <= 128) block_n = 128;
+  else {
+    const int64_t tiles256 = a->batch * m_blocks * ((a->N + 255) / 256);
+    if (tiles256 < (sm_count > 0 ? sm_count : 148)) block_n = 128;
+  }
+  if (const char* e = std::getenv("NOVA_B200_BLOCK_N")) {
+    const int v = std::atoi(e);
+    if ((v == 128 || v == 256) && plan->terms != 3) block_n = v;
+  }
+  pi.block_n = block_n;
+  const int64_t n_blocks = (a->N + block_n - 1) / block_n;
+  const int64_t tiles = a->batch * m_blocks * n_blocks;
+  if (tiles > kMaxExtent) return fail(NOVA_B200_ERR_TOO_LARGE, "gemm: more than 2^31-1 output tiles");
+  pi.tiles = tiles;
+  pi.stages = plan->terms == 3 ? 3 : (block_n == 256 ? 4 : 6);
+  pi.grid = static_cast<int32_t>(tiles < (sm_count > 0 ? sm_count : 148) ? tiles : (sm_count > 0 ? sm_count : 148));
+  return NOVA_B200_OK;
+}
+
+// rows x cols matrix with `cols` contiguous, pitch ld, `nb` batches `bstride` elements apart.
+int32_t encode_operand_map(DeviceContext* ctx, CUtensorMap* out, const void* base, int es, CUtensorMapDataType dt,
+                           int64_t rows, int64_t cols, int64_t ld, int64_t nb, int64_t bstride, uint32_t box_inner,
+                           uint32_t box_outer) {
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(nb)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es,
+                           nb > 1 ? static_cast<cuuint64_t>(bstride) * es : static_cast<cuuint64_t>(rows) * ld * es};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ctx->encode_tiled(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(NOVA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(r));
+  return NOVA_B200_OK;
+}
+
+template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages>
+int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int grid, int threads, cudaStream_t st) {
+  using L = GemmSmemLayout<kBlockN, (kTerms == 3 ? 2 : 1), kStages>;
+  auto kernel = nova_gemm_sm100_kernel<kBlockN, kElemBytes, kTerms, kAMn, kBMn, kStages>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  NOVA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
+    configured_device = dev;
+  }
+  kernel<<<grid, threads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+template <int kBlockN, int kElemBytes, int kTerms, int kStages>
+int32_t launch_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int grid, int threads,
+                      cudaStream_t st) {
+  if (!a_mn && b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, false, true, kStages>(maps, p, grid, threads, st);
+  if (!a_mn && !b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, false, false, kStages>(maps, p, grid, threads, st);
+  if (a_mn && b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, true, true, kStages>(maps, p, grid, threads, st);
+  return launch_instance<kBlockN, kElemBytes, kTerms, true, false, kStages>(maps, p, grid, threads, st);
+}
+
+uint32_t env_u32(const char* name, uint32_t dflt) {
+  const char* e = std::getenv(name);
+  return e ? static_cast<uint32_t>(std::strtoul(e, nullptr, 0)) : dflt;
+}
+
+}  // namespace
+
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
+  Plan plan;
+  int sm = 148;
+  int32_t st = validate_and_plan(args, &plan, sm);
+  if (st != NOVA_B200_OK) return st;
+  if (out) *out = plan.info;
+  return NOVA_B200_OK;
+}
+
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream) {
+  Plan plan;
+  int32_t st = validate_and_plan(a, &plan, ctx->sm_count);
+  if (st != NOVA_B200_OK) return st;
+  if (plan.empty) return NOVA_B200_OK;
+  const nova_b200_gemm_plan_info& pi = plan.info;
+
+  GemmKernelParams p{};
+  p.M = static_cast<int32_t>(a->M); p.N = static_cast<int32_t>(a->N); p.K = static_cast<int32_t>(a->K);
+  p.batch = static_cast<int32_t>(a->batch);
+  p.C = a->C; p.bias = a->bias; p.residual = a->residual;
+  p.ldc = a->ldc; p.stride_c = a->batch_stride_c; p.ldr = a->ldr; p.stride_r = a->batch_stride_r;
+  p.act = a->act; p.init = a->init; p.out_dtype = a->dtype_c;
+  p.status = ctx->status_word;
+
+  if (plan.k_zero) {
+    const int64_t n = a->batch * a->M * a->N;
+    const int grid = static_cast<int>(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
+    if (a->dtype_c == NOVA_B200_BF16) nova_gemm_k0_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+    else if (a->dtype_c == NOVA_B200_F16) nova_gemm_k0_kernel<__half><<<grid, 256, 0, stream>>>(p);
+    else nova_gemm_k0_kernel<float><<<grid, 256, 0, stream>>>(p);
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
+
+  const int es = plan.elem_bytes;
+  const int block_n = pi.block_n;
+  const int block_k = pi.block_k;
+  p.m_blocks = static_cast<int32_t>((a->M + kBlockM - 1) / kBlockM);
+  p.n_blocks = static_cast<int32_t>((a->N + block_n - 1) / block_n);
+  p.k_blocks = static_cast<int32_t>((a->K + block_k - 1) / block_k);
+  p.group_m = static_cast<int32_t>(env_u32("NOVA_B200_GROUP_M", 16));
+  if (p.group_m < 1) p.group_m = 1;
+  p.tiles = static_cast<int32_t>(pi.tiles);
+  p.a_batch_mul = a->batch_stride_a == 0 ? 0 : 1;
+  p.b_batch_mul = a->batch_stride_b == 0 ? 0 : 1;
+  p.loader_a = pi.loader_a; p.loader_b = pi.loader_b;
+  p.A = a->A; p.B = a->B; p.lda = a->lda; p.ldb = a->ldb;
+  p.stride_a = a->batch_stride_a; p.stride_b = a->batch_stride_b;
+  p.vec_store = pi.store_c == 0 ? 1 : 0;
+
+  // tcgen05 instruction descriptor: D=f32 (bits 4-5 = 1), A/B format (bits 7-9 / 10-12: f16=0, bf16=1, tf32=2),
+  // A/B major (bits 15/16: 1 = MN-major), N>>3 in bits 17-22, M>>4 in bits 24-28.
+  const uint32_t fmt = a->dtype_ab == NOVA_B200_F16 ? 0u : (a->dtype_ab == NOVA_B200_BF16 ? 1u : 2u);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((plan.a_mn ? 1u : 0u) << 15) | ((plan.b_mn ? 1u : 0u) << 16) |
+            (static_cast<uint32_t>(block_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+  // Shared-memory matrix descriptors (128-byte swizzle, version 1):
+  //   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused; one UMMA K step = 32 B.
+  //   MN-major: 128 B = one chunk of MN elements for one k; 8 k-rows = 1024 B (SBO); the next chunk of
+  //             MN elements starts BLOCK_K*128 B further (LBO); one UMMA K step = UMMA_K*128 B.
+  const uint32_t umma_k = 32u / es;
+  const uint32_t sbo = env_u32("NOVA_B200_DBG_SBO", 1024u);
+  const uint32_t lbo_mn = env_u32("NOVA_B200_DBG_LBO_MN", static_cast<uint32_t>(block_k) * kSwizzleBytes);
+  const uint32_t desc_hi = ((sbo >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);  // SBO | version=1 | SWIZZLE_128B
+  p.a_desc_hi = p.b_desc_hi = desc_hi;
+  p.a_desc_lbo = (plan.a_mn ? ((lbo_mn >> 4) & 0x3fffu) : 1u) << 16;
+  p.b_desc_lbo = (plan.b_mn ? ((lbo_mn >> 4) & 0x3fffu) : 1u) << 16;
+  p.a_kstep = plan.a_mn ? umma_k * kSwizzleBytes : 32u;
+  p.b_kstep = plan.b_mn ? umma_k * kSwizzleBytes : 32u;
+
+  // operand views (possibly redirected to the hi/lo scratch for 3xTF32)
+  const int64_t a_rows = a->trans_a ? a->K : a->M, a_cols = a->trans_a ? a->M : a->K;
+  const int64_t b_rows = a->trans_b ? a->N : a->K, b_cols = a->trans_b ? a->K : a->N;
+  const int64_t a_nb = a->batch_stride_a == 0 ? 1 : a->batch, b_nb = a->batch_stride_b == 0 ? 1 : a->batch;
+  const void* a_src[2] = {a->A, nullptr};
+  const void* b_src[2] = {a->B, nullptr};
+  int64_t a_ld = a->lda, b_ld = a->ldb, a_bs = a->batch_stride_a, b_bs = a->batch_stride_b;
+  if (plan.terms == 3) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    st = ensure_scratch(ctx, static_cast<size_t>(pi.scratch_bytes));
+    if (st != NOVA_B200_OK) return st;
+    const int64_t a_ldo = (a_cols + 3) & ~3ll, b_ldo = (b_cols + 3) & ~3ll;
+    float* s = static_cast<float*>(ctx->scratch);
+    float* a_hi = s; float* a_lo = a_hi + a_nb * a_rows * a_ldo;
+    float* b_hi = a_lo + a_nb * a_rows * a_ldo; float* b_lo = b_hi + b_nb * b_rows * b_ldo;
+    const int blocks = ctx->sm_count * 8;
+    nova_split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(a->A), a_hi, a_lo, a_nb * a_rows,
+                                                       static_cast<int32_t>(a_rows), static_cast<int32_t>(a_cols),
+                                                       a->lda, a->batch_stride_a, static_cast<int32_t>(a_ldo));
+    nova_split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows,
+                                                       static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols),
+                                                       a->ldb, a->batch_stride_b, static_cast<int32_t>(b_ldo));
+    NOVA_CUDA_OK(cudaGetLastError());
+    a_src[0] = a_hi; a_src[1] = a_lo; b_src[0] = b_hi; b_src[1] = b_lo;
+    a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;
+  }
+
+  CUtensorMap maps[4];
+  std::memset(maps, 0, sizeof(maps));
+  const CUtensorMapDataType tdt = a->dtype_ab == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                : a->dtype_ab == NOVA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const uint32_t chunk = static_cast<uint32_t>(block_k);  // 128 B of elements
+  for (int t = 0; t < (plan.terms == 3 ? 2 : 1); ++t) {
+    if (!pi.loader_a) {
+      st = encode_operand_map(ctx, &maps[t], a_src[t], es, tdt, a_rows, a_cols, a_ld, a_nb, a_bs, chunk,
+                              plan.a_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(kBlockM));
+      if (st != NOVA_B200_OK) return st;
+    }
+    if (!pi.loader_b) {
+      st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows, b_cols, b_ld, b_nb, b_bs, chunk,
+                              plan.b_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(block_n));
+      if (st != NOVA_B200_OK) return st;
+    }
+  }
+
+  const int threads = (pi.loader_a | pi.loader_b) ? kThreadsWithLoader : kThreadsTma;
+  const int grid = pi.grid;
+  if (es == 2) {
+    if (block_n == 256) return launch_majors<256, 2, 1, 4>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+    return launch_majors<128, 2, 1, 6>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+  }
+  if (plan.terms == 3) return launch_majors<128, 4, 3, 3>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+  if (block_n == 256) return launch_majors<256, 4, 1, 4>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+  return launch_majors<128, 4, 1, 6>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+}
+
+}  // namespace nova

@@ -1,0 +1,416 @@
+// HBM-bound companions of the contraction: layer_norm, softmax, gather, standalone activation and
+// row-broadcast add.  Each reads its input from HBM once and writes its output once: a row lives
+// in registers between the reduction and the normalisation pass (one warp per row up to 1024
+// elements, one 256-thread CTA per row up to 8192, a two-pass loop beyond that), all traffic moves
+// as 128-bit accesses when base and row pitch allow, and reductions are warp-shuffle trees.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "runtime.h"
+
+namespace nova {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ld_f32(T v);
+template <> __device__ __forceinline__ float ld_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float ld_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float ld_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T st_f32(float v);
+template <> __device__ __forceinline__ float st_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half st_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 st_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T e[VEC]; };
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Reduction over the TPR threads that share a row (TPR == 32: one warp; TPR == 256: the CTA).
+template <int TPR, bool kMax>
+__device__ __forceinline__ float row_reduce(float v, float* red_smem) {
+  v = kMax ? warp_max(v) : warp_sum(v);
+  if (TPR == 32) return v;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // protect red_smem from the previous reduction's readers
+  if (lane == 0) red_smem[warp] = v;
+  __syncthreads();
+  float r = lane < TPR / 32 ? red_smem[lane] : (kMax ? -INFINITY : 0.0f);
+  return kMax ? warp_max(r) : warp_sum(r);
+}
+
+constexpr int kRowThreads = 256;
+constexpr int kCacheElems = 32;  // elements of a row one thread keeps in registers
+
+// kMode 0: layer_norm, kMode 1: softmax.  CACHED: the row fits TPR * kCacheElems elements.
+template <typename T, int VEC, int TPR, bool CACHED, int kMode>
+__global__ void __launch_bounds__(kRowThreads)
+row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+           T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D) {
+  __shared__ float red[kRowThreads / 32];
+  constexpr int kRowsPerCta = kRowThreads / TPR;
+  constexpr int kMaxV = kCacheElems / VEC;
+  const int t = threadIdx.x % TPR;
+  const int sub = threadIdx.x / TPR;
+  const int nvec = D / VEC;  // host guarantees D % VEC == 0
+  using P = Pack<T, VEC>;
+  const float inv_d = 1.0f / static_cast<float>(D);
+
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta; row0 < rows;
+       row0 += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+    const int64_t row = row0 + sub;
+    const bool active = row < rows;  // whole warps are active or not when TPR == 32; TPR == 256 has one row
+    const P* xr = reinterpret_cast<const P*>(x + (active ? row : 0) * D);
+    P* yr = reinterpret_cast<P*>(y + (active ? row : 0) * D);
+    P cache[CACHED ? kMaxV : 1];
+
+    float s0 = kMode == 0 ? 0.0f : -INFINITY;  // layer_norm: sum; softmax: max
+    float s1 = 0.0f;                            // layer_norm: sum of squares
+    if (CACHED) {
+#pragma unroll
+      for (int k = 0; k < kMaxV; ++k) {
+        const int i = t + k * TPR;
+        if (active && i < nvec) {
+          cache[k] = xr[i];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float v = ld_f32<T>(cache[k].e[e]);
+            if (kMode == 0) { s0 += v; s1 += v * v; } else { s0 = fmaxf(s0, v); }
+          }
+        }
+      }
+    } else {
+      for (int i = t; active && i < nvec; i += TPR) {
+        const P pk = xr[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float v = ld_f32<T>(pk.e[e]);
+          if (kMode == 0) { s0 += v; s1 += v * v; } else { s0 = fmaxf(s0, v); }
+        }
+      }
+    }
+
+    if (kMode == 0) {
+      const float sum = row_reduce<TPR, false>(s0, red);
+      const float sq = row_reduce<TPR, false>(s1, red);
+      const float mean = sum * inv_d;
+      const float var = sq * inv_d - mean * mean;
+      const float rstd = rsqrtf(var + 1e-5f);
+      if (active && t == 0) {
+        if (mean_sum) mean_sum[row] = st_f32<T>(sum);
+        if (rstd_out) rstd_out[row] = st_f32<T>(rstd);
+      }
+      const P* gr = reinterpret_cast<const P*>(gamma);
+      const P* br = reinterpret_cast<const P*>(beta);
+      auto emit = [&](int i, const P& in) {
+        const P g = gr[i], b = br[i];
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          o.e[e] = st_f32<T>((ld_f32<T>(in.e[e]) - mean) * rstd * ld_f32<T>(g.e[e]) + ld_f32<T>(b.e[e]));
+        yr[i] = o;
+      };
+      if (CACHED) {
+#pragma unroll
+        for (int k = 0; k < kMaxV; ++k) {
+          const int i = t + k * TPR;
+          if (active && i < nvec) emit(i, cache[k]);
+        }
+      } else {
+        for (int i = t; active && i < nvec; i += TPR) emit(i, xr[i]);
+      }
+    } else {
+      const float m = row_reduce<TPR, true>(s0, red);
+      float part = 0.0f;
+      if (CACHED) {
+#pragma unroll
+        for (int k = 0; k < kMaxV; ++k) {
+          const int i = t + k * TPR;
+          if (active && i < nvec) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) part += __expf(ld_f32<T>(cache[k].e[e]) - m);
+          }
+        }
+      } else {
+        for (int i = t; active && i < nvec; i += TPR) {
+          const P pk = xr[i];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) part += __expf(ld_f32<T>(pk.e[e]) - m);
+        }
+      }
+      const float s = row_reduce<TPR, false>(part, red);
+      const float recip = 1.0f / fmaxf(s, 1.0e-7f);
+      auto emit = [&](int i, const P& in) {
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o.e[e] = st_f32<T>(__expf(ld_f32<T>(in.e[e]) - m) * recip);
+        yr[i] = o;
+      };
+      if (CACHED) {
+#pragma unroll
+        for (int k = 0; k < kMaxV; ++k) {
+          const int i = t + k * TPR;
+          if (active && i < nvec) emit(i, cache[k]);
+        }
+      } else {
+        for (int i = t; active && i < nvec; i += TPR) emit(i, xr[i]);
+      }
+    }
+  }
+}
+
+template <typename T, int VEC, int kMode>
+int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
+                          int64_t rows, int64_t D, int sm_count, cudaStream_t st) {
+  const T* xp = static_cast<const T*>(x);
+  const T* gp = static_cast<const T*>(gamma);
+  const T* bp = static_cast<const T*>(beta);
+  T* yp = static_cast<T*>(y);
+  T* mp = static_cast<T*>(mean_sum);
+  T* rp = static_cast<T*>(rstd);
+  const int d = static_cast<int>(D);
+  const int64_t max_grid = static_cast<int64_t>(sm_count) * 8;  // 8 resident 256-thread CTAs per SM
+  if (D <= 32 * kCacheElems) {
+    const int64_t ctas = (rows + 7) / 8;
+    const int grid = static_cast<int>(ctas < max_grid ? ctas : max_grid);
+    row_kernel<T, VEC, 32, true, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+  } else if (D <= kRowThreads * kCacheElems) {
+    const int grid = static_cast<int>(rows < max_grid ? rows : max_grid);
+    row_kernel<T, VEC, kRowThreads, true, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+  } else {
+    const int grid = static_cast<int>(rows < max_grid ? rows : max_grid);
+    row_kernel<T, VEC, kRowThreads, false, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+  }
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+template <int kMode>
+int32_t dispatch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
+                            int64_t rows, int64_t D, int32_t dtype, int sm_count, cudaStream_t st) {
+  const int es = dtype_bytes(dtype);
+  const int vec = 16 / es;
+  auto aligned16 = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec_ok = D % vec == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
+  switch (dtype) {
+    case NOVA_B200_F32:
+      return vec_ok ? launch_row_kernel<float, 4, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
+                    : launch_row_kernel<float, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+    case NOVA_B200_F16:
+      return vec_ok ? launch_row_kernel<__half, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
+                    : launch_row_kernel<__half, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+    case NOVA_B200_BF16:
+      return vec_ok
+                 ? launch_row_kernel<__nv_bfloat16, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
+                 : launch_row_kernel<__nv_bfloat16, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+    default:
+      return fail(NOVA_B200_ERR_UNSUPPORTED, "row op: dtype must be f32, f16 or bf16");
+  }
+}
+
+// ---------------------------------------------------------------- gather
+
+// One 16-byte (or W-byte) unit per thread; consecutive threads copy consecutive units of one row.
+template <typename U>
+__global__ void gather_kernel(const U* __restrict__ in, const void* __restrict__ idx, U* __restrict__ out, int64_t pre,
+                              int64_t axis_len, int64_t units_per_row, int64_t n_idx, int32_t idx_dtype,
+                              int32_t batched, unsigned long long* bad_count) {
+  const int64_t total = pre * n_idx * units_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t orow = i / units_per_row;
+    const int64_t u = i - orow * units_per_row;
+    const int64_t p = orow / n_idx;
+    const int64_t t = orow - p * n_idx;
+    const int64_t q = batched ? orow : t;
+    int64_t id;
+    if (idx_dtype == NOVA_B200_I16) id = static_cast<int64_t>(static_cast<const uint16_t*>(idx)[q]);  // zero-extended
+    else if (idx_dtype == NOVA_B200_I32) id = static_cast<int64_t>(static_cast<const int32_t*>(idx)[q]);
+    else id = static_cast<const int64_t*>(idx)[q];
+    U v{};
+    if (id >= 0 && id < axis_len) v = in[(p * axis_len + id) * units_per_row + u];
+    else if (u == 0 && bad_count) atomicAdd(bad_count, 1ull);
+    out[i] = v;
+  }
+}
+
+// ---------------------------------------------------------------- elementwise
+
+__device__ __forceinline__ float gelu_tanh_accurate(float x) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x, x * x, x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
+template <typename T, int VEC>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n, int32_t act) {
+  using P = Pack<T, VEC>;
+  const int64_t nv = n / VEC;
+  const P* xp = reinterpret_cast<const P*>(x);
+  P* yp = reinterpret_cast<P*>(y);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    P v = xp[i];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float f = ld_f32<T>(v.e[e]);
+      v.e[e] = st_f32<T>(act == NOVA_B200_ACT_RELU ? fmaxf(f, 0.0f)
+                                                    : (act == NOVA_B200_ACT_GELU_TANH ? gelu_tanh_accurate(f) : f));
+    }
+    yp[i] = v;
+  }
+}
+
+template <typename T, int VEC>
+__global__ void add_rowbcast_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows,
+                                    int64_t cols, int32_t b_is_full) {
+  using P = Pack<T, VEC>;
+  const int64_t cv = cols / VEC;
+  const int64_t nv = rows * cv;
+  const P* ap = reinterpret_cast<const P*>(a);
+  const P* bp = reinterpret_cast<const P*>(b);
+  P* op = reinterpret_cast<P*>(out);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const P va = ap[i];
+    const P vb = bp[b_is_full ? i : i % cv];
+    P o;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) o.e[e] = st_f32<T>(ld_f32<T>(va.e[e]) + ld_f32<T>(vb.e[e]));
+    op[i] = o;
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int sm_count) {
+  const int64_t want = (work_items + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sm_count) * 16;
+  return static_cast<int>(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace
+}  // namespace nova
+
+using namespace nova;
+
+extern "C" {
+
+int32_t nova_b200_layer_norm(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
+                             int64_t rows, int64_t D, int32_t dtype, void* stream) {
+  if (rows < 0 || D < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "layer_norm: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "layer_norm: dtype must be f32, f16 or bf16");
+  if (D > (1ll << 30)) return fail(NOVA_B200_ERR_TOO_LARGE, "layer_norm: D exceeds 2^30");
+  if (rows == 0 || D == 0) return NOVA_B200_OK;
+  if (!x || !gamma || !beta || !y) return fail(NOVA_B200_ERR_INVALID_ARG, "layer_norm: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  return dispatch_row_kernel<0>(x, gamma, beta, y, mean_sum, rstd, rows, D, dtype, ctx->sm_count,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32_t dtype, void* stream) {
+  if (rows < 0 || D < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "softmax: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "softmax: dtype must be f32, f16 or bf16");
+  if (D > (1ll << 30)) return fail(NOVA_B200_ERR_TOO_LARGE, "softmax: D exceeds 2^30");
+  if (rows == 0 || D == 0) return NOVA_B200_OK;
+  if (!x || !y) return fail(NOVA_B200_ERR_INVALID_ARG, "softmax: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  return dispatch_row_kernel<1>(x, nullptr, nullptr, y, nullptr, nullptr, rows, D, dtype, ctx->sm_count,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int32_t nova_b200_gather(const void* in, const void* idx, void* out, int64_t pre, int64_t axis_len, int64_t post,
+                         int64_t n_idx, int32_t idx_dtype, int32_t batched_idx, int32_t elem_bytes,
+                         int64_t* bad_count, void* stream) {
+  if (pre < 0 || axis_len < 0 || post < 0 || n_idx < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "gather: negative extent");
+  if (idx_dtype != NOVA_B200_I16 && idx_dtype != NOVA_B200_I32 && idx_dtype != NOVA_B200_I64)
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "gather: index dtype must be i16, i32 or i64");
+  if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8)
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "gather: element size must be 1, 2, 4 or 8 bytes");
+  if (pre == 0 || post == 0 || n_idx == 0) return NOVA_B200_OK;
+  if (!in || !idx || !out) return fail(NOVA_B200_ERR_INVALID_ARG, "gather: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t row_bytes = post * elem_bytes;
+  const uintptr_t align = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                          static_cast<uintptr_t>(row_bytes);
+  auto* bad = reinterpret_cast<unsigned long long*>(bad_count);
+  const int threads = 256;
+#define NOVA_GATHER(U)                                                                                          \
+  do {                                                                                                          \
+    const int64_t units = row_bytes / static_cast<int64_t>(sizeof(U));                                          \
+    gather_kernel<U><<<grid_for(pre * n_idx * units, threads, ctx->sm_count), threads, 0, s>>>(                 \
+        static_cast<const U*>(in), idx, static_cast<U*>(out), pre, axis_len, units, n_idx, idx_dtype,           \
+        batched_idx, bad);                                                                                      \
+  } while (0)
+  if (align % 16 == 0) NOVA_GATHER(uint4);
+  else if (align % 8 == 0) NOVA_GATHER(uint2);
+  else if (align % 4 == 0) NOVA_GATHER(uint32_t);
+  else if (align % 2 == 0) NOVA_GATHER(uint16_t);
+  else NOVA_GATHER(uint8_t);
+#undef NOVA_GATHER
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_activation(const void* x, void* y, int64_t n, int32_t dtype, int32_t act, void* stream) {
+  if (n < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "activation: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "activation: dtype must be f32, f16 or bf16");
+  if (act < NOVA_B200_ACT_NONE || act > NOVA_B200_ACT_GELU_TANH)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "activation: unknown activation");
+  if (n == 0) return NOVA_B200_OK;
+  if (!x || !y) return fail(NOVA_B200_ERR_INVALID_ARG, "activation: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype), vec = 16 / es;
+  const bool vec_ok = n % vec == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+  const int threads = 256;
+  const int grid = grid_for(vec_ok ? n / vec : n, threads, ctx->sm_count);
+#define NOVA_ACT(T, V) activation_kernel<T, V><<<grid, threads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), n, act)
+  if (dtype == NOVA_B200_F32) { if (vec_ok) NOVA_ACT(float, 4); else NOVA_ACT(float, 1); }
+  else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_ACT(__half, 8); else NOVA_ACT(__half, 1); }
+  else { if (vec_ok) NOVA_ACT(__nv_bfloat16, 8); else NOVA_ACT(__nv_bfloat16, 1); }
+#undef NOVA_ACT
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_add_rowbcast(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int32_t b_is_full,
+                               int32_t dtype, void* stream) {
+  if (rows < 0 || cols < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "add: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "add: dtype must be f32, f16 or bf16");
+  if (rows == 0 || cols == 0) return NOVA_B200_OK;
+  if (!a || !b || !out) return fail(NOVA_B200_ERR_INVALID_ARG, "add: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype), vec = 16 / es;
+  const bool vec_ok = cols % vec == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(b) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  const int threads = 256;
+  const int grid = grid_for(vec_ok ? rows * cols / vec : rows * cols, threads, ctx->sm_count);
+#define NOVA_ADD(T, V)                                                                                       \
+  add_rowbcast_kernel<T, V><<<grid, threads, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b),      \
+                                                     static_cast<T*>(out), rows, cols, b_is_full)
+  if (dtype == NOVA_B200_F32) { if (vec_ok) NOVA_ADD(float, 4); else NOVA_ADD(float, 1); }
+  else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_ADD(__half, 8); else NOVA_ADD(__half, 1); }
+  else { if (vec_ok) NOVA_ADD(__nv_bfloat16, 8); else NOVA_ADD(__nv_bfloat16, 1); }
+#undef NOVA_ADD
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+}  // extern "C"

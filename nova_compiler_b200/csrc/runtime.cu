@@ -1,0 +1,351 @@
+// libnova_b200 runtime: per-device contexts, error reporting, the C-ABI entry points for the
+// contraction (device-pointer, host-pointer and memref-descriptor forms).
+#include "runtime.h"
+
+#include <cstring>
+#include <map>
+#include <memory>
+#include <vector>
+
+namespace nova {
+
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream);
+
+namespace {
+thread_local std::string g_last_error;
+std::mutex g_ctx_mu;
+std::map<int, std::unique_ptr<DeviceContext>> g_contexts;
+}  // namespace
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int32_t fail(nova_b200_status st, const std::string& msg) {
+  g_last_error = msg;
+  return st;
+}
+
+DeviceContext* current_context(int32_t* status_out) {
+  int dev = -1;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    *status_out = fail(NOVA_B200_ERR_NO_DEVICE, "no CUDA device is visible; libnova_b200 has no CPU fallback");
+    return nullptr;
+  }
+  e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    *status_out = fail(NOVA_B200_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_ctx_mu);
+  auto it = g_contexts.find(dev);
+  if (it != g_contexts.end()) {
+    *status_out = NOVA_B200_OK;
+    return it->second.get();
+  }
+  auto ctx = std::make_unique<DeviceContext>();
+  ctx->device = dev;
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) {
+    *status_out = fail(NOVA_B200_ERR_CUDA, std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    return nullptr;
+  }
+  ctx->cc_major = prop.major;
+  ctx->cc_minor = prop.minor;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (prop.major != 10) {
+    *status_out = fail(NOVA_B200_ERR_NO_DEVICE, "device " + std::to_string(dev) + " is compute capability " +
+                                                    std::to_string(prop.major) + "." + std::to_string(prop.minor) +
+                                                    "; libnova_b200 is built for sm_100a only");
+    return nullptr;
+  }
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    cudaGetLastError();
+    *status_out = fail(NOVA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return nullptr;
+  }
+  ctx->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaMalloc(reinterpret_cast<void**>(&ctx->status_word), 256);
+  if (e == cudaSuccess) e = cudaMemset(ctx->status_word, 0, 256);
+  if (e != cudaSuccess) {
+    *status_out = fail(NOVA_B200_ERR_CUDA, std::string("status word allocation: ") + cudaGetErrorString(e));
+    return nullptr;
+  }
+  DeviceContext* raw = ctx.get();
+  g_contexts[dev] = std::move(ctx);
+  *status_out = NOVA_B200_OK;
+  return raw;
+}
+
+static int32_t grow(void** buf, size_t* have, size_t want, const char* what) {
+  if (*have >= want) return NOVA_B200_OK;
+  if (*buf) {
+    NOVA_CUDA_OK(cudaDeviceSynchronize());  // earlier launches may still read the old buffer
+    NOVA_CUDA_OK(cudaFree(*buf));
+    *buf = nullptr;
+    *have = 0;
+  }
+  size_t bytes = (want + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+  cudaError_t e = cudaMalloc(buf, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NOVA_B200_ERR_CUDA, std::string(what) + ": cudaMalloc of " + std::to_string(bytes) + " bytes failed: " +
+                                        cudaGetErrorString(e));
+  }
+  *have = bytes;
+  return NOVA_B200_OK;
+}
+
+int32_t ensure_scratch(DeviceContext* ctx, size_t bytes) { return grow(&ctx->scratch, &ctx->scratch_bytes, bytes, "scratch"); }
+int32_t ensure_staging(DeviceContext* ctx, size_t bytes) { return grow(&ctx->staging, &ctx->staging_bytes, bytes, "staging"); }
+
+}  // namespace nova
+
+using namespace nova;
+
+extern "C" {
+
+int32_t nova_b200_abi_version(void) { return NOVA_B200_ABI_VERSION; }
+
+const char* nova_b200_last_error_string(void) { return g_last_error.c_str(); }
+
+int32_t nova_b200_init(int32_t device) {
+  if (device >= 0) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+      cudaGetLastError();
+      return fail(NOVA_B200_ERR_NO_DEVICE, "no CUDA device is visible; libnova_b200 has no CPU fallback");
+    }
+    if (device >= count) return fail(NOVA_B200_ERR_INVALID_ARG, "nova_b200_init: device index out of range");
+    NOVA_CUDA_OK(cudaSetDevice(device));
+  }
+  int32_t st = NOVA_B200_OK;
+  current_context(&st);
+  return st;
+}
+
+int32_t nova_b200_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_ctx_mu);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  for (auto& kv : g_contexts) {
+    DeviceContext* c = kv.second.get();
+    if (cudaSetDevice(c->device) != cudaSuccess) continue;
+    cudaDeviceSynchronize();
+    if (c->status_word) cudaFree(c->status_word);
+    if (c->scratch) cudaFree(c->scratch);
+    if (c->staging) cudaFree(c->staging);
+  }
+  g_contexts.clear();
+  if (prev >= 0) cudaSetDevice(prev);
+  cudaGetLastError();
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_device_status(uint32_t* code_out) {
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  uint32_t code = 0;
+  NOVA_CUDA_OK(cudaDeviceSynchronize());
+  NOVA_CUDA_OK(cudaMemcpy(&code, ctx->status_word, 4, cudaMemcpyDeviceToHost));
+  if (code != 0) NOVA_CUDA_OK(cudaMemset(ctx->status_word, 0, 4));
+  if (code_out) *code_out = code;
+  if (code != 0)
+    return fail(NOVA_B200_ERR_DEVICE_TIMEOUT, "a bounded in-kernel wait gave up, code 0x" + [&] {
+      char b[16];
+      snprintf(b, sizeof b, "%x", code);
+      return std::string(b);
+    }());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
+  return gemm_plan_only(args, out);
+}
+
+int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream) {
+  // validate first so that argument errors are reported even on a machine without a GPU
+  nova_b200_gemm_plan_info info;
+  int32_t st = gemm_plan_only(args, &info);
+  if (st != NOVA_B200_OK) return st;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  return gemm_launch(ctx, args, static_cast<cudaStream_t>(stream));
+}
+
+int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
+  nova_b200_gemm_plan_info info;
+  int32_t st = gemm_plan_only(args, &info);
+  if (st != NOVA_B200_OK) return st;
+  if (args->batch == 0 || args->M == 0 || args->N == 0) return NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  const nova_b200_gemm_args& a = *args;
+  const int es = dtype_bytes(a.dtype_ab), os = dtype_bytes(a.dtype_c);
+  auto span = [](int64_t batch, int64_t bstride, int64_t rows, int64_t ld, int64_t cols) -> int64_t {
+    // elements from the first to one past the last addressed element
+    if (rows == 0 || cols == 0) return 0;
+    return (bstride == 0 ? 0 : (batch - 1) * bstride) + (rows - 1) * ld + cols;
+  };
+  const int64_t a_rows = a.trans_a ? a.K : a.M, a_cols = a.trans_a ? a.M : a.K;
+  const int64_t b_rows = a.trans_b ? a.N : a.K, b_cols = a.trans_b ? a.K : a.N;
+  const size_t a_bytes = a.K ? span(a.batch, a.batch_stride_a, a_rows, a.lda, a_cols) * es : 0;
+  const size_t b_bytes = a.K ? span(a.batch, a.batch_stride_b, b_rows, a.ldb, b_cols) * es : 0;
+  const size_t c_bytes = span(a.batch, a.batch_stride_c, a.M, a.ldc, a.N) * os;
+  const size_t bias_bytes = a.init == NOVA_B200_INIT_BIAS_ROW ? a.N * os : 0;
+  const size_t r_bytes = a.init == NOVA_B200_INIT_RESIDUAL_FULL ? span(a.batch, a.batch_stride_r, a.M, a.ldr, a.N) * os : 0;
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t total = up(a_bytes) + up(b_bytes) + up(c_bytes) + up(bias_bytes) + up(r_bytes);
+  std::lock_guard<std::mutex> lock(ctx->host_mu);
+  st = ensure_staging(ctx, total);
+  if (st != NOVA_B200_OK) return st;
+  char* base = static_cast<char*>(ctx->staging);
+  char* dA = base; char* dB = dA + up(a_bytes); char* dC = dB + up(b_bytes);
+  char* dBias = dC + up(c_bytes); char* dR = dBias + up(bias_bytes);
+  cudaStream_t s = nullptr;
+  if (a_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dA, a.A, a_bytes, cudaMemcpyHostToDevice, s));
+  if (b_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dB, a.B, b_bytes, cudaMemcpyHostToDevice, s));
+  if (bias_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dBias, a.bias, bias_bytes, cudaMemcpyHostToDevice, s));
+  if (r_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dR, a.residual, r_bytes, cudaMemcpyHostToDevice, s));
+  if (a.init == NOVA_B200_INIT_FROM_C || a.ldc != a.N || (a.batch > 1 && a.batch_stride_c != a.M * a.ldc))
+    NOVA_CUDA_OK(cudaMemcpyAsync(dC, a.C, c_bytes, cudaMemcpyHostToDevice, s));  // keep bytes the kernel does not write
+  nova_b200_gemm_args d = a;
+  d.A = dA; d.B = dB; d.C = dC; d.bias = dBias; d.residual = dR;
+  st = gemm_launch(ctx, &d, s);
+  if (st != NOVA_B200_OK) return st;
+  NOVA_CUDA_OK(cudaMemcpyAsync(a.C, dC, c_bytes, cudaMemcpyDeviceToHost, s));
+  NOVA_CUDA_OK(cudaStreamSynchronize(s));
+  return NOVA_B200_OK;
+}
+
+// ---------------------------------------------------------------- memref-descriptor entry points
+
+namespace {
+
+bool is_device_pointer(const void* p) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+// Maps a rank-2 (or the inner two dims of a rank-3) descriptor onto {pointer, pitch, transposed}.
+int32_t inner2(const int64_t* sizes, const int64_t* strides, int64_t* ld, int32_t* trans, const char* name) {
+  auto at_least = [](int64_t v, int64_t lo) { return v < lo ? lo : v; };
+  if (sizes[1] == 1 || strides[1] == 1) {
+    *trans = 0;
+    *ld = sizes[0] > 1 ? strides[0] : at_least(strides[0], sizes[1]);
+    return NOVA_B200_OK;
+  }
+  if (sizes[0] == 1 || strides[0] == 1) {
+    *trans = 1;
+    *ld = sizes[1] > 1 ? strides[1] : at_least(strides[1], sizes[0]);
+    return NOVA_B200_OK;
+  }
+  return fail(NOVA_B200_ERR_LAYOUT, std::string(name) + ": neither of the two inner strides is 1");
+}
+
+int32_t run_descriptor_gemm(nova_b200_gemm_args& g) {
+  const bool dev = is_device_pointer(g.C);
+  if (dev != is_device_pointer(g.A) || dev != is_device_pointer(g.B))
+    return fail(NOVA_B200_ERR_INVALID_ARG, "memref entry point: operands must be all host or all device memory");
+  if (dev) {
+    int32_t st = nova_b200_gemm(&g, nullptr);
+    if (st != NOVA_B200_OK) return st;
+    NOVA_CUDA_OK(cudaStreamSynchronize(nullptr));
+    return NOVA_B200_OK;
+  }
+  return nova_b200_gemm_host(&g);
+}
+
+}  // namespace
+
+int32_t _mlir_ciface_nova_b200_matmul(nova_b200_memref2d* C, nova_b200_memref2d* A, nova_b200_memref2d* B,
+                                      int32_t dtype) {
+  if (!C || !A || !B) return fail(NOVA_B200_ERR_INVALID_ARG, "matmul: null descriptor");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "matmul: dtype must be f32, f16 or bf16");
+  if (A->sizes[1] != B->sizes[0] || C->sizes[0] != A->sizes[0] || C->sizes[1] != B->sizes[1])
+    return fail(NOVA_B200_ERR_INVALID_ARG, "matmul: shapes do not compose");  // MatmulOp::verify, NovaOps.cpp:1247-1254
+  const int es = dtype_bytes(dtype);
+  nova_b200_gemm_args g{};
+  g.struct_size = sizeof(g);
+  g.dtype_ab = g.dtype_c = dtype;
+  g.batch = 1; g.M = A->sizes[0]; g.K = A->sizes[1]; g.N = B->sizes[1];
+  int32_t st, tc = 0;
+  if ((st = inner2(A->sizes, A->strides, &g.lda, &g.trans_a, "matmul A")) != NOVA_B200_OK) return st;
+  if ((st = inner2(B->sizes, B->strides, &g.ldb, &g.trans_b, "matmul B")) != NOVA_B200_OK) return st;
+  if ((st = inner2(C->sizes, C->strides, &g.ldc, &tc, "matmul C")) != NOVA_B200_OK) return st;
+  if (tc) return fail(NOVA_B200_ERR_LAYOUT, "matmul: C must have unit inner stride");
+  g.A = static_cast<char*>(A->aligned) + A->offset * es;
+  g.B = static_cast<char*>(B->aligned) + B->offset * es;
+  g.C = static_cast<char*>(C->aligned) + C->offset * es;
+  return run_descriptor_gemm(g);
+}
+
+int32_t _mlir_ciface_nova_b200_batch_matmul(nova_b200_memref3d* C, nova_b200_memref3d* A, nova_b200_memref3d* B,
+                                            int32_t ab_dtype, int32_t c_dtype) {
+  if (!C || !A || !B) return fail(NOVA_B200_ERR_INVALID_ARG, "batch_matmul: null descriptor");
+  if (!is_float_dtype(ab_dtype) || !is_float_dtype(c_dtype))
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "batch_matmul: dtypes must be f32, f16 or bf16");
+  if (A->sizes[0] != C->sizes[0] || (B->sizes[0] != C->sizes[0] && B->sizes[0] != 1) || A->sizes[2] != B->sizes[1] ||
+      C->sizes[1] != A->sizes[1] || C->sizes[2] != B->sizes[2])
+    return fail(NOVA_B200_ERR_INVALID_ARG, "batch_matmul: shapes do not compose");
+  nova_b200_gemm_args g{};
+  g.struct_size = sizeof(g);
+  g.dtype_ab = ab_dtype; g.dtype_c = c_dtype;
+  g.batch = C->sizes[0]; g.M = A->sizes[1]; g.K = A->sizes[2]; g.N = B->sizes[2];
+  int32_t st, tc = 0;
+  if ((st = inner2(A->sizes + 1, A->strides + 1, &g.lda, &g.trans_a, "batch_matmul A")) != NOVA_B200_OK) return st;
+  if ((st = inner2(B->sizes + 1, B->strides + 1, &g.ldb, &g.trans_b, "batch_matmul B")) != NOVA_B200_OK) return st;
+  if ((st = inner2(C->sizes + 1, C->strides + 1, &g.ldc, &tc, "batch_matmul C")) != NOVA_B200_OK) return st;
+  if (tc) return fail(NOVA_B200_ERR_LAYOUT, "batch_matmul: C must have unit inner stride");
+  g.batch_stride_a = A->strides[0];
+  g.batch_stride_b = B->sizes[0] == 1 ? 0 : B->strides[0];
+  g.batch_stride_c = C->strides[0];
+  const int es = dtype_bytes(ab_dtype), os = dtype_bytes(c_dtype);
+  g.A = static_cast<char*>(A->aligned) + A->offset * es;
+  g.B = static_cast<char*>(B->aligned) + B->offset * es;
+  g.C = static_cast<char*>(C->aligned) + C->offset * os;
+  return run_descriptor_gemm(g);
+}
+
+int32_t _mlir_ciface_nova_b200_linear(nova_b200_memref2d* Y, nova_b200_memref2d* X, nova_b200_memref2d* W,
+                                      nova_b200_memref1d* bias, int32_t dtype, int32_t act) {
+  if (!Y || !X || !W || !bias) return fail(NOVA_B200_ERR_INVALID_ARG, "linear: null descriptor");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "linear: dtype must be f32, f16 or bf16");
+  if (X->sizes[1] != W->sizes[0] || Y->sizes[0] != X->sizes[0] || Y->sizes[1] != W->sizes[1] ||
+      bias->sizes[0] != W->sizes[1])
+    return fail(NOVA_B200_ERR_INVALID_ARG, "linear: shapes do not compose");
+  if (bias->sizes[0] > 1 && bias->strides[0] != 1) return fail(NOVA_B200_ERR_LAYOUT, "linear: bias must be contiguous");
+  const int es = dtype_bytes(dtype);
+  nova_b200_gemm_args g{};
+  g.struct_size = sizeof(g);
+  g.dtype_ab = g.dtype_c = dtype;
+  g.act = act;
+  g.init = NOVA_B200_INIT_BIAS_ROW;
+  g.batch = 1; g.M = X->sizes[0]; g.K = X->sizes[1]; g.N = W->sizes[1];
+  int32_t st, tc = 0;
+  if ((st = inner2(X->sizes, X->strides, &g.lda, &g.trans_a, "linear X")) != NOVA_B200_OK) return st;
+  if ((st = inner2(W->sizes, W->strides, &g.ldb, &g.trans_b, "linear W")) != NOVA_B200_OK) return st;
+  if ((st = inner2(Y->sizes, Y->strides, &g.ldc, &tc, "linear Y")) != NOVA_B200_OK) return st;
+  if (tc) return fail(NOVA_B200_ERR_LAYOUT, "linear: Y must have unit inner stride");
+  g.A = static_cast<char*>(X->aligned) + X->offset * es;
+  g.B = static_cast<char*>(W->aligned) + W->offset * es;
+  g.C = static_cast<char*>(Y->aligned) + Y->offset * es;
+  g.bias = static_cast<char*>(bias->aligned) + bias->offset * es;
+  const bool dev = is_device_pointer(g.C);
+  if (dev != is_device_pointer(g.bias))
+    return fail(NOVA_B200_ERR_INVALID_ARG, "linear: operands must be all host or all device memory");
+  return run_descriptor_gemm(g);
+}
+
+}  // extern "C"

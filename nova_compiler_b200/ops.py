@@ -1,0 +1,311 @@
+"""Host-side mirror of the Nova operator surface for the matmul hot path, on torch CUDA tensors.
+
+Each function corresponds to one nova / linalg op as it reaches code generation in the reference
+and forwards to ONE call of the C ABI (include/nova_b200.h).  torch is used only to own device
+memory and streams; all arithmetic happens in libnova_b200's CUDA kernels.  There is no fallback:
+a missing library raises ImportError, a missing GPU raises NovaB200Error(ERR_NO_DEVICE).
+
+Shape and dtype rules follow the reference's op definitions:
+  * matmul        MatmulOp::inferReturnTypes (lib/Dialect/nova/NovaOps.cpp:1116-1285): [...,M,K] x [...,K,N],
+                  numpy-style batch broadcast, 1-D operands promoted, K mismatch is an error.
+  * linear        LinearOp (NovaOps.cpp:2075-2103): rank-2 or rank-3 input, 2-D weight shared across
+                  the batch without a copy (NovaToLinalgGeneric.cpp:1726-1753), result dtype = input dtype.
+  * gelu/relu/add/softmax/layer_norm/gather/reshape/transpose: see each docstring.
+One deliberate difference: 16-bit inputs accumulate in fp32 and return the INPUT dtype (the
+reference infers f16 for every 16-bit matmul, including bf16 x bf16, NovaOps.cpp:1198).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+_DT = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+_IDX = {torch.int16: L.I16, torch.int32: L.I32, torch.int64: L.I64}
+_ACT = {None: L.ACT_NONE, "none": L.ACT_NONE, "relu": L.ACT_RELU, "gelu": L.ACT_GELU_TANH, "gelu_tanh": L.ACT_GELU_TANH}
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, f"dtype {t.dtype} has no kernel (f32, f16, bf16 only)") from None
+
+
+def _require_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise L.NovaB200Error(L.ERR_NO_DEVICE, "tensor is not on a CUDA device; libnova_b200 has no CPU fallback")
+
+
+def _inner2(t: torch.Tensor) -> Tuple[int, bool]:
+    """(row pitch in elements, stored-transposed?) of the last two dims; copies never happen here."""
+    r, c = t.shape[-2], t.shape[-1]
+    sr, sc = t.stride(-2), t.stride(-1)
+    if sc == 1 or c == 1:
+        return (sr if r > 1 else max(sr, c)), False
+    if sr == 1 or r == 1:
+        return (sc if c > 1 else max(sc, r)), True
+    raise L.NovaB200Error(L.ERR_LAYOUT, "neither of the two inner strides is 1")
+
+
+def _batch_stride(t: torch.Tensor) -> int:
+    """Stride of a [B, R, C] tensor's batch dim; 0 when the batch is broadcast (expand) or of size 1."""
+    return 0 if t.shape[0] == 1 else t.stride(0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
+         out_dtype: Optional[torch.dtype] = None, accumulate_into_out: bool = False,
+         f32_mode: int = L.TF32X3) -> torch.Tensor:
+    """C[b] = act(init + A[b] @ B[b]) on rank-3 views; A: [B,M,K], B: [B or 1,K,N] (any of the two inner
+    dims may be the contiguous one: transposed views are passed as trans_a / trans_b, not copied)."""
+    _require_cuda(a, b, bias, residual, out)
+    if a.dim() != 3 or b.dim() != 3:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "gemm expects rank-3 views")
+    if a.dtype != b.dtype:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "A and B must share a dtype")
+    B_, M, K = a.shape
+    Bb, Kb, N = b.shape
+    if K != Kb:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, f"contraction dims differ: {K} vs {Kb}")  # NovaOps.cpp:1247-1254
+    if Bb not in (1, B_):
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "batch dims do not broadcast")
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is None:
+        out = torch.empty((B_, M, N), dtype=out_dtype, device=a.device)
+    g = L.GemmArgs()
+    g.struct_size = C.sizeof(L.GemmArgs)
+    g.dtype_ab, g.dtype_c = _dt(a), _DT[out_dtype]
+    g.lda, ta = _inner2(a)
+    g.ldb, tb = _inner2(b)
+    ldc, tc = _inner2(out)
+    if tc:
+        raise L.NovaB200Error(L.ERR_LAYOUT, "output must have unit inner stride")
+    g.trans_a, g.trans_b, g.ldc = int(ta), int(tb), ldc
+    g.act = _ACT[act]
+    g.f32_mode = f32_mode
+    g.batch, g.M, g.N, g.K = B_, M, N, K
+    g.A, g.B, g.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.batch_stride_a = _batch_stride(a) if B_ > 1 else 0
+    g.batch_stride_b = 0 if Bb == 1 else b.stride(0)
+    g.batch_stride_c = out.stride(0) if B_ > 1 else M * ldc
+    if a.shape[0] > 1 and a.stride(0) == 0:
+        g.batch_stride_a = 0
+    g.init = L.INIT_ZERO
+    if bias is not None:
+        if bias.dtype != out_dtype or bias.numel() != N or not bias.is_contiguous():
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "bias must be a contiguous [N] tensor of the output dtype")
+        g.init, g.bias = L.INIT_BIAS_ROW, bias.data_ptr()
+    elif residual is not None:
+        r3 = residual if residual.dim() == 3 else residual.unsqueeze(0)
+        if r3.dtype != out_dtype or tuple(r3.shape[-2:]) != (M, N) or r3.stride(-1) != 1:
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "residual must be [B,M,N] of the output dtype, unit inner stride")
+        g.init, g.residual, g.ldr = L.INIT_RESIDUAL_FULL, r3.data_ptr(), r3.stride(-2)
+        g.batch_stride_r = 0 if r3.shape[0] == 1 else r3.stride(0)
+    elif accumulate_into_out:
+        g.init = L.INIT_FROM_C
+    L.check(L.load().nova_b200_gemm(C.byref(g), _stream()))
+    return out
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, *, act: Optional[str] = None, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, f32_mode: int = L.TF32X3) -> torch.Tensor:
+    """nova.matmul (NovaMatmulOpLowering, NovaToLinalg.cpp:874-1050): rank 2 -> linalg.matmul; rank 3 ->
+    linalg.batch_matmul with a 2-D / batch-1 operand broadcast (here: batch stride 0, no materialised copy);
+    rank > 3 -> batch dims collapsed to one (metadata only) and expanded back."""
+    if a.dim() == 1 and b.dim() == 1:  # 1-D . 1-D -> scalar (NovaOps.cpp:1227-1240)
+        return matmul(a.unsqueeze(0), b.unsqueeze(1), act=act, out_dtype=out_dtype, f32_mode=f32_mode).reshape(())
+    squeeze_m = a.dim() == 1
+    squeeze_n = b.dim() == 1
+    if squeeze_m:
+        a = a.unsqueeze(0)
+    if squeeze_n:
+        b = b.unsqueeze(1)
+    batch_shape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    M, N = a.shape[-2], b.shape[-1]
+
+    def as3(t: torch.Tensor) -> torch.Tensor:
+        if t.dim() == 2 or all(s == 1 for s in t.shape[:-2]):
+            return t.reshape(1, t.shape[-2], t.shape[-1]) if t.dim() != 3 else t
+        t = t.expand(*batch_shape, t.shape[-2], t.shape[-1])
+        if len(batch_shape) == 1:
+            return t
+        # collapsing several batch dims must stay a view (tensor.collapse_shape is metadata)
+        try:
+            return t.view(-1, t.shape[-2], t.shape[-1])
+        except RuntimeError:
+            return t.reshape(-1, t.shape[-2], t.shape[-1])  # broadcast across an outer batch dim: materialise
+
+    a3, b3 = as3(a), as3(b)
+    nb = 1
+    for s in batch_shape:
+        nb *= s
+    if a3.shape[0] == 1 and nb > 1:
+        a3 = a3.expand(nb, -1, -1)
+    out3 = gemm(a3, b3, act=act, bias=bias, out_dtype=out_dtype, f32_mode=f32_mode)
+    out = out3.reshape(*batch_shape, M, N)
+    if squeeze_m:
+        out = out.squeeze(-2)
+    if squeeze_n:
+        out = out.squeeze(-1)
+    return out
+
+
+def batch_matmul(a: torch.Tensor, b: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
+                 out: Optional[torch.Tensor] = None, act: Optional[str] = None) -> torch.Tensor:
+    """linalg.batch_matmul ins(A[B,M,K], B[B,K,N]) outs(C[B,M,N]) with fp32 accumulation."""
+    return gemm(a, b, out=out, out_dtype=out_dtype, act=act)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, *, act: Optional[str] = None) -> torch.Tensor:
+    """nova.linear (+ optional trailing nova.gelu / nova.relu fused as the epilogue): Y = act(X @ W + bias),
+    X rank 2 or 3, W [K,N] shared across the batch, bias of N elements (any rank: flattened like
+    NovaToLinalgGeneric.cpp:1772-1784)."""
+    if x.dim() not in (2, 3):
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "linear: input must be rank 2 or 3")  # NovaOps.cpp:2097-2101
+    if w.dim() != 2:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "linear: weight must be rank 2")
+    x3 = x.unsqueeze(0) if x.dim() == 2 else x
+    # a contiguous [B,M,K] input with a shared weight is one [B*M,K] GEMM
+    if x3.dim() == 3 and x3.is_contiguous():
+        x3 = x3.reshape(1, -1, x3.shape[-1])
+    y = gemm(x3, w.unsqueeze(0), bias=bias.reshape(-1), act=act)
+    return y.reshape(*x.shape[:-1], w.shape[-1])
+
+
+def _unary(x: torch.Tensor, act: int) -> torch.Tensor:
+    _require_cuda(x)
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    L.check(L.load().nova_b200_activation(xc.data_ptr(), y.data_ptr(), xc.numel(), _dt(xc), act, _stream()))
+    return y
+
+
+def gelu(x: torch.Tensor) -> torch.Tensor:
+    """nova.gelu, tanh form (NovaGeluForwardPattern, NovaToLinalgGeneric.cpp:1277-1337)."""
+    return _unary(x, L.ACT_GELU_TANH)
+
+
+def relu(x: torch.Tensor) -> torch.Tensor:
+    """nova.relu -> max(x, 0) (NovaToLinalg.cpp:1053-1084)."""
+    return _unary(x, L.ACT_RELU)
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """nova.add where b either has a's shape or broadcasts along rows ([N] or [1,N] against [...,N]),
+    the forms next to a contraction (ltest/test_cpu.mlir: 8x10 + 1x10).  Other broadcasts are out of scope."""
+    _require_cuda(a, b)
+    if a.dtype != b.dtype:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "add: mixed dtypes are out of scope")
+    ac, bc = a.contiguous(), b.contiguous()
+    cols = ac.shape[-1]
+    full = bc.numel() == ac.numel() and bc.shape[-1] == cols
+    if not full and not (bc.numel() == cols and bc.shape[-1] == cols):
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "add: only same-shape or row-broadcast operands are supported")
+    out = torch.empty_like(ac)
+    L.check(L.load().nova_b200_add_rowbcast(ac.data_ptr(), bc.data_ptr(), out.data_ptr(), ac.numel() // cols, cols,
+                                            int(full), _dt(ac), _stream()))
+    return out
+
+
+def softmax(x: torch.Tensor, dimension: int = -1) -> torch.Tensor:
+    """nova.softmax (NovaSoftmaxForwardPattern, NovaToLinalgGeneric.cpp:1427-1534) along `dimension`
+    (default -1, negative wraps, :1439-1443).  Non-last dimensions are moved last and back."""
+    _require_cuda(x)
+    rank = x.dim()
+    dim = dimension
+    if dim > rank:
+        dim = rank - 1
+    if dim < 0:
+        dim += rank
+    xm = x.movedim(dim, -1).contiguous()
+    y = torch.empty_like(xm)
+    D = xm.shape[-1]
+    L.check(L.load().nova_b200_softmax(xm.data_ptr(), y.data_ptr(), xm.numel() // max(D, 1), D, _dt(xm), _stream()))
+    return y.movedim(-1, dim)
+
+
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
+    """nova.layer_norm over the last dim (NovaLayerNormPattern, NovaToLinalgGeneric.cpp:1997-2126).
+    Returns (y, mean_sum, rstd): mean_sum is the RAW row sum, as in the reference (:2121-2123)."""
+    _require_cuda(x, gamma, beta)
+    xc, g, b = x.contiguous(), gamma.contiguous(), beta.contiguous()
+    D = xc.shape[-1]
+    if g.numel() != D or b.numel() != D or g.dtype != xc.dtype or b.dtype != xc.dtype:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "layer_norm: gamma/beta must be [D] of x's dtype")
+    y = torch.empty_like(xc)
+    mean_sum = torch.empty(xc.shape[:-1], dtype=xc.dtype, device=xc.device)
+    rstd = torch.empty(xc.shape[:-1], dtype=xc.dtype, device=xc.device)
+    L.check(L.load().nova_b200_layer_norm(xc.data_ptr(), g.data_ptr(), b.data_ptr(), y.data_ptr(), mean_sum.data_ptr(),
+                                          rstd.data_ptr(), xc.numel() // max(D, 1), D, _dt(xc), _stream()))
+    return y, mean_sum, rstd
+
+
+def gather(inp: torch.Tensor, indices: torch.Tensor, axis: int = 0, *, return_bad_count: bool = False):
+    """nova.gather (NovaGatherOpLowering, NovaToLinalgGeneric.cpp:2372-2472; shapes NovaOps.cpp:1898-1946):
+    out[pre..., idx..., post...] = inp[pre..., indices[...], post...].  Leading index dims equal to inp's
+    leading dims act as batch dims.  i16 indices are zero-extended.  Bit-exact."""
+    _require_cuda(inp, indices)
+    if indices.dtype not in _IDX:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "gather: index dtype must be int16, int32 or int64")
+    x = inp.contiguous()
+    idx = indices.contiguous()
+    if axis < 0:
+        axis += x.dim()
+    batch_dims = 0
+    for i in range(min(axis, idx.dim())):
+        if x.shape[i] != idx.shape[i]:
+            break
+        batch_dims += 1
+    batched = axis > 0 and batch_dims == axis
+    if axis > 0 and not batched and batch_dims != 0:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "gather: partially batched indices are out of scope")
+    pre = 1
+    for s in x.shape[:axis]:
+        pre *= s
+    post = 1
+    for s in x.shape[axis + 1:]:
+        post *= s
+    idx_shape = tuple(idx.shape[batch_dims:]) if batched else tuple(idx.shape)
+    n_idx = 1
+    for s in idx_shape:
+        n_idx *= s
+    out = torch.empty(tuple(x.shape[:axis]) + idx_shape + tuple(x.shape[axis + 1:]), dtype=x.dtype, device=x.device)
+    bad = torch.zeros(1, dtype=torch.int64, device=x.device)
+    L.check(L.load().nova_b200_gather(x.data_ptr(), idx.data_ptr(), out.data_ptr(), pre, x.shape[axis], post, n_idx,
+                                      _IDX[idx.dtype], int(batched), x.element_size(), bad.data_ptr(), _stream()))
+    return (out, int(bad.item())) if return_bad_count else out
+
+
+def reshape(x: torch.Tensor, shape) -> torch.Tensor:
+    """nova.reshape -> tensor.reshape (ReshapeOpConverter, NovaToLinalg.cpp:2409-2434): a row-major
+    reinterpretation with equal element count (verify: NovaOps.cpp:1885-1895); no data movement."""
+    n = 1
+    for s in shape:
+        n *= s
+    if n != x.numel():
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "reshape: element counts differ")
+    return x.contiguous().view(*shape)
+
+
+def transpose(x: torch.Tensor, axes1: int = -1, axes2: int = -2) -> torch.Tensor:
+    """nova.transpose (NovaOps.td:832-843): swaps two dims; returned as a VIEW so that a following
+    matmul consumes it through trans_a / trans_b (the matmul_transpose_a fusion, NovaToLinalg.cpp:824-872)."""
+    return x.transpose(axes1, axes2)
+
+
+def device_status() -> int:
+    """Reads and clears the device status word (0 == every bounded in-kernel wait completed)."""
+    code = C.c_uint32(0)
+    st = L.load().nova_b200_device_status(C.byref(code))
+    if st not in (L.OK, L.ERR_DEVICE_TIMEOUT):
+        L.check(st)
+    return int(code.value)
