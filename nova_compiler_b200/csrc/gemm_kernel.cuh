@@ -400,7 +400,10 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
                   if (inner0 + e < inner_limit) v.w[e] = __ldg(reinterpret_cast<const uint32_t*>(src) + e);
               }
             }
-            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + ((ch ^ (r & 7)) << 4)) = v.u;
+            // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the
+            // 128-byte swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
+            const int sw = (kElemBytes == 4 && mn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
+            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v.u;
           }
         }
         fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core (async proxy)

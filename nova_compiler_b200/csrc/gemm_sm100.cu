@@ -120,14 +120,14 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
 // rows x cols matrix with `cols` contiguous, pitch ld, `nb` batches `bstride` elements apart.
 int32_t encode_operand_map(DeviceContext* ctx, CUtensorMap* out, const void* base, int es, CUtensorMapDataType dt,
                            int64_t rows, int64_t cols, int64_t ld, int64_t nb, int64_t bstride, uint32_t box_inner,
-                           uint32_t box_outer) {
+                           uint32_t box_outer, CUtensorMapSwizzle swizzle) {
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(nb)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * es,
                            nb > 1 ? static_cast<cuuint64_t>(bstride) * es : static_cast<cuuint64_t>(rows) * ld * es};
   cuuint32_t box[3] = {box_inner, box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = ctx->encode_tiled(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
-                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(NOVA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(r));
   return NOVA_B200_OK;
@@ -224,11 +224,17 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   //   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused; one UMMA K step = 32 B.
   //   MN-major: 128 B = one chunk of MN elements for one k; 8 k-rows = 1024 B (SBO); the next chunk of
   //             MN elements starts BLOCK_K*128 B further (LBO); one UMMA K step = UMMA_K*128 B.
+  //   MN-major 32-bit (tf32) operands exist only in the 128-byte swizzle with 32-byte atoms (layout type 1,
+  //             the tensor map's SWIZZLE_128B_ATOM_32B): its pattern repeats every 4 k-rows, so SBO = 512 B.
   const uint32_t umma_k = 32u / es;
-  const uint32_t sbo = env_u32("NOVA_B200_DBG_SBO", 1024u);
-  const uint32_t lbo_mn = env_u32("NOVA_B200_DBG_LBO_MN", static_cast<uint32_t>(block_k) * kSwizzleBytes);
-  const uint32_t desc_hi = ((sbo >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);  // SBO | version=1 | SWIZZLE_128B
-  p.a_desc_hi = p.b_desc_hi = desc_hi;
+  const uint32_t lbo_mn = static_cast<uint32_t>(block_k) * kSwizzleBytes;
+  auto desc_hi = [&](bool mn) {
+    const bool atom32 = mn && es == 4;
+    const uint32_t sbo = atom32 ? 512u : 1024u;
+    return ((sbo >> 4) & 0x3fffu) | (1u << 14) | ((atom32 ? 1u : 2u) << 29);  // SBO | version 1 | layout type
+  };
+  p.a_desc_hi = desc_hi(plan.a_mn);
+  p.b_desc_hi = desc_hi(plan.b_mn);
   p.a_desc_lbo = (plan.a_mn ? ((lbo_mn >> 4) & 0x3fffu) : 1u) << 16;
   p.b_desc_lbo = (plan.b_mn ? ((lbo_mn >> 4) & 0x3fffu) : 1u) << 16;
   p.a_kstep = plan.a_mn ? umma_k * kSwizzleBytes : 32u;
@@ -267,15 +273,20 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
                                 : a->dtype_ab == NOVA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const uint32_t chunk = static_cast<uint32_t>(block_k);  // 128 B of elements
+  auto swizzle_for = [&](bool mn) {
+    return mn && es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  };
   for (int t = 0; t < (plan.terms == 3 ? 2 : 1); ++t) {
     if (!pi.loader_a) {
       st = encode_operand_map(ctx, &maps[t], a_src[t], es, tdt, a_rows, a_cols, a_ld, a_nb, a_bs, chunk,
-                              plan.a_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(kBlockM));
+                              plan.a_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(kBlockM),
+                              swizzle_for(plan.a_mn));
       if (st != NOVA_B200_OK) return st;
     }
     if (!pi.loader_b) {
       st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows, b_cols, b_ld, b_nb, b_bs, chunk,
-                              plan.b_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(block_n));
+                              plan.b_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(block_n),
+                              swizzle_for(plan.b_mn));
       if (st != NOVA_B200_OK) return st;
     }
   }

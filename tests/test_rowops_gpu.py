@@ -1,0 +1,125 @@
+"""Parity of the row-wise kernels (layer_norm, softmax, gather, activation, add) against the CPU oracle.
+f32: rel-Frobenius <= 1e-5.  f16/bf16: the kernels compute in fp32 and round once, compared with the
+oracle in the same mode, <= 1e-3.  Gather / reshape / transpose: bit-exact."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from test_gemm_gpu import GOLD, _tdt, check, rand_bits, to_dev, to_host  # noqa: E402
+
+ROW_SHAPES = [(64, 384), (33, 1000), (16, 4096), (5, 8192), (3, 10000), (7, 37), (1, 1), (300, 2048)]
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_layer_norm(cuda, oracle, dt):
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(1)
+    for rows, D in ROW_SHAPES:
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 2.0)
+        g = rand_bits(oracle, rng, (D,), dt, "normal")
+        b = rand_bits(oracle, rng, (D,), dt, "normal")
+        y, ms, rs = ops.layer_norm(to_dev(cuda, x, dt), to_dev(cuda, g, dt), to_dev(cuda, b, dt))
+        wy, wms, wrs = oracle.layer_norm(x, g, b, dt, compute_f32=True)
+        check(oracle, to_host(cuda, y, dt), wy, dt)
+        check(oracle, to_host(cuda, ms, dt), wms, dt, tol=2e-3 if dt != "f32" else 1e-5)  # raw row sum
+        check(oracle, to_host(cuda, rs, dt), wrs, dt)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_softmax(cuda, oracle, dt):
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(2)
+    for rows, D in ROW_SHAPES:
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
+        y = ops.softmax(to_dev(cuda, x, dt))
+        check(oracle, to_host(cuda, y, dt), oracle.softmax(x, dt, compute_f32=True), dt)
+    # non-last dimension and the attention-score layout
+    x = rand_bits(oracle, rng, (4, 96, 50), "f32", "normal")
+    y = ops.softmax(to_dev(cuda, x, "f32"), dimension=1)
+    want = np.swapaxes(oracle.softmax(np.ascontiguousarray(np.swapaxes(x, 1, 2))), 1, 2)
+    check(oracle, to_host(cuda, y, "f32"), want, "f32")
+
+
+def test_row_ops_golden_vectors(cuda, oracle):
+    from nova_compiler_b200 import ops
+    z = np.load(GOLD)
+    y, ms, rs = ops.layer_norm(to_dev(cuda, z["layer_norm_f32.x"], "f32"), to_dev(cuda, z["layer_norm_f32.gamma"], "f32"),
+                               to_dev(cuda, z["layer_norm_f32.beta"], "f32"))
+    check(oracle, to_host(cuda, y, "f32"), z["layer_norm_f32.y"], "f32")
+    check(oracle, to_host(cuda, ms, "f32"), z["layer_norm_f32.mean_sum"], "f32")
+    check(oracle, to_host(cuda, rs, "f32"), z["layer_norm_f32.rstd"], "f32")
+    check(oracle, to_host(cuda, ops.softmax(to_dev(cuda, z["softmax_f32.x"], "f32")), "f32"), z["softmax_f32.y"], "f32")
+    out = ops.gather(cuda.from_numpy(z["gather_i16.table"]).cuda(), cuda.from_numpy(z["gather_i16.ids"]).cuda())
+    assert np.array_equal(out.cpu().numpy(), z["gather_i16.out"])
+
+
+def test_gather_bit_exact(cuda, oracle):
+    torch = cuda
+    from nova_compiler_b200 import ops
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+    # embedding lookup of ltest/test.mlir:17: [50304,384] table, [8,1024] i16 ids (zero-extended)
+    table = torch.randn(50304, 384, device="cuda", generator=g).to(torch.bfloat16)
+    ids = torch.randint(0, 50304, (8, 1024), device="cuda", generator=g)
+    out = ops.gather(table, ids.to(torch.int16))
+    assert torch.equal(out, table[ids])
+    want, bad = oracle.gather(to_host(torch, table, "bf16"), ids.cpu().numpy().astype(np.uint16).view(np.int16))
+    assert bad == 0 and np.array_equal(to_host(torch, out, "bf16"), want)
+    # odd row widths take the narrower copy units; i32 / i64 indices; axis 1 with batched indices
+    for width, dt in ((33, torch.float32), (7, torch.float16), (5, torch.int8), (1, torch.float64)):
+        t = torch.randint(-100, 100, (257, width), device="cuda", generator=g).to(dt)
+        idx = torch.randint(0, 257, (3, 19), device="cuda", generator=g)
+        assert torch.equal(ops.gather(t, idx.to(torch.int32)), t[idx])
+        assert torch.equal(ops.gather(t, idx), t[idx])
+    x = torch.randn(3, 10, 4, device="cuda", generator=g)
+    idx = torch.randint(0, 10, (3, 5), device="cuda", generator=g).to(torch.int32)
+    out = ops.gather(x, idx, axis=1)
+    assert torch.equal(out, torch.stack([x[i, idx[i].long()] for i in range(3)]))
+    # out-of-range indices: zero rows, counted
+    out, bad = ops.gather(table[:10], torch.tensor([3, 10, -1], device="cuda"), return_bad_count=True)
+    assert bad == 2 and torch.equal(out[0], table[3]) and not out[1:].any()
+
+
+def test_reshape_and_transpose_are_metadata(cuda, oracle):
+    torch = cuda
+    from nova_compiler_b200 import ops
+    x = torch.arange(8 * 1024 * 384, device="cuda", dtype=torch.float32).reshape(8, 1024, 384)
+    r = ops.reshape(x, (8192, 384))  # ltest/test.mlir:26-28
+    assert r.data_ptr() == x.data_ptr() and torch.equal(r.reshape(8, 1024, 384), x)
+    with pytest.raises(Exception):
+        ops.reshape(x, (8192, 385))
+    t = ops.transpose(x)
+    assert t.data_ptr() == x.data_ptr() and t.shape == (8, 384, 1024)
+    # a transposed view feeding a matmul is consumed through trans_a, not copied
+    a = torch.randn(64, 48, device="cuda")
+    b = torch.randn(64, 40, device="cuda")
+    got = ops.matmul(ops.transpose(a), b)
+    want = oracle.gemm(np.ascontiguousarray(a.cpu().numpy()), b.cpu().numpy(), trans_a=True)
+    check(oracle, got.cpu().numpy(), want, "f32")
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_activation_and_add(cuda, oracle, dt):
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(3)
+    for shape in ((1000, 333), (64, 64), (7,)):
+        x = rand_bits(oracle, rng, shape, dt, "normal", 2.0)
+        check(oracle, to_host(cuda, ops.gelu(to_dev(cuda, x, dt)), dt), oracle.activation(x, dt, "gelu_tanh", True), dt)
+        assert np.array_equal(to_host(cuda, ops.relu(to_dev(cuda, x, dt)), dt), oracle.activation(x, dt, "relu"))
+    a = rand_bits(oracle, rng, (8, 10), dt)
+    b = rand_bits(oracle, rng, (1, 10), dt)  # ltest/test_cpu.mlir: 8x10 + 1x10
+    assert np.array_equal(to_host(cuda, ops.add(to_dev(cuda, a, dt), to_dev(cuda, b, dt)), dt),
+                          oracle.add_rowbcast(a, b, dt))
+    assert np.array_equal(to_host(cuda, ops.add(to_dev(cuda, a, dt), to_dev(cuda, a, dt)), dt),
+                          oracle.add_rowbcast(a, a, dt))
+
+
+def test_test_cpu_mlir_graph_unfused(cuda, oracle):
+    """ltest/test_cpu.mlir as three separate ops (matmul, add, relu) equals the fused epilogue form."""
+    from nova_compiler_b200 import ops
+    z = np.load(GOLD)
+    a, b, bias = (to_dev(cuda, z[f"test_cpu_mlir.{k}"], "f32") for k in ("a", "b", "bias"))
+    unfused = ops.relu(ops.add(ops.matmul(a, b), bias.reshape(1, 10)))
+    check(oracle, to_host(cuda, unfused, "f32"), z["test_cpu_mlir.c"], "f32")
