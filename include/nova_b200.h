@@ -120,7 +120,7 @@ typedef struct nova_b200_gemm_args {
 typedef struct nova_b200_gemm_plan_info {
   int32_t loader_a;     /* 0 = TMA, 1 = predicated ld.global loader (unaligned base or pitch) */
   int32_t loader_b;
-  int32_t store_c;      /* 0 = 16-byte vector stores, 1 = element stores (unaligned C pitch)   */
+  int32_t store_c;      /* 0 = TMA stores of swizzled 32x128-byte boxes, 1 = element stores (unaligned C) */
   int32_t block_m, block_n, block_k;
   int32_t stages;
   int32_t grid;         /* persistent CTAs launched */

@@ -5,9 +5,11 @@
 //   warp 1      owns tensor memory (alloc/dealloc) and issues tcgen05.mma from one lane;
 //               tcgen05.commit releases ring stages and publishes finished accumulators.
 //   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (TMEM lane == output row),
-//               add bias / residual, apply ReLU / GELU, cast, store.  Two accumulator
+//               add bias / residual, apply ReLU / GELU, cast, stage 32x128-byte boxes in shared
+//               memory and write them with TMA stores (element stores when C is not 16-byte
+//               aligned).  Two accumulator
 //               buffers in TMEM let the epilogue of tile i overlap the mainloop of tile i+1.
-//   warps 6..9  (only launched when an operand cannot use TMA) predicated ld.global
+//   warps 6..13 (only launched when an operand cannot use TMA) predicated ld.global
 //               loader for operands whose base or pitch is not a multiple of 16 bytes.
 //
 // One CTA per SM; tiles are handed out round-robin in a grouped raster order so that
@@ -27,11 +29,11 @@ namespace nova {
 static constexpr int kBlockM = 128;          // UMMA M (cta_group::1): TMEM lane i holds output row i
 static constexpr int kSwizzleBytes = 128;    // operand rows in shared memory are 128 bytes
 static constexpr int kNumEpilogueWarps = 4;
-static constexpr int kNumLoaderWarps = 4;
+static constexpr int kNumLoaderWarps = 8;
 static constexpr int kFirstEpilogueWarp = 2;
 static constexpr int kFirstLoaderWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
 static constexpr int kThreadsTma = 32 * kFirstLoaderWarp;                      // 192
-static constexpr int kThreadsWithLoader = 32 * (kFirstLoaderWarp + kNumLoaderWarps);  // 320
+static constexpr int kThreadsWithLoader = 32 * (kFirstLoaderWarp + kNumLoaderWarps);  // 448
 
 struct GemmKernelParams {
   int32_t M, N, K, batch;
@@ -65,7 +67,11 @@ struct GemmSmemLayout {
   static constexpr int kRingBytes = kStages * kStageBytes;
   // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]; then tmem base + abort flag
   static constexpr int kNumBarriers = 2 * kStages + 4;
-  static constexpr int kBarrierOffset = kRingBytes;
+  // epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte boxes (double buffered)
+  static constexpr int kStageOutBox = 32 * kSwizzleBytes;
+  static constexpr int kStagingOffset = kRingBytes;
+  static constexpr int kStagingBytes = kNumEpilogueWarps * 2 * kStageOutBox;
+  static constexpr int kBarrierOffset = kStagingOffset + kStagingBytes;
   static constexpr int kMiscOffset = kBarrierOffset + 8 * kNumBarriers;
   static constexpr int kTotalBytes = kMiscOffset + 16;
   static constexpr int kDynamicBytes = kTotalBytes + 1024;  // slack to align the ring to 1024 bytes
@@ -112,24 +118,23 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-// One thread finishes 32 consecutive columns of one output row.
+// One thread finishes 32 consecutive columns of one output row: accumulator + init, activation.
+// `row_ok` guards the residual read of rows past M (their accumulators are zeros from the fill).
 template <typename OutT>
-__device__ __forceinline__ void epilogue_row_chunk(const GemmKernelParams& p, const uint32_t (&acc)[32], int32_t batch,
-                                                   int32_t row, int32_t col0) {
-  float v[32];
+__device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const uint32_t (&acc)[32], float (&v)[32],
+                                              int32_t batch, int32_t row, int32_t col0, bool row_ok) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
   const int32_t ncols = min(32, p.N - col0);
-  OutT* crow = reinterpret_cast<OutT*>(p.C) + static_cast<int64_t>(batch) * p.stride_c +
-               static_cast<int64_t>(row) * p.ldc + col0;
   if (p.init == NOVA_B200_INIT_BIAS_ROW) {
     const OutT* b = reinterpret_cast<const OutT*>(p.bias) + col0;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < ncols) v[j] += to_f32<OutT>(__ldg(b + j));
-  } else if (p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_FROM_C) {
+  } else if ((p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_FROM_C) && row_ok) {
     const OutT* r = p.init == NOVA_B200_INIT_FROM_C
-                        ? crow
+                        ? reinterpret_cast<const OutT*>(p.C) + static_cast<int64_t>(batch) * p.stride_c +
+                              static_cast<int64_t>(row) * p.ldc + col0
                         : reinterpret_cast<const OutT*>(p.residual) + static_cast<int64_t>(batch) * p.stride_r +
                               static_cast<int64_t>(row) * p.ldr + col0;
 #pragma unroll
@@ -143,20 +148,118 @@ __device__ __forceinline__ void epilogue_row_chunk(const GemmKernelParams& p, co
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f32(v[j]);
   }
-  constexpr int kPerVec = 16 / static_cast<int>(sizeof(OutT));
-  if (p.vec_store && ncols == 32) {
+}
+
+// Writes a staged box (32 rows x 128 B, swizzled) row by row with element stores, lane == column pair:
+// the path for outputs whose base or pitch is not 16-byte aligned.  Each store instruction covers a
+// contiguous span of one output row.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_store_rows(const GemmKernelParams& p, const uint8_t* box, int lane,
+                                                    int32_t batch, int32_t row0, int32_t col0) {
+  constexpr int kPerLane = 4 / static_cast<int>(sizeof(OutT));  // elements in one 32-bit word
+  OutT* cbase = reinterpret_cast<OutT*>(p.C) + static_cast<int64_t>(batch) * p.stride_c + col0 + lane * kPerLane;
+  const int32_t col = col0 + lane * kPerLane;
+#pragma unroll 4
+  for (int r = 0; r < 32; ++r) {
+    const int32_t row = row0 + r;
+    if (row >= p.M) break;  // uniform across the warp
+    union { uint32_t u; OutT e[kPerLane]; } w;
+    w.u = *reinterpret_cast<const uint32_t*>(box + r * kSwizzleBytes + (((lane >> 2) ^ (r & 7)) << 4) + (lane & 3) * 4);
+    OutT* dst = cbase + static_cast<int64_t>(row) * p.ldc;
 #pragma unroll
-    for (int j = 0; j < 32; j += kPerVec) {
-      union { uint4 u; OutT e[kPerVec]; } pk;
-#pragma unroll
-      for (int e = 0; e < kPerVec; ++e) pk.e[e] = from_f32<OutT>(v[j + e]);
-      *reinterpret_cast<uint4*>(crow + j) = pk.u;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) crow[j] = from_f32<OutT>(v[j]);
+    for (int e = 0; e < kPerLane; ++e)
+      if (col + e < p.N) dst[e] = w.e[e];
   }
+}
+
+// 32 columns of one row into the warp's staging box (32 rows x 128 B, 16-byte chunks XOR-swizzled by
+// row & 7, the layout a SWIZZLE_128B tensor map expects).  `first_chunk` is the index of the first
+// 16-byte chunk these 32 columns occupy within the 128-byte row.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_stage(uint8_t* box, const float (&v)[32], int lane, int first_chunk) {
+  constexpr int kPerVec = 16 / static_cast<int>(sizeof(OutT));
+#pragma unroll
+  for (int j = 0; j < 32; j += kPerVec) {
+    union { uint4 u; OutT e[kPerVec]; } pk;
+#pragma unroll
+    for (int e = 0; e < kPerVec; ++e) pk.e[e] = from_f32<OutT>(v[j + e]);
+    const int chunk = first_chunk + j / kPerVec;
+    *reinterpret_cast<uint4*>(box + lane * kSwizzleBytes + ((chunk ^ (lane & 7)) << 4)) = pk.u;
+  }
+}
+
+// One epilogue warp drains its 32 accumulator rows of one tile.
+template <typename OutT, int kBlockN>
+__device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const CUtensorMap* tmap_c, uint32_t taddr,
+                                              uint8_t* staging, uint32_t& box_iter, int lane, int32_t batch,
+                                              int32_t row0, int32_t n0) {
+  constexpr int kColsPerBox = kSwizzleBytes / static_cast<int>(sizeof(OutT));  // 64 (16-bit) or 32 (f32)
+  constexpr int kLoadsPerBox = kColsPerBox / 32;
+  const int32_t row = row0 + lane;
+  const bool row_ok = row < p.M;
+#pragma unroll 1
+  for (int c = 0; c < kBlockN / kColsPerBox; ++c) {
+    const int32_t col0 = n0 + c * kColsPerBox;
+    if (col0 >= p.N) break;  // uniform across the warp
+    uint8_t* box = staging + (box_iter & 1u) * (32 * kSwizzleBytes);
+    if (p.vec_store) {
+      // the box written two iterations ago must have been read out by its TMA store
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int h = 0; h < kLoadsPerBox; ++h) {
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * kColsPerBox + h * 32, r);
+      tmem_ld_wait();
+      float v[32];
+      epilogue_math<OutT>(p, r, v, batch, row, col0 + h * 32, row_ok);
+      epilogue_stage<OutT>(box, v, lane, h * (32 * static_cast<int>(sizeof(OutT)) / 16));
+    }
+    if (p.vec_store) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(tmap_c, smem_u32(box), col0, row0, batch);  // rows >= M and columns >= N are clipped
+        tma_store_commit();
+      }
+    } else {
+      __syncwarp();
+      epilogue_store_rows<OutT>(p, box, lane, batch, row0, col0);
+      __syncwarp();
+    }
+    ++box_iter;
+  }
+}
+
+// 16 bytes starting at an address with only element (2- or 4-byte) alignment, of which the first `nvalid`
+// bytes (> 0, a multiple of the element size) lie inside the matrix; the rest come back as zero.  Reads
+// only 16-byte-aligned chunks that contain at least one valid byte, so it never touches a page the
+// matrix does not.
+__device__ __forceinline__ uint4 load_unaligned_16(const uint8_t* src, int nvalid) {
+  const uintptr_t ga = reinterpret_cast<uintptr_t>(src);
+  const uint32_t sh = static_cast<uint32_t>(ga & 15u);
+  const uint4* p0 = reinterpret_cast<const uint4*>(ga - sh);
+  const uint4 lo = __ldg(p0);
+  uint4 hi = make_uint4(0u, 0u, 0u, 0u);
+  if (sh + static_cast<uint32_t>(nvalid) > 16u) hi = __ldg(p0 + 1);
+  // shift the 32-byte window right by sh bytes: whole words by selects, the rest by funnel shifts
+  uint32_t w[9] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w, 0u};
+  const bool s2 = (sh & 8u) != 0u, s1 = (sh & 4u) != 0u;
+  uint32_t b[7], c[5];
+#pragma unroll
+  for (int i = 0; i < 7; ++i) b[i] = s2 ? w[i + 2] : w[i];
+#pragma unroll
+  for (int i = 0; i < 5; ++i) c[i] = s1 ? b[i + 1] : b[i];
+  const uint32_t bs = (sh & 3u) * 8u;
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[i] = __funnelshift_r(c[i], c[i + 1], bs);
+    const int vb = nvalid - 4 * i;  // valid bytes in this word
+    o[i] = vb >= 4 ? o[i] : (vb <= 0 ? 0u : (o[i] & ((1u << (8 * vb)) - 1u)));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -168,7 +271,7 @@ template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kSt
 __global__ void __launch_bounds__(kThreadsWithLoader, 1)
 nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
                        const __grid_constant__ CUtensorMap tmap_b0, const __grid_constant__ CUtensorMap tmap_b1,
-                       const GemmKernelParams p) {
+                       const __grid_constant__ CUtensorMap tmap_c, const GemmKernelParams p) {
   constexpr int kOpTerms = kTerms == 3 ? 2 : 1;
   using L = GemmSmemLayout<kBlockN, kOpTerms, kStages>;
   constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;  // 64 (16-bit) or 32 (tf32): BLOCK_K and MN chunk
@@ -315,38 +418,36 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
   } else if (warp < kFirstLoaderWarp) {
     // ============================================================ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* staging = smem_gen + L::kStagingOffset + (warp - kFirstEpilogueWarp) * (2 * L::kStageOutBox);
+    if (p.vec_store && lane == 0) tma_prefetch_desc(&tmap_c);
     uint32_t tile_iter = 0;
+    uint32_t box_iter = 0;
     for (int32_t tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++tile_iter) {
       const TileCoord t = decode_tile(p, tile);
       const uint32_t acc = tile_iter & 1u;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag, p.status, kStatusEpilogueTmemFullWait)) break;
       tc_fence_after_sync();
-      const int32_t row = t.m_blk * kBlockM + q * 32 + lane;
+      const int32_t row0 = t.m_blk * kBlockM + q * 32;
       const int32_t n0 = t.n_blk * kBlockN;
       const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
-        const int32_t col0 = n0 + c * 32;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (row < p.M) {
-          if (p.out_dtype == NOVA_B200_BF16) epilogue_row_chunk<__nv_bfloat16>(p, r, t.batch, row, col0);
-          else if (p.out_dtype == NOVA_B200_F16) epilogue_row_chunk<__half>(p, r, t.batch, row, col0);
-          else epilogue_row_chunk<float>(p, r, t.batch, row, col0);
-        }
-      }
+      if (p.out_dtype == NOVA_B200_BF16)
+        epilogue_tile<__nv_bfloat16, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+      else if (p.out_dtype == NOVA_B200_F16)
+        epilogue_tile<__half, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+      else
+        epilogue_tile<float, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       tc_fence_before_sync();
       mbar_arrive(tmem_empty_bar(acc));
     }
+    if (p.vec_store && lane == 0) tma_store_wait_all<0>();  // staged boxes fully written before the CTA exits
+    __syncwarp();
   } else {
     // ============================================================ ld.global loader (operands TMA cannot address)
     // Each stage's operand tile is written exactly as TMA would write it: 128-byte rows whose
     // 16-byte chunks are XOR-swizzled with (row & 7); out-of-range elements are zero.
-    const int lw = warp - kFirstLoaderWarp;       // 0..3
-    const int lt = lw * 32 + lane;                // 0..127
+    const int lw = warp - kFirstLoaderWarp;
+    const int lt = lw * 32 + lane;  // 0 .. 32*kNumLoaderWarps-1
     uint32_t it = 0;
     bool ok = true;
     for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
@@ -375,35 +476,27 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
           //                                 row = chunk * BLOCK_K + k, 128 B span the chunk
           const int total_rows = mn ? (rows_mn / kElemsPerRow) * kBlockK : rows_mn;
           constexpr int kChunks = kSwizzleBytes / 16;  // 16-byte chunks per row
+          constexpr int kElemsPerChunk = 16 / kElemBytes;
+#pragma unroll 4
           for (int idx = lt; idx < total_rows * kChunks; idx += kNumLoaderWarps * 32) {
             const int r = idx / kChunks, ch = idx % kChunks;
             int64_t outer;  // index along the pitched (outer) global dimension
             int inner0;     // first index along the contiguous global dimension
             int outer_limit, inner_limit;
-            if (!mn) { outer = mn0 + r; inner0 = k0 + ch * (16 / kElemBytes); outer_limit = mn_limit; inner_limit = p.K; }
+            if (!mn) { outer = mn0 + r; inner0 = k0 + ch * kElemsPerChunk; outer_limit = mn_limit; inner_limit = p.K; }
             else {
               const int chunk = r / kBlockK, kk = r % kBlockK;
-              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + ch * (16 / kElemBytes);
+              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + ch * kElemsPerChunk;
               outer_limit = p.K; inner_limit = mn_limit;
             }
-            union { uint4 u; uint16_t h[8]; uint32_t w[4]; } v;
-            v.u = make_uint4(0u, 0u, 0u, 0u);
-            if (outer < outer_limit) {
-              const uint8_t* src = gbase + (outer * ld + inner0) * kElemBytes;
-              if (kElemBytes == 2) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (inner0 + e < inner_limit) v.h[e] = __ldg(reinterpret_cast<const uint16_t*>(src) + e);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (inner0 + e < inner_limit) v.w[e] = __ldg(reinterpret_cast<const uint32_t*>(src) + e);
-              }
-            }
+            // bytes of this 16-byte chunk that lie inside the matrix
+            const int nvalid = outer < outer_limit ? max(0, min(kElemsPerChunk, inner_limit - inner0)) * kElemBytes : 0;
+            const uint4 v = nvalid > 0 ? load_unaligned_16(gbase + (outer * ld + inner0) * kElemBytes, nvalid)
+                                       : make_uint4(0u, 0u, 0u, 0u);
             // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the
             // 128-byte swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
             const int sw = (kElemBytes == 4 && mn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
-            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v.u;
+            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v;
           }
         }
         fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core (async proxy)

@@ -144,7 +144,7 @@ int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int 
     NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
     configured_device = dev;
   }
-  kernel<<<grid, threads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+  kernel<<<grid, threads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }
@@ -267,7 +267,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;
   }
 
-  CUtensorMap maps[4];
+  CUtensorMap maps[5];  // A hi, A lo, B hi, B lo, C
   std::memset(maps, 0, sizeof(maps));
   const CUtensorMapDataType tdt = a->dtype_ab == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                 : a->dtype_ab == NOVA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -291,6 +291,16 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     }
   }
 
+  if (p.vec_store) {
+    // output boxes: 32 rows x 128 bytes, clipped by the tensor map at M and N
+    const int osz = plan.out_bytes;
+    const CUtensorMapDataType cdt = a->dtype_c == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                  : a->dtype_c == NOVA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    st = encode_operand_map(ctx, &maps[4], a->C, osz, cdt, a->M, a->N, a->ldc, a->batch, a->batch_stride_c,
+                            static_cast<uint32_t>(kSwizzleBytes / osz), 32u, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NOVA_B200_OK) return st;
+  }
   const int threads = (pi.loader_a | pi.loader_b) ? kThreadsWithLoader : kThreadsTma;
   const int grid = pi.grid;
   if (es == 2) {
