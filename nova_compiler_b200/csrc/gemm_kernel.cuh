@@ -30,6 +30,8 @@ static constexpr int kBlockM = 128;          // UMMA M (cta_group::1): TMEM lane
 static constexpr int kSwizzleBytes = 128;    // operand rows in shared memory are 128 bytes
 static constexpr int kNumEpilogueWarps = 4;
 static constexpr int kNumLoaderWarps = 8;
+static constexpr int kLoaderGroups = 4;  // loader warps split into groups that fill different ring stages concurrently
+static constexpr int kLoaderWarpsPerGroup = kNumLoaderWarps / kLoaderGroups;
 static constexpr int kFirstEpilogueWarp = 2;
 static constexpr int kFirstLoaderWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
 static constexpr int kThreadsTma = 32 * kFirstLoaderWarp;                      // 192
@@ -232,26 +234,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const C
   }
 }
 
-// 16 bytes starting at an address with only element (2- or 4-byte) alignment, of which the first `nvalid`
-// bytes (> 0, a multiple of the element size) lie inside the matrix; the rest come back as zero.  Reads
-// only 16-byte-aligned chunks that contain at least one valid byte, so it never touches a page the
-// matrix does not.
-__device__ __forceinline__ uint4 load_unaligned_16(const uint8_t* src, int nvalid) {
-  const uintptr_t ga = reinterpret_cast<uintptr_t>(src);
-  const uint32_t sh = static_cast<uint32_t>(ga & 15u);
-  const uint4* p0 = reinterpret_cast<const uint4*>(ga - sh);
-  const uint4 lo = __ldg(p0);
-  uint4 hi = make_uint4(0u, 0u, 0u, 0u);
-  if (sh + static_cast<uint32_t>(nvalid) > 16u) hi = __ldg(p0 + 1);
-  // shift the 32-byte window right by sh bytes: whole words by selects, the rest by funnel shifts
-  uint32_t w[9] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w, 0u};
-  const bool s2 = (sh & 8u) != 0u, s1 = (sh & 4u) != 0u;
+// Predicated 16-byte read-only load: zero when `pred` is false (no branch, so several can be in flight).
+__device__ __forceinline__ uint4 ldg_v4_if(const uint4* ptr, bool pred) {
+  uint4 v;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(ptr), "r"(static_cast<uint32_t>(pred)));
+  return v;
+}
+
+// The 16 bytes that start `sh` bytes (0..15, a multiple of the element size) into the 32-byte window
+// (lo, hi); bytes at or beyond `nvalid` come back as zero.  Whole words move by selects, the rest by
+// funnel shifts.
+__device__ __forceinline__ uint4 shift_window_16(const uint4& lo, const uint4& hi, int sh, int nvalid) {
+  const uint32_t w[9] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w, 0u};
+  const bool s2 = (sh & 8) != 0, s1 = (sh & 4) != 0;
   uint32_t b[7], c[5];
 #pragma unroll
   for (int i = 0; i < 7; ++i) b[i] = s2 ? w[i + 2] : w[i];
 #pragma unroll
   for (int i = 0; i < 5; ++i) c[i] = s1 ? b[i + 1] : b[i];
-  const uint32_t bs = (sh & 3u) * 8u;
+  const uint32_t bs = static_cast<uint32_t>(sh & 3) * 8u;
   uint32_t o[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -300,7 +307,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
 
   if (threadIdx.x == 0) {
     // arrivals per phase on a full barrier: the producer's expect_tx arrive, plus one per loader warp
-    const uint32_t full_count = 1u + (use_loader ? kNumLoaderWarps : 0u);
+    const uint32_t full_count = 1u + (use_loader ? kLoaderWarpsPerGroup : 0u);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), full_count);
       mbar_init(empty_bar(s), 1);
@@ -446,14 +453,18 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
     // ============================================================ ld.global loader (operands TMA cannot address)
     // Each stage's operand tile is written exactly as TMA would write it: 128-byte rows whose
     // 16-byte chunks are XOR-swizzled with (row & 7); out-of-range elements are zero.
+    // Group g fills the stages of k-block iterations it == g (mod kLoaderGroups): each group's global-memory
+    // latency overlaps the other groups' work, so several stages are in flight at once.
     const int lw = warp - kFirstLoaderWarp;
-    const int lt = lw * 32 + lane;  // 0 .. 32*kNumLoaderWarps-1
+    const int group = lw / kLoaderWarpsPerGroup;
+    const int lt = (lw % kLoaderWarpsPerGroup) * 32 + lane;  // 0 .. 32*kLoaderWarpsPerGroup-1
     uint32_t it = 0;
     bool ok = true;
     for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
       const TileCoord t = decode_tile(p, tile);
       const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        if (static_cast<int>(it % kLoaderGroups) != group) continue;
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kStatusLoaderEmptyWait)) { ok = false; break; }
@@ -475,28 +486,39 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
           //                     MN-major -> rows are grouped per chunk of kElemsPerRow M/N elements:
           //                                 row = chunk * BLOCK_K + k, 128 B span the chunk
           const int total_rows = mn ? (rows_mn / kElemsPerRow) * kBlockK : rows_mn;
-          constexpr int kChunks = kSwizzleBytes / 16;  // 16-byte chunks per row
-          constexpr int kElemsPerChunk = 16 / kElemBytes;
-#pragma unroll 4
-          for (int idx = lt; idx < total_rows * kChunks; idx += kNumLoaderWarps * 32) {
-            const int r = idx / kChunks, ch = idx % kChunks;
+          // One task = half a shared-memory row (64 contiguous bytes of global memory, four 16-byte chunks).
+          // The source is only element-aligned, so a task reads the up to five 16-byte-ALIGNED chunks that
+          // overlap its 64 bytes (all loads issued before any is used) and funnel-shifts them into place.
+          constexpr int kElemsPerHalf = 64 / kElemBytes;
+#pragma unroll 3
+          for (int task = lt; task < total_rows * 2; task += kLoaderWarpsPerGroup * 32) {
+            const int r = task >> 1, half = task & 1;
             int64_t outer;  // index along the pitched (outer) global dimension
             int inner0;     // first index along the contiguous global dimension
             int outer_limit, inner_limit;
-            if (!mn) { outer = mn0 + r; inner0 = k0 + ch * kElemsPerChunk; outer_limit = mn_limit; inner_limit = p.K; }
+            if (!mn) { outer = mn0 + r; inner0 = k0 + half * kElemsPerHalf; outer_limit = mn_limit; inner_limit = p.K; }
             else {
               const int chunk = r / kBlockK, kk = r % kBlockK;
-              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + ch * kElemsPerChunk;
+              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + half * kElemsPerHalf;
               outer_limit = p.K; inner_limit = mn_limit;
             }
-            // bytes of this 16-byte chunk that lie inside the matrix
-            const int nvalid = outer < outer_limit ? max(0, min(kElemsPerChunk, inner_limit - inner0)) * kElemBytes : 0;
-            const uint4 v = nvalid > 0 ? load_unaligned_16(gbase + (outer * ld + inner0) * kElemBytes, nvalid)
-                                       : make_uint4(0u, 0u, 0u, 0u);
-            // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the
-            // 128-byte swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
-            const int sw = (kElemBytes == 4 && mn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
-            *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v;
+            // bytes of these 64 that lie inside the matrix
+            const int nvalid = outer < outer_limit ? max(0, min(kElemsPerHalf, inner_limit - inner0)) * kElemBytes : 0;
+            const uintptr_t ga = reinterpret_cast<uintptr_t>(gbase + (outer * ld + inner0) * kElemBytes);
+            const int sh = static_cast<int>(ga & 15u);
+            const uint4* p0 = reinterpret_cast<const uint4*>(ga - sh);
+            uint4 w[5];
+#pragma unroll
+            for (int j = 0; j < 5; ++j) w[j] = ldg_v4_if(p0 + j, nvalid > 0 && 16 * j - sh < nvalid);  // chunk holds a valid byte
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 v = shift_window_16(w[c], w[c + 1], sh, nvalid - 16 * c);
+              const int ch = half * 4 + c;
+              // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the
+              // 128-byte swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
+              const int sw = (kElemBytes == 4 && mn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
+              *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v;
+            }
           }
         }
         fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core (async proxy)
