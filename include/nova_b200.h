@@ -147,6 +147,34 @@ int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan
  * form the reference's host harnesses use (driver.cpp:22-40: host descriptors in, result out). */
 int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args);
 
+/* The f32 (NOVA_B200_TF32X3) contraction for callers that cannot allocate device memory.
+ * No counterpart in the reference: its generated host code calls cudaMallocAsync freely
+ * (lib/Transforms/FixGpuLaunch.cpp:49-50).
+ *
+ * nova_b200_gemm splits f32 operands into hi/lo halves in a scratch buffer it obtains with cudaMalloc,
+ * and its per-device status word is allocated too.  Some callers must not allocate: a compiled graph
+ * running inside a memory-planned region that already owns the whole device, a plug-in under a host
+ * framework that forbids allocation on its streams, a latency-critical loop that may not take the
+ * allocator's locks.  This entry point computes the same result (same kernels, same arguments, device
+ * pointers for A, B, C, bias, residual) but keeps the scratch and the status word in ONE fixed array
+ * inside the library image and calls no cudaMalloc / cudaFree / allocating routine.
+ *
+ *  - Limit: the split needs 8 bytes per element of A and of B (rows padded to a multiple of 4
+ *    elements); the array holds 16 MiB of it (e.g. 1024x1024x1024, or batch 4 of 512^3).  Larger
+ *    requests return NOVA_B200_ERR_TOO_LARGE; non-f32 or TF32X1 requests return
+ *    NOVA_B200_ERR_UNSUPPORTED (they use no scratch: call nova_b200_gemm).
+ *  - Every GPU on which the library is loaded holds the 16 MiB + 256 B until the process exits.
+ *  - The first call on each device resolves the array's device address and the tensor-map encoder
+ *    (no allocation, but driver calls): make that first call outside any stream capture.
+ *  - All calls on a device share the array, and it keeps the previous call's contents.  Each call
+ *    clears the status word and rewrites every scratch byte it reads, so consecutive calls on one
+ *    stream are safe; calls that overlap on the GPU (different streams, or this and another process
+ *    thread) race on the scratch and give wrong results.
+ *  - wait_code_out == NULL: the call only enqueues.  Otherwise it synchronises `stream`, stores the
+ *    device-side wait code (0 = every bounded wait completed) and returns
+ *    NOVA_B200_ERR_DEVICE_TIMEOUT when it is non-zero. */
+int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream, uint32_t* wait_code_out);
+
 /* y = act(x), n elements, standalone nova.gelu / nova.relu (NovaToLinalgGeneric.cpp:1277-1337,
  * NovaToLinalg.cpp:1053-1084) for graphs where the activation is not adjacent to a contraction. */
 int32_t nova_b200_activation(const void* x_dev, void* y_dev, int64_t n, int32_t dtype, int32_t act, void* stream);

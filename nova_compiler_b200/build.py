@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libnova_b200.so")
-SOURCES = ["gemm_sm100.cu", "runtime.cu", "rowops.cu"]
+SOURCES = ["gemm_sm100.cu", "gemm_static_scratch.cu", "runtime.cu", "rowops.cu"]
 HEADERS = ["gemm_kernel.cuh", "ptx_sm100.cuh", "runtime.h", os.path.join("..", "..", "include", "nova_b200.h")]
 
 NVCC_FLAGS = [
