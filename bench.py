@@ -39,6 +39,8 @@ WORKLOADS = {
     "c3": ("linear bf16 X[8192,4096] W[4096,11008] + bias, GELU(tanh), bf16 out", "bf16", "bf16", 1, 8192, 11008, 4096,
            "bias_gelu"),
     "c4": ("batch_matmul f16 Q[256,2048,128] K^T[256,128,2048], f16 out", "f16", "f16", 256, 2048, 2048, 128, None),
+    "c4s": ("batch_matmul f16 Q[32,2048,128] K^T[32,128,2048] (C4 at one eighth of the batch, profiling-sized)", "f16", "f16", 32, 2048,
+            2048, 128, None),
     "c5a": ("GEMM bf16 16384^3", "bf16", "bf16", 1, 16384, 16384, 16384, None),
     "c5b": ("GEMM bf16 ragged 1000x1000x999", "bf16", "bf16", 1, 1000, 1000, 999, None),
     "c5c": ("GEMM bf16 ragged 4095x11007x4097", "bf16", "bf16", 1, 4095, 11007, 4097, None),

@@ -48,6 +48,7 @@ struct GemmKernelParams {
   uint32_t a_desc_lbo, b_desc_lbo;    // leading-byte-offset field, already shifted into bits 16..29
   uint32_t a_kstep, b_kstep;          // bytes the descriptor start address advances per UMMA K step
   int32_t loader_a, loader_b;         // 0 = TMA, 1 = ld.global loader warps
+  int32_t ring_stages;                // pair kernel: ring stages in use
   // raw operand views for the ld.global loader
   const void* A; const void* B;
   int64_t lda, ldb, stride_a, stride_b;
@@ -61,7 +62,7 @@ struct GemmKernelParams {
 };
 
 // kOpTerms: operand copies per stage (2 = hi and lo halves of the 3xTF32 split, else 1)
-template <int kBlockN, int kOpTerms, int kStages>
+template <int kBlockN, int kOpTerms, int kStages, int kEpiWarps = kNumEpilogueWarps>
 struct GemmSmemLayout {
   static constexpr int kATile = kBlockM * kSwizzleBytes;  // one operand term of A per stage
   static constexpr int kBTile = kBlockN * kSwizzleBytes;
@@ -72,7 +73,7 @@ struct GemmSmemLayout {
   // epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte boxes (double buffered)
   static constexpr int kStageOutBox = 32 * kSwizzleBytes;
   static constexpr int kStagingOffset = kRingBytes;
-  static constexpr int kStagingBytes = kNumEpilogueWarps * 2 * kStageOutBox;
+  static constexpr int kStagingBytes = kEpiWarps * 2 * kStageOutBox;
   static constexpr int kBarrierOffset = kStagingOffset + kStagingBytes;
   static constexpr int kMiscOffset = kBarrierOffset + 8 * kNumBarriers;
   static constexpr int kTotalBytes = kMiscOffset + 16;
@@ -190,17 +191,18 @@ __device__ __forceinline__ void epilogue_stage(uint8_t* box, const float (&v)[32
   }
 }
 
-// One epilogue warp drains its 32 accumulator rows of one tile.
-template <typename OutT, int kBlockN>
+// One epilogue warp drains kCols columns of its 32 accumulator rows, one 128-byte-wide box at a time.
+template <typename OutT, int kCols>
 __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const CUtensorMap* tmap_c, uint32_t taddr,
                                               uint8_t* staging, uint32_t& box_iter, int lane, int32_t batch,
                                               int32_t row0, int32_t n0) {
   constexpr int kColsPerBox = kSwizzleBytes / static_cast<int>(sizeof(OutT));  // 64 (16-bit) or 32 (f32)
   constexpr int kLoadsPerBox = kColsPerBox / 32;
+  constexpr int kChunkStep = 32 * static_cast<int>(sizeof(OutT)) / 16;  // 16-byte chunks per 32 columns
   const int32_t row = row0 + lane;
   const bool row_ok = row < p.M;
 #pragma unroll 1
-  for (int c = 0; c < kBlockN / kColsPerBox; ++c) {
+  for (int c = 0; c < kCols / kColsPerBox; ++c) {
     const int32_t col0 = n0 + c * kColsPerBox;
     if (col0 >= p.N) break;  // uniform across the warp
     uint8_t* box = staging + (box_iter & 1u) * (32 * kSwizzleBytes);
@@ -216,7 +218,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const C
       tmem_ld_wait();
       float v[32];
       epilogue_math<OutT>(p, r, v, batch, row, col0 + h * 32, row_ok);
-      epilogue_stage<OutT>(box, v, lane, h * (32 * static_cast<int>(sizeof(OutT)) / 16));
+      epilogue_stage<OutT>(box, v, lane, h * kChunkStep);
     }
     if (p.vec_store) {
       fence_proxy_async_smem();
@@ -274,13 +276,17 @@ __device__ __forceinline__ uint4 shift_window_16(const uint4& lo, const uint4& h
 // kElemBytes : 2 (f16 / bf16, kind::f16) or 4 (f32 read as tf32, kind::tf32)
 // kTerms     : 1, or 3 for the hi/lo split (operand term 0 = hi, 1 = lo; products lo*hi + hi*lo + hi*hi)
 // kAMn/kBMn  : operand is MN-major in global memory (A stored [K,M]; B stored [K,N]) instead of K-major
-template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages>
-__global__ void __launch_bounds__(kThreadsWithLoader, 1)
+// kLoader    : compiled with the ld.global loader warps (448 threads) or without them
+// kEpiWarps  : 4, or 8 for contractions so short that draining the accumulators dominates: two warps share
+//              each tensor-memory lane quarter and each drains half of the tile's columns
+template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages, bool kLoader, int kEpiWarps>
+__global__ void __launch_bounds__(kLoader ? kThreadsWithLoader : 32 * (kFirstEpilogueWarp + kEpiWarps), 1)
 nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
                        const __grid_constant__ CUtensorMap tmap_b0, const __grid_constant__ CUtensorMap tmap_b1,
                        const __grid_constant__ CUtensorMap tmap_c, const GemmKernelParams p) {
   constexpr int kOpTerms = kTerms == 3 ? 2 : 1;
-  using L = GemmSmemLayout<kBlockN, kOpTerms, kStages>;
+  using L = GemmSmemLayout<kBlockN, kOpTerms, kStages, kEpiWarps>;
+  static_assert(kEpiWarps == 4 || (kEpiWarps == 8 && !kLoader), "warp roles");
   constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;  // 64 (16-bit) or 32 (tf32): BLOCK_K and MN chunk
   constexpr int kBlockK = kElemsPerRow;
   constexpr int kUmmaK = 32 / kElemBytes;
@@ -303,7 +309,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const bool use_loader = (p.loader_a | p.loader_b) != 0;
+  const bool use_loader = kLoader && (p.loader_a | p.loader_b) != 0;
 
   if (threadIdx.x == 0) {
     // arrivals per phase on a full barrier: the producer's expect_tx arrive, plus one per loader warp
@@ -314,7 +320,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), kNumEpilogueWarps * 32);
+      mbar_init(tmem_empty_bar(a), kEpiWarps * 32);
     }
     *abort_flag = 0u;
     fence_mbar_init();
@@ -422,7 +428,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
       }
     }
     __syncwarp();
-  } else if (warp < kFirstLoaderWarp) {
+  } else if (warp < kFirstEpilogueWarp + kEpiWarps) {
     // ============================================================ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* staging = smem_gen + L::kStagingOffset + (warp - kFirstEpilogueWarp) * (2 * L::kStageOutBox);
@@ -435,21 +441,23 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag, p.status, kStatusEpilogueTmemFullWait)) break;
       tc_fence_after_sync();
+      constexpr int kColsPerWarp = kBlockN / (kEpiWarps / 4);
+      const int cg = (warp - kFirstEpilogueWarp) >> 2;  // which column group of the tile this warp drains
       const int32_t row0 = t.m_blk * kBlockM + q * 32;
-      const int32_t n0 = t.n_blk * kBlockN;
-      const uint32_t taddr = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+      const int32_t n0 = t.n_blk * kBlockN + cg * kColsPerWarp;
+      const uint32_t taddr = tmem_base + acc * kBlockN + cg * kColsPerWarp + (static_cast<uint32_t>(q * 32) << 16);
       if (p.out_dtype == NOVA_B200_BF16)
-        epilogue_tile<__nv_bfloat16, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__nv_bfloat16, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       else if (p.out_dtype == NOVA_B200_F16)
-        epilogue_tile<__half, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__half, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       else
-        epilogue_tile<float, kBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<float, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       tc_fence_before_sync();
       mbar_arrive(tmem_empty_bar(acc));
     }
     if (p.vec_store && lane == 0) tma_store_wait_all<0>();  // staged boxes fully written before the CTA exits
     __syncwarp();
-  } else {
+  } else if (kLoader) {
     // ============================================================ ld.global loader (operands TMA cannot address)
     // Each stage's operand tile is written exactly as TMA would write it: 128-byte rows whose
     // 16-byte chunks are XOR-swizzled with (row & 7); out-of-range elements are zero.

@@ -1,0 +1,225 @@
+// CTA-pair variant of the contraction kernel: two CTAs of one cluster (two SMs) compute one 256 x 256
+// output tile with tcgen05.mma.cta_group::2.
+//
+// Each CTA loads ITS 128 rows of A and ITS 128 columns of B (every CTA fetches its own boxes; nothing is
+// multicast), so a ring stage is 32 KB instead of 48 KB: six stages of look-ahead instead of four, and
+// a third less shared-memory fill traffic per SM.  The leader CTA (cluster rank 0) issues the MMAs; the
+// tensor cores of both SMs read A from their own shared memory and the two halves of B from both, and
+// each accumulates its 128 rows x 256 columns in its own tensor memory.
+//
+// Signalling (all waits are on barriers of the waiting CTA, all are bounded):
+//   full[s]       lives in the leader; armed by the leader's producer with the bytes of BOTH CTAs; the
+//                 peer's TMA loads count their bytes on it (cp.async.bulk.tensor ... cta_group::2).
+//   empty[s]      one per CTA; tcgen05.commit from the leader arrives on both (an arrival, no data).
+//   tmem_full[a]  one per CTA; same commit-to-both.
+//   tmem_empty[a] lives in the leader; the 4 epilogue warps of each CTA arrive on it (8 arrivals).
+//
+// Used when both operands can be loaded with TMA and the problem has at least a wave of 256 x 256 tiles;
+// everything else runs the single-CTA kernel of gemm_kernel.cuh.
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace nova {
+
+static constexpr int kPairBlockM = 256;  // rows per pair tile (128 per CTA)
+static constexpr int kPairBlockN = 256;  // columns per pair tile (each CTA loads 128 of them)
+static constexpr int kPairSubK = 2;     // 64-element K sub-blocks per ring stage: one barrier round trip per 128 K
+static constexpr int kPairStages = 3;
+
+struct PairSmemLayout {
+  static constexpr int kATile = kBlockM * kSwizzleBytes;             // 16 KB: this CTA's 128 rows
+  static constexpr int kBTile = (kPairBlockN / 2) * kSwizzleBytes;   // 16 KB: this CTA's 128 columns
+  static constexpr int kStageBytes = kPairSubK * (kATile + kBTile);
+  static constexpr int kRingBytes = kPairStages * kStageBytes;
+  static constexpr int kNumBarriers = 2 * kPairStages + 4;
+  static constexpr int kStageOutBox = 32 * kSwizzleBytes;
+  static constexpr int kStagingOffset = kRingBytes;
+  static constexpr int kStagingBytes = kNumEpilogueWarps * 2 * kStageOutBox;
+  static constexpr int kBarrierOffset = kStagingOffset + kStagingBytes;
+  static constexpr int kMiscOffset = kBarrierOffset + 8 * kNumBarriers;
+  static constexpr int kTotalBytes = kMiscOffset + 16;
+  static constexpr int kDynamicBytes = kTotalBytes + 1024;
+};
+
+// kElemBytes: 2 (f16/bf16) or 4 (f32 as single-pass tf32).  kAMn / kBMn as in the single-CTA kernel.
+// p.m_blocks counts 256-row blocks, p.n_blocks 256-column blocks.
+template <int kElemBytes, bool kAMn, bool kBMn>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsTma, 1)
+nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                            const __grid_constant__ CUtensorMap tmap_c, const GemmKernelParams p) {
+  using L = PairSmemLayout;
+  constexpr int kStages = kPairStages;
+  constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;
+  constexpr int kSubBlockK = kElemsPerRow;           // K elements per 128-byte row
+  constexpr int kBlockK = kPairSubK * kSubBlockK;    // K elements per ring stage
+  constexpr int kUmmaK = 32 / kElemBytes;
+  constexpr int kKSteps = kSubBlockK / kUmmaK;
+  constexpr int kHalfN = kPairBlockN / 2;
+  constexpr uint32_t kTmemCols = 2 * kPairBlockN;  // two 128-lane x 256-column accumulators per CTA
+  static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::kBarrierOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + 2 + a); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOffset + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);   // used in the leader only: its producer's arrive + both CTAs' bytes
+      mbar_init(empty_bar(s), 1);  // one commit arrival per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 2 * kNumEpilogueWarps);  // used in the leader only
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  // both CTAs' barriers exist before either CTA signals the other
+  cluster_sync_all();
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ============================================================ TMA producer (one per CTA)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int32_t tile = pair; ok && tile < p.tiles; tile += num_pairs) {
+        const TileCoord t = decode_tile(p, tile);
+        const int m0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM;
+        const int n0 = t.n_blk * kPairBlockN + static_cast<int>(rank) * kHalfN;
+        const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kStatusProducerEmptyWait)) { ok = false; break; }
+          const uint32_t stage = smem_base + s * L::kStageBytes;
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2u * L::kStageBytes);
+          const uint32_t bar = map_to_cta(full_bar(s), 0u);  // the leader's barrier counts both CTAs' bytes
+#pragma unroll
+          for (int sub = 0; sub < kPairSubK; ++sub) {
+            const int k0 = kb * kBlockK + sub * kSubBlockK;  // past K: the box is all zeros
+            const uint32_t adst = stage + sub * (L::kATile + L::kBTile);
+            if (!kAMn) {
+              tma_load_3d_pair(adst, &tmap_a, bar, k0, m0, za);
+            } else {
+#pragma unroll
+              for (int c = 0; c < kBlockM / kElemsPerRow; ++c)
+                tma_load_3d_pair(adst + c * (kSubBlockK * kSwizzleBytes), &tmap_a, bar, m0 + c * kElemsPerRow, k0, za);
+            }
+            const uint32_t bdst = adst + L::kATile;
+            if (!kBMn) {
+              tma_load_3d_pair(bdst, &tmap_b, bar, k0, n0, zb);
+            } else {
+#pragma unroll
+              for (int c = 0; c < kHalfN / kElemsPerRow; ++c)
+                tma_load_3d_pair(bdst + c * (kSubBlockK * kSwizzleBytes), &tmap_b, bar, n0 + c * kElemsPerRow, k0, zb);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer (leader CTA only)
+    if (rank == 0 && lane == 0) {
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int32_t tile = pair; ok && tile < p.tiles; tile += num_pairs, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kStatusMmaTmemEmptyWait)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kStatusMmaFullWait)) { ok = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < kPairSubK; ++sub) {
+            const uint32_t a_stage = smem_base + s * L::kStageBytes + sub * (L::kATile + L::kBTile);
+            const uint32_t b_stage = a_stage + L::kATile;
+#pragma unroll
+            for (int k = 0; k < kKSteps; ++k) {
+              const uint32_t accumulate = (kb | sub | k) == 0 ? 0u : 1u;
+              const uint64_t a_desc = make_smem_desc(a_stage + k * p.a_kstep, p.a_desc_lbo, p.a_desc_hi);
+              const uint64_t b_desc = make_smem_desc(b_stage + k * p.b_kstep, p.b_desc_lbo, p.b_desc_hi);
+              if (kElemBytes == 2) umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+              else umma_tf32_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+            }
+          }
+          umma_commit_pair(empty_bar(s), 3);  // both CTAs may refill their halves of this stage
+        }
+        if (ok) umma_commit_pair(tmem_full_bar(acc), 3);  // both CTAs' epilogues may drain
+      }
+    }
+    __syncwarp();
+  } else {
+    // ============================================================ epilogue (both CTAs)
+    const int q = warp & 3;
+    uint8_t* staging = smem_gen + L::kStagingOffset + (warp - kFirstEpilogueWarp) * (2 * L::kStageOutBox);
+    if (p.vec_store && lane == 0) tma_prefetch_desc(&tmap_c);
+    uint32_t tile_iter = 0;
+    uint32_t box_iter = 0;
+    for (int32_t tile = pair; tile < p.tiles; tile += num_pairs, ++tile_iter) {
+      const TileCoord t = decode_tile(p, tile);
+      const uint32_t acc = tile_iter & 1u;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      if (!mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag, p.status, kStatusEpilogueTmemFullWait)) break;
+      tc_fence_after_sync();
+      const int32_t row0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM + q * 32;
+      const int32_t n0 = t.n_blk * kPairBlockN;
+      const uint32_t taddr = tmem_base + acc * kPairBlockN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.out_dtype == NOVA_B200_BF16)
+        epilogue_tile<__nv_bfloat16, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+      else if (p.out_dtype == NOVA_B200_F16)
+        epilogue_tile<__half, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+      else
+        epilogue_tile<float, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0u));
+    }
+    if (p.vec_store && lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u && threadIdx.x == 0) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // let in-flight bulk copies land
+  }
+  // neither CTA may leave (or free tensor memory) while the other can still signal it or read its shared memory
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace nova

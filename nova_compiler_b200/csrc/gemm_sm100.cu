@@ -1,9 +1,11 @@
 // Host side of the contraction: argument validation, kernel selection ("plan"),
 // tensor-map encoding and launch.  See gemm_kernel.cuh for the device code.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
 #include "gemm_kernel.cuh"
+#include "gemm_kernel_pair.cuh"
 
 namespace nova {
 namespace {
@@ -16,6 +18,8 @@ struct Plan {
   int out_bytes = 2;
   bool k_zero = false;
   bool empty = false;
+  bool pair = false;  // CTA-pair kernel (cta_group::2, 256 x 256 tiles)
+  bool short_k = false;  // contraction so short that the epilogue dominates: 8 epilogue warps, 3 stages
 };
 
 constexpr int64_t kMaxExtent = (1ll << 31) - 1;
@@ -113,7 +117,32 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   if (tiles > kMaxExtent) return fail(NOVA_B200_ERR_TOO_LARGE, "gemm: more than 2^31-1 output tiles");
   pi.tiles = tiles;
   pi.stages = plan->terms == 3 ? 3 : (block_n == 256 ? 4 : 6);
-  pi.grid = static_cast<int32_t>(tiles < (sm_count > 0 ? sm_count : 148) ? tiles : (sm_count > 0 ? sm_count : 148));
+  const int sms = sm_count > 0 ? sm_count : 148;
+  pi.grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
+  // CTA pairs (two SMs per 256 x 256 tile) when both operands stream through TMA and there is at least
+  // one wave of pair tiles; smaller problems keep more SMs busy with single-CTA tiles.
+  const int64_t pair_tiles = a->batch * ((a->M + kPairBlockM - 1) / kPairBlockM) * ((a->N + kPairBlockN - 1) / kPairBlockN);
+  // (contractions shorter than two 128-element stages are bound by their epilogue, which pairs do not help)
+  bool pair = plan->terms == 1 && !pi.loader_a && !pi.loader_b && pair_tiles >= sms / 2 && a->K >= 256;
+  if (const char* e = std::getenv("NOVA_B200_PAIR")) {
+    if (std::atoi(e) == 0) pair = false;
+  }
+  plan->pair = pair;
+  // K <= 256 with full-width tiles: the mainloop of a tile is at most four k-blocks, the time goes into
+  // draining 128 x 256 accumulators, so trade one ring stage for a second set of epilogue warps.
+  plan->short_k = !pair && plan->terms == 1 && !pi.loader_a && !pi.loader_b && block_n == 256 && a->K <= 256 &&
+                  pi.store_c == 0;
+  if (const char* e = std::getenv("NOVA_B200_SHORT_K")) {
+    if (std::atoi(e) == 0) plan->short_k = false;
+  }
+  if (plan->short_k) pi.stages = 3;
+  if (pair) {
+    pi.block_m = kPairBlockM;
+    pi.block_n = kPairBlockN;
+    pi.stages = kPairStages;
+    pi.tiles = pair_tiles;
+    pi.grid = static_cast<int32_t>(2 * (pair_tiles < sms / 2 ? pair_tiles : sms / 2));
+  }
   return NOVA_B200_OK;
 }
 
@@ -133,10 +162,10 @@ int32_t encode_operand_map(DeviceContext* ctx, CUtensorMap* out, const void* bas
   return NOVA_B200_OK;
 }
 
-template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages>
-int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int grid, int threads, cudaStream_t st) {
-  using L = GemmSmemLayout<kBlockN, (kTerms == 3 ? 2 : 1), kStages>;
-  auto kernel = nova_gemm_sm100_kernel<kBlockN, kElemBytes, kTerms, kAMn, kBMn, kStages>;
+template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages, bool kLoader, int kEpiWarps>
+int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int grid, cudaStream_t st) {
+  using L = GemmSmemLayout<kBlockN, (kTerms == 3 ? 2 : 1), kStages, kEpiWarps>;
+  auto kernel = nova_gemm_sm100_kernel<kBlockN, kElemBytes, kTerms, kAMn, kBMn, kStages, kLoader, kEpiWarps>;
   static thread_local int configured_device = -1;
   int dev = 0;
   NOVA_CUDA_OK(cudaGetDevice(&dev));
@@ -144,18 +173,73 @@ int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int 
     NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes));
     configured_device = dev;
   }
-  kernel<<<grid, threads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  constexpr int kThreads = kLoader ? kThreadsWithLoader : 32 * (kFirstEpilogueWarp + kEpiWarps);
+  kernel<<<grid, kThreads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }
 
-template <int kBlockN, int kElemBytes, int kTerms, int kStages>
-int32_t launch_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int grid, int threads,
+template <int kBlockN, int kElemBytes, int kTerms, int kStages, bool kLoader, int kEpiWarps>
+int32_t launch_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int grid,
                       cudaStream_t st) {
-  if (!a_mn && b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, false, true, kStages>(maps, p, grid, threads, st);
-  if (!a_mn && !b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, false, false, kStages>(maps, p, grid, threads, st);
-  if (a_mn && b_mn) return launch_instance<kBlockN, kElemBytes, kTerms, true, true, kStages>(maps, p, grid, threads, st);
-  return launch_instance<kBlockN, kElemBytes, kTerms, true, false, kStages>(maps, p, grid, threads, st);
+  if (!a_mn && b_mn)
+    return launch_instance<kBlockN, kElemBytes, kTerms, false, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+  if (!a_mn && !b_mn)
+    return launch_instance<kBlockN, kElemBytes, kTerms, false, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+  if (a_mn && b_mn)
+    return launch_instance<kBlockN, kElemBytes, kTerms, true, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+  return launch_instance<kBlockN, kElemBytes, kTerms, true, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+}
+
+// the loader-warp build only exists for the single-term kernels (the 3xTF32 split re-lays its operands out)
+template <int kBlockN, int kElemBytes, int kStages>
+int32_t launch_single_term(bool loader, bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p,
+                           int grid, cudaStream_t st) {
+  if (loader) return launch_majors<kBlockN, kElemBytes, 1, kStages, true, 4>(a_mn, b_mn, maps, p, grid, st);
+  return launch_majors<kBlockN, kElemBytes, 1, kStages, false, 4>(a_mn, b_mn, maps, p, grid, st);
+}
+
+template <int kElemBytes, bool kAMn, bool kBMn>
+int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p, int sm_count, cudaStream_t st) {
+  auto kernel = nova_gemm_sm100_pair_kernel<kElemBytes, kAMn, kBMn>;
+  static thread_local int configured_device = -1;
+  static thread_local int max_pairs = 0;
+  int dev = 0;
+  NOVA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmemLayout::kDynamicBytes));
+    // how many 2-CTA clusters of this kernel can be resident at once (GPCs with an odd SM count strand one SM)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(kThreadsTma, 1, 1);
+    cfg.dynamicSmemBytes = PairSmemLayout::kDynamicBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    max_pairs = n < sm_count / 2 ? n : sm_count / 2;
+    if (std::getenv("NOVA_B200_DEBUG")) fprintf(stderr, "[nova_b200] pair kernel: %d resident clusters reported, using %d\n", n, max_pairs);
+    configured_device = dev;
+  }
+  const int pairs = p.tiles < max_pairs ? p.tiles : max_pairs;
+  kernel<<<2 * pairs, kThreadsTma, PairSmemLayout::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], p);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+template <int kElemBytes>
+int32_t launch_pair_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int sm_count,
+                           cudaStream_t st) {
+  if (!a_mn && b_mn) return launch_pair_instance<kElemBytes, false, true>(maps, p, sm_count, st);
+  if (!a_mn && !b_mn) return launch_pair_instance<kElemBytes, false, false>(maps, p, sm_count, st);
+  if (a_mn && b_mn) return launch_pair_instance<kElemBytes, true, true>(maps, p, sm_count, st);
+  return launch_pair_instance<kElemBytes, true, false>(maps, p, sm_count, st);
 }
 
 uint32_t env_u32(const char* name, uint32_t dflt) {
@@ -202,9 +286,11 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   const int es = plan.elem_bytes;
   const int block_n = pi.block_n;
   const int block_k = pi.block_k;
-  p.m_blocks = static_cast<int32_t>((a->M + kBlockM - 1) / kBlockM);
+  const int block_m = pi.block_m;  // 128, or 256 for a CTA pair
+  p.m_blocks = static_cast<int32_t>((a->M + block_m - 1) / block_m);
   p.n_blocks = static_cast<int32_t>((a->N + block_n - 1) / block_n);
-  p.k_blocks = static_cast<int32_t>((a->K + block_k - 1) / block_k);
+  const int stage_k = plan.pair ? block_k * kPairSubK : block_k;  // K elements consumed per ring stage
+  p.k_blocks = static_cast<int32_t>((a->K + stage_k - 1) / stage_k);
   p.group_m = static_cast<int32_t>(env_u32("NOVA_B200_GROUP_M", 16));
   if (p.group_m < 1) p.group_m = 1;
   p.tiles = static_cast<int32_t>(pi.tiles);
@@ -219,7 +305,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   // A/B major (bits 15/16: 1 = MN-major), N>>3 in bits 17-22, M>>4 in bits 24-28.
   const uint32_t fmt = a->dtype_ab == NOVA_B200_F16 ? 0u : (a->dtype_ab == NOVA_B200_BF16 ? 1u : 2u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((plan.a_mn ? 1u : 0u) << 15) | ((plan.b_mn ? 1u : 0u) << 16) |
-            (static_cast<uint32_t>(block_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+            (static_cast<uint32_t>(block_n >> 3) << 17) | (static_cast<uint32_t>(block_m >> 4) << 24);
   // Shared-memory matrix descriptors (128-byte swizzle, version 1):
   //   K-major : rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused; one UMMA K step = 32 B.
   //   MN-major: 128 B = one chunk of MN elements for one k; 8 k-rows = 1024 B (SBO); the next chunk of
@@ -285,7 +371,8 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     }
     if (!pi.loader_b) {
       st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows, b_cols, b_ld, b_nb, b_bs, chunk,
-                              plan.b_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(block_n),
+                              plan.b_mn ? static_cast<uint32_t>(block_k)
+                                        : static_cast<uint32_t>(plan.pair ? block_n / 2 : block_n),  // a pair CTA loads half of N
                               swizzle_for(plan.b_mn));
       if (st != NOVA_B200_OK) return st;
     }
@@ -301,15 +388,26 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
                             static_cast<uint32_t>(kSwizzleBytes / osz), 32u, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != NOVA_B200_OK) return st;
   }
-  const int threads = (pi.loader_a | pi.loader_b) ? kThreadsWithLoader : kThreadsTma;
-  const int grid = pi.grid;
-  if (es == 2) {
-    if (block_n == 256) return launch_majors<256, 2, 1, 4>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
-    return launch_majors<128, 2, 1, 6>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+  if (plan.pair) {
+    p.ring_stages = static_cast<int32_t>(env_u32("NOVA_B200_PAIR_STAGES", kPairStages));
+    if (p.ring_stages < 2 || p.ring_stages > kPairStages) p.ring_stages = kPairStages;
+    const CUtensorMap pm[3] = {maps[0], maps[2], maps[4]};
+    if (es == 2) return launch_pair_majors<2>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
+    return launch_pair_majors<4>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
   }
-  if (plan.terms == 3) return launch_majors<128, 4, 3, 3>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
-  if (block_n == 256) return launch_majors<256, 4, 1, 4>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
-  return launch_majors<128, 4, 1, 6>(plan.a_mn, plan.b_mn, maps, p, grid, threads, stream);
+  const bool loader = (pi.loader_a | pi.loader_b) != 0;
+  const int grid = pi.grid;
+  if (plan.terms == 3) return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps
+    if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  }
+  if (es == 2) {
+    if (block_n == 256) return launch_single_term<256, 2, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    return launch_single_term<128, 2, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  }
+  if (block_n == 256) return launch_single_term<256, 4, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  return launch_single_term<128, 4, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
 }
 
 }  // namespace nova

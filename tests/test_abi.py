@@ -59,8 +59,16 @@ def test_plan_aligned_operands_use_tma(lib):
     st, info = _plan(lib, _args(8192, 11008, 4096))
     assert st == L.OK
     assert (info.loader_a, info.loader_b, info.store_c) == (0, 0, 0)
-    assert (info.block_m, info.block_n, info.block_k, info.stages) == (128, 256, 64, 4)
-    assert info.tiles == 64 * 43 and info.grid == 148 and info.scratch_bytes == 0
+    # a wave of 256 x 256 tiles exists: CTA pairs, three ring stages of two 64-element K boxes each per CTA
+    assert (info.block_m, info.block_n, info.block_k, info.stages) == (256, 256, 64, 3)
+    assert info.tiles == 32 * 43 and info.grid == 148 and info.scratch_bytes == 0
+    # a single 2048^3 problem has only 64 pair tiles (and 128 tiles of 128 x 256): single-CTA 128 x 128 tiles
+    st, info = _plan(lib, _args(2048, 2048, 2048))
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 128, 6, 256, 148)
+    # a short contraction (K <= 256) is epilogue-bound: single-CTA 128 x 256 tiles, three 48 KB stages and a
+    # second set of epilogue warps
+    st, info = _plan(lib, _args(2048, 2048, 128, dt=L.F16, batch=256))
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles) == (128, 256, 3, 256 * 16 * 8)
 
 
 def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
@@ -91,7 +99,7 @@ def test_plan_small_problems_use_narrow_tiles(lib):
     st, info = _plan(lib, _args(8, 10, 16, dt=L.F16))
     assert st == L.OK and info.block_n == 128 and info.tiles == 1 and info.grid == 1
     st, info = _plan(lib, _args(1024, 1024, 1024, dt=L.F16, batch=32))
-    assert st == L.OK and info.block_n == 256 and info.tiles == 32 * 8 * 4
+    assert st == L.OK and (info.block_m, info.block_n) == (256, 256) and info.tiles == 32 * 4 * 4
 
 
 def test_argument_errors_are_reported_not_thrown(lib):
