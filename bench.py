@@ -101,6 +101,8 @@ def run_reference(args):
     import numpy as np
     from oracle import oracle as O
     w = args.workload
+    if w not in WORKLOADS:
+        raise SystemExit("--impl reference times the contraction workloads only")
     desc, dab, dc, B, M, N, K, epi = WORKLOADS[w]
     # a bounded sample: one batch (c4: narrow K makes rows cheap) and a row slice sized for ~0.3 s per step
     rows = max(1, min(M, int(2.0e8 / (2.0 * N * K))))
@@ -292,23 +294,26 @@ def run_gpu(args):
     if bias_np is not None:
         hbias = torch.from_numpy(bias_np).pin_memory()
         g.bias, g.init, g.act = hbias.data_ptr(), L.INIT_BIAS_ROW, L.ACT_GELU_TANH
-    e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
-        L.check(lib.nova_b200_gemm_host(C.byref(g)))
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        L.check(lib.nova_b200_gemm_host(C.byref(g)))
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "h2d_bytes_per_step": int(a_np.nbytes + b_np.nbytes + (bias_np.nbytes if bias_np is not None else 0)),
-           "d2h_bytes_per_step": int(hc.numel() * hc.element_size()),
-           "api": "nova_b200_gemm_host (pinned host buffers: H2D, kernel, D2H, sync every step)"}
+    e2e = None
+    if not args.profile:
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(2):
+            L.check(lib.nova_b200_gemm_host(C.byref(g)))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            L.check(lib.nova_b200_gemm_host(C.byref(g)))
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+        e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "steps": e2e_steps,
+               "h2d_bytes_per_step": int(a_np.nbytes + b_np.nbytes + (bias_np.nbytes if bias_np is not None else 0)),
+               "d2h_bytes_per_step": int(hc.numel() * hc.element_size()),
+               "api": "nova_b200_gemm_host (pinned host buffers: H2D, kernel, D2H, sync every step)"}
 
     line = None
     if rank == 0:
@@ -336,7 +341,7 @@ def run_gpu(args):
             "impl": "nova_b200", "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "roofline": roof, "pct_of_bf16_dense_peak_nominal": 100.0 * per_gpu / NOMINAL_BF16_TFLOPS,
         }
-        if world == 1:
+        if world == 1 and not args.profile:
             line["cpu_baseline"] = cpu_baseline(w)
     if world > 1:
         dist.barrier()
@@ -366,19 +371,84 @@ def cpu_baseline(w, budget_s=12.0):
                       "single-threaded scalar i/j/k nest as the reference's CPU pipeline emits it; extrapolates linearly"}
 
 
+# HBM-bound companions of the contraction: name -> (description, dtype, rows, D)
+ROW_WORKLOADS = {
+    "ln": ("nova.layer_norm bf16 [8192, 4096] (the rows that feed the C3 linear)", "bf16", 8192, 4096),
+    "softmax": ("nova.softmax f16 [65536, 2048] (attention-score rows, C4 layout, 32 of its 256 batches)", "f16", 65536, 2048),
+    "gather": ("nova.gather bf16 table [50304, 4096], 16384 i32 ids (embedding lookup)", "bf16", 16384, 4096),
+}
+
+
+def run_rowop(args):
+    """HBM roofline of the row-wise kernels: GB/s = (bytes read + bytes written) / event time."""
+    import torch
+    from nova_compiler_b200 import _lib as L
+    from nova_compiler_b200 import ops
+    torch.cuda.set_device(0)
+    L.check(L.load().nova_b200_init(0))
+    w = args.workload
+    desc, dt, rows, D = ROW_WORKLOADS[w]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[dt]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234)
+    n_sets = 4  # rotate inputs so a step never finds its rows in L2
+    if w == "gather":
+        table = torch.randn(50304, D, device="cuda", generator=g).to(tdt)
+        sets = [torch.randint(0, 50304, (rows,), device="cuda", generator=g).to(torch.int32) for _ in range(n_sets)]
+        byts = 2 * rows * D * 2 + rows * 4
+        fn = lambda i: ops.gather(table, sets[i % n_sets])
+    else:
+        sets = [torch.randn(rows, D, device="cuda", generator=g).to(tdt) for _ in range(n_sets)]
+        gamma = torch.randn(D, device="cuda", generator=g).to(tdt)
+        beta = torch.randn(D, device="cuda", generator=g).to(tdt)
+        byts = 2 * rows * D * 2 + (2 * D * 2 + 2 * rows * 2 if w == "ln" else 0)
+        fn = (lambda i: ops.layer_norm(sets[i % n_sets], gamma, beta)) if w == "ln" else (lambda i: ops.softmax(sets[i % n_sets]))
+    for i in range(max(args.warmup, 3)):
+        fn(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks, src = load_peaks()
+    gbs = byts / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "row-op HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dt, "data": "synthetic (seeded)", "impl": "nova_b200", "clocks": clocks, "gpu_launches": args.steps,
+        "config": {"workload": f"{w}: {desc}", "l2": f"rotating {n_sets} input sets; outputs are fresh allocations"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": src, "algorithmic_bytes_per_launch": byts,
+                     "frac_of_nominal_8000": gbs / 8000.0},
+    }), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(ROW_WORKLOADS))
     ap.add_argument("--impl", default="nova_b200", choices=["nova_b200", "reference"])
+    ap.add_argument("--profile", action="store_true",
+                    help="device-resident leg only (no end-to-end leg, no CPU baseline): for captures under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = args.steps or 10
         args.warmup = args.warmup if args.warmup is not None else 1
         return run_reference(args)
-    args.steps = args.steps or 200
+    if args.workload in ROW_WORKLOADS:
+        args.steps = args.steps or 100
+        args.warmup = args.warmup if args.warmup is not None else 5
+        return run_rowop(args)
+    args.steps = args.steps or (1000 if args.workload in ("c1", "c2", "c5b") else 200)
     args.warmup = args.warmup if args.warmup is not None else 10
     return run_gpu(args)
 

@@ -1,8 +1,9 @@
 // HBM-bound companions of the contraction: layer_norm, softmax, gather, standalone activation and
 // row-broadcast add.  Each reads its input from HBM once and writes its output once: a row lives
-// in registers between the reduction and the normalisation pass (one warp per row up to 1024
-// elements, one 256-thread CTA per row up to 8192, a two-pass loop beyond that), all traffic moves
-// as 128-bit accesses when base and row pitch allow, and reductions are warp-shuffle trees.
+// in registers between the reduction and the normalisation pass (one warp per row up to 512 16-byte
+// vectors = 4096 16-bit elements, with every load of the row issued before the first is consumed; one
+// 256-thread CTA per row up to 4096 vectors; a two-pass loop beyond that), all traffic moves as 128-bit
+// accesses when base and row pitch allow, and reductions are warp-shuffle trees.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -33,43 +34,56 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Reduction over the TPR threads that share a row (TPR == 32: one warp; TPR == 256: the CTA).
+// Reduction over the TPR threads that share a row (TPR == 32: one warp; 64/128/256: that many
+// consecutive threads of the CTA, i.e. TPR/32 consecutive warps, combined through shared memory).
 template <int TPR, bool kMax>
 __device__ __forceinline__ float row_reduce(float v, float* red_smem) {
   v = kMax ? warp_max(v) : warp_sum(v);
   if (TPR == 32) return v;
+  constexpr int kWarpsPerRow = TPR / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = (warp / kWarpsPerRow) * kWarpsPerRow;  // first warp of this thread's row
   __syncthreads();  // protect red_smem from the previous reduction's readers
   if (lane == 0) red_smem[warp] = v;
   __syncthreads();
-  float r = lane < TPR / 32 ? red_smem[lane] : (kMax ? -INFINITY : 0.0f);
+  float r = lane < kWarpsPerRow ? red_smem[first + lane] : (kMax ? -INFINITY : 0.0f);
   return kMax ? warp_max(r) : warp_sum(r);
 }
 
 constexpr int kRowThreads = 256;
-constexpr int kCacheElems = 32;  // elements of a row one thread keeps in registers
 
-// kMode 0: layer_norm, kMode 1: softmax.  CACHED: the row fits TPR * kCacheElems elements.
-template <typename T, int VEC, int TPR, bool CACHED, int kMode>
-__global__ void __launch_bounds__(kRowThreads)
+// kMode 0: layer_norm, kMode 1: softmax.  kMaxV > 0: a thread keeps up to kMaxV vectors of its row in
+// registers (the row fits TPR * kMaxV vectors); kMaxV == 0: two passes over global memory.  kMaxV is
+// picked as small as the row allows so that short rows leave registers for more resident warps.
+template <typename T, int VEC, int TPR, int kMaxV, int kMode>
+__global__ void __launch_bounds__(kRowThreads, (VEC > 1 && kMaxV > 0 && kMaxV <= 2) ? 6 : (VEC > 1 && kMaxV == 4 ? 5 : 1))
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
-           T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D) {
+           T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t prefetch_next) {
   __shared__ float red[kRowThreads / 32];
   constexpr int kRowsPerCta = kRowThreads / TPR;
-  constexpr int kMaxV = kCacheElems / VEC;
+  constexpr bool CACHED = kMaxV > 0;
   const int t = threadIdx.x % TPR;
   const int sub = threadIdx.x / TPR;
   const int nvec = D / VEC;  // host guarantees D % VEC == 0
   using P = Pack<T, VEC>;
   const float inv_d = 1.0f / static_cast<float>(D);
 
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta; row0 < rows;
-       row0 += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
+  // Persistent CTAs walk the rows.  Before a row is reduced, the CTA's NEXT row is prefetched into L2
+  // (one request per 128-byte line, no registers held), so HBM reads stay in flight through the
+  // reduction and store phases and the next row's loads are L2 hits.
+  const int64_t row_step = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta; row0 < rows; row0 += row_step) {
     const int64_t row = row0 + sub;
-    const bool active = row < rows;  // whole warps are active or not when TPR == 32; TPR == 256 has one row
+    const bool active = row < rows;  // uniform over the TPR threads of a row
     const P* xr = reinterpret_cast<const P*>(x + (active ? row : 0) * D);
     P* yr = reinterpret_cast<P*>(y + (active ? row : 0) * D);
-    P cache[CACHED ? kMaxV : 1];
+    P cache[CACHED ? kMaxV : 1];  // all the row's loads are issued before the first is consumed
+    if (prefetch_next && row + row_step < rows) {
+      const P* nx = reinterpret_cast<const P*>(x + (row + row_step) * D);
+      constexpr int kVecPerLine = 128 / static_cast<int>(sizeof(P));
+      for (int i = t * kVecPerLine; i < nvec; i += TPR * kVecPerLine)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + i));
+    }
 
     float s0 = kMode == 0 ? 0.0f : -INFINITY;  // layer_norm: sum; softmax: max
     float s1 = 0.0f;                            // layer_norm: sum of squares
@@ -176,18 +190,36 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
   T* mp = static_cast<T*>(mean_sum);
   T* rp = static_cast<T*>(rstd);
   const int d = static_cast<int>(D);
-  const int64_t max_grid = static_cast<int64_t>(sm_count) * 8;  // 8 resident 256-thread CTAs per SM
-  if (D <= 32 * kCacheElems) {
-    const int64_t ctas = (rows + 7) / 8;
-    const int grid = static_cast<int>(ctas < max_grid ? ctas : max_grid);
-    row_kernel<T, VEC, 32, true, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
-  } else if (D <= kRowThreads * kCacheElems) {
-    const int grid = static_cast<int>(rows < max_grid ? rows : max_grid);
-    row_kernel<T, VEC, kRowThreads, true, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+  const int64_t nvec = D / VEC;
+  // Measured on B200: rows handled by one warp (no CTA-wide barrier) run best as many short-lived CTAs;
+  // rows that need the whole CTA run best as persistent CTAs that prefetch their next row into L2.
+  auto launch_grid = [&](int tpr) {
+    const int64_t ctas = (rows * tpr + kRowThreads - 1) / kRowThreads;
+    const int64_t cap = static_cast<int64_t>(sm_count) * (tpr == 32 ? 32 : 8);
+    return static_cast<int>(ctas < cap ? ctas : cap);
+  };
+#define NOVA_ROW(TPR_, MAXV_)                                                                             \
+  row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_), kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, \
+                                                                                     d, (TPR_) == 32 ? 0 : 1)
+  // Vectors a thread keeps in registers are kept few (occupancy sets the bytes in flight per SM):
+  // longer rows get more threads, not more registers.
+  constexpr int kWarpMv = VEC == 1 ? 32 : (kMode == 0 ? 4 : 8);
+  if (VEC == 1) {
+    // scalar path (row length or base not 16-byte friendly)
+    if (nvec <= 32 * kWarpMv) NOVA_ROW(32, kWarpMv);
+    else if (nvec <= kRowThreads * kWarpMv) NOVA_ROW(kRowThreads, kWarpMv);
+    else NOVA_ROW(kRowThreads, 0);
   } else {
-    const int grid = static_cast<int>(rows < max_grid ? rows : max_grid);
-    row_kernel<T, VEC, kRowThreads, false, kMode><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+    if (nvec <= 32 * 2) NOVA_ROW(32, 2);
+    else if (nvec <= 32 * 4) NOVA_ROW(32, 4);
+    else if (nvec <= 32 * kWarpMv) NOVA_ROW(32, kWarpMv);
+    else if (nvec <= kRowThreads * 2) NOVA_ROW(kRowThreads, 2);
+    else if (nvec <= kRowThreads * 4) NOVA_ROW(kRowThreads, 4);
+    else if (nvec <= kRowThreads * 8) NOVA_ROW(kRowThreads, 8);
+    else if (nvec <= kRowThreads * 16) NOVA_ROW(kRowThreads, 16);
+    else NOVA_ROW(kRowThreads, 0);
   }
+#undef NOVA_ROW
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }
@@ -217,27 +249,42 @@ int32_t dispatch_row_kernel(const void* x, const void* gamma, const void* beta, 
 
 // ---------------------------------------------------------------- gather
 
-// One 16-byte (or W-byte) unit per thread; consecutive threads copy consecutive units of one row.
+// A group of G = 2^g_shift threads (G <= 32, a power of two >= the units in a row when that is < 32) copies
+// one output row: the group's threads take consecutive 16-byte (or W-byte) units, four in flight each.
+// The row's index is read once per thread; there are no divisions on the copy path.
 template <typename U>
-__global__ void gather_kernel(const U* __restrict__ in, const void* __restrict__ idx, U* __restrict__ out, int64_t pre,
-                              int64_t axis_len, int64_t units_per_row, int64_t n_idx, int32_t idx_dtype,
-                              int32_t batched, unsigned long long* bad_count) {
-  const int64_t total = pre * n_idx * units_per_row;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t orow = i / units_per_row;
-    const int64_t u = i - orow * units_per_row;
-    const int64_t p = orow / n_idx;
-    const int64_t t = orow - p * n_idx;
-    const int64_t q = batched ? orow : t;
+__global__ void __launch_bounds__(256)
+gather_kernel(const U* __restrict__ in, const void* __restrict__ idx, U* __restrict__ out, int64_t pre,
+              int64_t axis_len, int64_t units_per_row, int64_t n_idx, int32_t idx_dtype, int32_t batched,
+              int32_t g_shift, unsigned long long* bad_count) {
+  constexpr int kUnroll = 4;
+  const int64_t out_rows = pre * n_idx;
+  const int64_t G = int64_t(1) << g_shift;
+  const int64_t gthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t u0 = tid & (G - 1);
+  for (int64_t orow = tid >> g_shift; orow < out_rows; orow += gthreads >> g_shift) {
+    const int64_t p = n_idx == out_rows ? 0 : orow / n_idx;  // pre == 1 (embedding lookup): no division
+    const int64_t q = batched ? orow : orow - p * n_idx;
     int64_t id;
     if (idx_dtype == NOVA_B200_I16) id = static_cast<int64_t>(static_cast<const uint16_t*>(idx)[q]);  // zero-extended
     else if (idx_dtype == NOVA_B200_I32) id = static_cast<int64_t>(static_cast<const int32_t*>(idx)[q]);
     else id = static_cast<const int64_t*>(idx)[q];
-    U v{};
-    if (id >= 0 && id < axis_len) v = in[(p * axis_len + id) * units_per_row + u];
-    else if (u == 0 && bad_count) atomicAdd(bad_count, 1ull);
-    out[i] = v;
+    const bool ok = id >= 0 && id < axis_len;
+    if (!ok && u0 == 0 && bad_count) atomicAdd(bad_count, 1ull);
+    const U* src = in + (p * axis_len + (ok ? id : 0)) * units_per_row;
+    U* dst = out + orow * units_per_row;
+    for (int64_t u = u0; u < units_per_row; u += G * kUnroll) {
+      U v[kUnroll];
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k) {
+        v[k] = U{};
+        if (ok && u + k * G < units_per_row) v[k] = src[u + k * G];
+      }
+#pragma unroll
+      for (int k = 0; k < kUnroll; ++k)
+        if (u + k * G < units_per_row) dst[u + k * G] = v[k];
+    }
   }
 }
 
@@ -349,9 +396,11 @@ int32_t nova_b200_gather(const void* in, const void* idx, void* out, int64_t pre
 #define NOVA_GATHER(U)                                                                                          \
   do {                                                                                                          \
     const int64_t units = row_bytes / static_cast<int64_t>(sizeof(U));                                          \
-    gather_kernel<U><<<grid_for(pre * n_idx * units, threads, ctx->sm_count), threads, 0, s>>>(                 \
+    int g_shift = 0;                                                                                            \
+    while (g_shift < 5 && (int64_t(1) << g_shift) < units) ++g_shift;                                           \
+    gather_kernel<U><<<grid_for((pre * n_idx) << g_shift, threads, ctx->sm_count), threads, 0, s>>>(            \
         static_cast<const U*>(in), idx, static_cast<U*>(out), pre, axis_len, units, n_idx, idx_dtype,           \
-        batched_idx, bad);                                                                                      \
+        batched_idx, g_shift, bad);                                                                             \
   } while (0)
   if (align % 16 == 0) NOVA_GATHER(uint4);
   else if (align % 8 == 0) NOVA_GATHER(uint2);

@@ -1,0 +1,95 @@
+"""Partitioning of the contraction across the GPUs of one box (one process per GPU, torch.distributed).
+
+The reference has no multi-device code at all (its `#nova.device` attribute only separates host from
+GPU); this is the plumbing the north star adds on top of the single-GPU kernels:
+
+  * batched contractions (linalg.batch_matmul) shard by BATCH INDEX: rank r owns a contiguous range of
+    batches; no rank needs another rank's data, so there is no collective on the data path;
+  * one large GEMM shards by N-COLUMN SLABS: every rank holds A and its own column slab of B and produces
+    the same column slab of C (bit-identical to those columns of the unsharded product); a collective is
+    needed only when the caller wants the whole C on every rank: `gather_slabs` all-gathers the slabs
+    (NCCL over NVLink on GPUs, gloo on CPU) and re-interleaves them into a row-major [M, N] matrix.
+
+The contraction itself is passed in as a callable (default: ops.matmul, i.e. the CUDA kernels) so the
+partitioning logic can be exercised on CPU ranks with another callable.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def batch_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
+    """(first batch, number of batches) owned by `rank`: contiguous, sizes differ by at most one,
+    every batch owned exactly once; ranks beyond `batch` own nothing."""
+    if batch < 0 or world <= 0 or not 0 <= rank < world:
+        raise ValueError("bad partition request")
+    base, extra = divmod(batch, world)
+    count = base + (1 if rank < extra else 0)
+    start = rank * base + min(rank, extra)
+    return start, count
+
+
+def column_slab(n: int, world: int, rank: int, align: int = 64) -> Tuple[int, int]:
+    """(first column, number of columns) of rank's slab.  Slab boundaries are multiples of `align`
+    columns (64 columns = one 128-byte row of 16-bit elements, so every slab base keeps the 16-byte
+    alignment the tensor maps need); the last non-empty slab takes the ragged remainder."""
+    if n < 0 or world <= 0 or not 0 <= rank < world or align <= 0:
+        raise ValueError("bad partition request")
+    units = (n + align - 1) // align
+    ustart, ucount = batch_range(units, world, rank)
+    start = min(ustart * align, n)
+    stop = min((ustart + ucount) * align, n)
+    return start, stop - start
+
+
+def sharded_batch_matmul(a: torch.Tensor, b: torch.Tensor, rank: int, world: int,
+                         matmul_fn: Optional[Callable] = None) -> Tuple[torch.Tensor, Tuple[int, int]]:
+    """Computes this rank's batches of C = A @ B for A [B,M,K], B [B,K,N] (or [K,N] shared).
+    Returns (C[start:start+count], (start, count)).  No communication."""
+    if matmul_fn is None:
+        from . import ops
+        matmul_fn = ops.matmul
+    start, count = batch_range(a.shape[0], world, rank)
+    a_s = a[start:start + count]
+    b_s = b if b.dim() == 2 else b[start:start + count]
+    if count == 0:
+        return a.new_empty((0, a.shape[1], b.shape[-1])), (start, 0)
+    return matmul_fn(a_s, b_s), (start, count)
+
+
+def slab_matmul(a: torch.Tensor, b: torch.Tensor, rank: int, world: int,
+                matmul_fn: Optional[Callable] = None, **kw) -> Tuple[torch.Tensor, Tuple[int, int]]:
+    """Computes this rank's column slab of C = A @ B for A [M,K] (replicated) and B [K,N].  The slab of B
+    is a strided view (row pitch stays N), not a copy.  Returns (C[:, start:start+count], (start, count))."""
+    if matmul_fn is None:
+        from . import ops
+        matmul_fn = ops.matmul
+    start, count = column_slab(b.shape[1], world, rank)
+    if count == 0:
+        return a.new_empty((a.shape[0], 0)), (start, 0)
+    return matmul_fn(a, b[:, start:start + count], **kw), (start, count)
+
+
+def gather_slabs(c_slab: torch.Tensor, n: int, group=None) -> torch.Tensor:
+    """All-gathers the ranks' column slabs into the full row-major [M, N] matrix on every rank.
+    Slabs may have different widths (ragged N): they are padded to the widest for the collective."""
+    world = dist.get_world_size(group)
+    m = c_slab.shape[0]
+    widths = [column_slab(n, world, r)[1] for r in range(world)]
+    wmax = max(widths) if widths else 0
+    send = c_slab
+    if c_slab.shape[1] != wmax:
+        send = c_slab.new_zeros((m, wmax))
+        send[:, :c_slab.shape[1]] = c_slab
+    send = send.contiguous()
+    recv: List[torch.Tensor] = [torch.empty_like(send) for _ in range(world)]
+    dist.all_gather(recv, send, group=group)
+    out = c_slab.new_empty((m, n))
+    for r in range(world):
+        start, count = column_slab(n, world, r)
+        if count:
+            out[:, start:start + count] = recv[r][:, :count]
+    return out
