@@ -251,6 +251,41 @@ int32_t _mlir_ciface_nova_b200_batch_matmul(nova_b200_memref3d* C, nova_b200_mem
 int32_t _mlir_ciface_nova_b200_linear(nova_b200_memref2d* Y, nova_b200_memref2d* X, nova_b200_memref2d* W,
                                       nova_b200_memref1d* bias, int32_t dtype, int32_t act);
 
+/* ---- textual front-end ---------------------------------------------------------------------------
+ * Runs a function written in the restricted textual subset of the nova / linalg dialects that reaches
+ * the contraction path: nova.matmul / linear / gelu / relu / add / softmax / layer_norm / gather / reshape /
+ * transpose / cast / to_device, linalg.matmul / batch_matmul with linalg.fill + tensor.empty +
+ * arith.constant, bufferization.to_tensor / materialize_in_destination (the forms of the reference's
+ * ltest/ and test/pipeline-tests/ fixtures; tensor encodings such as #nova.device<"1"> are ignored, as
+ * lib/Transforms/RemDevAttr.cpp:33-41 strips them).  It is the stand-in for the lowering pass, which needs
+ * MLIR to build: shapes are inferred as the dialect does, `matmul + add + relu/gelu` chains are fused the
+ * way FuseMatmulBias and the epilogue classification would fuse them, a transpose feeding a contraction
+ * becomes trans_a / trans_b, and every step is one call of the entry points above.
+ * Replaces, for such graphs, nova-opt --nova-gpu-optimized-pipeline + a driver (tools/nova-opt/nova-opt.cpp:75-144,
+ * driver.cpp:17-40). */
+typedef struct nova_b200_module nova_b200_module;
+
+/* A contiguous row-major device buffer. */
+typedef struct nova_b200_tensor {
+  void* data;
+  int32_t dtype; /* nova_b200_dtype */
+  int32_t rank;  /* <= 6 */
+  int64_t shape[6];
+} nova_b200_tensor;
+
+/* Parses, infers shapes, checks that every op is in the subset.  Needs no GPU. */
+int32_t nova_b200_module_parse(const char* text, nova_b200_module** out);
+void nova_b200_module_free(nova_b200_module* m);
+/* Type of argument / result `index` of @func (data = NULL); *count receives how many there are.  `out` may be NULL. */
+int32_t nova_b200_module_signature(const nova_b200_module* m, const char* func, int32_t index, int32_t is_result,
+                                   nova_b200_tensor* out, int32_t* count);
+/* Human-readable list of the calls a run will make, after fusion.  Needs no GPU. */
+int32_t nova_b200_module_plan(const nova_b200_module* m, const char* func, char* buf, int64_t buflen);
+/* Runs @func: `args` in signature order, `results` caller-provided buffers in return order.  Intermediates
+ * are allocated with cudaMallocAsync on `stream` and freed when the call returns (stream-ordered). */
+int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const nova_b200_tensor* args, int32_t n_args,
+                             nova_b200_tensor* results, int32_t n_results, void* stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -54,6 +54,11 @@ def _memref(rank: int):
 
 MemRef1D, MemRef2D, MemRef3D = _memref(1), _memref(2), _memref(3)
 
+
+class Tensor(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.c_int64 * 6)]
+
+
 # every extern "C" symbol include/nova_b200.h declares: name -> (restype, argtypes)
 PROTOTYPES = {
     "nova_b200_init": (C.c_int32, [C.c_int32]),
@@ -73,6 +78,13 @@ PROTOTYPES = {
     "nova_b200_gather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                      C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "nova_b200_device_status": (C.c_int32, [C.POINTER(C.c_uint32)]),
+    "nova_b200_module_parse": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "nova_b200_module_free": (None, [C.c_void_p]),
+    "nova_b200_module_signature": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.POINTER(Tensor),
+                                                C.POINTER(C.c_int32)]),
+    "nova_b200_module_plan": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_int64]),
+    "nova_b200_module_run": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(Tensor), C.c_int32, C.POINTER(Tensor),
+                                          C.c_int32, C.c_void_p]),
     "_mlir_ciface_nova_b200_matmul": (C.c_int32, [C.POINTER(MemRef2D), C.POINTER(MemRef2D), C.POINTER(MemRef2D),
                                                   C.c_int32]),
     "_mlir_ciface_nova_b200_batch_matmul": (C.c_int32, [C.POINTER(MemRef3D), C.POINTER(MemRef3D), C.POINTER(MemRef3D),

@@ -15,8 +15,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libnova_b200.so")
-SOURCES = ["gemm_sm100.cu", "gemm_static_scratch.cu", "runtime.cu", "rowops.cu"]
-HEADERS = ["gemm_kernel.cuh", "ptx_sm100.cuh", "runtime.h", os.path.join("..", "..", "include", "nova_b200.h")]
+SOURCES = ["gemm_sm100.cu", "gemm_static_scratch.cu", "runtime.cu", "rowops.cu", "frontend_exec.cu",
+           "frontend_parse.cpp", "frontend_plan.cpp"]
+HEADERS = ["gemm_kernel.cuh", "gemm_kernel_pair.cuh", "ptx_sm100.cuh", "runtime.h", "frontend.h", os.path.join("..", "..", "include", "nova_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -37,7 +38,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(CSRC, src.replace(".cu", ".o"))
+        o = os.path.join(CSRC, os.path.splitext(src)[0] + ".o")
         objs.append(o)
         if force or _stale(o, [s] + headers):
             cmd = ["nvcc", *NVCC_FLAGS, "-c", s, "-o", o]

@@ -1,0 +1,399 @@
+// Shape / dtype inference and fusion for the textual front-end (see frontend.h).  No GPU needed.
+//
+// Inference follows the reference's op definitions: MatmulOp::inferReturnTypes
+// (lib/Dialect/nova/NovaOps.cpp:1116-1285: [...,M,K] x [...,K,N], numpy batch broadcast, K must match),
+// LinearOp (:2075-2103: rank 2 or 3 input), GatherOp (:1898-1946: leading equal dims are batch dims),
+// ReshapeOp verify (:1885-1895: equal element count), LayerNormOp (:2032-2054: stats drop the last dim).
+// One deliberate difference: 16-bit contractions keep their input dtype (the reference infers f16 for
+// all of them, :1198).
+//
+// Fusion mirrors FuseMatmulBias (lib/Transforms/FuseMatmulBias.cpp:95-193: a matmul whose only real
+// consumer is an elementwise add takes the other addend as its accumulator init) and the epilogue
+// classification (lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1876-1895: a trailing ReLU / GELU
+// within reach of the contraction runs in its epilogue).
+#include <set>
+#include <sstream>
+
+#include "frontend.h"
+
+namespace nova {
+namespace fe {
+namespace {
+
+const char* dtype_name(int32_t d) {
+  switch (d) {
+    case NOVA_B200_F32: return "f32";
+    case NOVA_B200_F16: return "f16";
+    case NOVA_B200_BF16: return "bf16";
+    case NOVA_B200_I16: return "i16";
+    case NOVA_B200_I32: return "i32";
+    case NOVA_B200_I64: return "i64";
+    default: return "?";
+  }
+}
+
+std::string type_str(const Type& t) {
+  std::ostringstream o;
+  o << "tensor<";
+  for (int64_t d : t.shape) o << d << "x";
+  o << dtype_name(t.dtype) << ">";
+  return o.str();
+}
+
+bool is_float(int32_t d) { return d == NOVA_B200_F32 || d == NOVA_B200_F16 || d == NOVA_B200_BF16; }
+
+struct Ctx {
+  const Function& f;
+  Plan& p;
+  std::string* err;
+  std::map<std::string, int> uses;            // SSA name -> number of uses
+  std::map<std::string, const Op*> producer;  // SSA name -> defining op
+  std::set<const Op*> absorbed;
+  bool fail(const Op& op, const std::string& msg) {
+    *err = "line " + std::to_string(op.line) + " (" + op.name + "): " + msg;
+    return false;
+  }
+  std::string canon(const std::string& n) const {  // %x and %x#0 name the same value
+    if (p.types.count(n)) return n;
+    if (p.types.count(n + "#0")) return n + "#0";
+    const size_t h = n.find("#0");
+    if (h != std::string::npos && p.types.count(n.substr(0, h))) return n.substr(0, h);
+    return n;
+  }
+  const Type* type_of(const std::string& n) const {
+    auto it = p.types.find(canon(n));
+    return it == p.types.end() ? nullptr : &it->second;
+  }
+};
+
+bool broadcast_batch(const std::vector<int64_t>& a, const std::vector<int64_t>& b, std::vector<int64_t>* out) {
+  const size_t n = std::max(a.size(), b.size());
+  out->assign(n, 1);
+  for (size_t i = 0; i < n; ++i) {
+    const int64_t da = i < n - a.size() ? 1 : a[i - (n - a.size())];
+    const int64_t db = i < n - b.size() ? 1 : b[i - (n - b.size())];
+    if (da != db && da != 1 && db != 1) return false;
+    (*out)[i] = da == 1 ? db : da;
+  }
+  return true;
+}
+
+// b broadcasts along the rows of a: [N], [1,N], [1,1,N] ... against [..., N]
+bool is_row_broadcast(const Type& a, const Type& b) {
+  if (a.shape.empty() || b.shape.empty()) return false;
+  if (b.shape.back() != a.shape.back()) return false;
+  for (size_t i = 0; i + 1 < b.shape.size(); ++i)
+    if (b.shape[i] != 1) return false;
+  return b.numel() == a.shape.back();
+}
+
+bool infer_matmul(Ctx& c, const Op& op, const Type& a, const Type& b, Type* out) {
+  if (!is_float(a.dtype) || a.dtype != b.dtype) return c.fail(op, "operands must share a float dtype (f32, f16, bf16)");
+  std::vector<int64_t> as = a.shape, bs = b.shape;
+  if (as.empty() || bs.empty()) return c.fail(op, "rank-0 operand");
+  const bool va = as.size() == 1, vb = bs.size() == 1;
+  if (va) as.insert(as.begin(), 1);
+  if (vb) bs.push_back(1);
+  if (as.back() != bs[bs.size() - 2])
+    return c.fail(op, "contraction dims differ: " + std::to_string(as.back()) + " vs " + std::to_string(bs[bs.size() - 2]));
+  std::vector<int64_t> batch;
+  if (!broadcast_batch(std::vector<int64_t>(as.begin(), as.end() - 2), std::vector<int64_t>(bs.begin(), bs.end() - 2), &batch))
+    return c.fail(op, "batch dims do not broadcast");
+  out->dtype = a.dtype;
+  out->shape = batch;
+  if (!va) out->shape.push_back(as[as.size() - 2]);
+  if (!vb) out->shape.push_back(bs.back());
+  return true;
+}
+
+}  // namespace
+
+bool plan_function(const Function& f, Plan* out, std::string* error) {
+  Ctx c{f, *out, error, {}, {}, {}};
+  Plan& p = *out;
+  for (size_t i = 0; i < f.arg_names.size(); ++i) p.types[f.arg_names[i]] = f.arg_types[i];
+  auto count_use = [&](const std::string& n) { c.uses[n]++; const size_t h = n.find('#'); if (h != std::string::npos && n.substr(h) == "#0") c.uses[n.substr(0, h)]++; };
+  for (const Op& op : f.ops) {
+    for (const std::string& o : op.operands) count_use(o);
+    for (const std::string& o : op.index_operands) count_use(o);
+    for (const std::string& r : op.results) c.producer[r] = &op;
+  }
+  for (const std::string& r : f.returned) count_use(r);
+
+  // ---- pass 1: types
+  for (const Op& op : f.ops) {
+    std::vector<const Type*> in;
+    for (const std::string& o : op.operands) {
+      const Type* t = c.type_of(o);
+      if (!t) return c.fail(op, "use of undefined value %" + o);
+      in.push_back(t);
+    }
+    auto set = [&](size_t k, const Type& t) { if (k < op.results.size()) p.types[op.results[k]] = t; };
+    const std::string& n = op.name;
+    if (n == "nova.matmul") {
+      if (in.size() != 2) return c.fail(op, "expects two operands");
+      Type t;
+      if (!infer_matmul(c, op, *in[0], *in[1], &t)) return false;
+      set(0, t);
+    } else if (n == "nova.linear") {
+      if (in.size() != 3) return c.fail(op, "expects input, weight, bias");
+      const Type &x = *in[0], &w = *in[1], &b = *in[2];
+      if (x.shape.size() != 2 && x.shape.size() != 3) return c.fail(op, "input must be rank 2 or 3");
+      if (w.shape.size() != 2) return c.fail(op, "weight must be rank 2");
+      if (x.shape.back() != w.shape[0]) return c.fail(op, "input and weight do not compose");
+      if (b.numel() != w.shape[1]) return c.fail(op, "bias must hold N elements");
+      if (!is_float(x.dtype) || x.dtype != w.dtype || x.dtype != b.dtype) return c.fail(op, "operands must share a float dtype");
+      Type t = x;
+      t.shape.back() = w.shape[1];
+      set(0, t);
+    } else if (n == "linalg.matmul" || n == "linalg.batch_matmul") {
+      if (in.size() != 3 || op.num_ins != 2) return c.fail(op, "expects ins(A, B) outs(C)");
+      const size_t r = n == "linalg.matmul" ? 2 : 3;
+      if (in[0]->shape.size() != r || in[1]->shape.size() != r || in[2]->shape.size() != r) return c.fail(op, "wrong operand rank");
+      const Type &a = *in[0], &b = *in[1], &cc = *in[2];
+      if (a.shape[r - 1] != b.shape[r - 2] || cc.shape[r - 2] != a.shape[r - 2] || cc.shape[r - 1] != b.shape[r - 1])
+        return c.fail(op, "shapes do not compose");
+      if (r == 3 && (a.shape[0] != cc.shape[0] || b.shape[0] != cc.shape[0])) return c.fail(op, "batch sizes differ");
+      if (!is_float(a.dtype) || a.dtype != b.dtype || !is_float(cc.dtype)) return c.fail(op, "unsupported dtypes");
+      set(0, cc);
+    } else if (n == "linalg.fill") {
+      if (in.size() != 2) return c.fail(op, "expects ins(scalar) outs(tensor)");
+      set(0, *in[1]);
+    } else if (n == "tensor.empty" || n == "arith.constant") {
+      if (op.result_types.empty()) return c.fail(op, "missing result type");
+      set(0, op.result_types[0]);
+    } else if (n == "nova.gelu" || n == "nova.relu" || n == "nova.softmax") {
+      if (in.size() != 1 || !is_float(in[0]->dtype)) return c.fail(op, "expects one float tensor");
+      set(0, *in[0]);
+    } else if (n == "nova.add") {
+      if (in.size() != 2) return c.fail(op, "expects two operands");
+      if (in[0]->dtype != in[1]->dtype || !is_float(in[0]->dtype)) return c.fail(op, "mixed or non-float dtypes are outside the supported subset");
+      if (in[0]->shape == in[1]->shape || is_row_broadcast(*in[0], *in[1])) set(0, *in[0]);
+      else if (is_row_broadcast(*in[1], *in[0])) set(0, *in[1]);
+      else return c.fail(op, "only same-shape or row-broadcast operands are supported");
+    } else if (n == "nova.layer_norm") {
+      if (in.size() != 3) return c.fail(op, "expects input, gamma, beta");
+      const Type& x = *in[0];
+      if (x.shape.empty() || in[1]->numel() != x.shape.back() || in[2]->numel() != x.shape.back())
+        return c.fail(op, "gamma / beta must hold D elements");
+      Type stats = x;
+      stats.shape.pop_back();
+      if (op.results.size() == 1) {  // `%y = nova.layer_norm` binds the first result; the others stay addressable as #1, #2
+        p.types[op.results[0]] = x;
+        p.types[op.results[0] + "#1"] = stats;
+        p.types[op.results[0] + "#2"] = stats;
+      } else {
+        set(0, x); set(1, stats); set(2, stats);
+      }
+    } else if (n == "nova.gather") {
+      if (in.size() != 1 || op.index_operands.size() != 1) return c.fail(op, "expects input [indices]");
+      const Type* idx = c.type_of(op.index_operands[0]);
+      if (!idx) return c.fail(op, "use of undefined value %" + op.index_operands[0]);
+      if (idx->dtype != NOVA_B200_I16 && idx->dtype != NOVA_B200_I32 && idx->dtype != NOVA_B200_I64)
+        return c.fail(op, "indices must be i16, i32 or i64");
+      const Type& x = *in[0];
+      int64_t axis = op.attrs.count("axis") ? op.attrs.at("axis") : 0;
+      if (axis < 0) axis += static_cast<int64_t>(x.shape.size());
+      if (axis < 0 || axis >= static_cast<int64_t>(x.shape.size())) return c.fail(op, "axis out of range");
+      size_t batch_dims = 0;
+      for (size_t i = 0; i < std::min<size_t>(axis, idx->shape.size()); ++i) {
+        if (x.shape[i] != idx->shape[i]) break;
+        ++batch_dims;
+      }
+      Type t;
+      t.dtype = x.dtype;
+      for (int64_t i = 0; i < axis; ++i) t.shape.push_back(x.shape[i]);
+      for (size_t i = batch_dims; i < idx->shape.size(); ++i) t.shape.push_back(idx->shape[i]);
+      for (size_t i = axis + 1; i < x.shape.size(); ++i) t.shape.push_back(x.shape[i]);
+      set(0, t);
+    } else if (n == "nova.reshape") {
+      if (in.size() != 1 || op.result_types.empty()) return c.fail(op, "expects `%x : Tin -> Tout`");
+      if (op.result_types[0].numel() != in[0]->numel()) return c.fail(op, "element counts differ");
+      Type t = op.result_types[0];
+      t.dtype = in[0]->dtype;
+      set(0, t);
+    } else if (n == "nova.transpose") {
+      if (in.size() != 1) return c.fail(op, "expects one operand");
+      Type t = *in[0];
+      const int64_t r = static_cast<int64_t>(t.shape.size());
+      int64_t a1 = op.attrs.count("axes1") ? op.attrs.at("axes1") : -1;
+      int64_t a2 = op.attrs.count("axes2") ? op.attrs.at("axes2") : -2;
+      if (a1 < 0) a1 += r;
+      if (a2 < 0) a2 += r;
+      if (r < 2 || a1 < 0 || a2 < 0 || a1 >= r || a2 >= r) return c.fail(op, "axes out of range");
+      std::swap(t.shape[a1], t.shape[a2]);
+      set(0, t);
+    } else if (n == "nova.cast") {
+      if (in.size() != 1 || op.result_types.empty()) return c.fail(op, "expects `%x : Tin -> Tout`");
+      if (!is_float(in[0]->dtype) || !is_float(op.result_types[0].dtype) || op.result_types[0].shape != in[0]->shape)
+        return c.fail(op, "only float-to-float casts of equal shape are supported");
+      set(0, op.result_types[0]);
+    } else if (n == "nova.to_device" || n == "bufferization.to_tensor") {
+      if (in.size() != 1) return c.fail(op, "expects one operand");
+      set(0, *in[0]);
+    } else if (n == "bufferization.materialize_in_destination") {
+      if (in.size() != 2) return c.fail(op, "expects `%t in writable %dest`");
+      if (in[0]->shape != in[1]->shape || in[0]->dtype != in[1]->dtype) return c.fail(op, "source and destination types differ");
+    } else {
+      return c.fail(op, "operation is outside the supported subset");
+    }
+    // written types, when present, must agree with what was inferred
+    if (!op.result_types.empty() && !op.results.empty() && n != "nova.reshape" && n != "nova.cast") {
+      const Type* got = c.type_of(op.results[0]);
+      if (got && (got->shape != op.result_types[0].shape))
+        return c.fail(op, "written result type " + type_str(op.result_types[0]) + " differs from the inferred " + type_str(*got));
+    }
+  }
+  for (const std::string& r : f.returned)
+    if (!c.type_of(r)) { *error = "return of undefined value %" + r; return false; }
+
+  // ---- pass 2: steps with fusion
+  auto single_user = [&](const std::string& v) -> const Op* {
+    if (c.uses[v] != 1) return nullptr;
+    for (const Op& u : f.ops) {
+      if (c.absorbed.count(&u)) continue;
+      for (const std::string& o : u.operands)
+        if (o == v) return &u;
+    }
+    return nullptr;
+  };
+  // a value can be used by a step emitted at op `at` only if it is an argument or defined by an earlier op
+  auto defined_before = [&](const std::string& v, const Op* at) {
+    auto it = c.producer.find(v);
+    if (it == c.producer.end()) {
+      const size_t h = v.find('#');
+      if (h != std::string::npos) it = c.producer.find(v.substr(0, h));
+      if (it == c.producer.end()) return true;  // a function argument
+    }
+    return it->second < at;  // ops live in one vector: address order is program order
+  };
+  const Op* current = nullptr;
+  auto absorb_tail = [&](Step& s, std::string v) {
+    const Type out_t = *c.type_of(v);
+    // accumulator init: the other addend of a following add (FuseMatmulBias)
+    if (s.bias.empty() && s.residual.empty() && s.act == NOVA_B200_ACT_NONE) {
+      const Op* u = single_user(v);
+      if (u && u->name == "nova.add" && u->operands.size() == 2) {
+        const std::string other = u->operands[0] == v ? u->operands[1] : u->operands[0];
+        const Type* ot = c.type_of(other);
+        if (ot && other != v && ot->dtype == out_t.dtype && defined_before(other, current)) {
+          bool fused = false;
+          if (ot->shape == out_t.shape) { s.residual = other; fused = true; }
+          else if (is_row_broadcast(out_t, *ot)) { s.bias = other; fused = true; }
+          if (fused) {
+            c.absorbed.insert(u);
+            s.note += " + " + u->name;
+            p.alias[v] = u->results[0];
+            v = u->results[0];
+          }
+        }
+      }
+    }
+    if (s.act == NOVA_B200_ACT_NONE) {
+      const Op* u = single_user(v);
+      if (u && (u->name == "nova.relu" || u->name == "nova.gelu")) {
+        s.act = u->name == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;
+        c.absorbed.insert(u);
+        s.note += " + " + u->name;
+        p.alias[v] = u->results[0];
+        v = u->results[0];
+      }
+    }
+    s.outputs = {v};
+  };
+
+  for (const Op& op : f.ops) {
+    if (c.absorbed.count(&op)) continue;
+    current = &op;
+    const std::string& n = op.name;
+    Step s;
+    s.attrs = op.attrs;
+    s.note = n;
+    if (n == "nova.matmul") {
+      s.kind = "gemm";
+      s.inputs = {op.operands[0], op.operands[1]};
+      absorb_tail(s, op.results[0]);
+    } else if (n == "nova.linear") {
+      s.kind = "gemm";
+      s.inputs = {op.operands[0], op.operands[1]};
+      s.bias = op.operands[2];
+      absorb_tail(s, op.results[0]);
+    } else if (n == "linalg.matmul" || n == "linalg.batch_matmul") {
+      s.kind = "gemm";
+      s.inputs = {op.operands[0], op.operands[1]};
+      // outs: a zero fill is INIT_ZERO; anything else is a live accumulator (bias / residual already moved there)
+      const std::string outs = op.operands[2];
+      const Op* prod = c.producer.count(outs) ? c.producer[outs] : nullptr;
+      bool zero = false;
+      if (prod && prod->name == "linalg.fill") {
+        const Op* cst = c.producer.count(prod->operands[0]) ? c.producer[prod->operands[0]] : nullptr;
+        zero = cst && cst->name == "arith.constant" && cst->fvalue == 0.0;
+      }
+      if (!zero) s.residual = outs;
+      absorb_tail(s, op.results[0]);
+    } else if (n == "nova.gelu" || n == "nova.relu") {
+      s.kind = "activation";
+      s.act = n == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;
+      s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.add") {
+      s.kind = "add";
+      s.inputs = op.operands; s.outputs = op.results;
+      if (!(c.type_of(op.operands[0])->shape == c.type_of(op.results[0])->shape)) std::swap(s.inputs[0], s.inputs[1]);
+    } else if (n == "nova.softmax") { s.kind = "softmax"; s.inputs = op.operands; s.outputs = op.results; }
+    else if (n == "nova.layer_norm") {
+      s.kind = "layer_norm"; s.inputs = op.operands;
+      if (op.results.size() == 1) s.outputs = {op.results[0], op.results[0] + "#1", op.results[0] + "#2"};
+      else s.outputs = op.results;
+    } else if (n == "nova.gather") { s.kind = "gather"; s.inputs = {op.operands[0], op.index_operands[0]}; s.outputs = op.results; }
+    else if (n == "nova.reshape") { s.kind = "reshape"; s.inputs = op.operands; s.outputs = op.results; }
+    else if (n == "nova.transpose") { s.kind = "transpose"; s.inputs = op.operands; s.outputs = op.results; }
+    else if (n == "nova.cast") { s.kind = "cast"; s.inputs = op.operands; s.outputs = op.results; }
+    else if (n == "nova.to_device" || n == "bufferization.to_tensor") { s.kind = "alias"; s.inputs = op.operands; s.outputs = op.results; }
+    else if (n == "bufferization.materialize_in_destination") { s.kind = "store_to_arg"; s.inputs = op.operands; }
+    else if (n == "linalg.fill") {
+      // a zero fill that only initialises a contraction is folded into it (INIT_ZERO)
+      const Op* cst = c.producer.count(op.operands[0]) ? c.producer[op.operands[0]] : nullptr;
+      bool only_gemm_outs = c.uses[op.results[0]] > 0;
+      for (const Op& u : f.ops)
+        for (size_t k = 0; k < u.operands.size(); ++k)
+          if (u.operands[k] == op.results[0] && !((u.name == "linalg.matmul" || u.name == "linalg.batch_matmul") && k == 2))
+            only_gemm_outs = false;
+      if (cst && cst->fvalue == 0.0 && only_gemm_outs) continue;
+      s.kind = "fill"; s.fvalue = cst ? cst->fvalue : 0.0; s.inputs = {op.operands[1]}; s.outputs = op.results;
+    } else if (n == "tensor.empty") { s.kind = "empty"; s.outputs = op.results; }
+    else if (n == "arith.constant") { continue; }
+    p.steps.push_back(s);
+  }
+  p.results = f.returned;
+  return true;
+}
+
+std::string describe_plan(const Function& f, const Plan& p) {
+  std::ostringstream o;
+  o << "func @" << f.name << "(";
+  for (size_t i = 0; i < f.arg_names.size(); ++i) o << (i ? ", " : "") << "%" << f.arg_names[i] << ": " << type_str(f.arg_types[i]);
+  o << ")\n";
+  for (const Step& s : p.steps) {
+    o << "  " << s.kind;
+    if (s.kind == "gemm") {
+      o << " init=" << (!s.bias.empty() ? "bias_row(%" + s.bias + ")" : !s.residual.empty() ? "residual(%" + s.residual + ")" : std::string("zero"));
+      o << " act=" << (s.act == NOVA_B200_ACT_RELU ? "relu" : s.act == NOVA_B200_ACT_GELU_TANH ? "gelu_tanh" : "none");
+    }
+    o << " (";
+    for (size_t i = 0; i < s.inputs.size(); ++i) o << (i ? ", " : "") << "%" << s.inputs[i];
+    o << ") -> (";
+    for (size_t i = 0; i < s.outputs.size(); ++i) {
+      o << (i ? ", " : "") << "%" << s.outputs[i];
+      auto it = p.types.find(s.outputs[i]);
+      if (it != p.types.end()) o << ": " << type_str(it->second);
+    }
+    o << ")  [" << s.note << "]\n";
+  }
+  o << "  return";
+  for (const std::string& r : p.results) o << " %" << r;
+  o << "\n";
+  return o.str();
+}
+
+}  // namespace fe
+}  // namespace nova

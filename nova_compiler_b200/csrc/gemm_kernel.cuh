@@ -554,26 +554,34 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
 
 // hi = x rounded to tf32 (round-to-nearest), lo = x - hi (exact in fp32); written to compact
 // [batch, rows, ld_out] buffers whose pitch is a multiple of 16 bytes whatever the input pitch was.
-__global__ void nova_split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
-                                       int64_t rows_total, int32_t rows_per_batch, int32_t cols, int64_t ld_in,
-                                       int64_t stride_in, int32_t ld_out) {
-  const int64_t n = rows_total * ld_out;
+// One launch splits both operands: blockIdx.y == 0 handles A, 1 handles B.
+struct SplitOperand {
+  const float* x;
+  float* hi;
+  float* lo;
+  int64_t rows_total, ld_in, stride_in;
+  int32_t rows_per_batch, cols, ld_out;
+};
+
+__global__ void nova_split_tf32_kernel(const SplitOperand oa, const SplitOperand ob) {
+  const SplitOperand& o = blockIdx.y == 0 ? oa : ob;
+  const int64_t n = o.rows_total * o.ld_out;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / ld_out;
-    const int32_t c = static_cast<int32_t>(i - r * ld_out);
+    const int64_t r = i / o.ld_out;
+    const int32_t c = static_cast<int32_t>(i - r * o.ld_out);
     float h = 0.0f, l = 0.0f;
-    if (c < cols) {
-      const int64_t b = r / rows_per_batch;
-      const int64_t rr = r - b * rows_per_batch;
-      const float v = x[b * stride_in + rr * ld_in + c];
+    if (c < o.cols) {
+      const int64_t b = r / o.rows_per_batch;
+      const int64_t rr = r - b * o.rows_per_batch;
+      const float v = o.x[b * o.stride_in + rr * o.ld_in + c];
       uint32_t hb;
       asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v));
       h = __uint_as_float(hb);
       l = v - h;
     }
-    hi[i] = h;
-    lo[i] = l;
+    o.hi[i] = h;
+    o.lo[i] = l;
   }
 }
 

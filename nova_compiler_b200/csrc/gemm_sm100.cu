@@ -1,5 +1,6 @@
 // Host side of the contraction: argument validation, kernel selection ("plan"),
 // tensor-map encoding and launch.  See gemm_kernel.cuh for the device code.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -341,13 +342,14 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     float* s = static_cast<float*>(ctx->scratch);
     float* a_hi = s; float* a_lo = a_hi + a_nb * a_rows * a_ldo;
     float* b_hi = a_lo + a_nb * a_rows * a_ldo; float* b_lo = b_hi + b_nb * b_rows * b_ldo;
-    const int blocks = ctx->sm_count * 8;
-    nova_split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(a->A), a_hi, a_lo, a_nb * a_rows,
-                                                       static_cast<int32_t>(a_rows), static_cast<int32_t>(a_cols),
-                                                       a->lda, a->batch_stride_a, static_cast<int32_t>(a_ldo));
-    nova_split_tf32_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows,
-                                                       static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols),
-                                                       a->ldb, a->batch_stride_b, static_cast<int32_t>(b_ldo));
+    SplitOperand oa{static_cast<const float*>(a->A), a_hi, a_lo, a_nb * a_rows, a->lda, a->batch_stride_a,
+                    static_cast<int32_t>(a_rows), static_cast<int32_t>(a_cols), static_cast<int32_t>(a_ldo)};
+    SplitOperand ob{static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows, a->ldb, a->batch_stride_b,
+                    static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols), static_cast<int32_t>(b_ldo)};
+    const int64_t biggest = std::max(a_nb * a_rows * a_ldo, b_nb * b_rows * b_ldo);
+    const int64_t want = (biggest + 255) / 256;
+    const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8)));
+    nova_split_tf32_kernel<<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
     NOVA_CUDA_OK(cudaGetLastError());
     a_src[0] = a_hi; a_src[1] = a_lo; b_src[0] = b_hi; b_src[1] = b_lo;
     a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;

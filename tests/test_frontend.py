@@ -1,0 +1,194 @@
+"""The textual front-end (nova_b200_module_*): the stand-in for the MLIR lowering pass.
+
+CPU part: parsing, shape inference and fusion planning of modules written in the reference's textual forms
+(the op syntax of ltest/*.mlir and test/pipeline-tests/*.mlir; shapes here are this test's own).
+GPU part: the planned calls run and match the CPU oracle applied op by op."""
+import numpy as np
+import pytest
+
+from nova_compiler_b200 import _lib as L
+from nova_compiler_b200.frontend import Module
+
+MLP = '''
+module {
+  func.func @main(%arg0: tensor<24x40xf32, #nova.device<"1">>,
+      %arg1: tensor<40x56xf32, #nova.device<"1">>,
+      %arg2: tensor<1x56xf32>) -> tensor<24x56xf32> {
+    %0 = nova.matmul %arg0, %arg1 : tensor<24x40xf32,#nova.device<"1">>, tensor<40x56xf32,#nova.device<"1">>
+    %1 = nova.add %0, %arg2 : tensor<24x56xf32>, tensor<1x56xf32>
+    %2 = nova.relu %1 : tensor<24x56xf32>
+    return %2 : tensor<24x56xf32>
+  }
+}
+'''
+
+BLOCK = '''
+func.func @block(%x: tensor<2x48x64xbf16>, %g: tensor<64xbf16>, %b: tensor<64xbf16>, %w1: tensor<64x136xbf16>,
+                 %b1: tensor<136xbf16>, %w2: tensor<136x64xbf16>, %b2: tensor<64xbf16>)
+    -> (tensor<2x48x64xbf16>, tensor<2x48x48xbf16>) attributes { llvm.emit_c_interface } {
+  %ln, %sum, %rstd = nova.layer_norm %x, %g, %b : tensor<2x48x64xbf16>, tensor<64xbf16>, tensor<64xbf16>
+  %h = nova.linear %ln, %w1, %b1 : tensor<2x48x64xbf16>, tensor<64x136xbf16>, tensor<136xbf16>
+  %a = nova.gelu %h : tensor<2x48x136xbf16>
+  %o = nova.linear %a, %w2, %b2 : tensor<2x48x136xbf16>, tensor<136x64xbf16>, tensor<64xbf16>
+  %r = nova.add %o, %x : tensor<2x48x64xbf16>, tensor<2x48x64xbf16>
+  %t = nova.transpose %ln axes1 = 2 axes2 = 1 : tensor<2x48x64xbf16>
+  %s = nova.matmul %ln, %t : tensor<2x48x64xbf16>, tensor<2x64x48xbf16>
+  %p = nova.softmax %s : tensor<2x48x48xbf16>
+  return %r, %p : tensor<2x48x64xbf16>, tensor<2x48x48xbf16>
+}
+'''
+
+LINALG = '''
+func.func @la(%A: tensor<100x300xf32>, %B: tensor<300x200xf32>, %bias: tensor<100x200xf32>) -> tensor<100x200xf32> {
+  %cst = arith.constant 0.000000e+00 : f32
+  %e = tensor.empty() : tensor<100x200xf32>
+  %f = linalg.fill ins(%cst : f32) outs(%e : tensor<100x200xf32>) -> tensor<100x200xf32>
+  %r = linalg.matmul ins(%A, %B : tensor<100x300xf32>, tensor<300x200xf32>) outs(%f : tensor<100x200xf32>) -> tensor<100x200xf32>
+  // the FuseMatmulBias output form: the bias IS the matmul's outs
+  %q = linalg.matmul ins(%A, %B : tensor<100x300xf32>, tensor<300x200xf32>) outs(%bias : tensor<100x200xf32>) -> tensor<100x200xf32>
+  %s = nova.add %r, %q : tensor<100x200xf32>, tensor<100x200xf32>
+  return %s : tensor<100x200xf32>
+}
+func.func @bmm(%A: tensor<4x64x256xf16>, %B: tensor<4x256x64xf16>, %out: memref<4x64x64xf16, 1>) {
+  %cst = arith.constant 0.0 : f16
+  %e = tensor.empty() : tensor<4x64x64xf16>
+  %f = linalg.fill ins(%cst : f16) outs(%e : tensor<4x64x64xf16>) -> tensor<4x64x64xf16>
+  %r = linalg.batch_matmul ins(%A, %B : tensor<4x64x256xf16>, tensor<4x256x64xf16>) outs(%f : tensor<4x64x64xf16>) -> tensor<4x64x64xf16>
+  bufferization.materialize_in_destination %r in writable %out : (tensor<4x64x64xf16>, memref<4x64x64xf16, 1>) -> ()
+  return
+}
+'''
+
+EMBED = '''
+func.func @embed(%table: tensor<500x96xf32>, %ids: tensor<8x16xi16>) -> tensor<128x96xf32> {
+  %0 = nova.gather %table [%ids] axis = 0 : tensor<500x96xf32>, tensor<8x16xi16> -> tensor<8x16x96xf32>
+  %1 = nova.reshape %0 : tensor<8x16x96xf32> -> tensor<128x96xf32>
+  %2 = nova.to_device %1 : tensor<128x96xf32> -> tensor<128x96xf32, #nova.device<"1">>
+  return %2 : tensor<128x96xf32>
+}
+'''
+
+
+def test_plan_fuses_bias_and_activation_into_one_call():
+    m = Module(MLP)
+    plan = m.plan("main")
+    assert plan.count("gemm") == 1 and "init=bias_row(%arg2)" in plan and "act=relu" in plan
+    assert "[nova.matmul + nova.add + nova.relu]" in plan
+    args, res = m.signature("main")
+    assert args == [(L.F32, (24, 40)), (L.F32, (40, 56)), (L.F32, (1, 56))] and res == [(L.F32, (24, 56))]
+
+
+def test_plan_of_a_transformer_style_block():
+    m = Module(BLOCK)
+    plan = m.plan("block")
+    lines = [l.strip() for l in plan.splitlines()]
+    assert lines[1].startswith("layer_norm")
+    assert "gemm init=bias_row(%b1) act=gelu_tanh" in lines[2] and "nova.linear + nova.gelu" in lines[2]
+    # the residual add after the second linear cannot displace its bias: it stays a separate step
+    assert "gemm init=bias_row(%b2) act=none" in lines[3]
+    assert lines[4].startswith("add")
+    assert lines[5].startswith("transpose") and lines[6].startswith("gemm init=zero") and lines[7].startswith("softmax")
+    _, res = m.signature("block")
+    assert res == [(L.BF16, (2, 48, 64)), (L.BF16, (2, 48, 48))]
+
+
+def test_plan_of_linalg_forms():
+    m = Module(LINALG)
+    plan = m.plan("la")
+    assert "fill" not in plan  # the zero fill is folded into the contraction
+    assert "gemm init=zero act=none (%A, %B) -> (%r" in plan
+    assert "gemm init=residual(%bias) act=none (%A, %B) -> (%q" in plan
+    plan = m.plan("bmm")
+    assert "gemm init=zero" in plan and "store_to_arg (%r, %out)" in plan
+    assert m.signature("bmm")[1] == []
+
+
+def test_errors_are_reported_with_line_numbers(lib):
+    import ctypes as C
+    h = C.c_void_p()
+
+    def parse(text):
+        st = lib.nova_b200_module_parse(text.encode(), C.byref(h))
+        return st, lib.nova_b200_last_error_string().decode()
+
+    st, msg = parse(MLP.replace("tensor<40x56xf32, #nova.device<\"1\">>,", "tensor<41x56xf32>,"))
+    assert st == L.ERR_UNSUPPORTED and "contraction dims differ: 40 vs 41" in msg and "line" in msg
+    st, msg = parse("func.func @f(%a: tensor<4x4xf32>) -> tensor<4x4xf32> {\n %0 = nova.sin %a : tensor<4x4xf32>\n return %0 : tensor<4x4xf32>\n}")
+    assert st == L.ERR_UNSUPPORTED and "nova.sin" in msg and "outside the supported subset" in msg
+    st, msg = parse("func.func @f(%a: tensor<?x4xf32>) -> tensor<4x4xf32> {\n return %a : tensor<4x4xf32>\n}")
+    assert st == L.ERR_INVALID_ARG and "dynamic shapes" in msg
+    st, msg = parse("func.func @f(%a: tensor<4x4xf32>) -> tensor<2x9xf32> {\n %0 = nova.reshape %a : tensor<4x4xf32> -> tensor<2x9xf32>\n return %0 : tensor<2x9xf32>\n}")
+    assert st == L.ERR_UNSUPPORTED and "element counts differ" in msg
+    st, msg = parse("this is not IR")
+    assert st == L.ERR_INVALID_ARG
+    assert lib.nova_b200_module_parse(None, C.byref(h)) == L.ERR_INVALID_ARG
+
+
+# ---------------------------------------------------------------------------------------------- GPU
+
+def _bits(torch, t):
+    t = t.contiguous().cpu()
+    return t.numpy() if t.dtype == torch.float32 else t.view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.gpu
+def test_run_mlp_matches_oracle(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(1)
+    a = torch.rand(24, 40, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(40, 56, device="cuda", generator=g) * 2 - 1
+    bias = torch.rand(1, 56, device="cuda", generator=g) * 2 - 1
+    y, = Module(MLP).run("main", a, b, bias)
+    want = oracle.gemm(a.cpu().numpy(), b.cpu().numpy(), bias=bias.cpu().numpy().reshape(-1), act="relu")
+    assert oracle.rel_fro(y.cpu().numpy(), want) <= 1e-5
+
+
+@pytest.mark.gpu
+def test_run_block_matches_oracle_op_by_op(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(2)
+    bf = torch.bfloat16
+    mk = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).to(bf)
+    x, gm, bt = mk(2, 48, 64), mk(64), mk(64)
+    w1, b1, w2, b2 = mk(64, 136, sc=0.1), mk(136, sc=0.1), mk(136, 64, sc=0.1), mk(64, sc=0.1)
+    r, p = Module(BLOCK).run("block", x, gm, bt, w1, b1, w2, b2)
+    B = lambda t: _bits(torch, t)
+    ln, _, _ = oracle.layer_norm(B(x), B(gm), B(bt), "bf16", compute_f32=True)
+    h = oracle.gemm(ln, B(w1), dtype_in="bf16", bias=B(b1), act="gelu_tanh")
+    o = oracle.gemm(h, B(w2), dtype_in="bf16", bias=B(b2))
+    want_r = oracle.add_rowbcast(o, B(x), "bf16")
+    s = oracle.gemm(ln, np.ascontiguousarray(np.swapaxes(ln, 1, 2)), dtype_in="bf16")
+    want_p = oracle.softmax(s, "bf16", compute_f32=True)
+    f = lambda bits: oracle.from_bits(bits, "bf16")
+    assert oracle.rel_fro(f(B(r)), f(want_r)) <= 4e-3   # three chained bf16 roundings
+    assert oracle.rel_fro(f(B(p)), f(want_p)) <= 4e-3
+
+
+@pytest.mark.gpu
+def test_run_linalg_forms_and_output_argument(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    A = torch.rand(100, 300, device="cuda", generator=g) * 2 - 1
+    Bm = torch.rand(300, 200, device="cuda", generator=g) * 2 - 1
+    bias = torch.rand(100, 200, device="cuda", generator=g) * 2 - 1
+    m = Module(LINALG)
+    s, = m.run("la", A, Bm, bias)
+    ab = oracle.gemm(A.cpu().numpy(), Bm.cpu().numpy())
+    abq = oracle.gemm(A.cpu().numpy(), Bm.cpu().numpy(), residual=bias.cpu().numpy())
+    assert oracle.rel_fro(s.cpu().numpy(), ab + abq) <= 1e-5
+    a16 = (torch.randn(4, 64, 256, device="cuda", generator=g) / 16).to(torch.float16)
+    b16 = (torch.randn(4, 256, 64, device="cuda", generator=g) / 16).to(torch.float16)
+    out = torch.zeros(4, 64, 64, device="cuda", dtype=torch.float16)
+    assert m.run("bmm", a16, b16, out) == []
+    want = oracle.gemm(_bits(torch, a16), _bits(torch, b16), dtype_in="f16")
+    assert oracle.rel_fro(oracle.from_bits(_bits(torch, out), "f16"), oracle.from_bits(want, "f16")) <= 1e-3
+
+
+@pytest.mark.gpu
+def test_run_embedding_is_bit_exact(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(4)
+    table = torch.randn(500, 96, device="cuda", generator=g)
+    ids = torch.randint(0, 500, (8, 16), device="cuda", generator=g).to(torch.int16)
+    y, = Module(EMBED).run("embed", table, ids)
+    assert torch.equal(y, table[ids.long()].reshape(128, 96))
