@@ -184,6 +184,12 @@ int32_t nova_b200_activation(const void* x_dev, void* y_dev, int64_t n, int32_t 
 int32_t nova_b200_add_rowbcast(const void* a_dev, const void* b_dev, void* out_dev, int64_t rows, int64_t cols,
                                int32_t b_is_full, int32_t dtype, void* stream);
 
+/* out[c] = sum over rows of x[r, c], fp32 accumulation: the bias gradient of nova.linear_backward, a column sum
+ * over the flattened batch*M rows (NovaLinearBackwardPattern, NovaToLinalgGeneric.cpp:1970-1985).  x is
+ * contiguous [rows, cols]; out holds cols elements of `dtype`.  Uses the per-device scratch for partial sums
+ * (calls on different streams of one device must not overlap). */
+int32_t nova_b200_column_sum(const void* x_dev, void* out_dev, int64_t rows, int64_t cols, int32_t dtype, void* stream);
+
 /* nova.layer_norm over the last dim of x[rows, D] (NovaLayerNormPattern,
  * NovaToLinalgGeneric.cpp:1997-2126): y = (x - mean) * rsqrt(var + 1e-5) * gamma + beta with
  * var = E[x^2] - mean^2; also returns the RAW row sum (not the mean) and rstd, as the reference does

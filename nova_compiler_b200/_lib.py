@@ -74,6 +74,7 @@ PROTOTYPES = {
                                            C.c_int32, C.c_void_p]),
     "nova_b200_layer_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "nova_b200_column_sum": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_softmax": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_gather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                      C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),

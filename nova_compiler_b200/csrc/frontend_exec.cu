@@ -272,6 +272,9 @@ struct Exec {
     else if (k == "add") {
       const int64_t cols = in[0].shape.back();
       st = nova_b200_add_rowbcast(in[0].ptr, in[1].ptr, out[0].ptr, n / cols, cols, in[1].numel() == n ? 1 : 0, in[0].dtype, stream);
+    } else if (k == "column_sum") {
+      const int64_t cols = in[0].shape.back();
+      st = nova_b200_column_sum(in[0].ptr, out[0].ptr, n / std::max<int64_t>(cols, 1), cols, in[0].dtype, stream);
     } else if (k == "softmax") {
       const int64_t r = static_cast<int64_t>(in[0].shape.size());
       int64_t dim = s.attrs.count("dimension") ? s.attrs.at("dimension") : -1;

@@ -156,6 +156,27 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
       if (r == 3 && (a.shape[0] != cc.shape[0] || b.shape[0] != cc.shape[0])) return c.fail(op, "batch sizes differ");
       if (!is_float(a.dtype) || a.dtype != b.dtype || !is_float(cc.dtype)) return c.fail(op, "unsupported dtypes");
       set(0, cc);
+    } else if (n == "nova.matmul_backward") {
+      // grad_a has a's type, grad_b has b's type (MatmulBackwardOp::inferReturnTypes, NovaOps.cpp:1287-1303)
+      if (in.size() != 3 || op.results.size() != 2) return c.fail(op, "expects grad_out, a, b and two results");
+      const Type &go = *in[0], &a = *in[1], &b = *in[2];
+      if (a.shape.size() < 2 || a.shape.size() != b.shape.size() || go.shape.size() != a.shape.size())
+        return c.fail(op, "operands must share a rank >= 2");
+      const size_t r = a.shape.size();
+      if (go.shape[r - 2] != a.shape[r - 2] || go.shape[r - 1] != b.shape[r - 1] || a.shape[r - 1] != b.shape[r - 2])
+        return c.fail(op, "shapes do not compose");
+      if (!is_float(a.dtype) || a.dtype != b.dtype || a.dtype != go.dtype) return c.fail(op, "operands must share a float dtype");
+      set(0, a); set(1, b);
+    } else if (n == "nova.linear_backward") {
+      // grad_input ~ input, grad_weight ~ weight, grad_bias = [N] (LinearBackwardOp::inferReturnTypes, NovaOps.cpp:2105-2128)
+      if (in.size() != 3 || op.results.size() != 3) return c.fail(op, "expects grad_out, input, weight and three results");
+      const Type &go = *in[0], &x = *in[1], &w = *in[2];
+      if (w.shape.size() != 2 || x.shape.empty() || x.shape.back() != w.shape[0] || go.shape.size() != x.shape.size() ||
+          go.shape.back() != w.shape[1])
+        return c.fail(op, "shapes do not compose");
+      if (!is_float(x.dtype) || x.dtype != w.dtype || x.dtype != go.dtype) return c.fail(op, "operands must share a float dtype");
+      Type gb; gb.dtype = w.dtype; gb.shape = {w.shape[1]};
+      set(0, x); set(1, w); set(2, gb);
     } else if (n == "linalg.fill") {
       if (in.size() != 2) return c.fail(op, "expects ins(scalar) outs(tensor)");
       set(0, *in[1]);
@@ -331,6 +352,42 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
       }
       if (!zero) s.residual = outs;
       absorb_tail(s, op.results[0]);
+    } else if (n == "nova.matmul_backward" || n == "nova.linear_backward") {
+      // Expanded into views + contractions (+ a column sum): the transposes are strided views that the
+      // contraction reads through trans_a / trans_b, the flattening of batch*M rows is a reshape view.
+      const std::string tag = "__bw" + std::to_string(op.line) + "_";
+      auto view = [&](const char* kind, const std::string& src, const std::string& dst, const Type& t,
+                      std::map<std::string, int64_t> attrs = {}) {
+        Step v; v.kind = kind; v.inputs = {src}; v.outputs = {dst}; v.attrs = attrs; v.note = n;
+        p.types[dst] = t;
+        p.steps.push_back(v);
+      };
+      auto swapped = [](Type t) { std::swap(t.shape[t.shape.size() - 1], t.shape[t.shape.size() - 2]); return t; };
+      auto gemm = [&](const std::string& a, const std::string& b, const std::string& out, const char* what) {
+        Step g; g.kind = "gemm"; g.inputs = {a, b}; g.outputs = {out}; g.note = n + std::string(" ") + what;
+        p.steps.push_back(g);
+      };
+      const std::string &go = op.operands[0], &x = op.operands[1], &w = op.operands[2];
+      const Type &tgo = *c.type_of(go), &tx = *c.type_of(x), &tw = *c.type_of(w);
+      if (n == "nova.matmul_backward") {
+        view("transpose", w, tag + "bt", swapped(tw));
+        gemm(go, tag + "bt", op.results[0], "grad_a = grad_out x b^T");
+        view("transpose", x, tag + "at", swapped(tx));
+        gemm(tag + "at", go, op.results[1], "grad_b = a^T x grad_out");
+      } else {
+        view("transpose", w, tag + "wt", swapped(tw));
+        gemm(go, tag + "wt", op.results[0], "grad_input = grad_out x W^T");
+        Type xf = tx, gf = tgo;
+        xf.shape = {tx.numel() / tx.shape.back(), tx.shape.back()};
+        gf.shape = {tgo.numel() / tgo.shape.back(), tgo.shape.back()};
+        view("reshape", x, tag + "xf", xf);
+        view("reshape", go, tag + "gf", gf);
+        view("transpose", tag + "xf", tag + "xft", swapped(xf));
+        gemm(tag + "xft", tag + "gf", op.results[1], "grad_weight = flatX^T x flatGo");
+        Step cs; cs.kind = "column_sum"; cs.inputs = {tag + "gf"}; cs.outputs = {op.results[2]}; cs.note = n + " grad_bias";
+        p.steps.push_back(cs);
+      }
+      continue;
     } else if (n == "nova.gelu" || n == "nova.relu") {
       s.kind = "activation";
       s.act = n == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;

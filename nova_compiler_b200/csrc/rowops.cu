@@ -7,6 +7,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "runtime.h"
 
 namespace nova {
@@ -334,6 +336,44 @@ __global__ void add_rowbcast_kernel(const T* __restrict__ a, const T* __restrict
   }
 }
 
+// Column sums of x[rows, cols] (the bias gradient of nova.linear_backward).  Pass 1: CTA (cx, ry) owns 64
+// columns and every gridDim.y-th block of 32 rows; a warp reads one row segment of 64 columns (128 B of
+// 16-bit data) per step, so loads are coalesced, and accumulates in fp32; the 8 warps' partials meet in shared
+// memory and one partial row per CTA goes to partial[ry, cols].  Pass 2 adds the gridDim.y partial rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+column_sum_partial_kernel(const T* __restrict__ x, float* __restrict__ partial, int64_t rows, int64_t cols) {
+  __shared__ float red[8][64];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * 64 + lane * 2;
+  float s0 = 0.0f, s1 = 0.0f;
+  for (int64_t r = static_cast<int64_t>(blockIdx.y) * 8 + warp; r < rows; r += static_cast<int64_t>(gridDim.y) * 8) {
+    const T* row = x + r * cols;
+    if (c0 < cols) s0 += ld_f32<T>(row[c0]);
+    if (c0 + 1 < cols) s1 += ld_f32<T>(row[c0 + 1]);
+  }
+  red[warp][lane * 2] = s0;
+  red[warp][lane * 2 + 1] = s1;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    const int64_t c = static_cast<int64_t>(blockIdx.x) * 64 + threadIdx.x;
+    if (c < cols) partial[static_cast<int64_t>(blockIdx.y) * cols + c] = t;
+  }
+}
+
+template <typename T>
+__global__ void column_sum_final_kernel(const float* __restrict__ partial, T* __restrict__ out, int64_t cols, int splits) {
+  for (int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; c < cols;
+       c += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float t = 0.0f;
+    for (int k = 0; k < splits; ++k) t += partial[static_cast<int64_t>(k) * cols + c];
+    out[c] = st_f32<T>(t);
+  }
+}
+
 int grid_for(int64_t work_items, int threads, int sm_count) {
   const int64_t want = (work_items + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(sm_count) * 16;
@@ -408,6 +448,39 @@ int32_t nova_b200_gather(const void* in, const void* idx, void* out, int64_t pre
   else if (align % 2 == 0) NOVA_GATHER(uint16_t);
   else NOVA_GATHER(uint8_t);
 #undef NOVA_GATHER
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_column_sum(const void* x, void* out, int64_t rows, int64_t cols, int32_t dtype, void* stream) {
+  if (rows < 0 || cols < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "column_sum: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "column_sum: dtype must be f32, f16 or bf16");
+  if (cols == 0) return NOVA_B200_OK;
+  if (!out || (rows > 0 && !x)) return fail(NOVA_B200_ERR_INVALID_ARG, "column_sum: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t col_tiles = (cols + 63) / 64;
+  // enough row splits to fill the machine, at most one per 8 rows
+  int64_t splits = (static_cast<int64_t>(ctx->sm_count) * 8 + col_tiles - 1) / col_tiles;
+  splits = std::max<int64_t>(1, std::min<int64_t>(splits, (rows + 7) / 8));
+  splits = std::min<int64_t>(splits, 65535);
+  std::lock_guard<std::mutex> lock(ctx->mu);  // the partial sums live in the per-device scratch
+  st = ensure_scratch(ctx, static_cast<size_t>(splits * cols) * sizeof(float));
+  if (st != NOVA_B200_OK) return st;
+  float* partial = static_cast<float*>(ctx->scratch);
+  const dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(splits));
+  const int fgrid = grid_for(cols, 256, ctx->sm_count);
+#define NOVA_COLSUM(T)                                                                                   \
+  do {                                                                                                   \
+    column_sum_partial_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(x), partial, rows, cols);    \
+    column_sum_final_kernel<T><<<fgrid, 256, 0, s>>>(partial, static_cast<T*>(out), cols, static_cast<int>(splits)); \
+  } while (0)
+  if (dtype == NOVA_B200_F32) NOVA_COLSUM(float);
+  else if (dtype == NOVA_B200_F16) NOVA_COLSUM(__half);
+  else NOVA_COLSUM(__nv_bfloat16);
+#undef NOVA_COLSUM
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }

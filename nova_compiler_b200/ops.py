@@ -181,6 +181,36 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, *, act: Optiona
     return y.reshape(*x.shape[:-1], w.shape[-1])
 
 
+def column_sum(x: torch.Tensor) -> torch.Tensor:
+    """Sum over all leading dims of x[..., C] -> [C], fp32 accumulation (grad_bias of nova.linear_backward)."""
+    _require_cuda(x)
+    xc = x.contiguous()
+    cols = xc.shape[-1]
+    out = torch.empty(cols, dtype=xc.dtype, device=xc.device)
+    L.check(L.load().nova_b200_column_sum(xc.data_ptr(), out.data_ptr(), xc.numel() // max(cols, 1), cols, _dt(xc),
+                                          _stream()))
+    return out
+
+
+def matmul_backward(grad_out: torch.Tensor, a: torch.Tensor, b: torch.Tensor):
+    """nova.matmul_backward (NovaOps.td:771-787; lowering NovaToLinalgGeneric.cpp:160-234):
+    grad_a = grad_out @ b^T (an NT contraction), grad_b = a^T @ grad_out (TN).  The transposes are views
+    consumed through trans_b / trans_a, never copies."""
+    return matmul(grad_out, b.transpose(-1, -2)), matmul(a.transpose(-1, -2), grad_out)
+
+
+def linear_backward(grad_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
+    """nova.linear_backward (NovaOps.td:1059-1066; lowering NovaToLinalgGeneric.cpp:1824-1995):
+    grad_input = grad_out @ W^T with W shared across the batch (:1867-1906), grad_weight = flatX^T @ flatGo over
+    the flattened batch*M rows (:1913-1963), grad_bias = column sum of flatGo (:1970-1985)."""
+    k, n = w.shape
+    grad_input = matmul(grad_out, w.transpose(0, 1))
+    xf = x.reshape(-1, k)
+    gf = grad_out.reshape(-1, n)
+    grad_weight = matmul(xf.transpose(0, 1), gf)
+    return grad_input, grad_weight, column_sum(gf)
+
+
 def _unary(x: torch.Tensor, act: int) -> torch.Tensor:
     _require_cuda(x)
     xc = x.contiguous()

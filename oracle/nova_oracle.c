@@ -459,6 +459,19 @@ void nova_oracle_layer_norm(const void* x, const void* gamma, const void* beta, 
   }
 }
 
+/* out[c] = sum_r x[r, c], rows ascending, fp32 accumulation (the grad_bias reduction of
+ * NovaLinearBackwardPattern, NovaToLinalgGeneric.cpp:1970-1985, over the flattened batch*M rows);
+ * compute_f32 == 0 rounds the running sum through dt after every add, as the reference does. */
+void nova_oracle_column_sum(const void* x, void* out, int64_t rows, int64_t cols, int dt, int compute_f32) {
+  const int ct = compute_f32 ? NOVA_F32 : dt;
+#pragma omp parallel for
+  for (int64_t c = 0; c < cols; ++c) {
+    float s = 0.0f;
+    for (int64_t r = 0; r < rows; ++r) s = round_through(s + load_elem(x, r * cols + c, dt), ct);
+    store_elem(out, c, dt, s);
+  }
+}
+
 /* ---------------------------------------------------------------- indexing (bit-exact) */
 
 /* nova.gather along `axis` viewed as [pre, axis_len, post] x indices[pre_or_1, n_idx]

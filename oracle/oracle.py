@@ -197,6 +197,16 @@ def layer_norm(x, gamma, beta, dt="f32", compute_f32=False):
     return y, mean_sum, rstd
 
 
+def column_sum(x, dt="f32", compute_f32=True):
+    x = np.ascontiguousarray(x, dtype=np_dtype(dt))
+    cols = x.shape[-1]
+    rows = x.size // cols
+    out = np.empty(cols, dtype=x.dtype)
+    lib().nova_oracle_column_sum(_ptr(x), _ptr(out), C.c_int64(rows), C.c_int64(cols), C.c_int(DTYPES[dt]),
+                                 C.c_int(int(compute_f32)))
+    return out
+
+
 def gather(inp, idx, axis=0):
     """nova.gather: out[pre..., idx..., post...] = inp[pre..., idx[...], post...].  Index tensors whose
     leading dims equal inp's leading `axis` dims are treated as batched (NovaOps.cpp:1898-1946)."""

@@ -192,3 +192,42 @@ def test_run_embedding_is_bit_exact(cuda, oracle):
     ids = torch.randint(0, 500, (8, 16), device="cuda", generator=g).to(torch.int16)
     y, = Module(EMBED).run("embed", table, ids)
     assert torch.equal(y, table[ids.long()].reshape(128, 96))
+
+
+BACKWARD = '''
+func.func @bw(%go: tensor<4x24x40xf32>, %x: tensor<4x24x56xf32>, %w: tensor<56x40xf32>,
+              %g2: tensor<24x40xf32>, %a: tensor<24x56xf32>, %b: tensor<56x40xf32>)
+    -> (tensor<4x24x56xf32>, tensor<56x40xf32>, tensor<40xf32>, tensor<24x56xf32>, tensor<56x40xf32>) {
+  %gi, %gw, %gb = nova.linear_backward %go, %x, %w : tensor<4x24x40xf32>, tensor<4x24x56xf32>, tensor<56x40xf32>
+  %ga, %gbm = nova.matmul_backward %g2, %a, %b : tensor<24x40xf32>, tensor<24x56xf32>, tensor<56x40xf32>
+  return %gi, %gw, %gb, %ga, %gbm : tensor<4x24x56xf32>, tensor<56x40xf32>, tensor<40xf32>, tensor<24x56xf32>, tensor<56x40xf32>
+}
+'''
+
+
+def test_plan_of_backward_ops_uses_views_not_copies():
+    plan = Module(BACKWARD).plan("bw")
+    assert plan.count("gemm") == 4 and plan.count("column_sum") == 1
+    assert "grad_input = grad_out x W^T" in plan and "grad_weight = flatX^T x flatGo" in plan
+    assert "grad_a = grad_out x b^T" in plan and "grad_b = a^T x grad_out" in plan
+    _, res = Module(BACKWARD).signature("bw")
+    assert [s for _, s in res] == [(4, 24, 56), (56, 40), (40,), (24, 56), (56, 40)]
+
+
+@pytest.mark.gpu
+def test_run_backward_ops_match_oracle(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(5)
+    r = lambda *s: torch.rand(*s, device="cuda", generator=g) * 2 - 1
+    go, x, w, g2, a, b = r(4, 24, 40), r(4, 24, 56), r(56, 40), r(24, 40), r(24, 56), r(56, 40)
+    gi, gw, gb, ga, gbm = Module(BACKWARD).run("bw", go, x, w, g2, a, b)
+    n = lambda t: t.cpu().numpy()
+    want_gi = oracle.gemm(n(go), np.ascontiguousarray(n(w).T))
+    xf, gf = n(x).reshape(96, 56), n(go).reshape(96, 40)
+    want_gw = oracle.gemm(np.ascontiguousarray(xf.T), gf)
+    want_gb = oracle.column_sum(gf)
+    assert oracle.rel_fro(n(gi), want_gi) <= 1e-5
+    assert oracle.rel_fro(n(gw), want_gw) <= 1e-5
+    assert oracle.rel_fro(n(gb), want_gb) <= 1e-5
+    assert oracle.rel_fro(n(ga), oracle.gemm(n(g2), np.ascontiguousarray(n(b).T))) <= 1e-5
+    assert oracle.rel_fro(n(gbm), oracle.gemm(np.ascontiguousarray(n(a).T), n(g2))) <= 1e-5

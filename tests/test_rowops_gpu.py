@@ -123,3 +123,26 @@ def test_test_cpu_mlir_graph_unfused(cuda, oracle):
     a, b, bias = (to_dev(cuda, z[f"test_cpu_mlir.{k}"], "f32") for k in ("a", "b", "bias"))
     unfused = ops.relu(ops.add(ops.matmul(a, b), bias.reshape(1, 10)))
     check(oracle, to_host(cuda, unfused, "f32"), z["test_cpu_mlir.c"], "f32")
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_column_sum_and_backward_ops(cuda, oracle, dt):
+    """grad_bias of nova.linear_backward (column sum over batch*M rows) and the NT / TN contractions of
+    nova.matmul_backward / nova.linear_backward, through the operator mirror."""
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(6)
+    for rows, cols in ((8192, 1536), (777, 333), (5, 1), (1, 40)):
+        x = rand_bits(oracle, rng, (rows, cols), dt, "normal")
+        got = to_host(cuda, ops.column_sum(to_dev(cuda, x, dt)), dt)
+        check(oracle, got, oracle.column_sum(x, dt), dt, tol=2e-3 if dt != "f32" else 1e-5)
+    go = rand_bits(oracle, rng, (3, 40, 72), dt, "normal")
+    x = rand_bits(oracle, rng, (3, 40, 56), dt, "normal")
+    w = rand_bits(oracle, rng, (56, 72), dt, "normal", 0.1)
+    gi, gw, gb = ops.linear_backward(to_dev(cuda, go, dt), to_dev(cuda, x, dt), to_dev(cuda, w, dt))
+    check(oracle, to_host(cuda, gi, dt), oracle.gemm(go, np.ascontiguousarray(w.T), dtype_in=dt), dt)
+    xf, gf = x.reshape(120, 56), go.reshape(120, 72)
+    check(oracle, to_host(cuda, gw, dt), oracle.gemm(np.ascontiguousarray(xf.T), gf, dtype_in=dt), dt)
+    check(oracle, to_host(cuda, gb, dt), oracle.column_sum(gf, dt), dt, tol=2e-3 if dt != "f32" else 1e-5)
+    ga, gbm = ops.matmul_backward(to_dev(cuda, go[0], dt), to_dev(cuda, x[0], dt), to_dev(cuda, w, dt))
+    check(oracle, to_host(cuda, ga, dt), oracle.gemm(go[0], np.ascontiguousarray(w.T), dtype_in=dt), dt)
+    check(oracle, to_host(cuda, gbm, dt), oracle.gemm(np.ascontiguousarray(x[0].T), go[0], dtype_in=dt), dt)
