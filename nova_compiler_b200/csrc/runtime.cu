@@ -101,6 +101,18 @@ static int32_t grow(void** buf, size_t* have, size_t want, const char* what) {
   return NOVA_B200_OK;
 }
 
+int32_t ensure_host_streams(DeviceContext* ctx) {
+  if (ctx->s_in) return NOVA_B200_OK;
+  NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking));
+  NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_comp, cudaStreamNonBlocking));
+  NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking));
+  for (int i = 0; i < 8; ++i) {
+    NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+    NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_comp[i], cudaEventDisableTiming));
+  }
+  return NOVA_B200_OK;
+}
+
 int32_t ensure_scratch(DeviceContext* ctx, size_t bytes) { return grow(&ctx->scratch, &ctx->scratch_bytes, bytes, "scratch"); }
 int32_t ensure_staging(DeviceContext* ctx, size_t bytes) { return grow(&ctx->staging, &ctx->staging_bytes, bytes, "staging"); }
 
@@ -140,6 +152,10 @@ int32_t nova_b200_shutdown(void) {
     if (c->status_word) cudaFree(c->status_word);
     if (c->scratch) cudaFree(c->scratch);
     if (c->staging) cudaFree(c->staging);
+    if (c->s_in) {
+      cudaStreamDestroy(c->s_in); cudaStreamDestroy(c->s_comp); cudaStreamDestroy(c->s_out);
+      for (int i = 0; i < 8; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
+    }
   }
   g_contexts.clear();
   if (prev >= 0) cudaSetDevice(prev);
@@ -208,13 +224,72 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   char* base = static_cast<char*>(ctx->staging);
   char* dA = base; char* dB = dA + up(a_bytes); char* dC = dB + up(b_bytes);
   char* dBias = dC + up(c_bytes); char* dR = dBias + up(bias_bytes);
+  const bool c_preload = a.init == NOVA_B200_INIT_FROM_C || a.ldc != a.N || (a.batch > 1 && a.batch_stride_c != a.M * a.ldc);
+
+  // Pipelined form: the problem is cut into up to 8 chunks (batches, or row blocks of a single matrix) and
+  // chunk i+1's host-to-device copy, chunk i's kernel and chunk i-1's device-to-host copy run concurrently
+  // on three streams, so the two PCIe directions overlap.  Needs chunkable layouts; else one shot below.
+  const bool by_batch = a.batch > 1 && a.batch_stride_a != 0 && a.batch_stride_c != 0 &&
+                        (a.init != NOVA_B200_INIT_RESIDUAL_FULL || a.batch_stride_r != 0);
+  const bool by_rows = a.batch == 1 && !a.trans_a && a.M >= 512 && a.K > 0;
+  if ((by_batch || by_rows) && a.K > 0) {
+    st = ensure_host_streams(ctx);
+    if (st != NOVA_B200_OK) return st;
+    cudaStream_t s_in = ctx->s_in, s_comp = ctx->s_comp, s_out = ctx->s_out;
+    const int64_t units = by_batch ? a.batch : (a.M + 255) / 256;   // batches, or 256-row blocks
+    const int n_chunks = static_cast<int>(units < 8 ? units : 8);
+    // operands every chunk needs
+    if (bias_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dBias, a.bias, bias_bytes, cudaMemcpyHostToDevice, s_in));
+    if (by_rows || a.batch_stride_b == 0) NOVA_CUDA_OK(cudaMemcpyAsync(dB, a.B, b_bytes, cudaMemcpyHostToDevice, s_in));
+    for (int c = 0; c < n_chunks; ++c) {
+      const int64_t u0 = units * c / n_chunks, u1 = units * (c + 1) / n_chunks;
+      nova_b200_gemm_args d = a;
+      int64_t a_off, c_off, r_off = 0, b_off = 0;  // element offsets of the chunk
+      size_t a_len, c_len, r_len = 0, b_len = 0;   // bytes of the chunk
+      if (by_batch) {
+        const int64_t nb = u1 - u0;
+        d.batch = nb;
+        a_off = u0 * a.batch_stride_a; c_off = u0 * a.batch_stride_c;
+        a_len = span(nb, a.batch_stride_a, a_rows, a.lda, a_cols) * es;
+        c_len = span(nb, a.batch_stride_c, a.M, a.ldc, a.N) * os;
+        if (a.batch_stride_b != 0) { b_off = u0 * a.batch_stride_b; b_len = span(nb, a.batch_stride_b, b_rows, a.ldb, b_cols) * es; }
+        if (r_bytes) { r_off = u0 * a.batch_stride_r; r_len = span(nb, a.batch_stride_r, a.M, a.ldr, a.N) * os; }
+      } else {
+        const int64_t r0 = u0 * 256, r1 = u1 * 256 < a.M ? u1 * 256 : a.M;
+        d.M = r1 - r0;
+        a_off = r0 * a.lda; c_off = r0 * a.ldc;
+        a_len = span(1, 0, d.M, a.lda, a_cols) * es;
+        c_len = span(1, 0, d.M, a.ldc, a.N) * os;
+        if (r_bytes) { r_off = r0 * a.ldr; r_len = span(1, 0, d.M, a.ldr, a.N) * os; }
+      }
+      NOVA_CUDA_OK(cudaMemcpyAsync(dA + a_off * es, static_cast<const char*>(a.A) + a_off * es, a_len, cudaMemcpyHostToDevice, s_in));
+      if (b_len) NOVA_CUDA_OK(cudaMemcpyAsync(dB + b_off * es, static_cast<const char*>(a.B) + b_off * es, b_len, cudaMemcpyHostToDevice, s_in));
+      if (r_len) NOVA_CUDA_OK(cudaMemcpyAsync(dR + r_off * os, static_cast<const char*>(a.residual) + r_off * os, r_len, cudaMemcpyHostToDevice, s_in));
+      if (c_preload) NOVA_CUDA_OK(cudaMemcpyAsync(dC + c_off * os, static_cast<const char*>(a.C) + c_off * os, c_len, cudaMemcpyHostToDevice, s_in));
+      NOVA_CUDA_OK(cudaEventRecord(ctx->ev_in[c], s_in));
+      NOVA_CUDA_OK(cudaStreamWaitEvent(s_comp, ctx->ev_in[c], 0));
+      d.A = dA + a_off * es;
+      d.B = dB + b_off * es;
+      d.C = dC + c_off * os;
+      d.bias = dBias;
+      d.residual = dR + r_off * os;
+      st = gemm_launch(ctx, &d, s_comp);
+      if (st != NOVA_B200_OK) { cudaDeviceSynchronize(); return st; }
+      NOVA_CUDA_OK(cudaEventRecord(ctx->ev_comp[c], s_comp));
+      NOVA_CUDA_OK(cudaStreamWaitEvent(s_out, ctx->ev_comp[c], 0));
+      NOVA_CUDA_OK(cudaMemcpyAsync(static_cast<char*>(a.C) + c_off * os, dC + c_off * os, c_len, cudaMemcpyDeviceToHost, s_out));
+    }
+    NOVA_CUDA_OK(cudaStreamSynchronize(s_out));
+    NOVA_CUDA_OK(cudaStreamSynchronize(s_in));
+    return NOVA_B200_OK;
+  }
+
   cudaStream_t s = nullptr;
   if (a_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dA, a.A, a_bytes, cudaMemcpyHostToDevice, s));
   if (b_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dB, a.B, b_bytes, cudaMemcpyHostToDevice, s));
   if (bias_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dBias, a.bias, bias_bytes, cudaMemcpyHostToDevice, s));
   if (r_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dR, a.residual, r_bytes, cudaMemcpyHostToDevice, s));
-  if (a.init == NOVA_B200_INIT_FROM_C || a.ldc != a.N || (a.batch > 1 && a.batch_stride_c != a.M * a.ldc))
-    NOVA_CUDA_OK(cudaMemcpyAsync(dC, a.C, c_bytes, cudaMemcpyHostToDevice, s));  // keep bytes the kernel does not write
+  if (c_preload) NOVA_CUDA_OK(cudaMemcpyAsync(dC, a.C, c_bytes, cudaMemcpyHostToDevice, s));  // keep bytes the kernel does not write
   nova_b200_gemm_args d = a;
   d.A = dA; d.B = dB; d.C = dC; d.bias = dBias; d.residual = dR;
   st = gemm_launch(ctx, &d, s);

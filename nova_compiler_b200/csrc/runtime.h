@@ -36,6 +36,9 @@ struct DeviceContext {
   void* staging = nullptr;          // device staging for the *_host entry points
   size_t staging_bytes = 0;
   EncodeTiledFn encode_tiled = nullptr;
+  // the *_host entry points pipeline H2D / kernel / D2H over three streams
+  cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[8] = {}, ev_comp[8] = {};
   std::mutex mu;       // guards scratch
   std::mutex host_mu;  // guards staging (the *_host entry points)
 };
@@ -47,6 +50,7 @@ DeviceContext* current_context(int32_t* status_out);
 // Grows ctx->scratch to at least `bytes` (device-synchronising only when it has to reallocate).
 int32_t ensure_scratch(DeviceContext* ctx, size_t bytes);
 int32_t ensure_staging(DeviceContext* ctx, size_t bytes);
+int32_t ensure_host_streams(DeviceContext* ctx);
 
 inline int dtype_bytes(int32_t dt) {
   switch (dt) {
