@@ -250,25 +250,112 @@ __device__ __forceinline__ uint4 ldg_v4_if(const uint4* ptr, bool pred) {
 }
 
 // The 16 bytes that start `sh` bytes (0..15, a multiple of the element size) into the 32-byte window
-// (lo, hi); bytes at or beyond `nvalid` come back as zero.  Whole words move by selects, the rest by
-// funnel shifts.
-__device__ __forceinline__ uint4 shift_window_16(const uint4& lo, const uint4& hi, int sh, int nvalid) {
-  const uint32_t w[9] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w, 0u};
-  const bool s2 = (sh & 8) != 0, s1 = (sh & 4) != 0;
-  uint32_t b[7], c[5];
-#pragma unroll
-  for (int i = 0; i < 7; ++i) b[i] = s2 ? w[i + 2] : w[i];
-#pragma unroll
-  for (int i = 0; i < 5; ++i) c[i] = s1 ? b[i + 1] : b[i];
+// (lo, hi).  `sh` is warp-uniform where this is called, so the switch does not diverge.
+__device__ __forceinline__ uint4 shift_window_16(const uint4& lo, const uint4& hi, int sh) {
   const uint32_t bs = static_cast<uint32_t>(sh & 3) * 8u;
-  uint32_t o[4];
+  uint4 o;
+  switch (sh >> 2) {
+    case 0:
+      o.x = __funnelshift_r(lo.x, lo.y, bs); o.y = __funnelshift_r(lo.y, lo.z, bs);
+      o.z = __funnelshift_r(lo.z, lo.w, bs); o.w = __funnelshift_r(lo.w, hi.x, bs);
+      break;
+    case 1:
+      o.x = __funnelshift_r(lo.y, lo.z, bs); o.y = __funnelshift_r(lo.z, lo.w, bs);
+      o.z = __funnelshift_r(lo.w, hi.x, bs); o.w = __funnelshift_r(hi.x, hi.y, bs);
+      break;
+    case 2:
+      o.x = __funnelshift_r(lo.z, lo.w, bs); o.y = __funnelshift_r(lo.w, hi.x, bs);
+      o.z = __funnelshift_r(hi.x, hi.y, bs); o.w = __funnelshift_r(hi.y, hi.z, bs);
+      break;
+    default:
+      o.x = __funnelshift_r(lo.w, hi.x, bs); o.y = __funnelshift_r(hi.x, hi.y, bs);
+      o.z = __funnelshift_r(hi.y, hi.z, bs); o.w = __funnelshift_r(hi.z, hi.w, bs);
+      break;
+  }
+  return o;
+}
+
+// zeroes the bytes at or beyond `nvalid` (0..16)
+__device__ __forceinline__ uint4 mask_tail_16(uint4 v, int nvalid) {
+  uint32_t o[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    o[i] = __funnelshift_r(c[i], c[i + 1], bs);
     const int vb = nvalid - 4 * i;  // valid bytes in this word
     o[i] = vb >= 4 ? o[i] : (vb <= 0 ? 0u : (o[i] & ((1u << (8 * vb)) - 1u)));
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+static constexpr int kLoaderUnroll = 8;  // warp tasks whose loads are issued before the first is consumed
+
+// Fills one operand tile of a ring stage from a matrix whose rows are only element-aligned.
+//
+// A warp task is four shared-memory rows x eight 16-byte chunks, lane = (row, chunk).  The four rows are 8
+// apart, so they share the misalignment `sh` of their global address (8 pitches are a multiple of 16 bytes).
+// Each lane loads the 16-byte-ALIGNED chunk that holds the first byte it needs — a warp instruction covers
+// four contiguous 128-byte spans — takes the following aligned chunk from the next lane by shuffle (the row's
+// last chunk loads it itself) and funnel-shifts the pair into place.  kLoaderUnroll tasks are in flight at
+// once.  kInterior: the stage has no row / column / K tail, so nothing is predicated or masked; otherwise an
+// aligned chunk is read only if it holds at least one byte of its row (never a foreign page) and bytes past
+// the matrix are zeroed.
+//   shared-memory row r (128 B): K-major  -> r indexes M (or N), the 128 B span BLOCK_K elements of K
+//                                MN-major -> r = chunk * BLOCK_K + k, the 128 B span one chunk of M (or N)
+template <int kElemBytes, bool kMn, int kBlockK, bool kInterior>
+__device__ __forceinline__ void loader_fill(uint8_t* __restrict__ dst, const uint8_t* __restrict__ gbase, int64_t ld,
+                                            int mn0, int k0, int mn_limit, int k_limit, int total_rows, int wg,
+                                            int lane) {
+  constexpr int kElemsPerChunk = 16 / kElemBytes;
+  constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;
+  const int sub = lane >> 3, ch = lane & 7;
+  const int ntasks = total_rows / 4;
+  const int64_t pitch = ld * kElemBytes;
+  for (int task0 = wg * kLoaderUnroll; task0 < ntasks; task0 += kLoaderWarpsPerGroup * kLoaderUnroll) {
+    uint4 lo[kLoaderUnroll], hi[kLoaderUnroll];
+    int meta[kLoaderUnroll];  // (nvalid << 20) | (sh << 16) | byte offset of the destination chunk
+#pragma unroll
+    for (int u = 0; u < kLoaderUnroll; ++u) {
+      const int task = task0 + u;
+      const bool live = task < ntasks;  // uniform across the warp
+      const int r = (task & 7) + 8 * (4 * (task >> 3) + sub);
+      int64_t outer;  // index along the pitched (outer) global dimension
+      int inner0;     // first index of this lane's chunk along the contiguous global dimension
+      if (!kMn) { outer = mn0 + r; inner0 = k0 + ch * kElemsPerChunk; }
+      else { outer = k0 + (r % kBlockK); inner0 = mn0 + (r / kBlockK) * kElemsPerRow + ch * kElemsPerChunk; }
+      const uint8_t* row_base = gbase + outer * pitch;
+      const uintptr_t ga = reinterpret_cast<uintptr_t>(row_base) + static_cast<uintptr_t>(inner0 * kElemBytes);
+      const int sh = static_cast<int>(ga & 15u);  // identical in all 32 lanes of the task
+      const uint4* p0 = reinterpret_cast<const uint4*>(ga - sh);
+      // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the 128-byte
+      // swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
+      const int sw = (kElemBytes == 4 && kMn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
+      int nvalid = 16;
+      if (kInterior) {
+        lo[u] = ldg_v4_if(p0, live);
+        hi[u] = ldg_v4_if(p0 + 1, live && ch == 7 && sh != 0);
+      } else {
+        const int outer_limit = kMn ? k_limit : mn_limit, inner_limit = kMn ? mn_limit : k_limit;
+        const bool row_ok = live && outer < outer_limit;
+        nvalid = row_ok ? max(0, min(kElemsPerChunk, inner_limit - inner0)) * kElemBytes : 0;
+        const uintptr_t row_end = reinterpret_cast<uintptr_t>(row_base) + static_cast<uintptr_t>(inner_limit) * kElemBytes;
+        lo[u] = ldg_v4_if(p0, row_ok && reinterpret_cast<uintptr_t>(p0) < row_end);
+        hi[u] = ldg_v4_if(p0 + 1, row_ok && ch == 7 && sh != 0 && reinterpret_cast<uintptr_t>(p0 + 1) < row_end);
+      }
+      meta[u] = (nvalid << 20) | (sh << 16) | (r * kSwizzleBytes + (sw << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kLoaderUnroll; ++u) {
+      if (task0 + u >= ntasks) break;  // uniform
+      uint4 nx;
+      nx.x = __shfl_down_sync(0xffffffffu, lo[u].x, 1);
+      nx.y = __shfl_down_sync(0xffffffffu, lo[u].y, 1);
+      nx.z = __shfl_down_sync(0xffffffffu, lo[u].z, 1);
+      nx.w = __shfl_down_sync(0xffffffffu, lo[u].w, 1);
+      if (ch == 7) nx = hi[u];
+      uint4 v = shift_window_16(lo[u], nx, (meta[u] >> 16) & 15);
+      if (!kInterior) v = mask_tail_16(v, meta[u] >> 20);
+      *reinterpret_cast<uint4*>(dst + (meta[u] & 0xffff)) = v;
+    }
+  }
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -465,7 +552,6 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
     // latency overlaps the other groups' work, so several stages are in flight at once.
     const int lw = warp - kFirstLoaderWarp;
     const int group = lw / kLoaderWarpsPerGroup;
-    const int lt = (lw % kLoaderWarpsPerGroup) * 32 + lane;  // 0 .. 32*kLoaderWarpsPerGroup-1
     uint32_t it = 0;
     bool ok = true;
     for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
@@ -494,39 +580,15 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
           //                     MN-major -> rows are grouped per chunk of kElemsPerRow M/N elements:
           //                                 row = chunk * BLOCK_K + k, 128 B span the chunk
           const int total_rows = mn ? (rows_mn / kElemsPerRow) * kBlockK : rows_mn;
-          // One task = half a shared-memory row (64 contiguous bytes of global memory, four 16-byte chunks).
-          // The source is only element-aligned, so a task reads the up to five 16-byte-ALIGNED chunks that
-          // overlap its 64 bytes (all loads issued before any is used) and funnel-shifts them into place.
-          constexpr int kElemsPerHalf = 64 / kElemBytes;
-#pragma unroll 3
-          for (int task = lt; task < total_rows * 2; task += kLoaderWarpsPerGroup * 32) {
-            const int r = task >> 1, half = task & 1;
-            int64_t outer;  // index along the pitched (outer) global dimension
-            int inner0;     // first index along the contiguous global dimension
-            int outer_limit, inner_limit;
-            if (!mn) { outer = mn0 + r; inner0 = k0 + half * kElemsPerHalf; outer_limit = mn_limit; inner_limit = p.K; }
-            else {
-              const int chunk = r / kBlockK, kk = r % kBlockK;
-              outer = k0 + kk; inner0 = mn0 + chunk * kElemsPerRow + half * kElemsPerHalf;
-              outer_limit = p.K; inner_limit = mn_limit;
-            }
-            // bytes of these 64 that lie inside the matrix
-            const int nvalid = outer < outer_limit ? max(0, min(kElemsPerHalf, inner_limit - inner0)) * kElemBytes : 0;
-            const uintptr_t ga = reinterpret_cast<uintptr_t>(gbase + (outer * ld + inner0) * kElemBytes);
-            const int sh = static_cast<int>(ga & 15u);
-            const uint4* p0 = reinterpret_cast<const uint4*>(ga - sh);
-            uint4 w[5];
-#pragma unroll
-            for (int j = 0; j < 5; ++j) w[j] = ldg_v4_if(p0 + j, nvalid > 0 && 16 * j - sh < nvalid);  // chunk holds a valid byte
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const uint4 v = shift_window_16(w[c], w[c + 1], sh, nvalid - 16 * c);
-              const int ch = half * 4 + c;
-              // 16-bit and K-major tiles: 16-byte chunks XOR (row & 7).  32-bit MN-major tiles use the
-              // 128-byte swizzle with 32-byte atoms: the 32-byte pair index XOR (row & 3).
-              const int sw = (kElemBytes == 4 && mn) ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
-              *reinterpret_cast<uint4*>(dst + r * kSwizzleBytes + (sw << 4)) = v;
-            }
+          const int wg = lw % kLoaderWarpsPerGroup;
+          // interior tiles (no row, column or K tail inside this stage) take the predicate-free path
+          const bool interior = mn0 + rows_mn <= mn_limit && k0 + kBlockK <= p.K;
+          if (mn) {
+            if (interior) loader_fill<kElemBytes, true, kBlockK, true>(dst, gbase, ld, mn0, k0, mn_limit, p.K, total_rows, wg, lane);
+            else loader_fill<kElemBytes, true, kBlockK, false>(dst, gbase, ld, mn0, k0, mn_limit, p.K, total_rows, wg, lane);
+          } else {
+            if (interior) loader_fill<kElemBytes, false, kBlockK, true>(dst, gbase, ld, mn0, k0, mn_limit, p.K, total_rows, wg, lane);
+            else loader_fill<kElemBytes, false, kBlockK, false>(dst, gbase, ld, mn0, k0, mn_limit, p.K, total_rows, wg, lane);
           }
         }
         fence_proxy_async_smem();  // make the generic-proxy writes visible to the tensor core (async proxy)
