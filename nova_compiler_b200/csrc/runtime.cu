@@ -106,7 +106,7 @@ int32_t ensure_host_streams(DeviceContext* ctx) {
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking));
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_comp, cudaStreamNonBlocking));
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking));
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < kHostChunks; ++i) {
     NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
     NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_comp[i], cudaEventDisableTiming));
   }
@@ -154,7 +154,7 @@ int32_t nova_b200_shutdown(void) {
     if (c->staging) cudaFree(c->staging);
     if (c->s_in) {
       cudaStreamDestroy(c->s_in); cudaStreamDestroy(c->s_comp); cudaStreamDestroy(c->s_out);
-      for (int i = 0; i < 8; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
+      for (int i = 0; i < kHostChunks; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
     }
   }
   g_contexts.clear();
@@ -237,7 +237,7 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
     if (st != NOVA_B200_OK) return st;
     cudaStream_t s_in = ctx->s_in, s_comp = ctx->s_comp, s_out = ctx->s_out;
     const int64_t units = by_batch ? a.batch : (a.M + 255) / 256;   // batches, or 256-row blocks
-    const int n_chunks = static_cast<int>(units < 8 ? units : 8);
+    const int n_chunks = static_cast<int>(units < kHostChunks ? units : kHostChunks);
     // operands every chunk needs
     if (bias_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dBias, a.bias, bias_bytes, cudaMemcpyHostToDevice, s_in));
     if (by_rows || a.batch_stride_b == 0) NOVA_CUDA_OK(cudaMemcpyAsync(dB, a.B, b_bytes, cudaMemcpyHostToDevice, s_in));

@@ -25,6 +25,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static constexpr int kHostChunks = 8;   // pipeline depth of the *_host entry points
+
 // Per-device state.  One instance per CUDA device the process touched through this library.
 struct DeviceContext {
   int device = -1;
@@ -38,7 +40,7 @@ struct DeviceContext {
   EncodeTiledFn encode_tiled = nullptr;
   // the *_host entry points pipeline H2D / kernel / D2H over three streams
   cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
-  cudaEvent_t ev_in[8] = {}, ev_comp[8] = {};
+  cudaEvent_t ev_in[kHostChunks] = {}, ev_comp[kHostChunks] = {};
   std::mutex mu;       // guards scratch
   std::mutex host_mu;  // guards staging (the *_host entry points)
 };

@@ -404,3 +404,27 @@ def test_nova_matmul_rank_rules(cuda, oracle):
 def test_no_bounded_wait_gave_up(cuda):
     from nova_compiler_b200 import ops
     assert ops.device_status() == 0
+
+
+def test_randomised_small_problems(cuda, oracle):
+    """Seeded random sweep over small extents, dtypes, operand majors, batch forms and epilogues: every
+    combination is one call through the C ABI checked against the oracle."""
+    rng = np.random.default_rng(20261125)
+    dims = list(range(1, 41)) + [63, 64, 65, 127, 128, 129, 255, 256, 257]
+    for trial in range(72):
+        dt = ("f32", "f16", "bf16")[trial % 3]
+        M, N, K = (int(rng.choice(dims)) for _ in range(3))
+        B = int(rng.choice([1, 1, 2, 3]))
+        ta, tb = bool(rng.integers(2)), bool(rng.integers(2))
+        shared_b = B > 1 and bool(rng.integers(2))
+        init = ("zero", "bias", "residual")[int(rng.integers(3))]
+        act = (None, "relu", "gelu")[int(rng.integers(3))]
+        a = rand_bits(oracle, rng, (B, K, M) if ta else (B, M, K), dt)
+        b = rand_bits(oracle, rng, ((N, K) if tb else (K, N)) if shared_b else ((B, N, K) if tb else (B, K, N)), dt)
+        bias = rand_bits(oracle, rng, (N,), dt) if init == "bias" else None
+        res = rand_bits(oracle, rng, (B, M, N), dt) if init == "residual" else None
+        want = oracle.gemm(a, b, dtype_in=dt, trans_a=ta, trans_b=tb, bias=bias, residual=res,
+                           act={"gelu": "gelu_tanh"}.get(act, act or "none"))
+        got = run_gpu(cuda, a, b if not shared_b else b[None], dt, trans_a=ta, trans_b=tb, bias=bias, residual=res, act=act)
+        err = oracle.rel_fro(oracle.from_bits(got, dt), oracle.from_bits(want, dt))
+        assert err <= TOL[dt], f"trial {trial}: {dt} B={B} M={M} N={N} K={K} ta={ta} tb={tb} shared_b={shared_b} {init} {act}: {err:.3e}"
