@@ -47,7 +47,11 @@ WORKLOADS = {
 }
 # DRAM bytes one launch moves according to ncu (dram__bytes_read.sum + dram__bytes_write.sum), per workload;
 # see profiles/.  None where no capture exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "c2": 173.7e6,      # 134.3 MB read + 39.4 MB written (part of the 67 MB output is still in L2 at kernel end)
+    "c3": 468.5e6,      # 308.0 MB read + 160.5 MB written
+    "c4": 8 * 243.4e6,  # captured on 32 of the 256 batches (c4s), scaled by 8: traffic is proportional to batches
+}
 
 
 def load_peaks():
@@ -330,7 +334,11 @@ def run_gpu(args):
         roof.update({"traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": f"{src} (cuBLAS bf16 burst / copy bandwidth)",
                      "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": byts,
                      "kernel_ms": ms_step, "frac_of_nominal_bf16_2250": per_gpu / NOMINAL_BF16_TFLOPS})
-        launches_per_step = 2 if dab == "f32" else 1  # f32: the hi/lo split kernel + the contraction
+        # the contraction, plus one launch when operands go through scratch first (the f32 hi/lo split, or the
+        # re-pitched copy of operands whose pitch no tensor map can describe)
+        info = L.GemmPlanInfo()
+        L.check(lib.nova_b200_gemm_plan(C.byref(g), C.byref(info)))
+        launches_per_step = 2 if info.scratch_bytes > 0 else 1
         line = {
             "metric": "batch-matmul/linear TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,

@@ -118,14 +118,15 @@ typedef struct nova_b200_gemm_args {
 
 /* How a call will be executed; filled by nova_b200_gemm_plan without launching anything. */
 typedef struct nova_b200_gemm_plan_info {
-  int32_t loader_a;     /* 0 = TMA, 1 = predicated ld.global loader (unaligned base or pitch) */
+  int32_t loader_a;     /* 0 = TMA; unaligned base or pitch: 1 = predicated ld.global loader warps,
+                           2 = re-pitched into aligned scratch first, then TMA (contractions of a few GFLOP or more) */
   int32_t loader_b;
   int32_t store_c;      /* 0 = TMA stores of swizzled 32x128-byte boxes, 1 = element stores (unaligned C) */
   int32_t block_m, block_n, block_k;
   int32_t stages;
   int32_t grid;         /* persistent CTAs launched */
   int64_t tiles;        /* output tiles over all batches */
-  int64_t scratch_bytes;/* device scratch the call uses (hi/lo split of f32 operands), else 0 */
+  int64_t scratch_bytes;/* device scratch the call uses (hi/lo split of f32 operands, re-pitched copies), else 0 */
 } nova_b200_gemm_plan_info;
 
 /* Binds the calling thread's current device (or `device` >= 0) : checks compute capability 10.x,

@@ -1,6 +1,6 @@
 """Builds libnova_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m nova_compiler_b200.build [--force] [--verbose]
+    python -m nova_compiler_b200.build [--force] [--verbose] [--trace]
 
 The library is a plain shared object with `extern "C"` entry points (include/nova_b200.h);
 it does not link against torch.  nvcc cross-compiles without a GPU present.
@@ -32,8 +32,12 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """trace=True compiles the kernels' role timelines in (NOVA_B200_TRACE=<file> then dumps them); such a
+    build is a few percent slower and is for diagnosis only."""
     headers = [os.path.join(CSRC, h) for h in HEADERS]
+    flags = NVCC_FLAGS + (["-DNOVA_B200_TRACE_BUILD"] if trace else [])
+    force = force or trace
     objs = []
     jobs = []
     for src in SOURCES:
@@ -41,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(CSRC, os.path.splitext(src)[0] + ".o")
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = ["nvcc", *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = ["nvcc", *flags, "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -59,4 +63,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -48,7 +48,9 @@ struct GemmKernelParams {
   uint32_t a_desc_lbo, b_desc_lbo;    // leading-byte-offset field, already shifted into bits 16..29
   uint32_t a_kstep, b_kstep;          // bytes the descriptor start address advances per UMMA K step
   int32_t loader_a, loader_b;         // 0 = TMA, 1 = ld.global loader warps
-  int32_t ring_stages;                // pair kernel: ring stages in use
+  // optional timeline (null unless the host asked for one): kTraceSlots clock64 samples per tile for the
+  // first kTraceTiles tiles of every CTA
+  long long* trace;
   // raw operand views for the ld.global loader
   const void* A; const void* B;
   int64_t lda, ldb, stride_a, stride_b;
@@ -82,6 +84,43 @@ struct GemmSmemLayout {
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_field, uint32_t hi) {
   return (static_cast<uint64_t>(hi) << 32) | static_cast<uint64_t>(lbo_field | ((addr >> 4) & 0x3fffu));
+}
+
+// Role timelines are compiled in only by a diagnostic build (-DNOVA_B200_TRACE_BUILD): even a never-taken
+// branch around a clock read in the producer and MMA loops costs a few percent of the tensor rate.
+#ifdef NOVA_B200_TRACE_BUILD
+static constexpr bool kTraceEnabled = true;
+#else
+static constexpr bool kTraceEnabled = false;
+#endif
+static constexpr int kTraceTiles = 16;
+static constexpr int kTraceSlots = 40;
+enum TraceSlot : int {
+  kTraceProducerFirst = 0,  // producer: first stage of the tile may be refilled
+  kTraceProducerLast = 1,   // producer: last load of the tile issued
+  kTraceMmaStart = 2,       // MMA issuer: accumulator free
+  kTraceMmaFirstFull = 3,   // MMA issuer: first stage of the tile has landed
+  kTraceMmaCommit = 4,      // MMA issuer: accumulator commit issued
+  kTraceEpiStart = 5,       // first epilogue warp: accumulator complete
+  kTraceEpiEnd = 6,         // first epilogue warp: accumulator released
+  kTraceKernel = 7,         // tile 0: kernel entry; tile 1: roles start; tile 2: teardown
+  kTraceMmaFullWait = 8,    // MMA issuer: cycles spent waiting for stages to land, this tile
+  kTraceProducerWait = 9,   // producer: cycles spent waiting for free stages, this tile
+  kTraceEpiStoreWait = 10,  // first epilogue warp: cycles spent waiting for staging boxes to be read out
+  kTraceEpiTmemWait = 11,   // first epilogue warp: cycles spent waiting for tensor-memory loads
+  kTraceEpiMath = 12,       // first epilogue warp: cycles in arithmetic and staging writes
+  kTraceEpiFence = 13,      // first epilogue warp: cycles in the proxy fence and warp barrier
+  kTraceEpiIssue = 14,      // first epilogue warp: cycles issuing the bulk store
+  kTraceEpiWarpStart = 16,  // + epilogue warp index: that warp saw the accumulator complete
+  kTraceEpiWarpEnd = 24,    // + epilogue warp index: that warp released the accumulator
+};
+__device__ __forceinline__ void trace_value(const long long* base, uint32_t tile_iter, int slot, long long v) {
+  if (kTraceEnabled && base != nullptr && tile_iter < static_cast<uint32_t>(kTraceTiles))
+    const_cast<long long*>(base)[(static_cast<size_t>(blockIdx.x) * kTraceTiles + tile_iter) * kTraceSlots + slot] = v;
+}
+__device__ __forceinline__ void trace_mark(const long long* base, uint32_t tile_iter, int slot) {
+  if (kTraceEnabled && base != nullptr && tile_iter < static_cast<uint32_t>(kTraceTiles))
+    const_cast<long long*>(base)[(static_cast<size_t>(blockIdx.x) * kTraceTiles + tile_iter) * kTraceSlots + slot] = clock64();
 }
 
 struct TileCoord {
@@ -192,10 +231,12 @@ __device__ __forceinline__ void epilogue_stage(uint8_t* box, const float (&v)[32
 }
 
 // One epilogue warp drains kCols columns of its 32 accumulator rows, one 128-byte-wide box at a time.
-template <typename OutT, int kCols>
+// kBoxes staging boxes per warp: with two, the TMA store of one box overlaps the whole of the next; with
+// one, it overlaps only the next box's first tensor-memory load and its arithmetic.
+template <typename OutT, int kCols, int kBoxes = 2>
 __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const CUtensorMap* tmap_c, uint32_t taddr,
                                               uint8_t* staging, uint32_t& box_iter, int lane, int32_t batch,
-                                              int32_t row0, int32_t n0) {
+                                              int32_t row0, int32_t n0, long long* waits = nullptr) {
   constexpr int kColsPerBox = kSwizzleBytes / static_cast<int>(sizeof(OutT));  // 64 (16-bit) or 32 (f32)
   constexpr int kLoadsPerBox = kColsPerBox / 32;
   constexpr int kChunkStep = 32 * static_cast<int>(sizeof(OutT)) / 16;  // 16-byte chunks per 32 columns
@@ -205,28 +246,41 @@ __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const C
   for (int c = 0; c < kCols / kColsPerBox; ++c) {
     const int32_t col0 = n0 + c * kColsPerBox;
     if (col0 >= p.N) break;  // uniform across the warp
-    uint8_t* box = staging + (box_iter & 1u) * (32 * kSwizzleBytes);
-    if (p.vec_store) {
-      // the box written two iterations ago must have been read out by its TMA store
-      if (lane == 0) tma_store_wait_read<1>();
-      __syncwarp();
-    }
+    uint8_t* box = staging + (kBoxes == 2 ? (box_iter & 1u) : 0u) * (32 * kSwizzleBytes);
 #pragma unroll
     for (int h = 0; h < kLoadsPerBox; ++h) {
       uint32_t r[32];
+      long long t0 = 0;
+      if (waits) t0 = clock64();
       tmem_ld_32x32(taddr + c * kColsPerBox + h * 32, r);
       tmem_ld_wait();
+      if (waits) waits[1] += clock64() - t0;
       float v[32];
+      if (waits) t0 = clock64();
       epilogue_math<OutT>(p, r, v, batch, row, col0 + h * 32, row_ok);
+      if (waits) waits[2] += clock64() - t0;
+      if (h == 0 && p.vec_store) {
+        // the TMA store that last used this box must have read it out
+        if (waits) t0 = clock64();
+        if (lane == 0) tma_store_wait_read<kBoxes - 1>();
+        __syncwarp();
+        if (waits) waits[0] += clock64() - t0;
+      }
+      if (waits) t0 = clock64();
       epilogue_stage<OutT>(box, v, lane, h * kChunkStep);
+      if (waits) waits[2] += clock64() - t0;
     }
     if (p.vec_store) {
+      long long t1 = 0;
+      if (waits) t1 = clock64();
       fence_proxy_async_smem();
       __syncwarp();
+      if (waits) { const long long t2 = clock64(); waits[3] += t2 - t1; t1 = t2; }
       if (lane == 0) {
         tma_store_3d(tmap_c, smem_u32(box), col0, row0, batch);  // rows >= M and columns >= N are clipped
         tma_store_commit();
       }
+      if (waits) waits[4] += clock64() - t1;
     } else {
       __syncwarp();
       epilogue_store_rows<OutT>(p, box, lane, batch, row0, col0);
@@ -644,6 +698,39 @@ __global__ void nova_split_tf32_kernel(const SplitOperand oa, const SplitOperand
     }
     o.hi[i] = h;
     o.lo[i] = l;
+  }
+}
+
+// Re-pitch: copies an operand whose base or row pitch is not a multiple of 16 bytes (so no tensor map can
+// describe it) into [batch, rows, ld_out] scratch whose pitch is, one 16-byte chunk per thread.  Source reads
+// are element-wise (consecutive threads read consecutive 16-byte spans of a row, so every sector is still
+// fetched once); columns past `cols` are written as zeros.  blockIdx.y == 0 handles oa, 1 handles ob (rows_total
+// == 0 skips an operand).
+struct RepitchOperand {
+  const void* src;
+  void* dst;
+  int64_t rows_total, ld_in, stride_in;  // elements
+  int32_t rows_per_batch, cols, ld_out;
+};
+
+template <typename ElemT>
+__global__ void nova_repitch_kernel(const RepitchOperand oa, const RepitchOperand ob) {
+  constexpr int kPerChunk = 16 / static_cast<int>(sizeof(ElemT));
+  const RepitchOperand& o = blockIdx.y == 0 ? oa : ob;
+  const int32_t chunks_per_row = o.ld_out / kPerChunk;
+  const int64_t n = o.rows_total * chunks_per_row;
+  const ElemT* src = static_cast<const ElemT*>(o.src);
+  uint4* dst = static_cast<uint4*>(o.dst);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / chunks_per_row;
+    const int32_t c0 = static_cast<int32_t>(i - r * chunks_per_row) * kPerChunk;
+    const int64_t b = r / o.rows_per_batch;
+    const ElemT* row = src + b * o.stride_in + (r - b * o.rows_per_batch) * o.ld_in + c0;
+    union { uint4 u; ElemT e[kPerChunk]; } v;
+#pragma unroll
+    for (int e = 0; e < kPerChunk; ++e) v.e[e] = c0 + e < o.cols ? __ldg(row + e) : ElemT(0);
+    dst[i] = v.u;
   }
 }
 

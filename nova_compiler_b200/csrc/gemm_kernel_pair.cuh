@@ -12,7 +12,7 @@
 //                 peer's TMA loads count their bytes on it (cp.async.bulk.tensor ... cta_group::2).
 //   empty[s]      one per CTA; tcgen05.commit from the leader arrives on both (an arrival, no data).
 //   tmem_full[a]  one per CTA; same commit-to-both.
-//   tmem_empty[a] lives in the leader; the 4 epilogue warps of each CTA arrive on it (8 arrivals).
+//   tmem_empty[a] lives in the leader; every epilogue warp of both CTAs arrives on it.
 //
 // Used when both operands can be loaded with TMA and the problem has at least a wave of 256 x 256 tiles;
 // everything else runs the single-CTA kernel of gemm_kernel.cuh.
@@ -25,8 +25,13 @@ static constexpr int kPairBlockM = 256;  // rows per pair tile (128 per CTA)
 static constexpr int kPairBlockN = 256;  // columns per pair tile (each CTA loads 128 of them)
 static constexpr int kPairSubK = 2;     // 64-element K sub-blocks per ring stage: one barrier round trip per 128 K
 static constexpr int kPairStages = 3;
+static constexpr int kPairEpilogueWarps = 4;  // 8 (one staging box each) measured the same on every shape
 
+// kEpiWarps epilogue warps per CTA (4 or 8).  The staging area is the same 32 KB either way: two boxes per
+// warp for four warps, one box per warp for eight.
+template <int kEpiWarps>
 struct PairSmemLayout {
+  static constexpr int kBoxesPerWarp = 8 / kEpiWarps;
   static constexpr int kATile = kBlockM * kSwizzleBytes;             // 16 KB: this CTA's 128 rows
   static constexpr int kBTile = (kPairBlockN / 2) * kSwizzleBytes;   // 16 KB: this CTA's 128 columns
   static constexpr int kStageBytes = kPairSubK * (kATile + kBTile);
@@ -34,7 +39,7 @@ struct PairSmemLayout {
   static constexpr int kNumBarriers = 2 * kPairStages + 4;
   static constexpr int kStageOutBox = 32 * kSwizzleBytes;
   static constexpr int kStagingOffset = kRingBytes;
-  static constexpr int kStagingBytes = kNumEpilogueWarps * 2 * kStageOutBox;
+  static constexpr int kStagingBytes = kEpiWarps * kBoxesPerWarp * kStageOutBox;
   static constexpr int kBarrierOffset = kStagingOffset + kStagingBytes;
   static constexpr int kMiscOffset = kBarrierOffset + 8 * kNumBarriers;
   static constexpr int kTotalBytes = kMiscOffset + 16;
@@ -43,11 +48,12 @@ struct PairSmemLayout {
 
 // kElemBytes: 2 (f16/bf16) or 4 (f32 as single-pass tf32).  kAMn / kBMn as in the single-CTA kernel.
 // p.m_blocks counts 256-row blocks, p.n_blocks 256-column blocks.
-template <int kElemBytes, bool kAMn, bool kBMn>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsTma, 1)
+template <int kElemBytes, bool kAMn, bool kBMn, int kEpiWarps>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (kFirstEpilogueWarp + kEpiWarps), 1)
 nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ CUtensorMap tmap_c, const GemmKernelParams p) {
-  using L = PairSmemLayout;
+  using L = PairSmemLayout<kEpiWarps>;
+  static_assert(kEpiWarps == 4 || kEpiWarps == 8, "one or two epilogue warps per tensor-memory lane quarter");
   constexpr int kStages = kPairStages;
   constexpr int kElemsPerRow = kSwizzleBytes / kElemBytes;
   constexpr int kSubBlockK = kElemsPerRow;           // K elements per 128-byte row
@@ -74,6 +80,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  if (threadIdx.x == 0) trace_mark(p.trace, 0, kTraceKernel);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -82,7 +89,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 2 * kNumEpilogueWarps);  // used in the leader only
+      mbar_init(tmem_empty_bar(a), 2 * kEpiWarps);  // used in the leader only
     }
     *abort_flag = 0u;
     fence_mbar_init();
@@ -98,6 +105,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  if (threadIdx.x == 0) trace_mark(p.trace, 1, kTraceKernel);
 
   if (warp == 0) {
     // ============================================================ TMA producer (one per CTA)
@@ -105,16 +113,21 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
       uint32_t it = 0;
+      uint32_t tile_iter = 0;
       bool ok = true;
-      for (int32_t tile = pair; ok && tile < p.tiles; tile += num_pairs) {
+      for (int32_t tile = pair; ok && tile < p.tiles; tile += num_pairs, ++tile_iter) {
         const TileCoord t = decode_tile(p, tile);
         const int m0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM;
         const int n0 = t.n_blk * kPairBlockN + static_cast<int>(rank) * kHalfN;
         const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
+        long long waited = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
+          const long long w0 = (kTraceEnabled && p.trace) ? clock64() : 0;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, kStatusProducerEmptyWait)) { ok = false; break; }
+          if (kTraceEnabled && p.trace) waited += clock64() - w0;
+          if (kb == 0) trace_mark(p.trace, tile_iter, kTraceProducerFirst);
           const uint32_t stage = smem_base + s * L::kStageBytes;
           if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2u * L::kStageBytes);
           const uint32_t bar = map_to_cta(full_bar(s), 0u);  // the leader's barrier counts both CTAs' bytes
@@ -139,6 +152,8 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             }
           }
         }
+        trace_mark(p.trace, tile_iter, kTraceProducerLast);
+        trace_value(p.trace, tile_iter, kTraceProducerWait, waited);
       }
     }
     __syncwarp();
@@ -153,11 +168,20 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         const uint32_t acc_ph = (tile_iter >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, abort_flag, p.status, kStatusMmaTmemEmptyWait)) break;
         tc_fence_after_sync();
+        trace_mark(p.trace, tile_iter, kTraceMmaStart);
         const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
+        long long waited = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
+          const long long w0 = (kTraceEnabled && p.trace) ? clock64() : 0;
           if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, kStatusMmaFullWait)) { ok = false; break; }
+          if (kTraceEnabled && p.trace) {
+            const long long w = clock64() - w0;
+            waited += w;
+            if (kb < 8) trace_value(p.trace, tile_iter, kTraceEpiWarpStart + kb, w);
+          }
+          if (kb == 0) trace_mark(p.trace, tile_iter, kTraceMmaFirstFull);
           tc_fence_after_sync();
 #pragma unroll
           for (int sub = 0; sub < kPairSubK; ++sub) {
@@ -175,13 +199,17 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
           umma_commit_pair(empty_bar(s), 3);  // both CTAs may refill their halves of this stage
         }
         if (ok) umma_commit_pair(tmem_full_bar(acc), 3);  // both CTAs' epilogues may drain
+        trace_mark(p.trace, tile_iter, kTraceMmaCommit);
+        trace_value(p.trace, tile_iter, kTraceMmaFullWait, waited);
       }
     }
     __syncwarp();
   } else {
     // ============================================================ epilogue (both CTAs)
     const int q = warp & 3;
-    uint8_t* staging = smem_gen + L::kStagingOffset + (warp - kFirstEpilogueWarp) * (2 * L::kStageOutBox);
+    constexpr int kColsPerWarp = kPairBlockN / (kEpiWarps / 4);
+    const int cg = (warp - kFirstEpilogueWarp) >> 2;  // which column group of the CTA's 256 columns this warp drains
+    uint8_t* staging = smem_gen + L::kStagingOffset + (warp - kFirstEpilogueWarp) * (L::kBoxesPerWarp * L::kStageOutBox);
     if (p.vec_store && lane == 0) tma_prefetch_desc(&tmap_c);
     uint32_t tile_iter = 0;
     uint32_t box_iter = 0;
@@ -190,19 +218,35 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       const uint32_t acc = tile_iter & 1u;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(tmem_full_bar(acc), acc_ph, abort_flag, p.status, kStatusEpilogueTmemFullWait)) break;
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_mark(p.trace, tile_iter, kTraceEpiStart);
       tc_fence_after_sync();
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_mark(p.trace, tile_iter, 35);
       const int32_t row0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM + q * 32;
-      const int32_t n0 = t.n_blk * kPairBlockN;
-      const uint32_t taddr = tmem_base + acc * kPairBlockN + (static_cast<uint32_t>(q * 32) << 16);
+      const int32_t n0 = t.n_blk * kPairBlockN + cg * kColsPerWarp;
+      const uint32_t taddr = tmem_base + acc * kPairBlockN + cg * kColsPerWarp + (static_cast<uint32_t>(q * 32) << 16);
+      long long waits[5] = {0, 0, 0, 0, 0};
+      long long* wp = (kTraceEnabled && p.trace != nullptr && warp == kFirstEpilogueWarp) ? waits : nullptr;
       if (p.out_dtype == NOVA_B200_BF16)
-        epilogue_tile<__nv_bfloat16, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__nv_bfloat16, kColsPerWarp, L::kBoxesPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0, wp);
       else if (p.out_dtype == NOVA_B200_F16)
-        epilogue_tile<__half, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__half, kColsPerWarp, L::kBoxesPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0, wp);
       else
-        epilogue_tile<float, kPairBlockN>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<float, kColsPerWarp, L::kBoxesPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0, wp);
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_mark(p.trace, tile_iter, 32);
       tc_fence_before_sync();
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_mark(p.trace, tile_iter, 33);
       __syncwarp();
+      if (warp == kFirstEpilogueWarp && lane == 0) trace_mark(p.trace, tile_iter, 34);
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0u));
+      if (lane == 0) trace_mark(p.trace, tile_iter, kTraceEpiWarpEnd + warp - kFirstEpilogueWarp);
+      if (warp == kFirstEpilogueWarp && lane == 0) {
+        trace_mark(p.trace, tile_iter, kTraceEpiEnd);
+        trace_value(p.trace, tile_iter, kTraceEpiStoreWait, waits[0]);
+        trace_value(p.trace, tile_iter, kTraceEpiTmemWait, waits[1]);
+        trace_value(p.trace, tile_iter, kTraceEpiMath, waits[2]);
+        trace_value(p.trace, tile_iter, kTraceEpiFence, waits[3]);
+        trace_value(p.trace, tile_iter, kTraceEpiIssue, waits[4]);
+      }
     }
     if (p.vec_store && lane == 0) tma_store_wait_all<0>();
     __syncwarp();
@@ -211,6 +255,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   // ------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark(p.trace, 2, kTraceKernel);
   if (*abort_flag != 0u && threadIdx.x == 0) {
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // let in-flight bulk copies land
   }

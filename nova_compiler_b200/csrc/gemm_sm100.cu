@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <vector>
 #include <cstring>
 
 #include "gemm_kernel.cuh"
@@ -21,6 +22,7 @@ struct Plan {
   bool empty = false;
   bool pair = false;  // CTA-pair kernel (cta_group::2, 256 x 256 tiles)
   bool short_k = false;  // contraction so short that the epilogue dominates: 8 epilogue warps, 3 stages
+  int64_t repitch_a_ld = 0, repitch_b_ld = 0;  // > 0: the operand is first copied to scratch with this pitch
 };
 
 constexpr int64_t kMaxExtent = (1ll << 31) - 1;
@@ -90,6 +92,29 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     pi.loader_a = tma_ok(a->A, a->lda, a->batch_stride_a) ? 0 : 1;
     pi.loader_b = tma_ok(a->B, a->ldb, a->batch_stride_b) ? 0 : 1;
     pi.scratch_bytes = 0;
+    // An operand no tensor map can describe is either read by the loader warps (no extra traffic, but the
+    // mainloop then runs at a fraction of the tensor rate) or first re-pitched into aligned scratch (one extra
+    // read and write of the operand, then the full-rate TMA kernels).  The copy wins once the contraction is
+    // large against the operand: from a few GFLOP on.
+    const double flops = 2.0 * static_cast<double>(a->batch) * a->M * a->N * a->K;
+    bool repitch = (pi.loader_a || pi.loader_b) && flops >= 4.0e9;
+    if (const char* e = std::getenv("NOVA_B200_REPITCH")) repitch = (pi.loader_a || pi.loader_b) && std::atoi(e) != 0;
+    if (repitch) {
+      const int per_chunk = 16 / es;
+      const int64_t a_rows = a->trans_a ? a->K : a->M, a_cols = a->trans_a ? a->M : a->K;
+      const int64_t b_rows = a->trans_b ? a->N : a->K, b_cols = a->trans_b ? a->K : a->N;
+      const int64_t a_b = a->batch_stride_a == 0 ? 1 : a->batch, b_b = a->batch_stride_b == 0 ? 1 : a->batch;
+      if (pi.loader_a) {
+        plan->repitch_a_ld = (a_cols + per_chunk - 1) / per_chunk * per_chunk;
+        pi.scratch_bytes += (a_b * a_rows * plan->repitch_a_ld * es + 255) / 256 * 256;
+        pi.loader_a = 2;
+      }
+      if (pi.loader_b) {
+        plan->repitch_b_ld = (b_cols + per_chunk - 1) / per_chunk * per_chunk;
+        pi.scratch_bytes += (b_b * b_rows * plan->repitch_b_ld * es + 255) / 256 * 256;
+        pi.loader_b = 2;
+      }
+    }
   }
   const int osz = plan->out_bytes;
   const bool c_vec = reinterpret_cast<uintptr_t>(a->C) % 16 == 0 && (a->ldc * osz) % 16 == 0 &&
@@ -99,40 +124,50 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   pi.block_m = kBlockM;
   pi.block_k = kSwizzleBytes / es;
   const int64_t m_blocks = (a->M + kBlockM - 1) / kBlockM;
-  // 256-wide tiles halve the A re-reads and use the whole of tensor memory; fall back to 128 when
-  // the problem would not even fill one wave of SMs with them.
+  // Tile shape.  Three candidates: 128 x 128 and 128 x 256 tiles on single CTAs (one per SM), 256 x 256 tiles on
+  // CTA pairs (one per two SMs).  Each is priced as waves x (cycles of one tile's K loop) + the part of a launch
+  // that does not overlap (launch, first loads, last epilogue), with constants fitted to B200 timings: every
+  // shape streams at 8.5-9.3 cycles per K element per wave (a 128 x 128 tile is bound by shared-memory reads,
+  // not by the tensor pipe, so it is no faster than a 128 x 256 one), never faster than its epilogue drains a
+  // tile; pairs stream ~7 % faster and cost a cluster launch and cluster barriers up front.
+  const int sms = sm_count > 0 ? sm_count : 148;
+  const bool both_tma = pi.loader_a != 1 && pi.loader_b != 1;
+  const int64_t n128 = (a->N + 127) / 128, n256 = (a->N + 255) / 256;
+  const int64_t tiles128 = a->batch * m_blocks * n128, tiles256 = a->batch * m_blocks * n256;
+  const int64_t pair_tiles = a->batch * ((a->M + kPairBlockM - 1) / kPairBlockM) * ((a->N + kPairBlockN - 1) / kPairBlockN);
+  auto waves = [](int64_t tiles, int64_t slots) { return static_cast<double>((tiles + slots - 1) / slots); };
+  const double kd = static_cast<double>(a->K);
+  const double cost128 = waves(tiles128, sms) * std::max(9.3 * kd, 3000.0) + 11000.0;
+  // (the short-K build below drains a 128 x 256 tile with eight warps)
+  const double drain256 = (a->K <= 256 && pi.store_c == 0) ? 3900.0 : 6000.0;
+  const double cost256 = waves(tiles256, sms) * std::max(9.1 * kd, drain256) + 11800.0;
+  const double cost_pair = waves(pair_tiles, sms / 2) * std::max(8.5 * kd, 5000.0) + 13100.0;
+  // (contractions shorter than two 128-element stages are bound by their epilogue, which pairs do not help)
+  bool pair = plan->terms == 1 && both_tma && a->K >= 256 && cost_pair <= cost128 && cost_pair <= cost256;
   int block_n = 256;
-  if (plan->terms == 3) block_n = 128;
+  if (plan->terms == 3) block_n = 128;  // two operand copies per stage: 256-wide stages do not fit
   else if (a->N <= 128) block_n = 128;
-  else {
-    const int64_t tiles256 = a->batch * m_blocks * ((a->N + 255) / 256);
-    if (tiles256 < (sm_count > 0 ? sm_count : 148)) block_n = 128;
-  }
+  else if (both_tma && plan->terms == 1) block_n = cost128 < cost256 ? 128 : 256;
+  else if (tiles256 < sms) block_n = 128;  // loader warps: keep every SM's loaders busy
   if (const char* e = std::getenv("NOVA_B200_BLOCK_N")) {
     const int v = std::atoi(e);
-    if ((v == 128 || v == 256) && plan->terms != 3) block_n = v;
+    if ((v == 128 || v == 256) && plan->terms != 3) { block_n = v; pair = false; }
+  }
+  if (const char* e = std::getenv("NOVA_B200_PAIR")) {
+    const int v = std::atoi(e);
+    if (v == 0) pair = false;
+    else pair = plan->terms == 1 && both_tma && a->K >= 256;
   }
   pi.block_n = block_n;
-  const int64_t n_blocks = (a->N + block_n - 1) / block_n;
-  const int64_t tiles = a->batch * m_blocks * n_blocks;
+  const int64_t tiles = block_n == 256 ? tiles256 : tiles128;
   if (tiles > kMaxExtent) return fail(NOVA_B200_ERR_TOO_LARGE, "gemm: more than 2^31-1 output tiles");
   pi.tiles = tiles;
   pi.stages = plan->terms == 3 ? 3 : (block_n == 256 ? 4 : 6);
-  const int sms = sm_count > 0 ? sm_count : 148;
   pi.grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
-  // CTA pairs (two SMs per 256 x 256 tile) when both operands stream through TMA and there is at least
-  // one wave of pair tiles; smaller problems keep more SMs busy with single-CTA tiles.
-  const int64_t pair_tiles = a->batch * ((a->M + kPairBlockM - 1) / kPairBlockM) * ((a->N + kPairBlockN - 1) / kPairBlockN);
-  // (contractions shorter than two 128-element stages are bound by their epilogue, which pairs do not help)
-  bool pair = plan->terms == 1 && !pi.loader_a && !pi.loader_b && pair_tiles >= sms / 2 && a->K >= 256;
-  if (const char* e = std::getenv("NOVA_B200_PAIR")) {
-    if (std::atoi(e) == 0) pair = false;
-  }
   plan->pair = pair;
   // K <= 256 with full-width tiles: the mainloop of a tile is at most four k-blocks, the time goes into
   // draining 128 x 256 accumulators, so trade one ring stage for a second set of epilogue warps.
-  plan->short_k = !pair && plan->terms == 1 && !pi.loader_a && !pi.loader_b && block_n == 256 && a->K <= 256 &&
-                  pi.store_c == 0;
+  plan->short_k = !pair && plan->terms == 1 && both_tma && block_n == 256 && a->K <= 256 && pi.store_c == 0;
   if (const char* e = std::getenv("NOVA_B200_SHORT_K")) {
     if (std::atoi(e) == 0) plan->short_k = false;
   }
@@ -200,20 +235,22 @@ int32_t launch_single_term(bool loader, bool a_mn, bool b_mn, const CUtensorMap*
   return launch_majors<kBlockN, kElemBytes, 1, kStages, false, 4>(a_mn, b_mn, maps, p, grid, st);
 }
 
-template <int kElemBytes, bool kAMn, bool kBMn>
+template <int kElemBytes, bool kAMn, bool kBMn, int kEpiWarps>
 int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p, int sm_count, cudaStream_t st) {
-  auto kernel = nova_gemm_sm100_pair_kernel<kElemBytes, kAMn, kBMn>;
+  constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpiWarps);
+  using PairSmem = PairSmemLayout<kEpiWarps>;
+  auto kernel = nova_gemm_sm100_pair_kernel<kElemBytes, kAMn, kBMn, kEpiWarps>;
   static thread_local int configured_device = -1;
   static thread_local int max_pairs = 0;
   int dev = 0;
   NOVA_CUDA_OK(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmemLayout::kDynamicBytes));
+    NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kDynamicBytes));
     // how many 2-CTA clusters of this kernel can be resident at once (GPCs with an odd SM count strand one SM)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(sm_count & ~1), 1, 1);
-    cfg.blockDim = dim3(kThreadsTma, 1, 1);
-    cfg.dynamicSmemBytes = PairSmemLayout::kDynamicBytes;
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = PairSmem::kDynamicBytes;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
@@ -229,18 +266,18 @@ int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p,
     configured_device = dev;
   }
   const int pairs = p.tiles < max_pairs ? p.tiles : max_pairs;
-  kernel<<<2 * pairs, kThreadsTma, PairSmemLayout::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], p);
+  kernel<<<2 * pairs, kThreads, PairSmem::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], p);
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }
 
-template <int kElemBytes>
+template <int kElemBytes, int kEpiWarps>
 int32_t launch_pair_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int sm_count,
                            cudaStream_t st) {
-  if (!a_mn && b_mn) return launch_pair_instance<kElemBytes, false, true>(maps, p, sm_count, st);
-  if (!a_mn && !b_mn) return launch_pair_instance<kElemBytes, false, false>(maps, p, sm_count, st);
-  if (a_mn && b_mn) return launch_pair_instance<kElemBytes, true, true>(maps, p, sm_count, st);
-  return launch_pair_instance<kElemBytes, true, false>(maps, p, sm_count, st);
+  if (!a_mn && b_mn) return launch_pair_instance<kElemBytes, false, true, kEpiWarps>(maps, p, sm_count, st);
+  if (!a_mn && !b_mn) return launch_pair_instance<kElemBytes, false, false, kEpiWarps>(maps, p, sm_count, st);
+  if (a_mn && b_mn) return launch_pair_instance<kElemBytes, true, true, kEpiWarps>(maps, p, sm_count, st);
+  return launch_pair_instance<kElemBytes, true, false, kEpiWarps>(maps, p, sm_count, st);
 }
 
 uint32_t env_u32(const char* name, uint32_t dflt) {
@@ -297,7 +334,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   p.tiles = static_cast<int32_t>(pi.tiles);
   p.a_batch_mul = a->batch_stride_a == 0 ? 0 : 1;
   p.b_batch_mul = a->batch_stride_b == 0 ? 0 : 1;
-  p.loader_a = pi.loader_a; p.loader_b = pi.loader_b;
+  p.loader_a = pi.loader_a == 1 ? 1 : 0; p.loader_b = pi.loader_b == 1 ? 1 : 0;
   p.A = a->A; p.B = a->B; p.lda = a->lda; p.ldb = a->ldb;
   p.stride_a = a->batch_stride_a; p.stride_b = a->batch_stride_b;
   p.vec_store = pi.store_c == 0 ? 1 : 0;
@@ -353,6 +390,31 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     NOVA_CUDA_OK(cudaGetLastError());
     a_src[0] = a_hi; a_src[1] = a_lo; b_src[0] = b_hi; b_src[1] = b_lo;
     a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;
+  } else if (plan.repitch_a_ld > 0 || plan.repitch_b_ld > 0) {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    st = ensure_scratch(ctx, static_cast<size_t>(pi.scratch_bytes));
+    if (st != NOVA_B200_OK) return st;
+    uint8_t* s = static_cast<uint8_t*>(ctx->scratch);
+    RepitchOperand oa{}, ob{};
+    int64_t biggest = 0;
+    if (plan.repitch_a_ld > 0) {
+      oa = RepitchOperand{a->A, s, a_nb * a_rows, a->lda, a->batch_stride_a, static_cast<int32_t>(a_rows),
+                          static_cast<int32_t>(a_cols), static_cast<int32_t>(plan.repitch_a_ld)};
+      a_src[0] = s; a_ld = plan.repitch_a_ld; a_bs = a_rows * a_ld;
+      s += (a_nb * a_rows * a_ld * es + 255) / 256 * 256;
+      biggest = std::max(biggest, a_nb * a_rows * a_ld * es / 16);
+    }
+    if (plan.repitch_b_ld > 0) {
+      ob = RepitchOperand{a->B, s, b_nb * b_rows, a->ldb, a->batch_stride_b, static_cast<int32_t>(b_rows),
+                          static_cast<int32_t>(b_cols), static_cast<int32_t>(plan.repitch_b_ld)};
+      b_src[0] = s; b_ld = plan.repitch_b_ld; b_bs = b_rows * b_ld;
+      biggest = std::max(biggest, b_nb * b_rows * b_ld * es / 16);
+    }
+    const int64_t want = (biggest + 255) / 256;
+    const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 16)));
+    if (es == 2) nova_repitch_kernel<uint16_t><<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
+    else nova_repitch_kernel<uint32_t><<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
+    NOVA_CUDA_OK(cudaGetLastError());
   }
 
   CUtensorMap maps[5];  // A hi, A lo, B hi, B lo, C
@@ -365,13 +427,13 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     return mn && es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   };
   for (int t = 0; t < (plan.terms == 3 ? 2 : 1); ++t) {
-    if (!pi.loader_a) {
+    if (pi.loader_a != 1) {
       st = encode_operand_map(ctx, &maps[t], a_src[t], es, tdt, a_rows, a_cols, a_ld, a_nb, a_bs, chunk,
                               plan.a_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(kBlockM),
                               swizzle_for(plan.a_mn));
       if (st != NOVA_B200_OK) return st;
     }
-    if (!pi.loader_b) {
+    if (pi.loader_b != 1) {
       st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows, b_cols, b_ld, b_nb, b_bs, chunk,
                               plan.b_mn ? static_cast<uint32_t>(block_k)
                                         : static_cast<uint32_t>(plan.pair ? block_n / 2 : block_n),  // a pair CTA loads half of N
@@ -391,13 +453,30 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     if (st != NOVA_B200_OK) return st;
   }
   if (plan.pair) {
-    p.ring_stages = static_cast<int32_t>(env_u32("NOVA_B200_PAIR_STAGES", kPairStages));
-    if (p.ring_stages < 2 || p.ring_stages > kPairStages) p.ring_stages = kPairStages;
     const CUtensorMap pm[3] = {maps[0], maps[2], maps[4]};
-    if (es == 2) return launch_pair_majors<2>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
-    return launch_pair_majors<4>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
+    // NOVA_B200_TRACE=<file> (diagnostic builds only): the launch is synchronous and every CTA's role timeline
+    // (clock64 samples, see TraceSlot) is written to the file as int64[grid][kTraceTiles][kTraceSlots].
+    const char* trace_path = kTraceEnabled ? std::getenv("NOVA_B200_TRACE") : nullptr;
+    const size_t trace_bytes = sizeof(long long) * pi.grid * kTraceTiles * kTraceSlots;
+    if (trace_path != nullptr) {
+      NOVA_CUDA_OK(cudaMalloc(&p.trace, trace_bytes));
+      NOVA_CUDA_OK(cudaMemsetAsync(p.trace, 0, trace_bytes, stream));
+    }
+    st = es == 2 ? launch_pair_majors<2, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream)
+                 : launch_pair_majors<4, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
+    if (trace_path != nullptr) {
+      std::vector<long long> host(trace_bytes / sizeof(long long));
+      cudaStreamSynchronize(stream);
+      cudaMemcpy(host.data(), p.trace, trace_bytes, cudaMemcpyDeviceToHost);
+      cudaFree(p.trace);
+      if (FILE* f = std::fopen(trace_path, "wb")) {
+        std::fwrite(host.data(), 1, trace_bytes, f);
+        std::fclose(f);
+      }
+    }
+    return st;
   }
-  const bool loader = (pi.loader_a | pi.loader_b) != 0;
+  const bool loader = pi.loader_a == 1 || pi.loader_b == 1;
   const int grid = pi.grid;
   if (plan.terms == 3) return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
   if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps

@@ -178,9 +178,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive on an mbarrier that may live in the peer CTA (shared::cluster address)
+// Arrive on an mbarrier that may live in the peer CTA (shared::cluster address).  CTA-scope release (the
+// default): the arrival only hands over tensor memory that tcgen05.wait::ld and the tcgen05 fence have
+// already ordered.  A cluster-scope release here stalls the warp for thousands of cycles per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Tiled load into THIS CTA's shared memory whose completion bytes are counted on an mbarrier that may
 // live in the peer CTA of the pair (no multicast: every CTA fetches its own boxes).

@@ -62,9 +62,13 @@ def test_plan_aligned_operands_use_tma(lib):
     # a wave of 256 x 256 tiles exists: CTA pairs, three ring stages of two 64-element K boxes each per CTA
     assert (info.block_m, info.block_n, info.block_k, info.stages) == (256, 256, 64, 3)
     assert info.tiles == 32 * 43 and info.grid == 148 and info.scratch_bytes == 0
-    # a single 2048^3 problem has only 64 pair tiles (and 128 tiles of 128 x 256): single-CTA 128 x 128 tiles
+    # a single 2048^3 problem is one wave of 128 x 256 tiles (128 of them): cheaper than one under-filled wave of
+    # pairs or two waves of 128 x 128 tiles
     st, info = _plan(lib, _args(2048, 2048, 2048))
-    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 128, 6, 256, 148)
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 256, 4, 128, 128)
+    # 1024^3: 32 tiles of 128 x 256 would leave most SMs idle; 64 tiles of 128 x 128
+    st, info = _plan(lib, _args(1024, 1024, 1024))
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 128, 6, 64, 64)
     # a short contraction (K <= 256) is epilogue-bound: single-CTA 128 x 256 tiles, three 48 KB stages and a
     # second set of epilogue warps
     st, info = _plan(lib, _args(2048, 2048, 128, dt=L.F16, batch=256))
@@ -72,12 +76,18 @@ def test_plan_aligned_operands_use_tma(lib):
 
 
 def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
-    # 1000 x 1000 x 999 bf16: A pitch 1998 B (not 16-byte aligned) -> loader; B, C pitch 2000 B -> TMA / vector stores
+    # 1000 x 1000 x 999 bf16: A pitch 1998 B (not 16-byte aligned) -> loader warps (2 GFLOP: a copy would not pay);
+    # B, C pitch 2000 B -> TMA / vector stores
     st, info = _plan(lib, _args(1000, 1000, 999))
     assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (1, 0, 0)
-    # 4095 x 11007 x 4097: every pitch is odd in bytes/16
+    # the same A pitch under a 16 GFLOP contraction: A is re-pitched into scratch (2000 rows of 1000 elements)
+    st, info = _plan(lib, _args(2000, 4000, 999))
+    assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (2, 0, 0)
+    assert info.scratch_bytes == (2000 * 1000 * 2 + 255) // 256 * 256
+    # 4095 x 11007 x 4097: every pitch is odd in bytes/16; both operands re-pitched, C written with element stores
     st, info = _plan(lib, _args(4095, 11007, 4097))
-    assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (1, 1, 1)
+    assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (2, 2, 1)
+    assert (info.block_m, info.block_n) == (256, 256)
     # an aligned pitch with a misaligned base also needs the loader
     st, info = _plan(lib, _args(256, 256, 256, a=0x1002))
     assert st == L.OK and info.loader_a == 1 and info.loader_b == 0

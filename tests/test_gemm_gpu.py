@@ -227,6 +227,38 @@ def test_unaligned_pitch_loader_matches_tma_bit_for_bit(cuda, oracle):
                                                                dtype_in="bf16"), "bf16")
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (False, True), (True, False), (True, True)])
+def test_unaligned_pitch_repitch_copy_matches_loader_bit_for_bit(cuda, oracle, dt, trans_a, trans_b):
+    """An operand no tensor map can describe is read by the loader warps (small contractions) or re-pitched into
+    aligned scratch and streamed with TMA (large ones).  NOVA_B200_REPITCH forces either: same bits, batched,
+    with a batch-shared B, for both operand majors."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    rng = np.random.default_rng(41)
+    Bn, M, N, K = 3, 203, 141, 275
+    a_shape = (Bn, K, M) if trans_a else (Bn, M, K)
+    b_shape = (1, N, K) if trans_b else (1, K, N)
+    a = rand_bits(oracle, rng, a_shape, dt)
+    b = rand_bits(oracle, rng, b_shape, dt)
+    ta, tb = to_dev(torch, a, dt), to_dev(torch, b, dt)
+    a3 = ta.transpose(1, 2) if trans_a else ta
+    b3 = tb.transpose(1, 2) if trans_b else tb
+    kw = dict(f32_mode=L.TF32X1) if dt == "f32" else {}
+    outs = {}
+    for mode in ("0", "1"):
+        os.environ["NOVA_B200_REPITCH"] = mode
+        try:
+            outs[mode] = ops.gemm(a3, b3, act="relu", **kw)
+            torch.cuda.synchronize()
+        finally:
+            del os.environ["NOVA_B200_REPITCH"]
+    assert torch.equal(outs["0"], outs["1"])
+    if dt != "f32":
+        want = oracle.gemm(a, b[0], dtype_in=dt, act="relu", trans_a=trans_a, trans_b=trans_b)
+        check(oracle, to_host(torch, outs["1"], dt), want, dt)
+
+
 def test_ragged_equals_zero_padded_problem_bit_for_bit(cuda, oracle):
     """Out-of-bounds fill replaces the reference's PadOperands copy: the ragged result is exactly the
     top-left block of the zero-padded problem."""
