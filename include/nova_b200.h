@@ -64,7 +64,11 @@ typedef enum nova_b200_dtype {
 typedef enum nova_b200_act {
   NOVA_B200_ACT_NONE = 0,
   NOVA_B200_ACT_RELU = 1,      /* nova.relu -> arith.maximumf(x, 0)  (NovaToLinalg.cpp:1053-1084)           */
-  NOVA_B200_ACT_GELU_TANH = 2  /* nova.gelu, tanh form (NovaToLinalgGeneric.cpp:1277-1337)                 */
+  NOVA_B200_ACT_GELU_TANH = 2, /* nova.gelu, tanh form (NovaToLinalgGeneric.cpp:1277-1337)                 */
+  NOVA_B200_ACT_GELU_TANH_GRAD = 3 /* contraction followed by nova.gelu_backward (NovaToLinalgGeneric.cpp:1339-1420):
+                                    * C = (init + A.B) * gelu_tanh'(Z).  Z, the forward pre-activation, is read through
+                                    * `residual` / `ldr` / `batch_stride_r` and is NOT added; init must then be ZERO,
+                                    * BIAS_ROW or FROM_C.  Only nova_b200_gemm* accept it. */
 } nova_b200_act;
 
 /* What the accumulator starts from.  FuseMatmulBias (lib/Transforms/FuseMatmulBias.cpp:95-193)
@@ -75,7 +79,9 @@ typedef enum nova_b200_acc_init {
   NOVA_B200_INIT_ZERO = 0,
   NOVA_B200_INIT_BIAS_ROW = 1,      /* bias[N], broadcast along rows                         */
   NOVA_B200_INIT_RESIDUAL_FULL = 2, /* residual[batch, M, N] (own pitch and batch stride)     */
-  NOVA_B200_INIT_FROM_C = 3         /* C holds the initial accumulator and is overwritten     */
+  NOVA_B200_INIT_FROM_C = 3,        /* C holds the initial accumulator and is overwritten     */
+  NOVA_B200_INIT_BIAS_AND_RESIDUAL = 4 /* bias[N] + residual[batch, M, N]: the "out + x + b_down" generic after
+                                        * the FFN-down contraction (docs/SelectLoweringStrategy_Report.md rows 15, 25) */
 } nova_b200_acc_init;
 
 typedef enum nova_b200_f32_mode {
@@ -179,6 +185,11 @@ int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream,
 /* y = act(x), n elements, standalone nova.gelu / nova.relu (NovaToLinalgGeneric.cpp:1277-1337,
  * NovaToLinalg.cpp:1053-1084) for graphs where the activation is not adjacent to a contraction. */
 int32_t nova_b200_activation(const void* x_dev, void* y_dev, int64_t n, int32_t dtype, int32_t act, void* stream);
+
+/* y = grad_out * gelu_tanh'(x), n elements: standalone nova.gelu_backward (NovaToLinalgGeneric.cpp:1339-1420;
+ * ltest/_gelu.mlir, ltest/test.mlir:41). */
+int32_t nova_b200_gelu_backward(const void* grad_out_dev, const void* x_dev, void* y_dev, int64_t n, int32_t dtype,
+                                void* stream);
 
 /* out[r, c] = a[r, c] + b[c]  (b_is_full == 0)  or  a[r, c] + b[r, c]: nova.add with a row-broadcast
  * operand (NovaToLinalg.cpp:115-194; the `[1,10]` bias of ltest/test_cpu.mlir). */

@@ -17,9 +17,9 @@ STATUS_NAMES = ["OK", "ERR_INVALID_ARG", "ERR_LAYOUT", "ERR_UNSUPPORTED", "ERR_C
 # nova_b200_dtype
 F32, F16, BF16, I16, I32, I64 = range(6)
 # nova_b200_act
-ACT_NONE, ACT_RELU, ACT_GELU_TANH = range(3)
+ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_TANH_GRAD = range(4)
 # nova_b200_acc_init
-INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_FROM_C = range(4)
+INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_FROM_C, INIT_BIAS_AND_RESIDUAL = range(5)
 # nova_b200_f32_mode
 TF32X3, TF32X1 = range(2)
 
@@ -70,6 +70,7 @@ PROTOTYPES = {
     "nova_b200_gemm_host": (C.c_int32, [C.POINTER(GemmArgs)]),
     "nova_b200_gemm_f32_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
     "nova_b200_activation": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
+    "nova_b200_gelu_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_add_rowbcast": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                            C.c_int32, C.c_void_p]),
     "nova_b200_layer_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

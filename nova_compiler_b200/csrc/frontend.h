@@ -65,6 +65,7 @@ struct Step {
   // gemm
   std::string bias, residual;
   int32_t act = NOVA_B200_ACT_NONE;
+  std::string act_operand;  // ACT_GELU_TANH_GRAD: the forward pre-activation the result is multiplied by
   bool accumulate_into_out = false;
   // misc
   std::map<std::string, int64_t> attrs;

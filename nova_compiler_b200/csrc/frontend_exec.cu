@@ -213,9 +213,16 @@ struct Exec {
       if ((st = get(s.bias, &aux)) != NOVA_B200_OK || (st = make_contiguous(aux, &aux)) != NOVA_B200_OK) return st;
       g.init = NOVA_B200_INIT_BIAS_ROW;
       g.bias = aux.ptr;
-    } else if (!s.residual.empty()) {
+    }
+    if (!s.residual.empty()) {
       if ((st = get(s.residual, &aux)) != NOVA_B200_OK || (st = make_contiguous(aux, &aux)) != NOVA_B200_OK) return st;
-      g.init = NOVA_B200_INIT_RESIDUAL_FULL;
+      g.init = s.bias.empty() ? NOVA_B200_INIT_RESIDUAL_FULL : NOVA_B200_INIT_BIAS_AND_RESIDUAL;
+      g.residual = aux.ptr;
+      g.ldr = g.N;
+      g.batch_stride_r = g.M * g.N;
+    }
+    if (s.act == NOVA_B200_ACT_GELU_TANH_GRAD) {
+      if ((st = get(s.act_operand, &aux)) != NOVA_B200_OK || (st = make_contiguous(aux, &aux)) != NOVA_B200_OK) return st;
       g.residual = aux.ptr;
       g.ldr = g.N;
       g.batch_stride_r = g.M * g.N;
@@ -269,6 +276,7 @@ struct Exec {
       if ((st = alloc(type_of(s.outputs[i]), &out[i])) != NOVA_B200_OK) return st;
     const int64_t n = in.empty() ? out[0].numel() : in[0].numel();
     if (k == "activation") st = nova_b200_activation(in[0].ptr, out[0].ptr, n, in[0].dtype, s.act, stream);
+    else if (k == "gelu_backward") st = nova_b200_gelu_backward(in[0].ptr, in[1].ptr, out[0].ptr, n, in[0].dtype, stream);
     else if (k == "add") {
       const int64_t cols = in[0].shape.back();
       st = nova_b200_add_rowbcast(in[0].ptr, in[1].ptr, out[0].ptr, n / cols, cols, in[1].numel() == n ? 1 : 0, in[0].dtype, stream);

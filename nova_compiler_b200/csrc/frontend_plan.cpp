@@ -186,6 +186,11 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu" || n == "nova.softmax") {
       if (in.size() != 1 || !is_float(in[0]->dtype)) return c.fail(op, "expects one float tensor");
       set(0, *in[0]);
+    } else if (n == "nova.gelu_backward") {
+      // (grad_out, input) -> the input's type (GeluBackwardOp::inferReturnTypes, NovaOps.cpp:2130)
+      if (in.size() != 2 || !is_float(in[1]->dtype) || in[0]->dtype != in[1]->dtype || !(in[0]->shape == in[1]->shape))
+        return c.fail(op, "expects grad_out and input of one float type and shape");
+      set(0, *in[1]);
     } else if (n == "nova.add") {
       if (in.size() != 2) return c.fail(op, "expects two operands");
       if (in[0]->dtype != in[1]->dtype || !is_float(in[0]->dtype)) return c.fail(op, "mixed or non-float dtypes are outside the supported subset");
@@ -289,27 +294,43 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     return it->second < at;  // ops live in one vector: address order is program order
   };
   const Op* current = nullptr;
+  // a contraction whose only user is nova.gelu_backward, as its grad_out operand: the multiplication by
+  // gelu'(input) moves into the contraction's epilogue (the residual pointer then carries `input`)
+  auto absorb_gelu_backward = [&](Step& s, std::string& v) {
+    if (s.act != NOVA_B200_ACT_NONE || !s.residual.empty()) return;
+    const Op* u = single_user(v);
+    if (!(u && u->name == "nova.gelu_backward" && u->operands.size() == 2 && u->operands[0] == v && u->operands[1] != v)) return;
+    if (!defined_before(u->operands[1], current)) return;
+    s.act = NOVA_B200_ACT_GELU_TANH_GRAD;
+    s.act_operand = u->operands[1];
+    c.absorbed.insert(u);
+    s.note += " + " + u->name;
+    p.alias[v] = u->results[0];
+    v = u->results[0];
+  };
   auto absorb_tail = [&](Step& s, std::string v) {
     const Type out_t = *c.type_of(v);
-    // accumulator init: the other addend of a following add (FuseMatmulBias)
-    if (s.bias.empty() && s.residual.empty() && s.act == NOVA_B200_ACT_NONE) {
+    // accumulator init: the other addend of a following add (FuseMatmulBias) -- a row-broadcast bias, a
+    // full-shape residual, or one of each ("out + x + b_down" after the FFN-down contraction)
+    for (int round = 0; round < 2 && s.act == NOVA_B200_ACT_NONE; ++round) {
       const Op* u = single_user(v);
-      if (u && u->name == "nova.add" && u->operands.size() == 2) {
-        const std::string other = u->operands[0] == v ? u->operands[1] : u->operands[0];
-        const Type* ot = c.type_of(other);
-        if (ot && other != v && ot->dtype == out_t.dtype && defined_before(other, current)) {
-          bool fused = false;
-          if (ot->shape == out_t.shape) { s.residual = other; fused = true; }
-          else if (is_row_broadcast(out_t, *ot)) { s.bias = other; fused = true; }
-          if (fused) {
-            c.absorbed.insert(u);
-            s.note += " + " + u->name;
-            p.alias[v] = u->results[0];
-            v = u->results[0];
-          }
-        }
+      if (!(u && u->name == "nova.add" && u->operands.size() == 2)) break;
+      const std::string other = u->operands[0] == v ? u->operands[1] : u->operands[0];
+      const Type* ot = c.type_of(other);
+      if (!(ot && other != v && ot->dtype == out_t.dtype && defined_before(other, current))) break;
+      bool fused = false;
+      if (ot->shape == out_t.shape) {
+        if (s.residual.empty()) { s.residual = other; fused = true; }
+      } else if (is_row_broadcast(out_t, *ot)) {
+        if (s.bias.empty()) { s.bias = other; fused = true; }
       }
+      if (!fused) break;
+      c.absorbed.insert(u);
+      s.note += " + " + u->name;
+      p.alias[v] = u->results[0];
+      v = u->results[0];
     }
+    absorb_gelu_backward(s, v);
     if (s.act == NOVA_B200_ACT_NONE) {
       const Op* u = single_user(v);
       if (u && (u->name == "nova.relu" || u->name == "nova.gelu")) {
@@ -363,8 +384,10 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
         p.steps.push_back(v);
       };
       auto swapped = [](Type t) { std::swap(t.shape[t.shape.size() - 1], t.shape[t.shape.size() - 2]); return t; };
-      auto gemm = [&](const std::string& a, const std::string& b, const std::string& out, const char* what) {
-        Step g; g.kind = "gemm"; g.inputs = {a, b}; g.outputs = {out}; g.note = n + std::string(" ") + what;
+      auto gemm = [&](const std::string& a, const std::string& b, std::string out, const char* what) {
+        Step g; g.kind = "gemm"; g.inputs = {a, b}; g.note = n + std::string(" ") + what;
+        absorb_gelu_backward(g, out);  // e.g. grad_input of the FFN-down layer feeding nova.gelu_backward
+        g.outputs = {out};
         p.steps.push_back(g);
       };
       const std::string &go = op.operands[0], &x = op.operands[1], &w = op.operands[2];
@@ -391,6 +414,9 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu") {
       s.kind = "activation";
       s.act = n == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;
+      s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.gelu_backward") {
+      s.kind = "gelu_backward";
       s.inputs = op.operands; s.outputs = op.results;
     } else if (n == "nova.add") {
       s.kind = "add";
@@ -433,8 +459,12 @@ std::string describe_plan(const Function& f, const Plan& p) {
   for (const Step& s : p.steps) {
     o << "  " << s.kind;
     if (s.kind == "gemm") {
-      o << " init=" << (!s.bias.empty() ? "bias_row(%" + s.bias + ")" : !s.residual.empty() ? "residual(%" + s.residual + ")" : std::string("zero"));
-      o << " act=" << (s.act == NOVA_B200_ACT_RELU ? "relu" : s.act == NOVA_B200_ACT_GELU_TANH ? "gelu_tanh" : "none");
+      o << " init=" << (!s.bias.empty() && !s.residual.empty() ? "bias_row(%" + s.bias + ")+residual(%" + s.residual + ")"
+                        : !s.bias.empty()                      ? "bias_row(%" + s.bias + ")"
+                        : !s.residual.empty()                  ? "residual(%" + s.residual + ")"
+                                                               : std::string("zero"));
+      o << " act=" << (s.act == NOVA_B200_ACT_RELU ? "relu" : s.act == NOVA_B200_ACT_GELU_TANH ? "gelu_tanh"
+                       : s.act == NOVA_B200_ACT_GELU_TANH_GRAD ? "gelu_tanh_grad(%" + s.act_operand + ")" : std::string("none"));
     }
     o << " (";
     for (size_t i = 0; i < s.inputs.size(); ++i) o << (i ? ", " : "") << "%" << s.inputs[i];

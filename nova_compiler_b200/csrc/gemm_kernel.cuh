@@ -150,6 +150,16 @@ __device__ __forceinline__ float gelu_tanh_f32(float x) {
   return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
 
+// d/dx of the tanh-form GELU: with s = sigmoid(2u), tanh(u) = 2s - 1, so 0.5(1 + tanh u) = s and
+// 1 - tanh^2 u = 4s(1 - s); u' = 0.79788456 * (1 + 0.134145 x^2)  (3 * 0.044715 = 0.134145).
+__device__ __forceinline__ float gelu_tanh_grad_f32(float x) {
+  const float x2 = x * x;
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x, x2, x);
+  const float s = __fdividef(1.0f, 1.0f + __expf(-2.0f * u));
+  const float du = 0.7978845608028654f * fmaf(0.134145f, x2, 1.0f);
+  return fmaf(2.0f * x * du, s * (1.0f - s), s);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
@@ -168,12 +178,14 @@ __device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const u
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
   const int32_t ncols = min(32, p.N - col0);
-  if (p.init == NOVA_B200_INIT_BIAS_ROW) {
+  if (p.init == NOVA_B200_INIT_BIAS_ROW || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) {
     const OutT* b = reinterpret_cast<const OutT*>(p.bias) + col0;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < ncols) v[j] += to_f32<OutT>(__ldg(b + j));
-  } else if ((p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_FROM_C) && row_ok) {
+  }
+  if ((p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_FROM_C ||
+       p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) && row_ok) {
     const OutT* r = p.init == NOVA_B200_INIT_FROM_C
                         ? reinterpret_cast<const OutT*>(p.C) + static_cast<int64_t>(batch) * p.stride_c +
                               static_cast<int64_t>(row) * p.ldc + col0
@@ -189,6 +201,13 @@ __device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const u
   } else if (p.act == NOVA_B200_ACT_GELU_TANH) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f32(v[j]);
+  } else if (p.act == NOVA_B200_ACT_GELU_TANH_GRAD && row_ok) {
+    // the forward pre-activation arrives through the residual pointer and is a multiplier, not an addend
+    const OutT* z = reinterpret_cast<const OutT*>(p.residual) + static_cast<int64_t>(batch) * p.stride_r +
+                    static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] *= gelu_tanh_grad_f32(to_f32<OutT>(z[j]));
   }
 }
 
@@ -746,12 +765,15 @@ __global__ void nova_gemm_k0_kernel(GemmKernelParams p) {
     const int64_t c = i - b * per_batch - r * p.N;
     OutT* dst = reinterpret_cast<OutT*>(p.C) + b * p.stride_c + r * p.ldc + c;
     float v = 0.0f;
-    if (p.init == NOVA_B200_INIT_BIAS_ROW) v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.bias)[c]);
-    else if (p.init == NOVA_B200_INIT_RESIDUAL_FULL)
-      v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.residual)[b * p.stride_r + r * p.ldr + c]);
+    if (p.init == NOVA_B200_INIT_BIAS_ROW || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL)
+      v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.bias)[c]);
+    if (p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL)
+      v += to_f32<OutT>(reinterpret_cast<const OutT*>(p.residual)[b * p.stride_r + r * p.ldr + c]);
     else if (p.init == NOVA_B200_INIT_FROM_C) v = to_f32<OutT>(*dst);
     if (p.act == NOVA_B200_ACT_RELU) v = fmaxf(v, 0.0f);
     else if (p.act == NOVA_B200_ACT_GELU_TANH) v = gelu_tanh_f32(v);
+    else if (p.act == NOVA_B200_ACT_GELU_TANH_GRAD)
+      v *= gelu_tanh_grad_f32(to_f32<OutT>(reinterpret_cast<const OutT*>(p.residual)[b * p.stride_r + r * p.ldr + c]));
     *dst = from_f32<OutT>(v);
   }
 }

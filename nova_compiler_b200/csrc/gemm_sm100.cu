@@ -34,9 +34,9 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   if (a->dtype_ab != NOVA_B200_F32 && a->dtype_ab != NOVA_B200_F16 && a->dtype_ab != NOVA_B200_BF16)
     return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: dtype_ab must be f32, f16 or bf16");
   if (!is_float_dtype(a->dtype_c)) return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: dtype_c must be f32, f16 or bf16");
-  if (a->act < NOVA_B200_ACT_NONE || a->act > NOVA_B200_ACT_GELU_TANH)
+  if (a->act < NOVA_B200_ACT_NONE || a->act > NOVA_B200_ACT_GELU_TANH_GRAD)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown activation");
-  if (a->init < NOVA_B200_INIT_ZERO || a->init > NOVA_B200_INIT_FROM_C)
+  if (a->init < NOVA_B200_INIT_ZERO || a->init > NOVA_B200_INIT_BIAS_AND_RESIDUAL)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown accumulator init");
   if (a->f32_mode != NOVA_B200_TF32X3 && a->f32_mode != NOVA_B200_TF32X1)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown f32_mode");
@@ -54,15 +54,18 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
 
   if (!a->C) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: C is null");
   if (!plan->k_zero && (!a->A || !a->B)) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: A or B is null");
-  if (a->init == NOVA_B200_INIT_BIAS_ROW && !a->bias) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: bias is null");
-  if (a->init == NOVA_B200_INIT_RESIDUAL_FULL && !a->residual)
+  if (init_has_bias(a->init) && !a->bias) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: bias is null");
+  if (a->act == NOVA_B200_ACT_GELU_TANH_GRAD && init_has_residual(a->init))
+    return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: with ACT_GELU_TANH_GRAD the residual pointer holds the pre-activation; "
+                                           "init must be ZERO, BIAS_ROW or FROM_C");
+  if (reads_residual(a->init, a->act) && !a->residual)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: residual is null");
   const int64_t a_inner = a->trans_a ? a->M : a->K;
   const int64_t b_inner = a->trans_b ? a->K : a->N;
   if (!plan->k_zero && (a->lda < a_inner || a->ldb < b_inner))
     return fail(NOVA_B200_ERR_LAYOUT, "gemm: lda/ldb smaller than the contiguous extent");
   if (a->ldc < a->N) return fail(NOVA_B200_ERR_LAYOUT, "gemm: ldc smaller than N");
-  if (a->init == NOVA_B200_INIT_RESIDUAL_FULL && a->ldr < a->N)
+  if (reads_residual(a->init, a->act) && a->ldr < a->N)
     return fail(NOVA_B200_ERR_LAYOUT, "gemm: ldr smaller than N");
   if (a->batch_stride_a < 0 || a->batch_stride_b < 0 || a->batch_stride_c < 0 || a->batch_stride_r < 0)
     return fail(NOVA_B200_ERR_LAYOUT, "gemm: negative batch stride");

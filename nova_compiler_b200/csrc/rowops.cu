@@ -316,6 +316,31 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ y, in
   }
 }
 
+// 0.5(1 + tanh u) + 0.5 x (1 - tanh^2 u) u', u = 0.79788456 (x + 0.044715 x^3)
+__device__ __forceinline__ float gelu_tanh_grad_accurate(float x) {
+  const float x2 = x * x;
+  const float t = tanhf(0.7978845608028654f * fmaf(0.044715f * x, x2, x));
+  const float du = 0.7978845608028654f * fmaf(0.134145f, x2, 1.0f);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+template <typename T, int VEC>
+__global__ void gelu_backward_kernel(const T* __restrict__ go, const T* __restrict__ x, T* __restrict__ y, int64_t n) {
+  using P = Pack<T, VEC>;
+  const int64_t nv = n / VEC;
+  const P* gp = reinterpret_cast<const P*>(go);
+  const P* xp = reinterpret_cast<const P*>(x);
+  P* yp = reinterpret_cast<P*>(y);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const P g = gp[i];
+    P v = xp[i];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) v.e[e] = st_f32<T>(ld_f32<T>(g.e[e]) * gelu_tanh_grad_accurate(ld_f32<T>(v.e[e])));
+    yp[i] = v;
+  }
+}
+
 template <typename T, int VEC>
 __global__ void add_rowbcast_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t rows,
                                     int64_t cols, int32_t b_is_full) {
@@ -505,6 +530,30 @@ int32_t nova_b200_activation(const void* x, void* y, int64_t n, int32_t dtype, i
   else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_ACT(__half, 8); else NOVA_ACT(__half, 1); }
   else { if (vec_ok) NOVA_ACT(__nv_bfloat16, 8); else NOVA_ACT(__nv_bfloat16, 1); }
 #undef NOVA_ACT
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_gelu_backward(const void* go, const void* x, void* y, int64_t n, int32_t dtype, void* stream) {
+  if (n < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "gelu_backward: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "gelu_backward: dtype must be f32, f16 or bf16");
+  if (n == 0) return NOVA_B200_OK;
+  if (!go || !x || !y) return fail(NOVA_B200_ERR_INVALID_ARG, "gelu_backward: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype), vec = 16 / es;
+  const bool vec_ok = n % vec == 0 && reinterpret_cast<uintptr_t>(go) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(y) % 16 == 0;
+  const int threads = 256;
+  const int grid = grid_for(vec_ok ? n / vec : n, threads, ctx->sm_count);
+#define NOVA_GB(T, V) \
+  gelu_backward_kernel<T, V><<<grid, threads, 0, s>>>(static_cast<const T*>(go), static_cast<const T*>(x), static_cast<T*>(y), n)
+  if (dtype == NOVA_B200_F32) { if (vec_ok) NOVA_GB(float, 4); else NOVA_GB(float, 1); }
+  else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_GB(__half, 8); else NOVA_GB(__half, 1); }
+  else { if (vec_ok) NOVA_GB(__nv_bfloat16, 8); else NOVA_GB(__nv_bfloat16, 1); }
+#undef NOVA_GB
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }

@@ -214,8 +214,8 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   const size_t a_bytes = a.K ? span(a.batch, a.batch_stride_a, a_rows, a.lda, a_cols) * es : 0;
   const size_t b_bytes = a.K ? span(a.batch, a.batch_stride_b, b_rows, a.ldb, b_cols) * es : 0;
   const size_t c_bytes = span(a.batch, a.batch_stride_c, a.M, a.ldc, a.N) * os;
-  const size_t bias_bytes = a.init == NOVA_B200_INIT_BIAS_ROW ? a.N * os : 0;
-  const size_t r_bytes = a.init == NOVA_B200_INIT_RESIDUAL_FULL ? span(a.batch, a.batch_stride_r, a.M, a.ldr, a.N) * os : 0;
+  const size_t bias_bytes = init_has_bias(a.init) ? a.N * os : 0;
+  const size_t r_bytes = reads_residual(a.init, a.act) ? span(a.batch, a.batch_stride_r, a.M, a.ldr, a.N) * os : 0;
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   const size_t total = up(a_bytes) + up(b_bytes) + up(c_bytes) + up(bias_bytes) + up(r_bytes);
   std::lock_guard<std::mutex> lock(ctx->host_mu);
@@ -230,7 +230,7 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   // chunk i+1's host-to-device copy, chunk i's kernel and chunk i-1's device-to-host copy run concurrently
   // on three streams, so the two PCIe directions overlap.  Needs chunkable layouts; else one shot below.
   const bool by_batch = a.batch > 1 && a.batch_stride_a != 0 && a.batch_stride_c != 0 &&
-                        (a.init != NOVA_B200_INIT_RESIDUAL_FULL || a.batch_stride_r != 0);
+                        (!reads_residual(a.init, a.act) || a.batch_stride_r != 0);
   const bool by_rows = a.batch == 1 && !a.trans_a && a.M >= 512 && a.K > 0;
   if ((by_batch || by_rows) && a.K > 0) {
     st = ensure_host_streams(ctx);

@@ -62,6 +62,12 @@ inline int dtype_bytes(int32_t dt) {
     default: return 0;
   }
 }
+inline bool init_has_bias(int32_t init) { return init == NOVA_B200_INIT_BIAS_ROW || init == NOVA_B200_INIT_BIAS_AND_RESIDUAL; }
+inline bool init_has_residual(int32_t init) {
+  return init == NOVA_B200_INIT_RESIDUAL_FULL || init == NOVA_B200_INIT_BIAS_AND_RESIDUAL;
+}
+// the residual pointer is read either as an addend or as the pre-activation of a fused nova.gelu_backward
+inline bool reads_residual(int32_t init, int32_t act) { return init_has_residual(init) || act == NOVA_B200_ACT_GELU_TANH_GRAD; }
 inline bool is_float_dtype(int32_t dt) { return dt == NOVA_B200_F32 || dt == NOVA_B200_F16 || dt == NOVA_B200_BF16; }
 
 #define NOVA_CUDA_OK(expr)                                                                          \

@@ -64,10 +64,15 @@ def _batch_stride(t: torch.Tensor) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
          out_dtype: Optional[torch.dtype] = None, accumulate_into_out: bool = False,
-         f32_mode: int = L.TF32X3) -> torch.Tensor:
+         f32_mode: int = L.TF32X3, gelu_grad_of: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[b] = act(init + A[b] @ B[b]) on rank-3 views; A: [B,M,K], B: [B or 1,K,N] (any of the two inner
-    dims may be the contiguous one: transposed views are passed as trans_a / trans_b, not copied)."""
-    _require_cuda(a, b, bias, residual, out)
+    dims may be the contiguous one: transposed views are passed as trans_a / trans_b, not copied).
+    gelu_grad_of=Z: C = (init + A @ B) * gelu_tanh'(Z), the contraction fused with a following
+    nova.gelu_backward (excludes residual and act)."""
+    _require_cuda(a, b, bias, residual, out, gelu_grad_of)
+    if gelu_grad_of is not None:
+        if residual is not None or act not in (None, "none"):
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "gelu_grad_of excludes residual and act")
     if a.dim() != 3 or b.dim() != 3:
         raise L.NovaB200Error(L.ERR_INVALID_ARG, "gemm expects rank-3 views")
     if a.dtype != b.dtype:
@@ -104,13 +109,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         if bias.dtype != out_dtype or bias.numel() != N or not bias.is_contiguous():
             raise L.NovaB200Error(L.ERR_INVALID_ARG, "bias must be a contiguous [N] tensor of the output dtype")
         g.init, g.bias = L.INIT_BIAS_ROW, bias.data_ptr()
-    elif residual is not None:
+    if residual is not None:
         r3 = residual if residual.dim() == 3 else residual.unsqueeze(0)
         if r3.dtype != out_dtype or tuple(r3.shape[-2:]) != (M, N) or r3.stride(-1) != 1:
             raise L.NovaB200Error(L.ERR_INVALID_ARG, "residual must be [B,M,N] of the output dtype, unit inner stride")
-        g.init, g.residual, g.ldr = L.INIT_RESIDUAL_FULL, r3.data_ptr(), r3.stride(-2)
+        g.init = L.INIT_BIAS_AND_RESIDUAL if bias is not None else L.INIT_RESIDUAL_FULL
+        g.residual, g.ldr = r3.data_ptr(), r3.stride(-2)
         g.batch_stride_r = 0 if r3.shape[0] == 1 else r3.stride(0)
-    elif accumulate_into_out:
+    if gelu_grad_of is not None:
+        z3 = gelu_grad_of if gelu_grad_of.dim() == 3 else gelu_grad_of.unsqueeze(0)
+        if z3.dtype != out_dtype or tuple(z3.shape[-2:]) != (M, N) or z3.stride(-1) != 1:
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "gelu_grad_of must be [B,M,N] of the output dtype, unit inner stride")
+        g.act, g.residual, g.ldr = L.ACT_GELU_TANH_GRAD, z3.data_ptr(), z3.stride(-2)
+        g.batch_stride_r = 0 if z3.shape[0] == 1 else z3.stride(0)
+    if accumulate_into_out:
+        if bias is not None or residual is not None:
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "accumulate_into_out excludes bias and residual")
         g.init = L.INIT_FROM_C
     L.check(L.load().nova_b200_gemm(C.byref(g), _stream()))
     return out
@@ -222,6 +236,17 @@ def _unary(x: torch.Tensor, act: int) -> torch.Tensor:
 def gelu(x: torch.Tensor) -> torch.Tensor:
     """nova.gelu, tanh form (NovaGeluForwardPattern, NovaToLinalgGeneric.cpp:1277-1337)."""
     return _unary(x, L.ACT_GELU_TANH)
+
+
+def gelu_backward(grad_out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """nova.gelu_backward: grad_out * d/dx gelu_tanh(x) (NovaGeluBackwardPattern, NovaToLinalgGeneric.cpp:1339-1420)."""
+    _require_cuda(grad_out, x)
+    if grad_out.shape != x.shape or grad_out.dtype != x.dtype:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "gelu_backward: grad_out and input must share shape and dtype")
+    gc, xc = grad_out.contiguous(), x.contiguous()
+    y = torch.empty_like(xc)
+    L.check(L.load().nova_b200_gelu_backward(gc.data_ptr(), xc.data_ptr(), y.data_ptr(), xc.numel(), _dt(xc), _stream()))
+    return y
 
 
 def relu(x: torch.Tensor) -> torch.Tensor:

@@ -37,10 +37,14 @@
 #define ACT_NONE 0
 #define ACT_RELU 1
 #define ACT_GELU_TANH 2
+#define ACT_GELU_TANH_GRAD 3 /* multiply by gelu_tanh'(z), z read through the residual pointer */
 
 #define INIT_ZERO 0
 #define INIT_BIAS_ROW 1      /* bias[n] broadcast along rows (FuseMatmulBias.cpp:149-173) */
 #define INIT_RESIDUAL_FULL 2 /* full [B,M,N] tensor as accumulator init (:147-148)        */
+#define INIT_BIAS_AND_RESIDUAL 4 /* bias[n] + residual[b,m,n]: the "out + x + b_down" generic that follows the FFN-down
+                                    contraction (docs/SelectLoweringStrategy_Report.md rows 15 and 25); 3 is the CUDA
+                                    library's in-place form, which this restatement does not need */
 
 /* ---------------------------------------------------------------- dtype helpers */
 
@@ -158,6 +162,34 @@ static inline float gelu_tanh_steps(float x, int dt) {
   float onePT = round_through(1.0f + t, dt);
   float halfX = round_through(0.5f * x, dt);
   return round_through(halfX * onePT, dt);
+}
+
+/* grad_out * d/dx gelu_tanh(x), the op sequence of NovaGeluBackwardPattern
+ * (NovaToLinalgGeneric.cpp:1339-1420): g = s*(x + c*x^3), g' = s*(1 + 0.134145*x^2),
+ * term1 = 0.5*(1 + tanh g), term2 = 0.5*x*((1 - tanh^2 g)*g'), result = go*(term1 + term2),
+ * with the reference's constants (s = 0.797884583f) and every intermediate rounded through `dt`. */
+static inline float gelu_tanh_grad_steps(float go, float x, int dt) {
+  const float cs2p = round_through(0.797884583f, dt);
+  const float c004 = round_through(4.471500e-02f, dt);
+  const float c013 = round_through(0.134145f, dt);
+  float x2 = round_through(x * x, dt);
+  float x3 = round_through(x2 * x, dt);
+  float cubic = round_through(c004 * x3, dt);
+  float inner = round_through(x + cubic, dt);
+  float gx = round_through(cs2p * inner, dt);
+  float xsq_c = round_through(x2 * c013, dt);
+  float polyG = round_through(1.0f + xsq_c, dt);
+  float dgx = round_through(polyG * cs2p, dt);
+  float tanhG = round_through(tanhf(gx), dt);
+  float tanh2 = round_through(tanhG * tanhG, dt);
+  float onePT = round_through(1.0f + tanhG, dt);
+  float term1 = round_through(0.5f * onePT, dt);
+  float omT2 = round_through(1.0f - tanh2, dt);
+  float t2a = round_through(dgx * omT2, dt);
+  float t2b = round_through(x * t2a, dt);
+  float term2 = round_through(0.5f * t2b, dt);
+  float dGelu = round_through(term1 + term2, dt);
+  return round_through(go * dGelu, dt);
 }
 
 static inline float apply_act(float v, int act, int dt) {
@@ -288,6 +320,8 @@ int nova_oracle_gemm(const oracle_gemm_args* g) {
             if (g->init == INIT_BIAS_ROW) v = load_elem(g->bias, j, g->dtype_out);
             else if (g->init == INIT_RESIDUAL_FULL)
               v = load_elem(g->residual, b * g->stride_r + i * g->ldr + j, g->dtype_out);
+            else if (g->init == INIT_BIAS_AND_RESIDUAL)
+              v = load_elem(g->bias, j, g->dtype_out) + load_elem(g->residual, b * g->stride_r + i * g->ldr + j, g->dtype_out);
           }
           acc[j] = v;
           if (acc64) acc64[j] = (double)v;
@@ -303,9 +337,16 @@ int nova_oracle_gemm(const oracle_gemm_args* g) {
             if (g->init == INIT_BIAS_ROW) add = load_elem(g->bias, j, g->dtype_out);
             else if (g->init == INIT_RESIDUAL_FULL)
               add = load_elem(g->residual, b * g->stride_r + i * g->ldr + j, g->dtype_out);
+            else if (g->init == INIT_BIAS_AND_RESIDUAL) {
+              v = round_through(v + load_elem(g->bias, j, g->dtype_out), act_dt);
+              add = load_elem(g->residual, b * g->stride_r + i * g->ldr + j, g->dtype_out);
+            }
             v = round_through(v + add, act_dt);
           }
-          v = apply_act(v, g->act, act_dt);
+          if (g->act == ACT_GELU_TANH_GRAD) /* `residual` holds the forward pre-activation, not an addend */
+            v = gelu_tanh_grad_steps(v, load_elem(g->residual, b * g->stride_r + i * g->ldr + j, g->dtype_out), act_dt);
+          else
+            v = apply_act(v, g->act, act_dt);
           store_elem(Cb, i * g->ldc + j, g->dtype_out, v);
         }
       }
@@ -369,6 +410,14 @@ int nova_oracle_gemm_scalar_rows(const oracle_gemm_args* g, int64_t row_begin, i
  * (nova.gelu / nova.relu lower to an all-parallel linalg.generic in the
  * element type: NovaToLinalgGeneric.cpp:1277-1337, NovaToLinalg.cpp:1053-1084).
  * compute_f32 != 0 evaluates in fp32 and rounds once (fused-epilogue form). */
+/* y = grad_out * gelu_tanh'(x) over n elements (nova.gelu_backward: an all-parallel two-input
+ * linalg.generic in the element type, NovaToLinalgGeneric.cpp:1339-1420). */
+void nova_oracle_gelu_backward(const void* go, const void* x, void* y, int64_t n, int dt, int compute_f32) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i)
+    store_elem(y, i, dt, gelu_tanh_grad_steps(load_elem(go, i, dt), load_elem(x, i, dt), compute_f32 ? NOVA_F32 : dt));
+}
+
 void nova_oracle_activation(const void* x, void* y, int64_t n, int dt, int act, int compute_f32) {
 #pragma omp parallel for
   for (int64_t i = 0; i < n; ++i) {

@@ -18,8 +18,8 @@ from . import build as _build
 F32, F16, BF16 = 0, 1, 2
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 ACC = {"f32": 0, "result": 1, "f64": 2}
-ACT = {"none": 0, "relu": 1, "gelu_tanh": 2}
-INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL = 0, 1, 2
+ACT = {"none": 0, "relu": 1, "gelu_tanh": 2, "gelu_tanh_grad": 3}
+INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_BIAS_AND_RESIDUAL = 0, 1, 2, 4
 
 
 class _GemmArgs(C.Structure):
@@ -95,7 +95,10 @@ def _gemm_args(A, B, Cout, dtype_in, dtype_out, acc, act, bias, residual, trans_
     g = _GemmArgs()
     g.dtype_in, g.dtype_out = DTYPES[dtype_in], DTYPES[dtype_out]
     g.acc_mode, g.act = ACC[acc], ACT[act]
-    g.init = INIT_BIAS_ROW if bias is not None else (INIT_RESIDUAL_FULL if residual is not None else INIT_ZERO)
+    if bias is not None and residual is not None:
+        g.init = INIT_BIAS_AND_RESIDUAL
+    else:
+        g.init = INIT_BIAS_ROW if bias is not None else (INIT_RESIDUAL_FULL if residual is not None else INIT_ZERO)
     g.trans_a, g.trans_b, g.bias_after = int(trans_a), int(trans_b), int(bias_after)
     g.batch, g.M, g.N, g.K = batch, M, N, K
     g.lda, g.ldb, g.ldc, g.ldr = A3.shape[2], B3.shape[2], N, N
@@ -110,10 +113,16 @@ def _gemm_args(A, B, Cout, dtype_in, dtype_out, acc, act, bias, residual, trans_
 
 
 def gemm(A, B, *, dtype_in="f32", dtype_out=None, acc="f32", act="none", bias=None, residual=None,
-         trans_a=False, trans_b=False, bias_after=False):
+         trans_a=False, trans_b=False, bias_after=False, gelu_grad_of=None):
     """C = act(init + A @ B).  A: [M,K] or [B,M,K]; B: [K,N] (shared across the batch) or [B,K,N].
-    bias: [N] of dtype_out; residual: [B,M,N] / [M,N] of dtype_out.  Returns storage array of dtype_out."""
+    bias: [N] of dtype_out; residual: [B,M,N] / [M,N] of dtype_out.  gelu_grad_of=Z ([B,M,N] / [M,N]):
+    C = (init + A @ B) * gelu_tanh'(Z), the contraction followed by nova.gelu_backward (excludes residual
+    and act).  Returns storage array of dtype_out."""
     dtype_out = dtype_out or dtype_in
+    if gelu_grad_of is not None:
+        if residual is not None or act != "none":
+            raise ValueError("gelu_grad_of excludes residual and act")
+        act = "gelu_tanh_grad"
     A = np.ascontiguousarray(A, dtype=np_dtype(dtype_in))
     B = np.ascontiguousarray(B, dtype=np_dtype(dtype_in))
     if bias is not None:
@@ -126,6 +135,11 @@ def gemm(A, B, *, dtype_in="f32", dtype_out=None, acc="f32", act="none", bias=No
     N = B3.shape[1] if trans_b else B3.shape[2]
     out = np.zeros((A3.shape[0], M, N), dtype=np_dtype(dtype_out))
     g, _ = _gemm_args(A, B, out, dtype_in, dtype_out, acc, act, bias, residual, trans_a, trans_b, bias_after)
+    if gelu_grad_of is not None:
+        z = np.ascontiguousarray(gelu_grad_of, dtype=np_dtype(dtype_out))
+        if z.size != out.size:
+            raise ValueError("gelu_grad_of must have the shape of the result")
+        g.residual = z.ctypes.data
     rc = lib().nova_oracle_gemm(C.byref(g))
     if rc != 0:
         raise RuntimeError(f"nova_oracle_gemm failed: {rc}")
@@ -157,6 +171,18 @@ def activation(x, dt="f32", act="gelu_tanh", compute_f32=False):
     y = np.empty_like(x)
     lib().nova_oracle_activation(_ptr(x), _ptr(y), C.c_int64(x.size), C.c_int(DTYPES[dt]), C.c_int(ACT[act]),
                                  C.c_int(int(compute_f32)))
+    return y
+
+
+def gelu_backward(grad_out, x, dt="f32", compute_f32=False):
+    """grad_out * gelu_tanh'(x) (nova.gelu_backward)."""
+    go = np.ascontiguousarray(grad_out, dtype=np_dtype(dt))
+    x = np.ascontiguousarray(x, dtype=np_dtype(dt))
+    if go.shape != x.shape:
+        raise ValueError("gelu_backward: shapes differ")
+    y = np.empty_like(x)
+    lib().nova_oracle_gelu_backward(_ptr(go), _ptr(x), _ptr(y), C.c_int64(x.size), C.c_int(DTYPES[dt]),
+                                    C.c_int(int(compute_f32)))
     return y
 
 

@@ -84,10 +84,9 @@ def test_plan_of_a_transformer_style_block():
     lines = [l.strip() for l in plan.splitlines()]
     assert lines[1].startswith("layer_norm")
     assert "gemm init=bias_row(%b1) act=gelu_tanh" in lines[2] and "nova.linear + nova.gelu" in lines[2]
-    # the residual add after the second linear cannot displace its bias: it stays a separate step
-    assert "gemm init=bias_row(%b2) act=none" in lines[3]
-    assert lines[4].startswith("add")
-    assert lines[5].startswith("transpose") and lines[6].startswith("gemm init=zero") and lines[7].startswith("softmax")
+    # the residual add after the second linear joins its bias in one epilogue ("out + x + b_down")
+    assert "gemm init=bias_row(%b2)+residual(%x) act=none" in lines[3] and "nova.linear + nova.add" in lines[3]
+    assert lines[4].startswith("transpose") and lines[5].startswith("gemm init=zero") and lines[6].startswith("softmax")
     _, res = m.signature("block")
     assert res == [(L.BF16, (2, 48, 64)), (L.BF16, (2, 48, 48))]
 
@@ -155,8 +154,7 @@ def test_run_block_matches_oracle_op_by_op(cuda, oracle):
     B = lambda t: _bits(torch, t)
     ln, _, _ = oracle.layer_norm(B(x), B(gm), B(bt), "bf16", compute_f32=True)
     h = oracle.gemm(ln, B(w1), dtype_in="bf16", bias=B(b1), act="gelu_tanh")
-    o = oracle.gemm(h, B(w2), dtype_in="bf16", bias=B(b2))
-    want_r = oracle.add_rowbcast(o, B(x), "bf16")
+    want_r = oracle.gemm(h, B(w2), dtype_in="bf16", bias=B(b2), residual=B(x))
     s = oracle.gemm(ln, np.ascontiguousarray(np.swapaxes(ln, 1, 2)), dtype_in="bf16")
     want_p = oracle.softmax(s, "bf16", compute_f32=True)
     f = lambda bits: oracle.from_bits(bits, "bf16")
@@ -231,3 +229,58 @@ def test_run_backward_ops_match_oracle(cuda, oracle):
     assert oracle.rel_fro(n(gb), want_gb) <= 1e-5
     assert oracle.rel_fro(n(ga), oracle.gemm(n(g2), np.ascontiguousarray(n(b).T))) <= 1e-5
     assert oracle.rel_fro(n(gbm), oracle.gemm(np.ascontiguousarray(n(a).T), n(g2))) <= 1e-5
+
+
+# the FFN backward chain of ltest/test.mlir:39-42: linear_backward -> gelu_backward -> linear_backward
+FFN_BACKWARD = '''
+func.func @ffn_bw(%gy: tensor<2x24x40xbf16>, %h: tensor<2x24x72xbf16>, %w2: tensor<72x40xbf16>,
+                  %z: tensor<2x24x72xbf16>, %x: tensor<2x24x40xbf16>, %w1: tensor<40x72xbf16>,
+                  %m: tensor<24x72xbf16>, %zz: tensor<24x40xbf16>)
+    -> (tensor<2x24x40xbf16>, tensor<40x72xbf16>, tensor<72xbf16>, tensor<24x40xbf16>, tensor<2x24x72xbf16>) {
+  %gh, %gw2, %gb2 = nova.linear_backward %gy, %h, %w2 : tensor<2x24x40xbf16>, tensor<2x24x72xbf16>, tensor<72x40xbf16>
+  %gz = nova.gelu_backward %gh, %z : tensor<2x24x72xbf16>, tensor<2x24x72xbf16>
+  %gx, %gw1, %gb1 = nova.linear_backward %gz, %x, %w1 : tensor<2x24x72xbf16>, tensor<2x24x40xbf16>, tensor<40x72xbf16>
+  %p = nova.matmul %m, %w2 : tensor<24x72xbf16>, tensor<72x40xbf16>
+  %q = nova.gelu_backward %p, %zz : tensor<24x40xbf16>, tensor<24x40xbf16>
+  %s = nova.gelu_backward %z, %h : tensor<2x24x72xbf16>, tensor<2x24x72xbf16>
+  return %gx, %gw1, %gb1, %q, %s : tensor<2x24x40xbf16>, tensor<40x72xbf16>, tensor<72xbf16>, tensor<24x40xbf16>, tensor<2x24x72xbf16>
+}
+'''
+
+
+def test_plan_fuses_gelu_backward_into_the_producing_contraction():
+    plan = Module(FFN_BACKWARD).plan("ffn_bw")
+    lines = [l.strip() for l in plan.splitlines()]
+    # grad_input of the second layer is multiplied by gelu'(%z) in the contraction's epilogue ...
+    fused = [l for l in lines if "grad_input = grad_out x W^T + nova.gelu_backward" in l]
+    assert len(fused) == 1 and "act=gelu_tanh_grad(%z)" in fused[0] and "-> (%gz" in fused[0]
+    # ... its other two contractions still read the unfused %gy, and %gz feeds the first layer's backward
+    assert sum("gemm" in l for l in lines) == 5
+    assert any(l.startswith("gemm") and "nova.matmul + nova.gelu_backward" in l and "act=gelu_tanh_grad(%zz)" in l for l in lines)
+    # a gelu_backward whose grad_out is not a contraction result stays a step of its own
+    assert sum(l.startswith("gelu_backward") for l in lines) == 1
+
+
+@pytest.mark.gpu
+def test_run_ffn_backward_chain_matches_oracle(cuda, oracle):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(9)
+    bf = torch.bfloat16
+    r = lambda *s, sc=1.0: ((torch.rand(*s, device="cuda", generator=g) * 2 - 1) * sc).to(bf)
+    gy, h, w2, z = r(2, 24, 40), r(2, 24, 72), r(72, 40, sc=0.3), r(2, 24, 72, sc=2.0)
+    x, w1, m, zz = r(2, 24, 40), r(40, 72, sc=0.3), r(24, 72), r(24, 40, sc=2.0)
+    gx, gw1, gb1, q, s = Module(FFN_BACKWARD).run("ffn_bw", gy, h, w2, z, x, w1, m, zz)
+    B = lambda t: _bits(torch, t)
+    f = lambda bits: oracle.from_bits(bits, "bf16")
+    T = lambda bits: np.ascontiguousarray(np.swapaxes(bits, -1, -2))
+    gz = oracle.gemm(B(gy), T(B(w2)), dtype_in="bf16", gelu_grad_of=B(z))       # fused epilogue form
+    want_gx = oracle.gemm(gz, T(B(w1)), dtype_in="bf16")
+    want_gw1 = oracle.gemm(T(B(x).reshape(48, 40)), gz.reshape(48, 72), dtype_in="bf16")
+    want_gb1 = oracle.column_sum(gz.reshape(48, 72), "bf16")
+    want_q = oracle.gemm(B(m), B(w2), dtype_in="bf16", gelu_grad_of=B(zz))
+    want_s = oracle.gelu_backward(B(z), B(h), "bf16", compute_f32=True)
+    assert oracle.rel_fro(f(B(gx)), f(want_gx)) <= 4e-3    # two chained bf16 roundings
+    assert oracle.rel_fro(f(B(gw1)), f(want_gw1)) <= 4e-3
+    assert oracle.rel_fro(f(B(gb1)), f(want_gb1)) <= 4e-3
+    assert oracle.rel_fro(f(B(q)), f(want_q)) <= 1e-3
+    assert oracle.rel_fro(f(B(s)), f(want_s)) <= 1e-3

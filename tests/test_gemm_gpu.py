@@ -148,16 +148,38 @@ def test_operand_majors(cuda, oracle, dt, trans_a, trans_b):
 
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("act", [None, "relu", "gelu"])
-@pytest.mark.parametrize("init", ["zero", "bias", "residual"])
+@pytest.mark.parametrize("init", ["zero", "bias", "residual", "bias+residual"])
 def test_epilogues(cuda, oracle, dt, act, init):
     rng = np.random.default_rng(17)
     B, M, N, K = 2, 130, 264, 96
     a = rand_bits(oracle, rng, (B, M, K), dt, "normal")
     b = rand_bits(oracle, rng, (B, K, N), dt, "normal", 0.1)
-    bias = rand_bits(oracle, rng, (N,), dt, "normal") if init == "bias" else None
-    res = rand_bits(oracle, rng, (B, M, N), dt, "normal") if init == "residual" else None
+    bias = rand_bits(oracle, rng, (N,), dt, "normal") if "bias" in init else None
+    res = rand_bits(oracle, rng, (B, M, N), dt, "normal") if "residual" in init else None
     want = oracle.gemm(a, b, dtype_in=dt, bias=bias, residual=res, act={"gelu": "gelu_tanh"}.get(act, act or "none"))
     check(oracle, run_gpu(cuda, a, b, dt, bias=bias, residual=res, act=act), want, dt)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gelu_backward_epilogue_and_standalone_op(cuda, oracle, dt, with_bias):
+    """C = (bias + A @ B) * gelu_tanh'(Z): the contraction followed by nova.gelu_backward, in one launch; and the
+    standalone op.  Z spans the region where the derivative dips below zero and where it saturates."""
+    torch = cuda
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(29)
+    B, M, N, K = 2, 150, 200, 72
+    a = rand_bits(oracle, rng, (B, M, K), dt, "normal")
+    b = rand_bits(oracle, rng, (B, K, N), dt, "normal", 0.1)
+    z = rand_bits(oracle, rng, (B, M, N), dt, "normal", 2.5)
+    bias = rand_bits(oracle, rng, (N,), dt, "normal") if with_bias else None
+    want = oracle.gemm(a, b, dtype_in=dt, bias=bias, gelu_grad_of=z)
+    got = run_gpu(torch, a, b, dt, bias=bias, gelu_grad_of=to_dev(torch, z, dt))
+    check(oracle, got, want, dt)
+    if not with_bias:
+        go = rand_bits(oracle, rng, (B, M, N), dt, "normal")
+        y = ops.gelu_backward(to_dev(torch, go, dt), to_dev(torch, z, dt))
+        check(oracle, to_host(torch, y, dt), oracle.gelu_backward(go, z, dt, compute_f32=True), dt, tol=TOL[dt] if dt != "f32" else 1e-6)
 
 
 def test_accumulate_into_live_output(cuda, oracle):
