@@ -124,8 +124,8 @@ typedef struct nova_b200_gemm_args {
 
 /* How a call will be executed; filled by nova_b200_gemm_plan without launching anything. */
 typedef struct nova_b200_gemm_plan_info {
-  int32_t loader_a;     /* 0 = TMA; unaligned base or pitch: 1 = predicated ld.global loader warps,
-                           2 = re-pitched into aligned scratch first, then TMA (contractions of a few GFLOP or more) */
+  int32_t loader_a;     /* 0 = TMA; unaligned base or pitch: 2 = re-pitched into aligned scratch first, then TMA
+                           (the default), 1 = predicated ld.global loader warps (NOVA_B200_REPITCH=0) */
   int32_t loader_b;
   int32_t store_c;      /* 0 = TMA stores of swizzled 32x128-byte boxes, 1 = element stores (unaligned C) */
   int32_t block_m, block_n, block_k;
@@ -185,6 +185,15 @@ int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream,
 /* y = act(x), n elements, standalone nova.gelu / nova.relu (NovaToLinalgGeneric.cpp:1277-1337,
  * NovaToLinalg.cpp:1053-1084) for graphs where the activation is not adjacent to a contraction. */
 int32_t nova_b200_activation(const void* x_dev, void* y_dev, int64_t n, int32_t dtype, int32_t act, void* stream);
+
+/* nova.layer_norm_backward over [rows, D] (NovaLayerNormBackwardPattern, NovaToLinalgGeneric.cpp:2128-2376;
+ * operand order of NovaOps.td:1038-1049): grad_y, x [rows, D]; gamma [D]; mean_sum, rstd [rows] as the forward
+ * (nova_b200_layer_norm) returned them -- mean_sum is the RAW row sum.  Writes dx [rows, D], dgamma [D], dbeta [D].
+ * gy and x are read once and dx written once; the column sums use the library's per-device scratch.  Rows of more
+ * than 2048 sixteen-byte vectors (2048 elements when a pointer or D is not 16-byte aligned) are refused. */
+int32_t nova_b200_layer_norm_backward(const void* grad_y_dev, const void* x_dev, const void* gamma_dev,
+                                      const void* mean_sum_dev, const void* rstd_dev, void* dx_dev, void* dgamma_dev,
+                                      void* dbeta_dev, int64_t rows, int64_t D, int32_t dtype, void* stream);
 
 /* y = grad_out * gelu_tanh'(x), n elements: standalone nova.gelu_backward (NovaToLinalgGeneric.cpp:1339-1420;
  * ltest/_gelu.mlir, ltest/test.mlir:41). */

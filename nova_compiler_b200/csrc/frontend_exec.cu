@@ -276,7 +276,11 @@ struct Exec {
       if ((st = alloc(type_of(s.outputs[i]), &out[i])) != NOVA_B200_OK) return st;
     const int64_t n = in.empty() ? out[0].numel() : in[0].numel();
     if (k == "activation") st = nova_b200_activation(in[0].ptr, out[0].ptr, n, in[0].dtype, s.act, stream);
-    else if (k == "gelu_backward") st = nova_b200_gelu_backward(in[0].ptr, in[1].ptr, out[0].ptr, n, in[0].dtype, stream);
+    else if (k == "layer_norm_backward") {
+      const int64_t D = in[1].shape.back();
+      st = nova_b200_layer_norm_backward(in[0].ptr, in[1].ptr, in[2].ptr, in[3].ptr, in[4].ptr, out[0].ptr, out[1].ptr,
+                                         out[2].ptr, in[1].numel() / std::max<int64_t>(D, 1), D, in[1].dtype, stream);
+    } else if (k == "gelu_backward") st = nova_b200_gelu_backward(in[0].ptr, in[1].ptr, out[0].ptr, n, in[0].dtype, stream);
     else if (k == "add") {
       const int64_t cols = in[0].shape.back();
       st = nova_b200_add_rowbcast(in[0].ptr, in[1].ptr, out[0].ptr, n / cols, cols, in[1].numel() == n ? 1 : 0, in[0].dtype, stream);

@@ -186,6 +186,17 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu" || n == "nova.softmax") {
       if (in.size() != 1 || !is_float(in[0]->dtype)) return c.fail(op, "expects one float tensor");
       set(0, *in[0]);
+    } else if (n == "nova.layer_norm_backward") {
+      // (grad_y, x, gamma, mean_sum, rstd) -> (x's type, gamma's, gamma's)  (NovaOps.td:1038-1049, NovaOps.cpp:2055-2075)
+      if (in.size() != 5) return c.fail(op, "expects grad_y, x, gamma, mean_sum, rstd");
+      const Type& x = *in[1];
+      if (!is_float(x.dtype) || x.shape.empty() || !(in[0]->shape == x.shape) || in[2]->numel() != x.shape.back() ||
+          in[3]->numel() != x.numel() / std::max<int64_t>(x.shape.back(), 1) || in[4]->numel() != in[3]->numel())
+        return c.fail(op, "operand shapes do not agree");
+      for (int i = 0; i < 5; ++i)
+        if (in[i]->dtype != x.dtype) return c.fail(op, "mixed dtypes are outside the supported subset");
+      if (op.results.size() != 3) return c.fail(op, "produces grad_x, grad_gamma, grad_beta");
+      set(0, x); set(1, *in[2]); set(2, *in[2]);
     } else if (n == "nova.gelu_backward") {
       // (grad_out, input) -> the input's type (GeluBackwardOp::inferReturnTypes, NovaOps.cpp:2130)
       if (in.size() != 2 || !is_float(in[1]->dtype) || in[0]->dtype != in[1]->dtype || !(in[0]->shape == in[1]->shape))
@@ -414,6 +425,9 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu") {
       s.kind = "activation";
       s.act = n == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;
+      s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.layer_norm_backward") {
+      s.kind = "layer_norm_backward";
       s.inputs = op.operands; s.outputs = op.results;
     } else if (n == "nova.gelu_backward") {
       s.kind = "gelu_backward";

@@ -399,6 +399,122 @@ __global__ void column_sum_final_kernel(const float* __restrict__ partial, T* __
   }
 }
 
+// layer_norm_backward.  One CTA walks rows r = blockIdx.x, blockIdx.x + gridDim.x, ...; thread t owns the same
+// vectors (t, t + blockDim.x, ...) of every row, so the per-column sums for dgamma / dbeta accumulate in its
+// registers over all the CTA's rows while dx is produced from the same single read of gy and x.  Per row:
+//   mean = mean_sum/D, xhat = (x - mean) rstd, gyg = gy gamma, s1 = sum gyg, s2 = sum gyg xhat (one block
+//   reduction of the pair), dx = ((gyg - s1/D) - xhat s2/D) rstd.
+// The CTA's column sums go to partial[blockIdx.x][0|1][D] (fp32); ln_backward_finish_kernel adds them up.
+// HBM traffic: gy, x read once, dx written once (+ the small partials).
+template <typename T, int VEC, int kMaxV>
+__global__ void __launch_bounds__(kRowThreads)
+ln_backward_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
+                   const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
+                   float* __restrict__ partial, int64_t rows, int32_t D) {
+  __shared__ float red[2][kRowThreads / 32];
+  using P = Pack<T, VEC>;
+  const int nvec = D / VEC;
+  const int nthreads = blockDim.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = nthreads >> 5;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  P gam[kMaxV];
+  float dg[kMaxV][VEC], db[kMaxV][VEC];
+#pragma unroll
+  for (int i = 0; i < kMaxV; ++i) {
+    const int v = threadIdx.x + i * nthreads;
+    if (v < nvec) gam[i] = reinterpret_cast<const P*>(gamma)[v];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) dg[i][e] = db[i][e] = 0.0f;
+  }
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const P* gyr = reinterpret_cast<const P*>(gy + r * D);
+    const P* xr = reinterpret_cast<const P*>(x + r * D);
+    P pg[kMaxV], px[kMaxV];
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = threadIdx.x + i * nthreads;
+      if (v < nvec) { pg[i] = gyr[v]; px[i] = xr[v]; }
+    }
+    const float mean = ld_f32<T>(mean_sum[r]) * inv_d;
+    const float rs = ld_f32<T>(rstd[r]);
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      if (threadIdx.x + i * nthreads < nvec) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float g = ld_f32<T>(pg[i].e[e]);
+          const float xhat = (ld_f32<T>(px[i].e[e]) - mean) * rs;
+          const float gyg = g * ld_f32<T>(gam[i].e[e]);
+          s1 += gyg;
+          s2 = fmaf(gyg, xhat, s2);
+          dg[i][e] = fmaf(g, xhat, dg[i][e]);
+          db[i][e] += g;
+        }
+      }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (nwarps > 1) {
+      __syncthreads();  // the previous row's readers are done with red
+      if (lane == 0) { red[0][warp] = s1; red[1][warp] = s2; }
+      __syncthreads();
+      s1 = warp_sum(lane < nwarps ? red[0][lane] : 0.0f);
+      s2 = warp_sum(lane < nwarps ? red[1][lane] : 0.0f);
+    }
+    const float m1 = s1 * inv_d, m2 = s2 * inv_d;
+    P* dxr = reinterpret_cast<P*>(dx + r * D);
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int v = threadIdx.x + i * nthreads;
+      if (v < nvec) {
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float xhat = (ld_f32<T>(px[i].e[e]) - mean) * rs;
+          const float gyg = ld_f32<T>(pg[i].e[e]) * ld_f32<T>(gam[i].e[e]);
+          o.e[e] = st_f32<T>(((gyg - m1) - xhat * m2) * rs);
+        }
+        dxr[v] = o;
+      }
+    }
+  }
+  float* pdg = partial + static_cast<size_t>(blockIdx.x) * 2 * D;
+  float* pdb = pdg + D;
+#pragma unroll
+  for (int i = 0; i < kMaxV; ++i) {
+    const int v = threadIdx.x + i * nthreads;
+    if (v < nvec) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { pdg[v * VEC + e] = dg[i][e]; pdb[v * VEC + e] = db[i][e]; }
+    }
+  }
+}
+
+// dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta[c] likewise from [cta][1][c]; several CTA slices per
+// column are combined through shared memory so that short D still fills the machine.
+template <typename T>
+__global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int32_t n_partials, int32_t D,
+                                          T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float sh[2][8][32];
+  const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 8)
+  float a = 0.0f, b = 0.0f;
+  if (c < D)
+    for (int p = threadIdx.y; p < n_partials; p += 8) {
+      a += partial[static_cast<size_t>(p) * 2 * D + c];
+      b += partial[static_cast<size_t>(p) * 2 * D + D + c];
+    }
+  sh[0][threadIdx.y][threadIdx.x] = a;
+  sh[1][threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < D) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { a += sh[0][k][threadIdx.x]; b += sh[1][k][threadIdx.x]; }
+    dgamma[c] = st_f32<T>(a);
+    dbeta[c] = st_f32<T>(b);
+  }
+}
+
 int grid_for(int64_t work_items, int threads, int sm_count) {
   const int64_t want = (work_items + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(sm_count) * 16;
@@ -424,6 +540,66 @@ int32_t nova_b200_layer_norm(const void* x, const void* gamma, const void* beta,
   if (!ctx) return st;
   return dispatch_row_kernel<0>(x, gamma, beta, y, mean_sum, rstd, rows, D, dtype, ctx->sm_count,
                                 static_cast<cudaStream_t>(stream));
+}
+
+int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const void* gamma, const void* mean_sum,
+                                      const void* rstd, void* dx, void* dgamma, void* dbeta, int64_t rows, int64_t D,
+                                      int32_t dtype, void* stream) {
+  if (rows < 0 || D < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "layer_norm_backward: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "layer_norm_backward: dtype must be f32, f16 or bf16");
+  if (D == 0) return NOVA_B200_OK;
+  if (!dgamma || !dbeta) return fail(NOVA_B200_ERR_INVALID_ARG, "layer_norm_backward: null pointer");
+  if (rows > 0 && (!grad_y || !x || !gamma || !mean_sum || !rstd || !dx))
+    return fail(NOVA_B200_ERR_INVALID_ARG, "layer_norm_backward: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype);
+  const uintptr_t align = reinterpret_cast<uintptr_t>(grad_y) | reinterpret_cast<uintptr_t>(x) |
+                          reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(dx);
+  const int vec = (align % 16 == 0 && (D * es) % 16 == 0) ? 16 / es : 1;
+  const int64_t nvec = D / vec;
+  if (nvec > static_cast<int64_t>(kRowThreads) * 8)
+    return fail(NOVA_B200_ERR_UNSUPPORTED,
+                "layer_norm_backward: rows longer than 2048 sixteen-byte vectors (or 2048 elements when unaligned)");
+  // threads: a multiple of 32 covering the row with as few vectors per thread as possible
+  const int threads = static_cast<int>(nvec >= kRowThreads ? kRowThreads : (nvec + 31) / 32 * 32);
+  const int per_thread = static_cast<int>((nvec + threads - 1) / threads);
+  const int max_v = per_thread <= 1 ? 1 : per_thread <= 2 ? 2 : per_thread <= 4 ? 4 : 8;
+  const int resident = std::max(1, std::min(8, 2048 / threads / (max_v >= 4 ? 2 : 1)));
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows, static_cast<int64_t>(ctx->sm_count) * resident)));
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    st = ensure_scratch(ctx, static_cast<size_t>(grid) * 2 * D * sizeof(float));
+    if (st != NOVA_B200_OK) return st;
+  }
+  float* partial = static_cast<float*>(ctx->scratch);
+#define NOVA_LNB(T, V, MV)                                                                                             \
+  ln_backward_kernel<T, V, MV><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x),      \
+                                                        static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
+                                                        static_cast<const T*>(rstd), static_cast<T*>(dx), partial,     \
+                                                        rows, static_cast<int32_t>(D))
+#define NOVA_LNB_MV(T, V)                                                                       \
+  do {                                                                                          \
+    if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);                  \
+    else if (max_v == 4) NOVA_LNB(T, V, 4); else NOVA_LNB(T, V, 8);                             \
+  } while (0)
+  if (dtype == NOVA_B200_F32) { if (vec > 1) NOVA_LNB_MV(float, 4); else NOVA_LNB_MV(float, 1); }
+  else if (dtype == NOVA_B200_F16) { if (vec > 1) NOVA_LNB_MV(__half, 8); else NOVA_LNB_MV(__half, 1); }
+  else { if (vec > 1) NOVA_LNB_MV(__nv_bfloat16, 8); else NOVA_LNB_MV(__nv_bfloat16, 1); }
+#undef NOVA_LNB_MV
+#undef NOVA_LNB
+  NOVA_CUDA_OK(cudaGetLastError());
+  const int fin_grid = static_cast<int>((D + 31) / 32);
+  if (dtype == NOVA_B200_F32)
+    ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
+  else if (dtype == NOVA_B200_F16)
+    ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
+  else
+    ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
 }
 
 int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32_t dtype, void* stream) {

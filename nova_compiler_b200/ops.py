@@ -304,6 +304,28 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
     return y, mean_sum, rstd
 
 
+def layer_norm_backward(grad_y: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, mean_sum: torch.Tensor,
+                        rstd: torch.Tensor):
+    """nova.layer_norm_backward (NovaLayerNormBackwardPattern, NovaToLinalgGeneric.cpp:2128-2376): returns
+    (dx, dgamma, dbeta) from grad_y, x, gamma and the (mean_sum, rstd) the forward saved."""
+    _require_cuda(grad_y, x, gamma, mean_sum, rstd)
+    gc, xc, g = grad_y.contiguous(), x.contiguous(), gamma.contiguous()
+    ms, rs = mean_sum.contiguous(), rstd.contiguous()
+    D = xc.shape[-1]
+    rows = xc.numel() // max(D, 1)
+    if gc.shape != xc.shape or g.numel() != D or ms.numel() != rows or rs.numel() != rows:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "layer_norm_backward: operand shapes do not agree")
+    if any(t.dtype != xc.dtype for t in (gc, g, ms, rs)):
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "layer_norm_backward: mixed dtypes are out of scope")
+    dx = torch.empty_like(xc)
+    dgamma = torch.empty_like(g)
+    dbeta = torch.empty_like(g)
+    L.check(L.load().nova_b200_layer_norm_backward(gc.data_ptr(), xc.data_ptr(), g.data_ptr(), ms.data_ptr(), rs.data_ptr(),
+                                                   dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), rows, D, _dt(xc),
+                                                   _stream()))
+    return dx, dgamma, dbeta
+
+
 def gather(inp: torch.Tensor, indices: torch.Tensor, axis: int = 0, *, return_bad_count: bool = False):
     """nova.gather (NovaGatherOpLowering, NovaToLinalgGeneric.cpp:2372-2472; shapes NovaOps.cpp:1898-1946):
     out[pre..., idx..., post...] = inp[pre..., indices[...], post...].  Leading index dims equal to inp's

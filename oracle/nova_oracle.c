@@ -508,6 +508,59 @@ void nova_oracle_layer_norm(const void* x, const void* gamma, const void* beta, 
   }
 }
 
+/* layer_norm_backward over [rows, D], following NovaLayerNormBackwardPattern
+ * (NovaToLinalgGeneric.cpp:2128-2376; operands gy, x, gamma, mean_sum, rstd per NovaOps.td:1038-1049,
+ * mean_sum being the RAW row sum the forward saved):
+ *   mean = mean_sum*invD; xhat = (x-mean)*rstd; gyg = gy*gamma;
+ *   s1 = sum_d gyg, s2 = sum_d gyg*xhat  (d ascending);
+ *   dx = ((gyg - s1*invD) - xhat*(s2*invD)) * rstd;
+ *   dgamma[d] = sum_rows gy*xhat, dbeta[d] = sum_rows gy  (rows ascending),
+ * every intermediate rounded through the compute type. */
+void nova_oracle_layer_norm_backward(const void* gy, const void* x, const void* gamma, const void* mean_sum,
+                                     const void* rstd_in, void* dx, void* dgamma, void* dbeta, int64_t rows,
+                                     int64_t D, int dt, int compute_f32) {
+  const int ct = compute_f32 ? NOVA_F32 : dt;
+  const float invD = round_through(1.0f / (float)D, ct);
+#pragma omp parallel for
+  for (int64_t r = 0; r < rows; ++r) {
+    const float mean = round_through(load_elem(mean_sum, r, dt) * invD, ct);
+    const float rstd = load_elem(rstd_in, r, dt);
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int64_t d = 0; d < D; ++d) {
+      float gyg = round_through(load_elem(gy, r * D + d, dt) * load_elem(gamma, d, dt), ct);
+      float diff = round_through(load_elem(x, r * D + d, dt) - mean, ct);
+      float xhat = round_through(diff * rstd, ct);
+      float gygx = round_through(gyg * xhat, ct);
+      s1 = round_through(gyg + s1, ct);
+      s2 = round_through(gygx + s2, ct);
+    }
+    const float meanS1 = round_through(s1 * invD, ct), meanS2 = round_through(s2 * invD, ct);
+    for (int64_t d = 0; d < D; ++d) {
+      float gyg = round_through(load_elem(gy, r * D + d, dt) * load_elem(gamma, d, dt), ct);
+      float diff = round_through(load_elem(x, r * D + d, dt) - mean, ct);
+      float xhat = round_through(diff * rstd, ct);
+      float t1 = round_through(gyg - meanS1, ct);
+      float t2 = round_through(xhat * meanS2, ct);
+      float t3 = round_through(t1 - t2, ct);
+      store_elem(dx, r * D + d, dt, round_through(t3 * rstd, ct));
+    }
+  }
+#pragma omp parallel for
+  for (int64_t d = 0; d < D; ++d) {
+    float dg = 0.0f, db = 0.0f;
+    for (int64_t r = 0; r < rows; ++r) {
+      const float mean = round_through(load_elem(mean_sum, r, dt) * invD, ct);
+      const float g = load_elem(gy, r * D + d, dt);
+      float diff = round_through(load_elem(x, r * D + d, dt) - mean, ct);
+      float xhat = round_through(diff * load_elem(rstd_in, r, dt), ct);
+      dg = round_through(dg + round_through(g * xhat, ct), ct);
+      db = round_through(db + g, ct);
+    }
+    store_elem(dgamma, d, dt, dg);
+    store_elem(dbeta, d, dt, db);
+  }
+}
+
 /* out[c] = sum_r x[r, c], rows ascending, fp32 accumulation (the grad_bias reduction of
  * NovaLinearBackwardPattern, NovaToLinalgGeneric.cpp:1970-1985, over the flattened batch*M rows);
  * compute_f32 == 0 rounds the running sum through dt after every add, as the reference does. */

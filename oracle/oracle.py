@@ -223,6 +223,26 @@ def layer_norm(x, gamma, beta, dt="f32", compute_f32=False):
     return y, mean_sum, rstd
 
 
+def layer_norm_backward(grad_y, x, gamma, mean_sum, rstd, dt="f32", compute_f32=False):
+    """(dx, dgamma, dbeta) of nova.layer_norm_backward; mean_sum is the raw row sum the forward returned."""
+    gy = np.ascontiguousarray(grad_y, dtype=np_dtype(dt))
+    x = np.ascontiguousarray(x, dtype=np_dtype(dt))
+    gamma = np.ascontiguousarray(gamma, dtype=np_dtype(dt)).reshape(-1)
+    mean_sum = np.ascontiguousarray(mean_sum, dtype=np_dtype(dt)).reshape(-1)
+    rstd = np.ascontiguousarray(rstd, dtype=np_dtype(dt)).reshape(-1)
+    D = x.shape[-1]
+    rows = x.size // D
+    if gy.shape != x.shape or gamma.size != D or mean_sum.size != rows or rstd.size != rows:
+        raise ValueError("layer_norm_backward: operand shapes do not agree")
+    dx = np.empty_like(x)
+    dgamma = np.empty(D, dtype=x.dtype)
+    dbeta = np.empty(D, dtype=x.dtype)
+    lib().nova_oracle_layer_norm_backward(_ptr(gy), _ptr(x), _ptr(gamma), _ptr(mean_sum), _ptr(rstd), _ptr(dx),
+                                          _ptr(dgamma), _ptr(dbeta), C.c_int64(rows), C.c_int64(D),
+                                          C.c_int(DTYPES[dt]), C.c_int(int(compute_f32)))
+    return dx, dgamma, dbeta
+
+
 def column_sum(x, dt="f32", compute_f32=True):
     x = np.ascontiguousarray(x, dtype=np_dtype(dt))
     cols = x.shape[-1]

@@ -76,21 +76,25 @@ def test_plan_aligned_operands_use_tma(lib):
 
 
 def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
-    # 1000 x 1000 x 999 bf16: A pitch 1998 B (not 16-byte aligned) -> loader warps (2 GFLOP: a copy would not pay);
-    # B, C pitch 2000 B -> TMA / vector stores
+    # 1000 x 1000 x 999 bf16: A pitch 1998 B (not 16-byte aligned): re-pitched into scratch (1000 rows of 1000
+    # elements), then TMA; B, C pitch 2000 B -> TMA / vector stores
     st, info = _plan(lib, _args(1000, 1000, 999))
-    assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (1, 0, 0)
-    # the same A pitch under a 16 GFLOP contraction: A is re-pitched into scratch (2000 rows of 1000 elements)
-    st, info = _plan(lib, _args(2000, 4000, 999))
     assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (2, 0, 0)
-    assert info.scratch_bytes == (2000 * 1000 * 2 + 255) // 256 * 256
+    assert info.scratch_bytes == (1000 * 1000 * 2 + 255) // 256 * 256
+    # NOVA_B200_REPITCH=0: read in place by the loader warps, no scratch
+    os.environ["NOVA_B200_REPITCH"] = "0"
+    try:
+        st, info = _plan(lib, _args(1000, 1000, 999))
+    finally:
+        del os.environ["NOVA_B200_REPITCH"]
+    assert st == L.OK and (info.loader_a, info.loader_b, info.scratch_bytes) == (1, 0, 0)
     # 4095 x 11007 x 4097: every pitch is odd in bytes/16; both operands re-pitched, C written with element stores
     st, info = _plan(lib, _args(4095, 11007, 4097))
     assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (2, 2, 1)
     assert (info.block_m, info.block_n) == (256, 256)
     # an aligned pitch with a misaligned base also needs the loader
     st, info = _plan(lib, _args(256, 256, 256, a=0x1002))
-    assert st == L.OK and info.loader_a == 1 and info.loader_b == 0
+    assert st == L.OK and info.loader_a == 2 and info.loader_b == 0
 
 
 def test_plan_f32_modes(lib):

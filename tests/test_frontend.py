@@ -284,3 +284,54 @@ def test_run_ffn_backward_chain_matches_oracle(cuda, oracle):
     assert oracle.rel_fro(f(B(gb1)), f(want_gb1)) <= 4e-3
     assert oracle.rel_fro(f(B(q)), f(want_q)) <= 1e-3
     assert oracle.rel_fro(f(B(s)), f(want_s)) <= 1e-3
+
+
+# forward + backward of one pre-norm FFN block, the op chain of ltest/test.mlir:20-43 at small sizes
+BLOCK_TRAIN = '''
+func.func @train(%x: tensor<2x16x40xf32>, %g: tensor<40xf32>, %b: tensor<40xf32>, %w1: tensor<40x72xf32>,
+                 %b1: tensor<72xf32>, %w2: tensor<72x40xf32>, %b2: tensor<40xf32>, %gy: tensor<2x16x40xf32>)
+    -> (tensor<2x16x40xf32>, tensor<2x16x40xf32>, tensor<40xf32>, tensor<40xf32>, tensor<40x72xf32>, tensor<72x40xf32>) {
+  %ln, %sum, %rstd = nova.layer_norm %x, %g, %b : tensor<2x16x40xf32>, tensor<40xf32>, tensor<40xf32>
+  %z = nova.linear %ln, %w1, %b1 : tensor<2x16x40xf32>, tensor<40x72xf32>, tensor<72xf32>
+  %h = nova.gelu %z : tensor<2x16x72xf32>
+  %o = nova.linear %h, %w2, %b2 : tensor<2x16x72xf32>, tensor<72x40xf32>, tensor<40xf32>
+  %y = nova.add %o, %x : tensor<2x16x40xf32>, tensor<2x16x40xf32>
+  %gh, %gw2, %gb2 = nova.linear_backward %gy, %h, %w2 : tensor<2x16x40xf32>, tensor<2x16x72xf32>, tensor<72x40xf32>
+  %gz = nova.gelu_backward %gh, %z : tensor<2x16x72xf32>, tensor<2x16x72xf32>
+  %gln, %gw1, %gb1 = nova.linear_backward %gz, %ln, %w1 : tensor<2x16x72xf32>, tensor<2x16x40xf32>, tensor<40x72xf32>
+  %gx0, %gg, %gbeta = nova.layer_norm_backward %gln, %x, %g, %sum, %rstd : tensor<2x16x40xf32>, tensor<2x16x40xf32>, tensor<40xf32>, tensor<2x16xf32>, tensor<2x16xf32>
+  %gx = nova.add %gx0, %gy : tensor<2x16x40xf32>, tensor<2x16x40xf32>
+  return %y, %gx, %gg, %gbeta, %gw1, %gw2 : tensor<2x16x40xf32>, tensor<2x16x40xf32>, tensor<40xf32>, tensor<40xf32>, tensor<40x72xf32>, tensor<72x40xf32>
+}
+'''
+
+
+def test_plan_of_a_training_step_keeps_the_pre_activation_for_the_backward():
+    plan = Module(BLOCK_TRAIN).plan("train")
+    lines = [l.strip() for l in plan.splitlines()]
+    # %z is needed by gelu_backward, so the forward GELU is NOT folded into the first linear's epilogue
+    assert any(l.startswith("gemm init=bias_row(%b1) act=none") for l in lines)
+    assert any(l.startswith("activation") for l in lines)
+    assert any("act=gelu_tanh_grad(%z)" in l for l in lines)
+    assert sum(l.startswith("layer_norm_backward") for l in lines) == 1
+
+
+@pytest.mark.gpu
+def test_run_training_step_matches_autograd(cuda):
+    """The whole block, forward and backward, against torch autograd in float64 (an independent check of the chain
+    rule; the per-op parity against the oracle is in the other tests)."""
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(11)
+    r = lambda *s, sc=1.0: (torch.rand(*s, device="cuda", generator=g) * 2 - 1) * sc
+    x, gm, bt = r(2, 16, 40), r(40) + 1.5, r(40)
+    w1, b1, w2, b2, gy = r(40, 72, sc=0.3), r(72, sc=0.3), r(72, 40, sc=0.3), r(40, sc=0.3), r(2, 16, 40)
+    y, gx, gg, gbeta, gw1, gw2 = Module(BLOCK_TRAIN).run("train", x, gm, bt, w1, b1, w2, b2, gy)
+    d = lambda t: t.detach().double().requires_grad_(True)
+    X, G, Bt, W1, B1, W2, B2 = map(d, (x, gm, bt, w1, b1, w2, b2))
+    ln = torch.nn.functional.layer_norm(X, (40,), G, Bt, eps=1e-5)
+    Y = torch.nn.functional.gelu(ln @ W1 + B1, approximate="tanh") @ W2 + B2 + X
+    Y.backward(gy.double())
+    rel = lambda a, b: float((a.double() - b).norm() / b.norm())
+    assert rel(y, Y.detach()) <= 1e-5
+    assert rel(gx, X.grad) <= 2e-5 and rel(gg, G.grad) <= 2e-5 and rel(gbeta, Bt.grad) <= 2e-5
+    assert rel(gw1, W1.grad) <= 2e-5 and rel(gw2, W2.grad) <= 2e-5

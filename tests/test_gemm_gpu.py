@@ -243,7 +243,12 @@ def test_unaligned_pitch_loader_matches_tma_bit_for_bit(cuda, oracle):
     bp = torch.zeros(1, K, 336, device="cuda", dtype=torch.bfloat16); bp[:, :, :N] = b
     cp = torch.zeros(1, M, 336, device="cuda", dtype=torch.bfloat16)
     aligned = ops.gemm(ap[:, :, :K], bp[:, :, :N], out=cp[:, :, :N])
-    ragged = ops.gemm(a, b)  # pitches 514 B / 666 B: neither is a multiple of 16
+    os.environ["NOVA_B200_REPITCH"] = "0"  # read in place by the loader warps
+    try:
+        ragged = ops.gemm(a, b)  # pitches 514 B / 666 B: neither is a multiple of 16
+        torch.cuda.synchronize()
+    finally:
+        del os.environ["NOVA_B200_REPITCH"]
     assert torch.equal(aligned, ragged)
     check(oracle, to_host(torch, ragged, "bf16"), oracle.gemm(to_host(torch, a, "bf16"), to_host(torch, b, "bf16"),
                                                                dtype_in="bf16"), "bf16")

@@ -146,3 +146,35 @@ def test_column_sum_and_backward_ops(cuda, oracle, dt):
     ga, gbm = ops.matmul_backward(to_dev(cuda, go[0], dt), to_dev(cuda, x[0], dt), to_dev(cuda, w, dt))
     check(oracle, to_host(cuda, ga, dt), oracle.gemm(go[0], np.ascontiguousarray(w.T), dtype_in=dt), dt)
     check(oracle, to_host(cuda, gbm, dt), oracle.gemm(np.ascontiguousarray(x[0].T), go[0], dtype_in=dt), dt)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_layer_norm_backward(cuda, oracle, dt):
+    """dx, dgamma, dbeta from the saved (mean_sum, rstd) of the forward; vectorised and element-wise row shapes,
+    one to many rows per CTA; fp32 arithmetic rounded once, as the oracle's compute_f32 mode."""
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(6)
+    for rows, D in [(64, 384), (8192, 384), (33, 1000), (700, 4096), (5, 8192), (7, 37), (1, 1), (300, 2048), (40, 16384)]:
+        if dt == "f32" and D > 8192:
+            continue  # beyond 2048 sixteen-byte vectors: refused (checked below)
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 2.0)
+        g = rand_bits(oracle, rng, (D,), dt, "normal")
+        b = rand_bits(oracle, rng, (D,), dt, "normal")
+        gy = rand_bits(oracle, rng, (rows, D), dt, "normal")
+        _, ms, rs = oracle.layer_norm(x, g, b, dt, compute_f32=True)
+        dx, dg, db = ops.layer_norm_backward(to_dev(cuda, gy, dt), to_dev(cuda, x, dt), to_dev(cuda, g, dt),
+                                             to_dev(cuda, ms, dt), to_dev(cuda, rs, dt))
+        wdx, wdg, wdb = oracle.layer_norm_backward(gy, x, g, ms, rs, dt, compute_f32=True)
+        check(oracle, to_host(cuda, dx, dt), wdx, dt)
+        # column sums over `rows` terms: fp32 on both sides, summation order differs
+        check(oracle, to_host(cuda, dg, dt), wdg, dt, tol=2e-3 if dt != "f32" else 2e-5)
+        check(oracle, to_host(cuda, db, dt), wdb, dt, tol=2e-3 if dt != "f32" else 2e-5)
+    # zero rows: the column sums are zeros, nothing else is touched
+    z = cuda.zeros(0, 64, device="cuda")
+    dx, dg, db = ops.layer_norm_backward(z, z, cuda.ones(64, device="cuda"), cuda.zeros(0, device="cuda"), cuda.zeros(0, device="cuda"))
+    assert dx.shape == (0, 64) and float(dg.abs().sum()) == 0.0 and float(db.abs().sum()) == 0.0
+    from nova_compiler_b200 import _lib as L
+    big = cuda.zeros(2, 8192 + 4, device="cuda")
+    with pytest.raises(L.NovaB200Error) as e:
+        ops.layer_norm_backward(big, big, cuda.ones(8196, device="cuda"), cuda.zeros(2, device="cuda"), cuda.ones(2, device="cuda"))
+    assert e.value.status == L.ERR_UNSUPPORTED
