@@ -223,6 +223,28 @@ int32_t nova_b200_layer_norm(const void* x_dev, const void* gamma_dev, const voi
  * NovaToLinalgGeneric.cpp:1427-1534): e = exp(x - max), out = e * (1 / max(sum e, 1e-7)). */
 int32_t nova_b200_softmax(const void* x_dev, void* y_dev, int64_t rows, int64_t D, int32_t dtype, void* stream);
 
+/* nova.sce over the last dim of logits[rows, C] with one target class per row (NovaSceForwardLowering,
+ * NovaToLinalgGeneric.cpp:801-1010): softmax_out = exp(x - max) / max(sum, 1e-7) and
+ * loss_out[0] = mean over rows of log(max(sum, 1e-7)) - (x[target] - max).  Targets narrower than 32 bits are
+ * zero-extended; a target outside [0, C) contributes x[target] = 0 and is counted in *bad_count_dev (int64, may be
+ * NULL).  The row statistics pass through the library's per-device scratch. */
+int32_t nova_b200_sce(const void* logits_dev, const void* targets_dev, void* softmax_out_dev, void* loss_out_dev,
+                      int64_t rows, int64_t C, int32_t dtype, int32_t idx_dtype, int64_t* bad_count_dev, void* stream);
+
+/* nova.sce_backward, class dim last (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137):
+ * grad[r, c] = (softmax[r, c] - (c == target[r])) * (1 / rows). */
+int32_t nova_b200_sce_backward(const void* softmax_dev, const void* targets_dev, void* grad_dev, int64_t rows, int64_t C,
+                               int32_t dtype, int32_t idx_dtype, void* stream);
+
+/* nova.scatter_add (NovaScatterAddOpLowering, NovaToLinalg.cpp:1086-1294) IN PLACE on the canonical view
+ * inout[pre, axis_len, post], idx[n_idx], src[pre, n_idx, post]: inout[p, idx[i], q] += src[p, i, q] with atomic
+ * adds (repeated indices accumulate in an unspecified order, as in the reference); indices outside [0, axis_len)
+ * are skipped and counted in *bad_count_dev (int64, may be NULL).  The caller copies `input` first when the op's
+ * input must survive. */
+int32_t nova_b200_scatter_add(void* inout_dev, const void* idx_dev, const void* src_dev, int64_t pre, int64_t axis_len,
+                              int64_t post, int64_t n_idx, int32_t idx_dtype, int32_t dtype, int64_t* bad_count_dev,
+                              void* stream);
+
 /* nova.gather (NovaGatherOpLowering, NovaToLinalgGeneric.cpp:2372-2472) on the canonical view
  * in[pre, axis_len, post], idx[n_idx] (or idx[pre, n_idx] when batched_idx != 0) -> out[pre, n_idx, post].
  * Bit-exact row copies.  Indices < 32 bits wide are zero-extended (:2446-2449).  Out-of-range

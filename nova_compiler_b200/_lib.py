@@ -70,6 +70,12 @@ PROTOTYPES = {
     "nova_b200_gemm_host": (C.c_int32, [C.POINTER(GemmArgs)]),
     "nova_b200_gemm_f32_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
     "nova_b200_activation": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]),
+    "nova_b200_sce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
+                                  C.c_int32, C.c_void_p, C.c_void_p]),
+    "nova_b200_sce_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
+                                           C.c_int32, C.c_void_p]),
+    "nova_b200_scatter_add": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "nova_b200_layer_norm_backward": (C.c_int32, [C.c_void_p] * 8 + [C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_gelu_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_add_rowbcast": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,

@@ -276,7 +276,23 @@ struct Exec {
       if ((st = alloc(type_of(s.outputs[i]), &out[i])) != NOVA_B200_OK) return st;
     const int64_t n = in.empty() ? out[0].numel() : in[0].numel();
     if (k == "activation") st = nova_b200_activation(in[0].ptr, out[0].ptr, n, in[0].dtype, s.act, stream);
-    else if (k == "layer_norm_backward") {
+    else if (k == "sce" || k == "sce_backward") {
+      const int64_t Cn = in[0].shape.back();
+      const int64_t rows = in[0].numel() / std::max<int64_t>(Cn, 1);
+      if (k == "sce") st = nova_b200_sce(in[0].ptr, in[1].ptr, out[0].ptr, out[1].ptr, rows, Cn, in[0].dtype, in[1].dtype, nullptr, stream);
+      else st = nova_b200_sce_backward(in[0].ptr, in[1].ptr, out[0].ptr, rows, Cn, in[0].dtype, in[1].dtype, stream);
+    } else if (k == "scatter_add") {
+      const int64_t r = static_cast<int64_t>(in[0].shape.size());
+      int64_t axis = s.attrs.count("axis") ? s.attrs.at("axis") : 0;
+      if (axis < 0) axis += r;
+      int64_t pre = 1, post = 1;
+      for (int64_t i = 0; i < axis; ++i) pre *= in[0].shape[i];
+      for (int64_t i = axis + 1; i < r; ++i) post *= in[0].shape[i];
+      NOVA_CUDA_OK(cudaMemcpyAsync(out[0].ptr, in[0].ptr, static_cast<size_t>(in[0].numel()) * dtype_bytes(in[0].dtype),
+                                   cudaMemcpyDeviceToDevice, stream));
+      st = nova_b200_scatter_add(out[0].ptr, in[1].ptr, in[2].ptr, pre, in[0].shape[axis], post, in[2].shape[axis],
+                                 in[1].dtype, in[0].dtype, nullptr, stream);
+    } else if (k == "layer_norm_backward") {
       const int64_t D = in[1].shape.back();
       st = nova_b200_layer_norm_backward(in[0].ptr, in[1].ptr, in[2].ptr, in[3].ptr, in[4].ptr, out[0].ptr, out[1].ptr,
                                          out[2].ptr, in[1].numel() / std::max<int64_t>(D, 1), D, in[1].dtype, stream);

@@ -301,7 +301,26 @@ bool parse_statement(const std::string& text, int line, Op* op, std::string* err
       if (!c.accept(']')) return fail_at(line, "expected ']'", err);
       continue;
     }
-    if (c.peek('{')) { c.skip_group(); continue; }
+    if (c.peek('{')) {  // attribute dictionary: integer entries (`{dim = -1 : i64}`) are kept, the rest ignored
+      const size_t b = c.i;
+      c.skip_group();
+      const std::string d = c.s.substr(b, c.i - b);
+      for (size_t i = 0; i < d.size();) {
+        if (!(std::isalpha(static_cast<unsigned char>(d[i])) || d[i] == '_')) { ++i; continue; }
+        size_t j = i;
+        while (j < d.size() && (std::isalnum(static_cast<unsigned char>(d[j])) || d[j] == '_' || d[j] == '.')) ++j;
+        size_t k = j;
+        while (k < d.size() && d[k] == ' ') ++k;
+        if (k < d.size() && d[k] == '=') {
+          ++k;
+          while (k < d.size() && d[k] == ' ') ++k;
+          if (k < d.size() && (d[k] == '-' || std::isdigit(static_cast<unsigned char>(d[k]))))
+            op->attrs[d.substr(i, j - i)] = std::strtoll(d.c_str() + k, nullptr, 10);
+        }
+        i = j;
+      }
+      continue;
+    }
     if (c.accept('(')) {  // (name = value)
       const std::string k = c.ident();
       if (!c.accept('=')) return fail_at(line, "expected '=' in attribute", err);

@@ -186,6 +186,40 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu" || n == "nova.softmax") {
       if (in.size() != 1 || !is_float(in[0]->dtype)) return c.fail(op, "expects one float tensor");
       set(0, *in[0]);
+    } else if (n == "nova.sce") {
+      // (logits [..., C], targets [...]) -> (softmax ~ logits, loss [1])  (SceOp::inferReturnTypes, NovaOps.cpp:1648-1677)
+      if (in.size() != 2 || !is_float(in[0]->dtype) || is_float(in[1]->dtype) || in[0]->shape.empty())
+        return c.fail(op, "expects float logits and integer targets");
+      if (in[1]->numel() != in[0]->numel() / std::max<int64_t>(in[0]->shape.back(), 1))
+        return c.fail(op, "one target per row of logits");
+      if (op.results.size() != 2) return c.fail(op, "produces softmax and loss");
+      Type loss = *in[0];
+      loss.shape = {1};
+      set(0, *in[0]); set(1, loss);
+    } else if (n == "nova.sce_backward") {
+      // (softmax, targets) {dim} -> grad ~ softmax  (SceBackwardOp::inferReturnTypes, NovaOps.cpp:2148-2160)
+      if (in.size() != 2 || !is_float(in[0]->dtype) || is_float(in[1]->dtype) || in[0]->shape.empty())
+        return c.fail(op, "expects the forward's softmax and integer targets");
+      const int64_t r = static_cast<int64_t>(in[0]->shape.size());
+      const int64_t dim = op.attrs.count("dim") ? op.attrs.at("dim") : -1;
+      if (dim != -1 && dim != r - 1) return c.fail(op, "only the last dimension as class dimension is supported");
+      if (in[1]->numel() != in[0]->numel() / std::max<int64_t>(in[0]->shape.back(), 1))
+        return c.fail(op, "one target per row");
+      set(0, *in[0]);
+    } else if (n == "nova.scatter_add") {
+      // (input, indices, src) axis -> input's type; shapes match except at axis (ScatterAddOp::verify, NovaOps.cpp:1990-2026)
+      if (in.size() != 3 || !is_float(in[0]->dtype) || is_float(in[1]->dtype) || in[2]->dtype != in[0]->dtype)
+        return c.fail(op, "expects float input, integer indices, src of the input's type");
+      const int64_t r = static_cast<int64_t>(in[0]->shape.size());
+      int64_t axis = op.attrs.count("axis") ? op.attrs.at("axis") : 0;
+      if (axis < 0) axis += r;
+      if (static_cast<int64_t>(in[2]->shape.size()) != r) return c.fail(op, "input and src must have same rank");
+      if (axis < 0 || axis >= r) return c.fail(op, "axis is out of bounds");
+      for (int64_t i = 0; i < r; ++i) {
+        if (i == axis) { if (in[2]->shape[i] != in[1]->numel()) return c.fail(op, "src dimension at axis must match index size"); }
+        else if (in[0]->shape[i] != in[2]->shape[i]) return c.fail(op, "input and src shapes must match except at axis");
+      }
+      set(0, *in[0]);
     } else if (n == "nova.layer_norm_backward") {
       // (grad_y, x, gamma, mean_sum, rstd) -> (x's type, gamma's, gamma's)  (NovaOps.td:1038-1049, NovaOps.cpp:2055-2075)
       if (in.size() != 5) return c.fail(op, "expects grad_y, x, gamma, mean_sum, rstd");
@@ -425,6 +459,9 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu" || n == "nova.relu") {
       s.kind = "activation";
       s.act = n == "nova.relu" ? NOVA_B200_ACT_RELU : NOVA_B200_ACT_GELU_TANH;
+      s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.sce" || n == "nova.sce_backward" || n == "nova.scatter_add") {
+      s.kind = n.substr(5);
       s.inputs = op.operands; s.outputs = op.results;
     } else if (n == "nova.layer_norm_backward") {
       s.kind = "layer_norm_backward";

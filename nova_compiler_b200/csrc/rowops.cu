@@ -60,7 +60,8 @@ constexpr int kRowThreads = 256;
 template <typename T, int VEC, int TPR, int kMaxV, int kMode>
 __global__ void __launch_bounds__(kRowThreads, (VEC > 1 && kMaxV > 0 && kMaxV <= 2) ? 6 : (VEC > 1 && kMaxV == 4 ? 5 : 1))
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
-           T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t prefetch_next) {
+           T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t prefetch_next,
+           float* __restrict__ row_stats) {  // softmax only, optional: {row max, sum of exp(x - max)} per row
   __shared__ float red[kRowThreads / 32];
   constexpr int kRowsPerCta = kRowThreads / TPR;
   constexpr bool CACHED = kMaxV > 0;
@@ -162,6 +163,7 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
         }
       }
       const float s = row_reduce<TPR, false>(part, red);
+      if (row_stats != nullptr && active && t == 0) { row_stats[2 * row] = m; row_stats[2 * row + 1] = s; }
       const float recip = 1.0f / fmaxf(s, 1.0e-7f);
       auto emit = [&](int i, const P& in) {
         P o;
@@ -184,7 +186,7 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
 
 template <typename T, int VEC, int kMode>
 int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
-                          int64_t rows, int64_t D, int sm_count, cudaStream_t st) {
+                          int64_t rows, int64_t D, int sm_count, cudaStream_t st, float* stats) {
   const T* xp = static_cast<const T*>(x);
   const T* gp = static_cast<const T*>(gamma);
   const T* bp = static_cast<const T*>(beta);
@@ -202,7 +204,7 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
   };
 #define NOVA_ROW(TPR_, MAXV_)                                                                             \
   row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_), kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, \
-                                                                                     d, (TPR_) == 32 ? 0 : 1)
+                                                                                     d, (TPR_) == 32 ? 0 : 1, stats)
   // Vectors a thread keeps in registers are kept few (occupancy sets the bytes in flight per SM):
   // longer rows get more threads, not more registers.
   constexpr int kWarpMv = VEC == 1 ? 32 : (kMode == 0 ? 4 : 8);
@@ -228,22 +230,22 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
 
 template <int kMode>
 int32_t dispatch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
-                            int64_t rows, int64_t D, int32_t dtype, int sm_count, cudaStream_t st) {
+                            int64_t rows, int64_t D, int32_t dtype, int sm_count, cudaStream_t st, float* stats = nullptr) {
   const int es = dtype_bytes(dtype);
   const int vec = 16 / es;
   auto aligned16 = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec_ok = D % vec == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   switch (dtype) {
     case NOVA_B200_F32:
-      return vec_ok ? launch_row_kernel<float, 4, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
-                    : launch_row_kernel<float, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+      return vec_ok ? launch_row_kernel<float, 4, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
+                    : launch_row_kernel<float, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
     case NOVA_B200_F16:
-      return vec_ok ? launch_row_kernel<__half, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
-                    : launch_row_kernel<__half, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+      return vec_ok ? launch_row_kernel<__half, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
+                    : launch_row_kernel<__half, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
     case NOVA_B200_BF16:
       return vec_ok
-                 ? launch_row_kernel<__nv_bfloat16, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st)
-                 : launch_row_kernel<__nv_bfloat16, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st);
+                 ? launch_row_kernel<__nv_bfloat16, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
+                 : launch_row_kernel<__nv_bfloat16, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
     default:
       return fail(NOVA_B200_ERR_UNSUPPORTED, "row op: dtype must be f32, f16 or bf16");
   }
@@ -515,6 +517,89 @@ __global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int
   }
 }
 
+// ---------------------------------------------------------------- softmax cross-entropy, scatter_add
+
+__device__ __forceinline__ int64_t load_index(const void* idx, int64_t q, int32_t idx_dtype) {
+  if (idx_dtype == NOVA_B200_I16) return static_cast<int64_t>(static_cast<const uint16_t*>(idx)[q]);  // zero-extended
+  if (idx_dtype == NOVA_B200_I32) return static_cast<int64_t>(static_cast<const int32_t*>(idx)[q]);
+  return static_cast<const int64_t*>(idx)[q];
+}
+
+// loss = mean over rows of log(max(sum_exp, 1e-7)) - (x[target] - max), from the {max, sum_exp} pairs the softmax
+// kernel left per row.  One CTA: every thread sums its rows in ascending order, then a fixed tree, so the result
+// does not depend on scheduling.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sce_loss_kernel(const T* __restrict__ logits, const void* __restrict__ targets, const float* __restrict__ row_stats,
+                T* __restrict__ loss, int64_t rows, int64_t C, int32_t idx_dtype, unsigned long long* bad) {
+  __shared__ float red[32];
+  float acc = 0.0f;
+  unsigned long long my_bad = 0;
+  for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+    const int64_t t = load_index(targets, r, idx_dtype);
+    float xt = 0.0f;
+    if (t < 0 || t >= C) ++my_bad; else xt = ld_f32<T>(logits[r * C + t]);
+    acc += logf(fmaxf(row_stats[2 * r + 1], 1.0e-7f)) - (xt - row_stats[2 * r]);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) loss[0] = st_f32<T>(rows > 0 ? v / static_cast<float>(rows) : 0.0f);
+  }
+  if (bad != nullptr && my_bad != 0) atomicAdd(bad, my_bad);
+}
+
+// grad[r, c] = (softmax[r, c] - (c == target[r])) * inv_n; one 16-byte vector per thread.
+template <typename T, int VEC>
+__global__ void sce_backward_kernel(const T* __restrict__ sm, const void* __restrict__ targets, T* __restrict__ grad,
+                                    int64_t rows, int64_t C, int32_t idx_dtype, float inv_n) {
+  using P = Pack<T, VEC>;
+  const int64_t vec_per_row = C / VEC;
+  const int64_t n = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int64_t c0 = (i - r * vec_per_row) * VEC;
+    const int64_t t = load_index(targets, r, idx_dtype);
+    P v = reinterpret_cast<const P*>(sm)[i];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float p = ld_f32<T>(v.e[e]);
+      if (c0 + e == t) p += -1.0f;
+      v.e[e] = st_f32<T>(p * inv_n);
+    }
+    reinterpret_cast<P*>(grad)[i] = v;
+  }
+}
+
+__device__ __forceinline__ void atomic_add_elem(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add_elem(__half* p, __half v) { atomicAdd(p, v); }
+__device__ __forceinline__ void atomic_add_elem(__nv_bfloat16* p, __nv_bfloat16 v) { atomicAdd(p, v); }
+
+// inout[p, idx[i], q] += src[p, i, q]; one thread per src element, atomics because indices may repeat.
+template <typename T>
+__global__ void scatter_add_kernel(T* __restrict__ inout, const void* __restrict__ idx, const T* __restrict__ src,
+                                   int64_t pre, int64_t axis_len, int64_t post, int64_t n_idx, int32_t idx_dtype,
+                                   unsigned long long* bad) {
+  const int64_t n = pre * n_idx * post;
+  for (int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; e < n;
+       e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t q = e % post;
+    const int64_t pi = e / post;
+    const int64_t i = pi % n_idx;
+    const int64_t p = pi / n_idx;
+    const int64_t t = load_index(idx, i, idx_dtype);
+    if (t < 0 || t >= axis_len) {
+      if (bad != nullptr && q == 0) atomicAdd(bad, 1ull);
+      continue;
+    }
+    atomic_add_elem(inout + (p * axis_len + t) * post + q, src[e]);
+  }
+}
+
 int grid_for(int64_t work_items, int threads, int sm_count) {
   const int64_t want = (work_items + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(sm_count) * 16;
@@ -613,6 +698,93 @@ int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32
   if (!ctx) return st;
   return dispatch_row_kernel<1>(x, nullptr, nullptr, y, nullptr, nullptr, rows, D, dtype, ctx->sm_count,
                                 static_cast<cudaStream_t>(stream));
+}
+
+static bool is_index_dtype(int32_t dt) { return dt == NOVA_B200_I16 || dt == NOVA_B200_I32 || dt == NOVA_B200_I64; }
+
+int32_t nova_b200_sce(const void* logits, const void* targets, void* softmax_out, void* loss_out, int64_t rows, int64_t C,
+                      int32_t dtype, int32_t idx_dtype, int64_t* bad_count, void* stream) {
+  if (rows < 0 || C < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "sce: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce: dtype must be f32, f16 or bf16");
+  if (!is_index_dtype(idx_dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce: target dtype must be i16, i32 or i64");
+  if (C > (1ll << 30)) return fail(NOVA_B200_ERR_TOO_LARGE, "sce: C exceeds 2^30");
+  if (!loss_out) return fail(NOVA_B200_ERR_INVALID_ARG, "sce: null pointer");
+  if (rows > 0 && C > 0 && (!logits || !targets || !softmax_out)) return fail(NOVA_B200_ERR_INVALID_ARG, "sce: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    st = ensure_scratch(ctx, static_cast<size_t>(std::max<int64_t>(rows, 1)) * 2 * sizeof(float));
+    if (st != NOVA_B200_OK) return st;
+  }
+  float* stats = static_cast<float*>(ctx->scratch);
+  if (rows > 0 && C > 0) {
+    st = dispatch_row_kernel<1>(logits, nullptr, nullptr, softmax_out, nullptr, nullptr, rows, C, dtype, ctx->sm_count, s, stats);
+    if (st != NOVA_B200_OK) return st;
+  }
+  const int64_t loss_rows = C > 0 ? rows : 0;
+  auto* bad = reinterpret_cast<unsigned long long*>(bad_count);
+  if (dtype == NOVA_B200_F32)
+    sce_loss_kernel<float><<<1, 1024, 0, s>>>(static_cast<const float*>(logits), targets, stats, static_cast<float*>(loss_out), loss_rows, C, idx_dtype, bad);
+  else if (dtype == NOVA_B200_F16)
+    sce_loss_kernel<__half><<<1, 1024, 0, s>>>(static_cast<const __half*>(logits), targets, stats, static_cast<__half*>(loss_out), loss_rows, C, idx_dtype, bad);
+  else
+    sce_loss_kernel<__nv_bfloat16><<<1, 1024, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), targets, stats, static_cast<__nv_bfloat16*>(loss_out), loss_rows, C, idx_dtype, bad);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_sce_backward(const void* softmax, const void* targets, void* grad, int64_t rows, int64_t C, int32_t dtype,
+                               int32_t idx_dtype, void* stream) {
+  if (rows < 0 || C < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "sce_backward: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce_backward: dtype must be f32, f16 or bf16");
+  if (!is_index_dtype(idx_dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce_backward: target dtype must be i16, i32 or i64");
+  if (rows == 0 || C == 0) return NOVA_B200_OK;
+  if (!softmax || !targets || !grad) return fail(NOVA_B200_ERR_INVALID_ARG, "sce_backward: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype), vec = 16 / es;
+  const bool vec_ok = C % vec == 0 && reinterpret_cast<uintptr_t>(softmax) % 16 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0;
+  const float inv_n = static_cast<float>(1.0 / static_cast<double>(rows));
+  const int threads = 256;
+  const int grid = grid_for(vec_ok ? rows * C / vec : rows * C, threads, ctx->sm_count);
+#define NOVA_SCEB(T, V)                                                                                                  \
+  sce_backward_kernel<T, V><<<grid, threads, 0, s>>>(static_cast<const T*>(softmax), targets, static_cast<T*>(grad), rows, C, \
+                                                     idx_dtype, inv_n)
+  if (dtype == NOVA_B200_F32) { if (vec_ok) NOVA_SCEB(float, 4); else NOVA_SCEB(float, 1); }
+  else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_SCEB(__half, 8); else NOVA_SCEB(__half, 1); }
+  else { if (vec_ok) NOVA_SCEB(__nv_bfloat16, 8); else NOVA_SCEB(__nv_bfloat16, 1); }
+#undef NOVA_SCEB
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_scatter_add(void* inout, const void* idx, const void* src, int64_t pre, int64_t axis_len, int64_t post,
+                              int64_t n_idx, int32_t idx_dtype, int32_t dtype, int64_t* bad_count, void* stream) {
+  if (pre < 0 || axis_len < 0 || post < 0 || n_idx < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "scatter_add: negative extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "scatter_add: dtype must be f32, f16 or bf16");
+  if (!is_index_dtype(idx_dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "scatter_add: index dtype must be i16, i32 or i64");
+  if (pre == 0 || post == 0 || n_idx == 0) return NOVA_B200_OK;
+  if (!inout || !idx || !src) return fail(NOVA_B200_ERR_INVALID_ARG, "scatter_add: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = 256;
+  const int grid = grid_for(pre * n_idx * post, threads, ctx->sm_count);
+  auto* bad = reinterpret_cast<unsigned long long*>(bad_count);
+  if (dtype == NOVA_B200_F32)
+    scatter_add_kernel<float><<<grid, threads, 0, s>>>(static_cast<float*>(inout), idx, static_cast<const float*>(src), pre, axis_len, post, n_idx, idx_dtype, bad);
+  else if (dtype == NOVA_B200_F16)
+    scatter_add_kernel<__half><<<grid, threads, 0, s>>>(static_cast<__half*>(inout), idx, static_cast<const __half*>(src), pre, axis_len, post, n_idx, idx_dtype, bad);
+  else
+    scatter_add_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(static_cast<__nv_bfloat16*>(inout), idx, static_cast<const __nv_bfloat16*>(src), pre, axis_len, post, n_idx, idx_dtype, bad);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
 }
 
 int32_t nova_b200_gather(const void* in, const void* idx, void* out, int64_t pre, int64_t axis_len, int64_t post,

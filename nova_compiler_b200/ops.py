@@ -362,6 +362,75 @@ def gather(inp: torch.Tensor, indices: torch.Tensor, axis: int = 0, *, return_ba
     return (out, int(bad.item())) if return_bad_count else out
 
 
+def sce(logits: torch.Tensor, targets: torch.Tensor, *, return_bad_count: bool = False):
+    """nova.sce (NovaSceForwardLowering, NovaToLinalgGeneric.cpp:801-1010): sparse softmax cross-entropy over the
+    last dim.  Returns (softmax, loss[1]) as the op does (NovaOps.cpp:1648-1677)."""
+    _require_cuda(logits, targets)
+    if targets.dtype not in _IDX:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "sce: target dtype must be int16, int32 or int64")
+    x, t = logits.contiguous(), targets.contiguous()
+    Cn = x.shape[-1] if x.dim() else 1
+    rows = x.numel() // max(Cn, 1)
+    if t.numel() != rows:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "sce: one target per row of logits")
+    sm = torch.empty_like(x)
+    loss = torch.empty(1, dtype=x.dtype, device=x.device)
+    bad = torch.zeros(1, dtype=torch.int64, device=x.device)
+    L.check(L.load().nova_b200_sce(x.data_ptr(), t.data_ptr(), sm.data_ptr(), loss.data_ptr(), rows, Cn, _dt(x),
+                                   _IDX[t.dtype], bad.data_ptr(), _stream()))
+    return (sm, loss, int(bad.item())) if return_bad_count else (sm, loss)
+
+
+def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    """nova.sce_backward (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137): (softmax - one_hot) / rows."""
+    _require_cuda(softmax_, targets)
+    if dim not in (-1, softmax_.dim() - 1):
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "sce_backward: the class dimension must be the last one")
+    if targets.dtype not in _IDX:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "sce_backward: target dtype must be int16, int32 or int64")
+    p, t = softmax_.contiguous(), targets.contiguous()
+    Cn = p.shape[-1]
+    rows = p.numel() // max(Cn, 1)
+    if t.numel() != rows:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "sce_backward: one target per row")
+    g = torch.empty_like(p)
+    L.check(L.load().nova_b200_sce_backward(p.data_ptr(), t.data_ptr(), g.data_ptr(), rows, Cn, _dt(p), _IDX[t.dtype],
+                                            _stream()))
+    return g
+
+
+def scatter_add(inp: torch.Tensor, indices: torch.Tensor, src: torch.Tensor, axis: int = 0, *,
+                return_bad_count: bool = False):
+    """nova.scatter_add (NovaScatterAddOpLowering, NovaToLinalg.cpp:1086-1294; verify NovaOps.cpp:1990-2026): a copy
+    of inp with src added at `indices` along `axis`; shapes match except at axis, one index per src slice."""
+    _require_cuda(inp, indices, src)
+    if indices.dtype not in _IDX:
+        raise L.NovaB200Error(L.ERR_UNSUPPORTED, "scatter_add: index dtype must be int16, int32 or int64")
+    if inp.dim() != src.dim() or inp.dtype != src.dtype:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "scatter_add: input and src must share rank and dtype")
+    if axis < 0:
+        axis += inp.dim()
+    if not 0 <= axis < inp.dim():
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "scatter_add: axis out of bounds")
+    for i in range(inp.dim()):
+        if i != axis and inp.shape[i] != src.shape[i]:
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "scatter_add: input and src shapes must match except at axis")
+    if indices.numel() != src.shape[axis]:
+        raise L.NovaB200Error(L.ERR_INVALID_ARG, "scatter_add: src dimension at axis must match index size")
+    out = inp.contiguous().clone()
+    s, idx = src.contiguous(), indices.contiguous()
+    pre = 1
+    for d in out.shape[:axis]:
+        pre *= d
+    post = 1
+    for d in out.shape[axis + 1:]:
+        post *= d
+    bad = torch.zeros(1, dtype=torch.int64, device=out.device)
+    L.check(L.load().nova_b200_scatter_add(out.data_ptr(), idx.data_ptr(), s.data_ptr(), pre, out.shape[axis], post,
+                                           s.shape[axis], _IDX[idx.dtype], _dt(out), bad.data_ptr(), _stream()))
+    return (out, int(bad.item())) if return_bad_count else out
+
+
 def reshape(x: torch.Tensor, shape) -> torch.Tensor:
     """nova.reshape -> tensor.reshape (ReshapeOpConverter, NovaToLinalg.cpp:2409-2434): a row-major
     reinterpretation with equal element count (verify: NovaOps.cpp:1885-1895); no data movement."""

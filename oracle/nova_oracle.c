@@ -574,6 +574,91 @@ void nova_oracle_column_sum(const void* x, void* out, int64_t rows, int64_t cols
   }
 }
 
+/* ---------------------------------------------------------------- loss */
+
+static inline int64_t load_index(const void* idx, int64_t q, int idx_bits) {
+  if (idx_bits == 16) return (int64_t)((const uint16_t*)idx)[q]; /* zero-extended, as nova.gather / scatter_add do */
+  if (idx_bits == 32) return (int64_t)((const int32_t*)idx)[q];
+  return ((const int64_t*)idx)[q];
+}
+
+/* nova.sce over logits [rows, C] and targets [rows] (NovaSceForwardLowering, NovaToLinalgGeneric.cpp:801-1010):
+ *   max = max_c x; sumExp = sum_c exp(x - max) (c ascending); softmax = exp(x - max) / max(sumExp, 1e-7);
+ *   loss_r = log(max(sumExp, 1e-7)) - (x[target_r] - max);  loss = mean_r loss_r (rows ascending).
+ * Returns softmax [rows, C] and loss [1].  A target outside [0, C) contributes x[target] = 0 and is counted
+ * in the return value (the reference's gather would read out of bounds). */
+int64_t nova_oracle_sce(const void* logits, const void* targets, void* softmax, void* loss, int64_t rows, int64_t C,
+                        int dt, int idx_bits, int compute_f32) {
+  const int ct = compute_f32 ? NOVA_F32 : dt;
+  const float eps = round_through(1.0e-7f, ct);
+  int64_t bad = 0;
+  float* psl = (float*)malloc(sizeof(float) * (size_t)(rows > 0 ? rows : 1));
+  if (!psl) return -1;
+#pragma omp parallel for reduction(+ : bad)
+  for (int64_t r = 0; r < rows; ++r) {
+    float m = -INFINITY;
+    for (int64_t c = 0; c < C; ++c) m = fmaxf(m, load_elem(logits, r * C + c, dt));
+    float sum = 0.0f;
+    for (int64_t c = 0; c < C; ++c) {
+      float sh = round_through(load_elem(logits, r * C + c, dt) - m, ct);
+      sum = round_through(sum + round_through(expf(sh), ct), ct);
+    }
+    const float safe = fmaxf(sum, eps);
+    for (int64_t c = 0; c < C; ++c) {
+      float sh = round_through(load_elem(logits, r * C + c, dt) - m, ct);
+      store_elem(softmax, r * C + c, dt, round_through(round_through(expf(sh), ct) / safe, ct));
+    }
+    const int64_t t = load_index(targets, r, idx_bits);
+    float xt = 0.0f;
+    if (t < 0 || t >= C) ++bad; else xt = load_elem(logits, r * C + t, dt);
+    const float lse = round_through(logf(safe), ct);
+    psl[r] = round_through(lse - round_through(xt - m, ct), ct);
+  }
+  float total = 0.0f;
+  for (int64_t r = 0; r < rows; ++r) total = round_through(total + psl[r], ct);
+  store_elem(loss, 0, dt, rows > 0 ? round_through(total / (float)rows, ct) : 0.0f);
+  free(psl);
+  return bad;
+}
+
+/* nova.sce_backward (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137): scatter_add of -1 at the target
+ * class of every row of the forward's softmax, then a multiplication by the constant 1/N, N = rows. */
+int64_t nova_oracle_sce_backward(const void* softmax, const void* targets, void* grad, int64_t rows, int64_t C, int dt,
+                                 int idx_bits, int compute_f32) {
+  const int ct = compute_f32 ? NOVA_F32 : dt;
+  const float inv_n = round_through((float)(1.0 / (double)(rows > 0 ? rows : 1)), ct);
+  int64_t bad = 0;
+#pragma omp parallel for reduction(+ : bad)
+  for (int64_t r = 0; r < rows; ++r) {
+    const int64_t t = load_index(targets, r, idx_bits);
+    if (t < 0 || t >= C) ++bad;
+    for (int64_t c = 0; c < C; ++c) {
+      float p = load_elem(softmax, r * C + c, dt);
+      if (c == t) p = round_through(p + -1.0f, ct);
+      store_elem(grad, r * C + c, dt, round_through(p * inv_n, ct));
+    }
+  }
+  return bad;
+}
+
+/* nova.scatter_add along `axis` viewed as inout [pre, axis_len, post], src [pre, n_idx, post], indices [n_idx]
+ * (NovaScatterAddOpLowering, NovaToLinalg.cpp:1086-1294): inout[p, idx[i], q] += src[p, i, q], src walked in
+ * row-major order, indices outside [0, axis_len) skipped (and counted in the return value). */
+int64_t nova_oracle_scatter_add(void* inout, const void* idx, const void* src, int64_t pre, int64_t axis_len, int64_t post,
+                                int64_t n_idx, int idx_bits, int dt) {
+  int64_t bad = 0;
+  for (int64_t p = 0; p < pre; ++p)
+    for (int64_t i = 0; i < n_idx; ++i) {
+      const int64_t t = load_index(idx, i, idx_bits);
+      if (t < 0 || t >= axis_len) { ++bad; continue; }
+      for (int64_t q = 0; q < post; ++q) {
+        const int64_t d = (p * axis_len + t) * post + q;
+        store_elem(inout, d, dt, round_through(load_elem(inout, d, dt) + load_elem(src, (p * n_idx + i) * post + q, dt), dt));
+      }
+    }
+  return bad;
+}
+
 /* ---------------------------------------------------------------- indexing (bit-exact) */
 
 /* nova.gather along `axis` viewed as [pre, axis_len, post] x indices[pre_or_1, n_idx]

@@ -283,6 +283,63 @@ def gather(inp, idx, axis=0):
     return out, int(bad)
 
 
+def _idx_view(idx):
+    idx = np.ascontiguousarray(idx)
+    bits = idx.dtype.itemsize * 8
+    if bits not in (16, 32, 64):
+        raise ValueError("index dtype must be 16, 32 or 64 bits wide")
+    return (idx.view(np.uint16) if bits == 16 else idx), bits
+
+
+def sce(logits, targets, dt="f32", compute_f32=False):
+    """nova.sce over the last dim: returns (softmax, loss[1], out-of-range target count)."""
+    x = np.ascontiguousarray(logits, dtype=np_dtype(dt))
+    t, bits = _idx_view(targets)
+    Cn = x.shape[-1]
+    rows = x.size // Cn
+    if t.size != rows:
+        raise ValueError("sce: one target per row")
+    sm = np.empty_like(x)
+    loss = np.empty(1, dtype=x.dtype)
+    lib().nova_oracle_sce.restype = C.c_int64
+    bad = lib().nova_oracle_sce(_ptr(x), _ptr(t), _ptr(sm), _ptr(loss), C.c_int64(rows), C.c_int64(Cn),
+                                C.c_int(DTYPES[dt]), C.c_int(bits), C.c_int(int(compute_f32)))
+    return sm, loss, int(bad)
+
+
+def sce_backward(softmax, targets, dt="f32", compute_f32=False):
+    """nova.sce_backward over the last dim: (softmax - one_hot(targets)) / rows."""
+    p = np.ascontiguousarray(softmax, dtype=np_dtype(dt))
+    t, bits = _idx_view(targets)
+    Cn = p.shape[-1]
+    rows = p.size // Cn
+    if t.size != rows:
+        raise ValueError("sce_backward: one target per row")
+    g = np.empty_like(p)
+    lib().nova_oracle_sce_backward.restype = C.c_int64
+    lib().nova_oracle_sce_backward(_ptr(p), _ptr(t), _ptr(g), C.c_int64(rows), C.c_int64(Cn), C.c_int(DTYPES[dt]),
+                                   C.c_int(bits), C.c_int(int(compute_f32)))
+    return g
+
+
+def scatter_add(inp, indices, src, axis=0, dt="f32"):
+    """nova.scatter_add: a copy of inp with src added at indices along axis; returns (out, skipped count)."""
+    out = np.array(inp, dtype=np_dtype(dt), copy=True, order="C")
+    src = np.ascontiguousarray(src, dtype=np_dtype(dt))
+    t, bits = _idx_view(indices)
+    if axis < 0:
+        axis += out.ndim
+    pre = int(np.prod(out.shape[:axis], dtype=np.int64))
+    post = int(np.prod(out.shape[axis + 1:], dtype=np.int64))
+    n_idx = src.shape[axis]
+    if t.size != n_idx or src.shape[:axis] != out.shape[:axis] or src.shape[axis + 1:] != out.shape[axis + 1:]:
+        raise ValueError("scatter_add: shapes must match except at axis; one index per src slice")
+    lib().nova_oracle_scatter_add.restype = C.c_int64
+    bad = lib().nova_oracle_scatter_add(_ptr(out), _ptr(t), _ptr(src), C.c_int64(pre), C.c_int64(out.shape[axis]),
+                                        C.c_int64(post), C.c_int64(n_idx), C.c_int(bits), C.c_int(DTYPES[dt]))
+    return out, int(bad)
+
+
 def transpose_last2(x):
     x = np.ascontiguousarray(x)
     R, Cc = x.shape[-2], x.shape[-1]

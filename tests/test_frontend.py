@@ -335,3 +335,55 @@ def test_run_training_step_matches_autograd(cuda):
     assert rel(y, Y.detach()) <= 1e-5
     assert rel(gx, X.grad) <= 2e-5 and rel(gg, G.grad) <= 2e-5 and rel(gbeta, Bt.grad) <= 2e-5
     assert rel(gw1, W1.grad) <= 2e-5 and rel(gw2, W2.grad) <= 2e-5
+
+
+# the loss end of ltest/test.mlir:24-30,33-34: vocabulary matmul -> sce -> sce_backward -> the two backward matmuls
+LOSS = '''
+func.func @loss(%h: tensor<2x12x40xf32>, %wv: tensor<40x96xf32>, %tgt: tensor<2x12xi16>, %emb: tensor<96x40xf32>)
+    -> (tensor<1xf32>, tensor<24x40xf32>, tensor<40x96xf32>, tensor<96x40xf32>) {
+  %0 = nova.reshape %h : tensor<2x12x40xf32> -> tensor<24x40xf32>
+  %1 = nova.matmul %0, %wv : tensor<24x40xf32>, tensor<40x96xf32>
+  %2 = nova.reshape %1 : tensor<24x96xf32> -> tensor<2x12x96xf32>
+  %sm, %l = nova.sce %2, %tgt : tensor<2x12x96xf32>, tensor<2x12xi16>
+  %g = nova.sce_backward %sm, %tgt {dim = -1 : i64} : tensor<2x12x96xf32>, tensor<2x12xi16>
+  %3 = nova.reshape %g : tensor<2x12x96xf32> -> tensor<24x96xf32>
+  %4 = nova.transpose %0 : tensor<24x40xf32>
+  %5 = nova.transpose %wv : tensor<40x96xf32>
+  %gh = nova.matmul %3, %5 : tensor<24x96xf32>, tensor<96x40xf32>
+  %gw = nova.matmul %4, %3 : tensor<40x24xf32>, tensor<24x96xf32>
+  %ids = nova.reshape %tgt : tensor<2x12xi16> -> tensor<24xi16>
+  %ge = nova.scatter_add %emb, %ids, %gh axis = 0 : tensor<96x40xf32>, tensor<24xi16>, tensor<24x40xf32> -> tensor<96x40xf32>
+  return %l, %gh, %gw, %ge : tensor<1xf32>, tensor<24x40xf32>, tensor<40x96xf32>, tensor<96x40xf32>
+}
+'''
+
+
+def test_plan_of_the_loss_end():
+    plan = Module(LOSS).plan("loss")
+    lines = [l.strip() for l in plan.splitlines()]
+    assert sum(l.startswith("sce ") for l in lines) == 1 and sum(l.startswith("sce_backward") for l in lines) == 1
+    assert sum(l.startswith("scatter_add") for l in lines) == 1 and sum(l.startswith("gemm") for l in lines) == 3
+    _, res = Module(LOSS).signature("loss")
+    assert res == [(L.F32, (1,)), (L.F32, (24, 40)), (L.F32, (40, 96)), (L.F32, (96, 40))]
+    bad = LOSS.replace("{dim = -1 : i64}", "{dim = 0 : i64}")
+    with pytest.raises(Exception) as e:
+        Module(bad).plan("loss")
+    assert "last dimension" in str(e.value)
+
+
+@pytest.mark.gpu
+def test_run_loss_end_matches_autograd(cuda):
+    torch = cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(21)
+    r = lambda *s, sc=1.0: (torch.rand(*s, device="cuda", generator=g) * 2 - 1) * sc
+    h, wv, emb = r(2, 12, 40), r(40, 96, sc=0.5), r(96, 40)
+    tgt = torch.randint(0, 96, (2, 12), device="cuda", generator=g).to(torch.int16)
+    l, gh, gw, ge = Module(LOSS).run("loss", h, wv, tgt, emb)
+    H, W = h.double().reshape(24, 40).requires_grad_(True), wv.double().requires_grad_(True)
+    loss = torch.nn.functional.cross_entropy(H @ W, tgt.long().reshape(-1))
+    loss.backward()
+    rel = lambda a, b: float((a.double() - b).norm() / b.norm())
+    assert abs(float(l[0]) - float(loss.detach())) <= 1e-5 * abs(float(loss.detach()))
+    assert rel(gh, H.grad) <= 2e-5 and rel(gw, W.grad) <= 2e-5
+    want_ge = emb.double().index_add(0, tgt.long().reshape(-1), H.grad)
+    assert rel(ge, want_ge) <= 1e-6

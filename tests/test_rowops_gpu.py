@@ -8,7 +8,7 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-from test_gemm_gpu import GOLD, _tdt, check, rand_bits, to_dev, to_host  # noqa: E402
+from test_gemm_gpu import GOLD, TOL, _tdt, check, rand_bits, to_dev, to_host  # noqa: E402
 
 ROW_SHAPES = [(64, 384), (33, 1000), (16, 4096), (5, 8192), (3, 10000), (7, 37), (1, 1), (300, 2048)]
 
@@ -178,3 +178,75 @@ def test_layer_norm_backward(cuda, oracle, dt):
     with pytest.raises(L.NovaB200Error) as e:
         ops.layer_norm_backward(big, big, cuda.ones(8196, device="cuda"), cuda.zeros(2, device="cuda"), cuda.ones(2, device="cuda"))
     assert e.value.status == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_sce_forward_and_backward(cuda, oracle, dt):
+    """nova.sce / nova.sce_backward over the last dim: softmax, mean loss and gradient against the oracle (fp32
+    arithmetic rounded once on both sides); short, vector-friendly and vocabulary-sized rows; i16 targets above
+    32767 (zero-extended) and an out-of-range target."""
+    from nova_compiler_b200 import ops
+    torch = cuda
+    rng = np.random.default_rng(8)
+    for rows, C, it in [(64, 10, np.int32), (33, 1000, np.int64), (24, 50304, np.uint16), (7, 37, np.int32), (300, 2048, np.int64)]:
+        x = rand_bits(oracle, rng, (rows, C), dt, "normal", 3.0)
+        t = rng.integers(0, C, size=rows).astype(it)
+        t_dev = torch.from_numpy(t.view(np.int16) if it == np.uint16 else t).cuda()
+        sm, loss = ops.sce(to_dev(torch, x, dt), t_dev)
+        wsm, wloss, bad = oracle.sce(x, t.view(np.int16) if it == np.uint16 else t, dt, compute_f32=True)
+        assert bad == 0
+        # The oracle adds the C exponentials one after the other in fp32, as the reference's reduction does; over a
+        # 50304-term row that running sum is itself ~4e-5 off.  The kernel's tree sum is checked against float64 too.
+        long_row = dt == "f32" and C > 16384
+        check(oracle, to_host(torch, sm, dt), wsm, dt, tol=1e-4 if long_row else None)
+        check(oracle, to_host(torch, loss, dt), wloss, dt, tol=2e-3 if dt != "f32" else 1e-5)
+        if dt == "f32":
+            x64 = x.astype(np.float64)
+            e = np.exp(x64 - x64.max(-1, keepdims=True))
+            assert oracle.rel_fro(to_host(torch, sm, dt), e / e.sum(-1, keepdims=True)) <= 2e-6
+        g = ops.sce_backward(sm, t_dev)
+        wg = oracle.sce_backward(to_host(torch, sm, dt), t.view(np.int16) if it == np.uint16 else t, dt, compute_f32=True)
+        check(oracle, to_host(torch, g, dt), wg, dt, tol=TOL[dt] if dt != "f32" else 1e-6)
+    # an out-of-range target: counted, contributes x[target] = 0
+    x = rand_bits(oracle, rng, (5, 16), dt, "normal")
+    t = np.array([1, 99, 3, 0, 15], dtype=np.int32)
+    sm, loss, bad = ops.sce(to_dev(torch, x, dt), torch.from_numpy(t).cuda(), return_bad_count=True)
+    wsm, wloss, wbad = oracle.sce(x, t, dt, compute_f32=True)
+    assert bad == wbad == 1
+    check(oracle, to_host(torch, loss, dt), wloss, dt, tol=2e-3 if dt != "f32" else 1e-5)
+
+
+def test_scatter_add(cuda, oracle):
+    """out = input; out[.., idx[i], ..] += src[.., i, ..]: unique indices compare bit for bit, repeated indices (atomics,
+    unspecified order) within fp32 rounding; out-of-range indices are skipped and counted."""
+    from nova_compiler_b200 import ops
+    torch = cuda
+    rng = np.random.default_rng(12)
+    inp = rng.normal(size=(500, 96)).astype(np.float32)
+    idx = rng.permutation(500)[:128].astype(np.int32)
+    src = rng.normal(size=(128, 96)).astype(np.float32)
+    out = ops.scatter_add(torch.from_numpy(inp).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(src).cuda(), 0)
+    want, _ = oracle.scatter_add(inp, idx, src, 0)
+    assert np.array_equal(out.cpu().numpy(), want)  # the embedding-gradient form of nova.gather's backward
+    # repeated + out-of-range indices, middle axis, i16 indices
+    inp = rng.normal(size=(3, 40, 8)).astype(np.float32)
+    idx = np.array([5, 5, 5, 39, 0, 200, 7, 5], dtype=np.int16)
+    src = rng.normal(size=(3, 8, 8)).astype(np.float32)
+    out, bad = ops.scatter_add(torch.from_numpy(inp).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(src).cuda(), 1,
+                               return_bad_count=True)
+    want, wbad = oracle.scatter_add(inp, idx, src, 1)
+    assert bad == 3 and wbad == 3  # one bad index, seen once per leading slice
+    assert oracle.rel_fro(out.cpu().numpy(), want) <= 1e-6
+    # the flat form nova.sce_backward lowers to: -1 at row * C + target
+    p = rng.random(size=(6 * 10,)).astype(np.float32)
+    flat = (np.arange(6) * 10 + rng.integers(0, 10, size=6)).astype(np.int64)
+    out = ops.scatter_add(torch.from_numpy(p).cuda(), torch.from_numpy(flat).cuda(), torch.full((6,), -1.0, device="cuda"), 0)
+    want, _ = oracle.scatter_add(p, flat, np.full(6, -1.0, np.float32), 0)
+    assert np.array_equal(out.cpu().numpy(), want)
+    for dt in ("f16", "bf16"):
+        a = rand_bits(oracle, rng, (50, 16), dt)
+        s = rand_bits(oracle, rng, (20, 16), dt)
+        ix = rng.permutation(50)[:20].astype(np.int32)
+        out = ops.scatter_add(to_dev(torch, a, dt), torch.from_numpy(ix).cuda(), to_dev(torch, s, dt), 0)
+        want, _ = oracle.scatter_add(a, ix, s, 0, dt)
+        assert np.array_equal(to_host(torch, out, dt), want)
