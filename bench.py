@@ -406,6 +406,9 @@ ROW_WORKLOADS = {
     "ln": ("nova.layer_norm bf16 [8192, 4096] (the rows that feed the C3 linear)", "bf16", 8192, 4096),
     "softmax": ("nova.softmax f16 [65536, 2048] (attention-score rows, C4 layout, 32 of its 256 batches)", "f16", 65536, 2048),
     "gather": ("nova.gather bf16 table [50304, 4096], 16384 i32 ids (embedding lookup)", "bf16", 16384, 4096),
+    "ln_bwd": ("nova.layer_norm_backward bf16 [8192, 4096] (dx, dgamma, dbeta from one read of gy and x)", "bf16", 8192, 4096),
+    "sce": ("nova.sce f32 logits [8192, 50304], i16 targets (softmax + mean loss; the vocabulary rows of ltest/test.mlir)", "f32", 8192, 50304),
+    "sce_bwd": ("nova.sce_backward f32 [8192, 50304]", "f32", 8192, 50304),
 }
 
 
@@ -418,7 +421,8 @@ def run_rowop(args):
     L.check(L.load().nova_b200_init(0))
     w = args.workload
     desc, dt, rows, D = ROW_WORKLOADS[w]
-    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[dt]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dt]
+    es = 4 if dt == "f32" else 2
     g = torch.Generator(device="cuda")
     g.manual_seed(1234)
     n_sets = 4  # rotate inputs so a step never finds its rows in L2
@@ -427,6 +431,23 @@ def run_rowop(args):
         sets = [torch.randint(0, 50304, (rows,), device="cuda", generator=g).to(torch.int32) for _ in range(n_sets)]
         byts = 2 * rows * D * 2 + rows * 4
         fn = lambda i: ops.gather(table, sets[i % n_sets])
+    elif w in ("sce", "sce_bwd"):
+        n_sets = 2  # 1.65 GB per tensor
+        sets = [torch.randn(rows, D, device="cuda", generator=g) * 3.0 for _ in range(n_sets)]
+        tg = torch.randint(0, D, (rows,), device="cuda", generator=g).to(torch.int16)
+        byts = 2 * rows * D * es + rows * 2
+        if w == "sce":
+            fn = lambda i: ops.sce(sets[i % n_sets], tg)
+        else:
+            sets = [ops.sce(x, tg)[0] for x in sets]
+            fn = lambda i: ops.sce_backward(sets[i % n_sets], tg)
+    elif w == "ln_bwd":
+        sets = [torch.randn(rows, D, device="cuda", generator=g).to(tdt) for _ in range(n_sets)]
+        gys = [torch.randn(rows, D, device="cuda", generator=g).to(tdt) for _ in range(n_sets)]
+        gamma = torch.randn(D, device="cuda", generator=g).to(tdt)
+        stats = [ops.layer_norm(x, gamma, gamma)[1:] for x in sets]
+        byts = 3 * rows * D * es + 3 * D * es + 2 * rows * es
+        fn = lambda i: ops.layer_norm_backward(gys[i % n_sets], sets[i % n_sets], gamma, *stats[i % n_sets])
     else:
         sets = [torch.randn(rows, D, device="cuda", generator=g).to(tdt) for _ in range(n_sets)]
         gamma = torch.randn(D, device="cuda", generator=g).to(tdt)
@@ -451,7 +472,8 @@ def run_rowop(args):
     print(json.dumps({
         "metric": "row-op HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": dt, "data": "synthetic (seeded)", "impl": "nova_b200", "clocks": clocks, "gpu_launches": args.steps,
+        "dtype": dt, "data": "synthetic (seeded)", "impl": "nova_b200", "clocks": clocks,
+        "gpu_launches": args.steps * {"ln_bwd": 2, "sce": 2}.get(w, 1),  # ln_bwd: + column-sum finish; sce: + loss kernel
         "config": {"workload": f"{w}: {desc}", "l2": f"rotating {n_sets} input sets; outputs are fresh allocations"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                      "traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": src, "algorithmic_bytes_per_launch": byts,

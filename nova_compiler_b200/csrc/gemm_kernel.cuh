@@ -170,6 +170,25 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// 32 consecutive elements of one row of an epilogue operand (residual, live C, GELU pre-activation) as floats:
+// 16-byte loads when the span is whole and aligned, guarded element loads at ragged edges.
+template <typename OutT>
+__device__ __forceinline__ void load_row32(const OutT* ptr, int32_t ncols, float (&out)[32]) {
+  constexpr int kPerVec = 16 / static_cast<int>(sizeof(OutT));
+  if (ncols == 32 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u) {
+#pragma unroll
+    for (int j = 0; j < 32; j += kPerVec) {
+      union { uint4 u; OutT e[kPerVec]; } pk;
+      pk.u = *reinterpret_cast<const uint4*>(ptr + j);
+#pragma unroll
+      for (int e = 0; e < kPerVec; ++e) out[j + e] = to_f32<OutT>(pk.e[e]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = j < ncols ? to_f32<OutT>(ptr[j]) : 0.0f;
+  }
+}
+
 // One thread finishes 32 consecutive columns of one output row: accumulator + init, activation.
 // `row_ok` guards the residual read of rows past M (their accumulators are zeros from the fill).
 template <typename OutT>
@@ -191,9 +210,10 @@ __device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const u
                               static_cast<int64_t>(row) * p.ldc + col0
                         : reinterpret_cast<const OutT*>(p.residual) + static_cast<int64_t>(batch) * p.stride_r +
                               static_cast<int64_t>(row) * p.ldr + col0;
+    float add[32];
+    load_row32<OutT>(r, ncols, add);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) v[j] += to_f32<OutT>(r[j]);
+    for (int j = 0; j < 32; ++j) v[j] += add[j];
   }
   if (p.act == NOVA_B200_ACT_RELU) {
 #pragma unroll
@@ -205,9 +225,10 @@ __device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const u
     // the forward pre-activation arrives through the residual pointer and is a multiplier, not an addend
     const OutT* z = reinterpret_cast<const OutT*>(p.residual) + static_cast<int64_t>(batch) * p.stride_r +
                     static_cast<int64_t>(row) * p.ldr + col0;
+    float zf[32];
+    load_row32<OutT>(z, ncols, zf);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (j < ncols) v[j] *= gelu_tanh_grad_f32(to_f32<OutT>(z[j]));
+    for (int j = 0; j < 32; ++j) v[j] *= gelu_tanh_grad_f32(zf[j]);
   }
 }
 

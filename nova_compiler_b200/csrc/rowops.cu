@@ -53,6 +53,7 @@ __device__ __forceinline__ float row_reduce(float v, float* red_smem) {
 }
 
 constexpr int kRowThreads = 256;
+constexpr int kLongUnroll = 8;  // vectors a thread keeps in flight when a row is too long for its registers
 
 // kMode 0: layer_norm, kMode 1: softmax.  kMaxV > 0: a thread keeps up to kMaxV vectors of its row in
 // registers (the row fits TPR * kMaxV vectors); kMaxV == 0: two passes over global memory.  kMaxV is
@@ -89,7 +90,7 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
     }
 
     float s0 = kMode == 0 ? 0.0f : -INFINITY;  // layer_norm: sum; softmax: max
-    float s1 = 0.0f;                            // layer_norm: sum of squares
+    float s1 = 0.0f;                            // layer_norm: sum of squares; long softmax rows: running sum of exp
     if (CACHED) {
 #pragma unroll
       for (int k = 0; k < kMaxV; ++k) {
@@ -104,12 +105,33 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
         }
       }
     } else {
-      for (int i = t; active && i < nvec; i += TPR) {
-        const P pk = xr[i];
+      // kLongUnroll independent loads per thread and trip: long rows run on few CTAs, so the bytes in flight
+      // have to come from each thread
+      for (int i0 = t; active && i0 < nvec; i0 += TPR * kLongUnroll) {
+        P pks[kLongUnroll];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float v = ld_f32<T>(pk.e[e]);
-          if (kMode == 0) { s0 += v; s1 += v * v; } else { s0 = fmaxf(s0, v); }
+        for (int u = 0; u < kLongUnroll; ++u)
+          if (i0 + u * TPR < nvec) pks[u] = xr[i0 + u * TPR];
+#pragma unroll
+        for (int u = 0; u < kLongUnroll; ++u) {
+        if (i0 + u * TPR >= nvec) break;
+        const P pk = pks[u];
+        if (kMode == 0) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float v = ld_f32<T>(pk.e[e]);
+            s0 += v;
+            s1 += v * v;
+          }
+        } else {
+          // online softmax: the running sum is kept relative to the running maximum, so the row is read once here
+          float vm = ld_f32<T>(pk.e[0]);
+#pragma unroll
+          for (int e = 1; e < VEC; ++e) vm = fmaxf(vm, ld_f32<T>(pk.e[e]));
+          if (vm > s0) { s1 *= __expf(s0 - vm); s0 = vm; }
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) s1 += __expf(ld_f32<T>(pk.e[e]) - s0);
+        }
         }
       }
     }
@@ -141,11 +163,20 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
           if (active && i < nvec) emit(i, cache[k]);
         }
       } else {
-        for (int i = t; active && i < nvec; i += TPR) emit(i, xr[i]);
+        for (int i0 = t; active && i0 < nvec; i0 += TPR * kLongUnroll) {
+          P pks[kLongUnroll];
+#pragma unroll
+          for (int u = 0; u < kLongUnroll; ++u)
+            if (i0 + u * TPR < nvec) pks[u] = xr[i0 + u * TPR];
+#pragma unroll
+          for (int u = 0; u < kLongUnroll; ++u)
+            if (i0 + u * TPR < nvec) emit(i0 + u * TPR, pks[u]);
+        }
       }
     } else {
       const float m = row_reduce<TPR, true>(s0, red);
       float part = 0.0f;
+      if (!CACHED) part = s0 == -INFINITY ? 0.0f : s1 * __expf(s0 - m);  // this thread's sum, rescaled to the row max
       if (CACHED) {
 #pragma unroll
         for (int k = 0; k < kMaxV; ++k) {
@@ -154,12 +185,6 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
 #pragma unroll
             for (int e = 0; e < VEC; ++e) part += __expf(ld_f32<T>(cache[k].e[e]) - m);
           }
-        }
-      } else {
-        for (int i = t; active && i < nvec; i += TPR) {
-          const P pk = xr[i];
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) part += __expf(ld_f32<T>(pk.e[e]) - m);
         }
       }
       const float s = row_reduce<TPR, false>(part, red);
@@ -178,7 +203,15 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
           if (active && i < nvec) emit(i, cache[k]);
         }
       } else {
-        for (int i = t; active && i < nvec; i += TPR) emit(i, xr[i]);
+        for (int i0 = t; active && i0 < nvec; i0 += TPR * kLongUnroll) {
+          P pks[kLongUnroll];
+#pragma unroll
+          for (int u = 0; u < kLongUnroll; ++u)
+            if (i0 + u * TPR < nvec) pks[u] = xr[i0 + u * TPR];
+#pragma unroll
+          for (int u = 0; u < kLongUnroll; ++u)
+            if (i0 + u * TPR < nvec) emit(i0 + u * TPR, pks[u]);
+        }
       }
     }
   }
@@ -197,13 +230,19 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
   const int64_t nvec = D / VEC;
   // Measured on B200: rows handled by one warp (no CTA-wide barrier) run best as many short-lived CTAs;
   // rows that need the whole CTA run best as persistent CTAs that prefetch their next row into L2.
-  auto launch_grid = [&](int tpr) {
+  auto launch_grid = [&](int tpr, int max_v) {
     const int64_t ctas = (rows * tpr + kRowThreads - 1) / kRowThreads;
-    const int64_t cap = static_cast<int64_t>(sm_count) * (tpr == 32 ? 32 : 8);
+    int64_t cap = static_cast<int64_t>(sm_count) * (tpr == 32 ? 32 : 8);
+    if (max_v == 0) {
+      // rows too long for registers are read twice: keep the rows in flight within ~64 MB so that the second
+      // read finds them in L2 (126 MB) instead of HBM
+      const int64_t row_bytes = D * static_cast<int64_t>(sizeof(T));
+      cap = std::max<int64_t>(sm_count, std::min<int64_t>(cap, (64ll << 20) / std::max<int64_t>(row_bytes, 1)));
+    }
     return static_cast<int>(ctas < cap ? ctas : cap);
   };
 #define NOVA_ROW(TPR_, MAXV_)                                                                             \
-  row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_), kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, \
+  row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_, MAXV_), kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, \
                                                                                      d, (TPR_) == 32 ? 0 : 1, stats)
   // Vectors a thread keeps in registers are kept few (occupancy sets the bytes in flight per SM):
   // longer rows get more threads, not more registers.
@@ -408,12 +447,12 @@ __global__ void column_sum_final_kernel(const float* __restrict__ partial, T* __
 //   reduction of the pair), dx = ((gyg - s1/D) - xhat s2/D) rstd.
 // The CTA's column sums go to partial[blockIdx.x][0|1][D] (fp32); ln_backward_finish_kernel adds them up.
 // HBM traffic: gy, x read once, dx written once (+ the small partials).
-template <typename T, int VEC, int kMaxV>
-__global__ void __launch_bounds__(kRowThreads)
+template <typename T, int VEC, int kMaxV, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
 ln_backward_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
                    const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
                    float* __restrict__ partial, int64_t rows, int32_t D) {
-  __shared__ float red[2][kRowThreads / 32];
+  __shared__ float red[2][kMaxThreads / 32];
   using P = Pack<T, VEC>;
   const int nvec = D / VEC;
   const int nthreads = blockDim.x;
@@ -431,6 +470,15 @@ ln_backward_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* _
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const P* gyr = reinterpret_cast<const P*>(gy + r * D);
     const P* xr = reinterpret_cast<const P*>(x + r * D);
+    if (r + gridDim.x < rows) {  // the CTA's next row on its way into L2 while this one is reduced and stored
+      constexpr int kVecPerLine = 128 / static_cast<int>(sizeof(P));
+      const P* ng = reinterpret_cast<const P*>(gy + (r + gridDim.x) * D);
+      const P* nx = reinterpret_cast<const P*>(x + (r + gridDim.x) * D);
+      for (int i = threadIdx.x * kVecPerLine; i < nvec; i += nthreads * kVecPerLine) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(ng + i));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + i));
+      }
+    }
     P pg[kMaxV], px[kMaxV];
 #pragma unroll
     for (int i = 0; i < kMaxV; ++i) {
@@ -498,11 +546,11 @@ ln_backward_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* _
 template <typename T>
 __global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int32_t n_partials, int32_t D,
                                           T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  __shared__ float sh[2][8][32];
-  const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 8)
+  __shared__ float sh[2][32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 32)
   float a = 0.0f, b = 0.0f;
   if (c < D)
-    for (int p = threadIdx.y; p < n_partials; p += 8) {
+    for (int p = threadIdx.y; p < n_partials; p += 32) {
       a += partial[static_cast<size_t>(p) * 2 * D + c];
       b += partial[static_cast<size_t>(p) * 2 * D + D + c];
     }
@@ -511,7 +559,7 @@ __global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int
   __syncthreads();
   if (threadIdx.y == 0 && c < D) {
 #pragma unroll
-    for (int k = 1; k < 8; ++k) { a += sh[0][k][threadIdx.x]; b += sh[1][k][threadIdx.x]; }
+    for (int k = 1; k < 32; ++k) { a += sh[0][k][threadIdx.x]; b += sh[1][k][threadIdx.x]; }
     dgamma[c] = st_f32<T>(a);
     dbeta[c] = st_f32<T>(b);
   }
@@ -648,11 +696,14 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   if (nvec > static_cast<int64_t>(kRowThreads) * 8)
     return fail(NOVA_B200_ERR_UNSUPPORTED,
                 "layer_norm_backward: rows longer than 2048 sixteen-byte vectors (or 2048 elements when unaligned)");
-  // threads: a multiple of 32 covering the row with as few vectors per thread as possible
-  const int threads = static_cast<int>(nvec >= kRowThreads ? kRowThreads : (nvec + 31) / 32 * 32);
+  // One vector per thread (64 registers, 2048 resident threads per SM) for rows of up to 1024 vectors; longer rows
+  // keep 2-8 vectors per thread in 256-thread CTAs.  Threads: a multiple of 32 covering the row.
+  const bool wide = nvec <= 1024;
+  const int threads = static_cast<int>(wide ? (nvec + 31) / 32 * 32 : kRowThreads);
   const int per_thread = static_cast<int>((nvec + threads - 1) / threads);
   const int max_v = per_thread <= 1 ? 1 : per_thread <= 2 ? 2 : per_thread <= 4 ? 4 : 8;
-  const int resident = std::max(1, std::min(8, 2048 / threads / (max_v >= 4 ? 2 : 1)));
+  // few persistent CTAs: every CTA ends with 2*D floats of column sums that the finish kernel has to read back
+  const int resident = wide ? std::max(1, std::min(8, 2048 / threads)) : (max_v >= 4 ? 1 : 2);
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows, static_cast<int64_t>(ctx->sm_count) * resident)));
   {
     std::lock_guard<std::mutex> lock(ctx->mu);
@@ -661,7 +712,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   }
   float* partial = static_cast<float*>(ctx->scratch);
 #define NOVA_LNB(T, V, MV)                                                                                             \
-  ln_backward_kernel<T, V, MV><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x),      \
+  ln_backward_kernel<T, V, MV, (MV) == 1 ? 1024 : kRowThreads><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x),      \
                                                         static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
                                                         static_cast<const T*>(rstd), static_cast<T*>(dx), partial,     \
                                                         rows, static_cast<int32_t>(D))
@@ -678,11 +729,11 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   NOVA_CUDA_OK(cudaGetLastError());
   const int fin_grid = static_cast<int>((D + 31) / 32);
   if (dtype == NOVA_B200_F32)
-    ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
+    ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
   else if (dtype == NOVA_B200_F16)
-    ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
+    ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
   else
-    ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 8), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
+    ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }
