@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "runtime.h"
 
@@ -217,6 +218,68 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
   }
 }
 
+// softmax of rows too long for registers but not for shared memory (up to 220 KB, e.g. a 50304-entry f32
+// vocabulary row): one 1024-thread CTA per SM stages its row in shared memory while it takes the running
+// max / sum (four 16-byte loads in flight per thread), then normalises out of shared memory.  HBM sees the row
+// once in each direction; the two-pass kernel re-read it from HBM because the rows in flight plus their
+// outputs do not fit L2 (measured 4.1 GB read for a 1.65 GB input).
+constexpr int kSmemRowThreads = 1024;
+constexpr int kSmemRowBytes = 220 * 1024;
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kSmemRowThreads)
+softmax_smem_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int32_t D, float* __restrict__ row_stats) {
+  extern __shared__ uint4 row_smem_raw[];
+  __shared__ float red[kSmemRowThreads / 32];
+  using P = Pack<T, VEC>;
+  P* sm = reinterpret_cast<P*>(row_smem_raw);
+  const int nvec = D / VEC;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  constexpr int kU = 4;
+  auto block_reduce = [&](float v, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();  // the previous reduction's readers are done with red
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const float r = red[lane];  // 32 warps
+    return is_max ? warp_max(r) : warp_sum(r);
+  };
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const P* xr = reinterpret_cast<const P*>(x + row * D);
+    P* yr = reinterpret_cast<P*>(y + row * D);
+    float m = -INFINITY, s = 0.0f;
+    for (int i0 = t; i0 < nvec; i0 += kSmemRowThreads * kU) {
+      P pks[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u)
+        if (i0 + u * kSmemRowThreads < nvec) pks[u] = xr[i0 + u * kSmemRowThreads];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int i = i0 + u * kSmemRowThreads;
+        if (i >= nvec) break;
+        sm[i] = pks[u];  // read back by this same thread below: no barrier needed for the staging itself
+        float vm = ld_f32<T>(pks[u].e[0]);
+#pragma unroll
+        for (int e = 1; e < VEC; ++e) vm = fmaxf(vm, ld_f32<T>(pks[u].e[e]));
+        if (vm > m) { s *= __expf(m - vm); m = vm; }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s += __expf(ld_f32<T>(pks[u].e[e]) - m);
+      }
+    }
+    const float row_max = block_reduce(m, true);
+    const float total = block_reduce(m == -INFINITY ? 0.0f : s * __expf(m - row_max), false);
+    if (row_stats != nullptr && t == 0) { row_stats[2 * row] = row_max; row_stats[2 * row + 1] = total; }
+    const float recip = 1.0f / fmaxf(total, 1.0e-7f);
+    for (int i = t; i < nvec; i += kSmemRowThreads) {
+      const P in = sm[i];
+      P o;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) o.e[e] = st_f32<T>(__expf(ld_f32<T>(in.e[e]) - row_max) * recip);
+      yr[i] = o;
+    }
+  }
+}
+
 template <typename T, int VEC, int kMode>
 int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
                           int64_t rows, int64_t D, int sm_count, cudaStream_t st, float* stats) {
@@ -260,7 +323,13 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     else if (nvec <= kRowThreads * 4) NOVA_ROW(kRowThreads, 4);
     else if (nvec <= kRowThreads * 8) NOVA_ROW(kRowThreads, 8);
     else if (nvec <= kRowThreads * 16) NOVA_ROW(kRowThreads, 16);
-    else NOVA_ROW(kRowThreads, 0);
+    else if (kMode == 1 && D * static_cast<int64_t>(sizeof(T)) <= kSmemRowBytes) {
+      auto kernel = softmax_smem_kernel<T, VEC>;
+      const int smem = static_cast<int>(D * sizeof(T));
+      NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemRowBytes));
+      const int grid = static_cast<int>(rows < sm_count ? rows : sm_count);
+      kernel<<<grid, kSmemRowThreads, smem, st>>>(xp, yp, rows, d, stats);
+    } else NOVA_ROW(kRowThreads, 0);
   }
 #undef NOVA_ROW
   NOVA_CUDA_OK(cudaGetLastError());
@@ -541,6 +610,105 @@ ln_backward_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* _
   }
 }
 
+// The same for rows of at most kMaxThreads vectors, kRowsPer rows per trip: one vector per thread and row, all
+// 2 * kRowsPer loads of a trip issued before the first is used and ONE block reduction for the trip's
+// 2 * kRowsPer sums, so the per-row latency chain (load, shuffle tree, two barriers, store) is paid once per
+// kRowsPer rows.
+template <typename T, int VEC, int kRowsPer, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
+ln_backward_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
+                        const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
+                        float* __restrict__ partial, int64_t rows, int32_t D) {
+  __shared__ float red[2 * kRowsPer][kMaxThreads / 32];
+  using P = Pack<T, VEC>;
+  const int nvec = D / VEC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const bool mine = static_cast<int>(threadIdx.x) < nvec;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  P gam;
+  float dg[VEC], db[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) { dg[e] = db[e] = 0.0f; gam.e[e] = st_f32<T>(0.0f); }
+  if (mine) gam = reinterpret_cast<const P*>(gamma)[threadIdx.x];
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPer;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * kRowsPer; r0 < rows; r0 += step) {
+    P pg[kRowsPer], px[kRowsPer];
+    float mean[kRowsPer], rs[kRowsPer], s[2 * kRowsPer];
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      if (mine && r < rows) {
+        pg[k] = reinterpret_cast<const P*>(gy + r * D)[threadIdx.x];
+        px[k] = reinterpret_cast<const P*>(x + r * D)[threadIdx.x];
+      }
+    }
+    if (mine && (threadIdx.x * sizeof(P)) % 128 == 0) {  // the trip after this one, one request per 128-byte line
+#pragma unroll
+      for (int k = 0; k < kRowsPer; ++k) {
+        const int64_t r = r0 + step + k;
+        if (r < rows) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const P*>(gy + r * D) + threadIdx.x));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const P*>(x + r * D) + threadIdx.x));
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      const bool live = r < rows;
+      mean[k] = live ? ld_f32<T>(mean_sum[r]) * inv_d : 0.0f;
+      rs[k] = live ? ld_f32<T>(rstd[r]) : 0.0f;
+      float s1 = 0.0f, s2 = 0.0f;
+      if (mine && live) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float g = ld_f32<T>(pg[k].e[e]);
+          const float xhat = (ld_f32<T>(px[k].e[e]) - mean[k]) * rs[k];
+          const float gyg = g * ld_f32<T>(gam.e[e]);
+          s1 += gyg;
+          s2 = fmaf(gyg, xhat, s2);
+          dg[e] = fmaf(g, xhat, dg[e]);
+          db[e] += g;
+        }
+      }
+      s[2 * k] = warp_sum(s1);
+      s[2 * k + 1] = warp_sum(s2);
+    }
+    if (nwarps > 1) {
+      __syncthreads();  // the previous trip's readers are done with red
+      if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < 2 * kRowsPer; ++j) red[j][warp] = s[j];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 2 * kRowsPer; ++j) s[j] = warp_sum(lane < nwarps ? red[j][lane] : 0.0f);
+    }
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      if (mine && r < rows) {
+        const float m1 = s[2 * k] * inv_d, m2 = s[2 * k + 1] * inv_d;
+        const P qg = pg[k], qx = px[k];  // (re-reading them from L1 to free registers was measured: slower)
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float xhat = (ld_f32<T>(qx.e[e]) - mean[k]) * rs[k];
+          const float gyg = ld_f32<T>(qg.e[e]) * ld_f32<T>(gam.e[e]);
+          o.e[e] = st_f32<T>(((gyg - m1) - xhat * m2) * rs[k]);
+        }
+        reinterpret_cast<P*>(dx + r * D)[threadIdx.x] = o;
+      }
+    }
+  }
+  if (mine) {
+    float* pdg = partial + static_cast<size_t>(blockIdx.x) * 2 * D;
+    float* pdb = pdg + D;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { pdg[threadIdx.x * VEC + e] = dg[e]; pdb[threadIdx.x * VEC + e] = db[e]; }
+  }
+}
+
 // dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta[c] likewise from [cta][1][c]; several CTA slices per
 // column are combined through shared memory so that short D still fills the machine.
 template <typename T>
@@ -550,10 +718,26 @@ __global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int
   const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 32)
   float a = 0.0f, b = 0.0f;
   if (c < D)
-    for (int p = threadIdx.y; p < n_partials; p += 32) {
+  {
+    float a1 = 0.0f, b1 = 0.0f, a2 = 0.0f, b2 = 0.0f, a3 = 0.0f, b3 = 0.0f;
+    int p = threadIdx.y;
+    for (; p + 96 < n_partials; p += 128) {  // four independent loads per sum in flight
+      a += partial[static_cast<size_t>(p) * 2 * D + c];
+      b += partial[static_cast<size_t>(p) * 2 * D + D + c];
+      a1 += partial[static_cast<size_t>(p + 32) * 2 * D + c];
+      b1 += partial[static_cast<size_t>(p + 32) * 2 * D + D + c];
+      a2 += partial[static_cast<size_t>(p + 64) * 2 * D + c];
+      b2 += partial[static_cast<size_t>(p + 64) * 2 * D + D + c];
+      a3 += partial[static_cast<size_t>(p + 96) * 2 * D + c];
+      b3 += partial[static_cast<size_t>(p + 96) * 2 * D + D + c];
+    }
+    for (; p < n_partials; p += 32) {
       a += partial[static_cast<size_t>(p) * 2 * D + c];
       b += partial[static_cast<size_t>(p) * 2 * D + D + c];
     }
+    a += a1 + a2 + a3;
+    b += b1 + b2 + b3;
+  }
   sh[0][threadIdx.y][threadIdx.x] = a;
   sh[1][threadIdx.y][threadIdx.x] = b;
   __syncthreads();
@@ -703,8 +887,12 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   const int per_thread = static_cast<int>((nvec + threads - 1) / threads);
   const int max_v = per_thread <= 1 ? 1 : per_thread <= 2 ? 2 : per_thread <= 4 ? 4 : 8;
   // few persistent CTAs: every CTA ends with 2*D floats of column sums that the finish kernel has to read back
-  const int resident = wide ? std::max(1, std::min(8, 2048 / threads)) : (max_v >= 4 ? 1 : 2);
-  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows, static_cast<int64_t>(ctx->sm_count) * resident)));
+  // rows of up to 512 vectors: four rows per trip in one 128-register CTA per SM (measured best of 1, 2, 4 rows
+  // per trip and of one or two CTAs per SM on [8192, 4096] bf16)
+  const int rows_per = threads <= 512 ? 4 : 1;
+  int resident = !wide ? (max_v >= 4 ? 1 : 2) : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
+  const int64_t row_blocks = wide ? (rows + rows_per - 1) / rows_per : rows;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(row_blocks, static_cast<int64_t>(ctx->sm_count) * resident)));
   {
     std::lock_guard<std::mutex> lock(ctx->mu);
     st = ensure_scratch(ctx, static_cast<size_t>(grid) * 2 * D * sizeof(float));
@@ -716,15 +904,22 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
                                                         static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
                                                         static_cast<const T*>(rstd), static_cast<T*>(dx), partial,     \
                                                         rows, static_cast<int32_t>(D))
+#define NOVA_LNB_ROWS(T, V, R, B)                                                                                     \
+  ln_backward_rows_kernel<T, V, R, B><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
+                                                              static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
+                                                              static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
+                                                              static_cast<int32_t>(D))
 #define NOVA_LNB_MV(T, V)                                                                       \
   do {                                                                                          \
-    if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);                  \
+    if (wide && rows_per == 4) NOVA_LNB_ROWS(T, V, 4, 512);                                     \
+    else if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);             \
     else if (max_v == 4) NOVA_LNB(T, V, 4); else NOVA_LNB(T, V, 8);                             \
   } while (0)
   if (dtype == NOVA_B200_F32) { if (vec > 1) NOVA_LNB_MV(float, 4); else NOVA_LNB_MV(float, 1); }
   else if (dtype == NOVA_B200_F16) { if (vec > 1) NOVA_LNB_MV(__half, 8); else NOVA_LNB_MV(__half, 1); }
   else { if (vec > 1) NOVA_LNB_MV(__nv_bfloat16, 8); else NOVA_LNB_MV(__nv_bfloat16, 1); }
 #undef NOVA_LNB_MV
+#undef NOVA_LNB_ROWS
 #undef NOVA_LNB
   NOVA_CUDA_OK(cudaGetLastError());
   const int fin_grid = static_cast<int>((D + 31) / 32);

@@ -36,6 +36,15 @@ def test_softmax(cuda, oracle, dt):
         x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
         y = ops.softmax(to_dev(cuda, x, dt))
         check(oracle, to_host(cuda, y, dt), oracle.softmax(x, dt, compute_f32=True), dt)
+    # rows beyond the register cache: staged in shared memory (up to 220 KB) or read twice (longer).  The oracle adds
+    # the exponentials one by one in fp32, which drifts ~4e-5 over such rows; f32 is also checked against float64.
+    for rows, D in [(4, 50304), (2, 70000)]:
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
+        y = to_host(cuda, ops.softmax(to_dev(cuda, x, dt)), dt)
+        check(oracle, y, oracle.softmax(x, dt, compute_f32=True), dt, tol=1e-4 if dt == "f32" else None)
+        if dt == "f32":
+            e = np.exp(x.astype(np.float64) - x.astype(np.float64).max(-1, keepdims=True))
+            assert oracle.rel_fro(y, e / e.sum(-1, keepdims=True)) <= 2e-6
     # non-last dimension and the attention-score layout
     x = rand_bits(oracle, rng, (4, 96, 50), "f32", "normal")
     y = ops.softmax(to_dev(cuda, x, "f32"), dimension=1)
