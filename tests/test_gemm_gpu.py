@@ -440,6 +440,37 @@ def test_gemm_host_and_memref_entry_points(cuda, oracle, lib):
                                              C.byref(memref(b, L.MemRef2D)), L.F32) == L.ERR_LAYOUT
 
 
+@pytest.mark.parametrize("shape", [(6, 70, 90, 48), (1, 1100, 136, 64)])  # chunked by batch / by 256-row blocks
+def test_gemm_host_pipeline_carries_epilogue_operands(cuda, oracle, lib, shape):
+    """nova_b200_gemm_host cuts the problem into chunks that overlap copies and kernels; the residual (an addend, or
+    the pre-activation of a fused gelu_backward) has to be cut the same way."""
+    from nova_compiler_b200 import _lib as L
+    rng = np.random.default_rng(43)
+    Bn, M, N, K = shape
+    a = oracle.to_bits(rng.normal(size=(Bn, M, K)).astype(np.float32), "bf16")
+    b = oracle.to_bits(rng.normal(size=(Bn, K, N)).astype(np.float32) / 8, "bf16")
+    bias = oracle.to_bits(rng.normal(size=N).astype(np.float32), "bf16")
+    aux = oracle.to_bits(rng.normal(size=(Bn, M, N)).astype(np.float32) * 2, "bf16")
+    for mode in ("bias+residual", "gelu_grad"):
+        c = np.zeros((Bn, M, N), np.uint16)
+        g = L.GemmArgs()
+        g.struct_size = C.sizeof(L.GemmArgs)
+        g.dtype_ab = g.dtype_c = L.BF16
+        g.batch, g.M, g.N, g.K = Bn, M, N, K
+        g.lda, g.ldb, g.ldc, g.ldr = K, N, N, N
+        g.batch_stride_a, g.batch_stride_b, g.batch_stride_c, g.batch_stride_r = M * K, K * N, M * N, M * N
+        g.A, g.B, g.C = a.ctypes.data, b.ctypes.data, c.ctypes.data
+        g.bias, g.residual = bias.ctypes.data, aux.ctypes.data
+        if mode == "bias+residual":
+            g.init = L.INIT_BIAS_AND_RESIDUAL
+            want = oracle.gemm(a, b, dtype_in="bf16", bias=bias, residual=aux)
+        else:
+            g.init, g.act = L.INIT_BIAS_ROW, L.ACT_GELU_TANH_GRAD
+            want = oracle.gemm(a, b, dtype_in="bf16", bias=bias, gelu_grad_of=aux)
+        L.check(lib.nova_b200_gemm_host(C.byref(g)))
+        check(oracle, c, want, "bf16")
+
+
 def test_nova_matmul_rank_rules(cuda, oracle):
     """nova.matmul shape rules (MatmulOp::inferReturnTypes, NovaOps.cpp:1116-1285)."""
     torch = cuda
