@@ -2,8 +2,9 @@
 // output tile with tcgen05.mma.cta_group::2.
 //
 // Each CTA loads ITS 128 rows of A and ITS 128 columns of B (every CTA fetches its own boxes; nothing is
-// multicast), so a ring stage is 32 KB instead of 48 KB: six stages of look-ahead instead of four, and
-// a third less shared-memory fill traffic per SM.  The leader CTA (cluster rank 0) issues the MMAs; the
+// multicast): a third less shared-memory fill traffic per SM and per unit of work than a single-CTA 128 x 256
+// tile.  A ring stage holds two 64-element K boxes of each operand (64 KB per CTA, three stages): the fixed cost
+// of a stage hand-over is paid once per 128 K.  The leader CTA (cluster rank 0) issues the MMAs; the
 // tensor cores of both SMs read A from their own shared memory and the two halves of B from both, and
 // each accumulates its 128 rows x 256 columns in its own tensor memory.
 //
@@ -14,8 +15,8 @@
 //   tmem_full[a]  one per CTA; same commit-to-both.
 //   tmem_empty[a] lives in the leader; every epilogue warp of both CTAs arrives on it.
 //
-// Used when both operands can be loaded with TMA and the problem has at least a wave of 256 x 256 tiles;
-// everything else runs the single-CTA kernel of gemm_kernel.cuh.
+// Used when both operands can be loaded with TMA, K >= 256 and the tile cost model of the launcher prices pairs
+// below single-CTA tiles; everything else runs the single-CTA kernel of gemm_kernel.cuh.
 #pragma once
 #include "gemm_kernel.cuh"
 

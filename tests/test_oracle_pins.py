@@ -97,7 +97,7 @@ def test_reference_faithful_low_precision_mode_differs_but_is_close(oracle):
     B = oracle.to_bits(rng.normal(size=(256, 16)).astype(np.float32) / 16, "bf16")
     n = oracle.from_bits(oracle.gemm(A, B, dtype_in="bf16", acc="f32"), "bf16")
     r = oracle.from_bits(oracle.gemm(A, B, dtype_in="bf16", acc="result"), "bf16")
-    assert 0 < oracle.rel_fro(r, n) < 0.1  # bf16 accumulation loses bits, as the survey notes
+    assert 0 < oracle.rel_fro(r, n) < 0.1  # bf16 accumulation loses bits
 
 
 def test_dtype_converters_match_numpy_and_torch(oracle):
