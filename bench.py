@@ -51,6 +51,7 @@ NCU_TRAFFIC_BYTES = {
     "c2": 173.7e6,      # 134.3 MB read + 39.4 MB written (part of the 67 MB output is still in L2 at kernel end)
     "c3": 468.5e6,      # 308.0 MB read + 160.5 MB written
     "c4": 8 * 243.4e6,  # captured on 32 of the 256 batches (c4s), scaled by 8: traffic is proportional to batches
+    "c5c": 207.7e6,     # the contraction kernel: 140.2 MB read + 67.5 MB written (the re-pitch copy before it: 203.8 MB)
 }
 
 
