@@ -636,7 +636,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
       tc_fence_before_sync();
       mbar_arrive(tmem_empty_bar(acc));
     }
-    if (p.vec_store && lane == 0) tma_store_wait_all<0>();  // staged boxes fully written before the CTA exits
+    if (p.vec_store && lane == 0) tma_store_wait_read<0>();  // staged boxes read out before shared memory goes away
     __syncwarp();
   } else if (kLoader) {
     // ============================================================ ld.global loader (operands TMA cannot address)

@@ -249,7 +249,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         trace_value(p.trace, tile_iter, kTraceEpiIssue, waits[4]);
       }
     }
-    if (p.vec_store && lane == 0) tma_store_wait_all<0>();
+    if (p.vec_store && lane == 0) tma_store_wait_read<0>();  // staged boxes read out before shared memory goes away
     __syncwarp();
   }
 

@@ -134,26 +134,32 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   // tile; pairs stream ~7 % faster and cost a cluster launch and cluster barriers up front.
   const int sms = sm_count > 0 ? sm_count : 148;
   const bool both_tma = pi.loader_a != 1 && pi.loader_b != 1;
-  const int64_t n128 = (a->N + 127) / 128, n256 = (a->N + 255) / 256;
+  const int64_t n64 = (a->N + 63) / 64, n128 = (a->N + 127) / 128, n256 = (a->N + 255) / 256;
+  const int64_t tiles64 = a->batch * m_blocks * n64;
   const int64_t tiles128 = a->batch * m_blocks * n128, tiles256 = a->batch * m_blocks * n256;
   const int64_t pair_tiles = a->batch * ((a->M + kPairBlockM - 1) / kPairBlockM) * ((a->N + kPairBlockN - 1) / kPairBlockN);
   auto waves = [](int64_t tiles, int64_t slots) { return static_cast<double>((tiles + slots - 1) / slots); };
   const double kd = static_cast<double>(a->K);
+  // (128 x 64 tiles only pay when the problem is a fraction of a wave: twice the CTAs, each half the K-loop work)
+  const double cost64 = waves(tiles64, sms) * std::max(7.0 * kd, 2000.0) + 10500.0;
   const double cost128 = waves(tiles128, sms) * std::max(9.3 * kd, 3000.0) + 11000.0;
   // (the short-K build below drains a 128 x 256 tile with eight warps)
   const double drain256 = (a->K <= 256 && pi.store_c == 0) ? 3900.0 : 6000.0;
   const double cost256 = waves(tiles256, sms) * std::max(9.1 * kd, drain256) + 11800.0;
   const double cost_pair = waves(pair_tiles, sms / 2) * std::max(8.5 * kd, 5000.0) + 13100.0;
   // (contractions shorter than two 128-element stages are bound by their epilogue, which pairs do not help)
-  bool pair = plan->terms == 1 && both_tma && a->K >= 256 && cost_pair <= cost128 && cost_pair <= cost256;
+  bool pair = plan->terms == 1 && both_tma && a->K >= 256 && cost_pair <= cost128 && cost_pair <= cost256 &&
+              cost_pair <= cost64;
   int block_n = 256;
-  if (plan->terms == 3) block_n = 128;  // two operand copies per stage: 256-wide stages do not fit
+  if (plan->terms == 3) block_n = tiles128 <= sms / 4 ? 64 : 128;  // two operand copies per stage: 256 does not fit
+  else if (both_tma && plan->terms == 1 && cost64 < cost128 && (a->N <= 128 || cost64 < cost256)) block_n = 64;
   else if (a->N <= 128) block_n = 128;
   else if (both_tma && plan->terms == 1) block_n = cost128 < cost256 ? 128 : 256;
   else if (tiles256 < sms) block_n = 128;  // loader warps: keep every SM's loaders busy
   if (const char* e = std::getenv("NOVA_B200_BLOCK_N")) {
     const int v = std::atoi(e);
     if ((v == 128 || v == 256) && plan->terms != 3) { block_n = v; pair = false; }
+    if (v == 64 && (plan->terms == 3 || both_tma)) { block_n = v; pair = false; }
   }
   if (const char* e = std::getenv("NOVA_B200_PAIR")) {
     const int v = std::atoi(e);
@@ -161,10 +167,10 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     else pair = plan->terms == 1 && both_tma && a->K >= 256;
   }
   pi.block_n = block_n;
-  const int64_t tiles = block_n == 256 ? tiles256 : tiles128;
+  const int64_t tiles = block_n == 256 ? tiles256 : (block_n == 128 ? tiles128 : tiles64);
   if (tiles > kMaxExtent) return fail(NOVA_B200_ERR_TOO_LARGE, "gemm: more than 2^31-1 output tiles");
   pi.tiles = tiles;
-  pi.stages = plan->terms == 3 ? 3 : (block_n == 256 ? 4 : 6);
+  pi.stages = plan->terms == 3 ? (block_n == 64 ? 4 : 3) : (block_n == 256 ? 4 : (block_n == 128 ? 6 : 8));
   pi.grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
   plan->pair = pair;
   // K <= 256 with full-width tiles: the mainloop of a tile is at most four k-blocks, the time goes into
@@ -480,7 +486,14 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   }
   const bool loader = pi.loader_a == 1 || pi.loader_b == 1;
   const int grid = pi.grid;
-  if (plan.terms == 3) return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  if (plan.terms == 3) {
+    if (block_n == 64) return launch_majors<64, 4, 3, 4, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  }
+  if (block_n == 64) {  // TMA-only build: narrow tiles are chosen only for operands tensor maps can describe
+    if (es == 2) return launch_majors<64, 2, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    return launch_majors<64, 4, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  }
   if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps
     if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
     return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);

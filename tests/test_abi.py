@@ -66,9 +66,12 @@ def test_plan_aligned_operands_use_tma(lib):
     # pairs or two waves of 128 x 128 tiles
     st, info = _plan(lib, _args(2048, 2048, 2048))
     assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 256, 4, 128, 128)
-    # 1024^3: 32 tiles of 128 x 256 would leave most SMs idle; 64 tiles of 128 x 128
+    # 1536^3: 144 tiles of 128 x 128 fill one wave
+    st, info = _plan(lib, _args(1536, 1536, 1536))
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 128, 6, 144, 144)
+    # 1024^3: even 64 tiles of 128 x 128 leave most SMs idle; 128 tiles of 128 x 64 (eight 24 KB stages)
     st, info = _plan(lib, _args(1024, 1024, 1024))
-    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 128, 6, 64, 64)
+    assert st == L.OK and (info.block_m, info.block_n, info.stages, info.tiles, info.grid) == (128, 64, 8, 128, 128)
     # a short contraction (K <= 256) is epilogue-bound: single-CTA 128 x 256 tiles, three 48 KB stages and a
     # second set of epilogue warps
     st, info = _plan(lib, _args(2048, 2048, 128, dt=L.F16, batch=256))
@@ -99,7 +102,10 @@ def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
 
 def test_plan_f32_modes(lib):
     st, info = _plan(lib, _args(512, 512, 512, dt=L.F32))
-    assert st == L.OK and info.block_n == 128 and info.block_k == 32 and info.stages == 3
+    # 16 tiles of 128 x 128 would use 16 SMs: 128 x 64 tiles, four stages of hi and lo copies of both operands
+    assert st == L.OK and info.block_n == 64 and info.block_k == 32 and info.stages == 4 and info.tiles == 32
+    st2, big = _plan(lib, _args(4096, 4096, 512, dt=L.F32))
+    assert st2 == L.OK and big.block_n == 128 and big.stages == 3
     assert info.scratch_bytes == 2 * 4 * (512 * 512 + 512 * 512)  # hi and lo copies of A and B
     st, info = _plan(lib, _args(512, 512, 512, dt=L.F32, f32_mode=L.TF32X1))
     assert st == L.OK and info.scratch_bytes == 0
@@ -111,7 +117,7 @@ def test_plan_f32_modes(lib):
 
 def test_plan_small_problems_use_narrow_tiles(lib):
     st, info = _plan(lib, _args(8, 10, 16, dt=L.F16))
-    assert st == L.OK and info.block_n == 128 and info.tiles == 1 and info.grid == 1
+    assert st == L.OK and info.block_n == 64 and info.tiles == 1 and info.grid == 1
     st, info = _plan(lib, _args(1024, 1024, 1024, dt=L.F16, batch=32))
     assert st == L.OK and (info.block_m, info.block_n) == (256, 256) and info.tiles == 32 * 4 * 4
 
