@@ -721,23 +721,35 @@ struct SplitOperand {
 
 __global__ void nova_split_tf32_kernel(const SplitOperand oa, const SplitOperand ob) {
   const SplitOperand& o = blockIdx.y == 0 ? oa : ob;
-  const int64_t n = o.rows_total * o.ld_out;
+  // four output columns per thread (ld_out is a multiple of 4 and the scratch is 16-byte aligned); the input is
+  // read as one float4 when its row start allows, else element-wise
+  const int32_t quads = o.ld_out >> 2;
+  const int64_t n = o.rows_total * quads;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / o.ld_out;
-    const int32_t c = static_cast<int32_t>(i - r * o.ld_out);
-    float h = 0.0f, l = 0.0f;
-    if (c < o.cols) {
-      const int64_t b = r / o.rows_per_batch;
-      const int64_t rr = r - b * o.rows_per_batch;
-      const float v = o.x[b * o.stride_in + rr * o.ld_in + c];
-      uint32_t hb;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v));
-      h = __uint_as_float(hb);
-      l = v - h;
+    const int64_t r = i / quads;
+    const int32_t c = static_cast<int32_t>(i - r * quads) << 2;
+    const int64_t b = r / o.rows_per_batch;
+    const float* src = o.x + b * o.stride_in + (r - b * o.rows_per_batch) * o.ld_in + c;
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (c + 4 <= o.cols && (reinterpret_cast<uintptr_t>(src) & 15u) == 0u) {
+      const float4 q = *reinterpret_cast<const float4*>(src);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < o.cols) v[e] = src[e];
     }
-    o.hi[i] = h;
-    o.lo[i] = l;
+    float h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      uint32_t hb;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v[e]));
+      h[e] = __uint_as_float(hb);
+      l[e] = v[e] - h[e];
+    }
+    reinterpret_cast<float4*>(o.hi)[i] = make_float4(h[0], h[1], h[2], h[3]);
+    reinterpret_cast<float4*>(o.lo)[i] = make_float4(l[0], l[1], l[2], l[3]);
   }
 }
 

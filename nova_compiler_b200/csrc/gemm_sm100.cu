@@ -392,7 +392,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     SplitOperand ob{static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows, a->ldb, a->batch_stride_b,
                     static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols), static_cast<int32_t>(b_ldo)};
     const int64_t biggest = std::max(a_nb * a_rows * a_ldo, b_nb * b_rows * b_ldo);
-    const int64_t want = (biggest + 255) / 256;
+    const int64_t want = (biggest / 4 + 255) / 256;  // four elements per thread
     const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8)));
     nova_split_tf32_kernel<<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
     NOVA_CUDA_OK(cudaGetLastError());
