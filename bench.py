@@ -52,6 +52,8 @@ NCU_TRAFFIC_BYTES = {
     "c3": 468.5e6,      # 308.0 MB read + 160.5 MB written
     "c4": 8 * 243.4e6,  # captured on 32 of the 256 batches (c4s), scaled by 8: traffic is proportional to batches
     "c5c": 207.7e6,     # the contraction kernel: 140.2 MB read + 67.5 MB written (the re-pitch copy before it: 203.8 MB)
+    # row kernels (reads match the inputs exactly; part of each output is still in L2 when the kernel ends)
+    "ln": 92.3e6, "ln_bwd": 176.0e6, "softmax": 489.8e6, "sce": 3246.0e6, "sce_bwd": 3252.9e6, "gather": 209.2e6,
 }
 
 
