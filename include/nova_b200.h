@@ -101,8 +101,17 @@ typedef enum nova_b200_f32_mode {
  * Layout: all tensors row-major with unit inner stride; ld* are row pitches in ELEMENTS,
  * batch strides are in elements (0 = the same matrix for every batch).  With trans_a the buffer
  * holds A as [K, M] (lda >= M); with trans_b it holds B as [N, K] (ldb >= K).  Accumulation is
- * always fp32.  Ragged M/N/K need no padding.  Operands whose base or pitch is not a multiple of
- * 16 bytes are read through a non-TMA loader instead of being repacked (see nova_b200_gemm_plan). */
+ * always fp32.  Ragged M/N/K need no padding of extents.
+ *
+ * Scratch: two kinds of call pass their operands through library-owned device scratch first (scratch_bytes > 0 in
+ * nova_b200_gemm_plan): f32 operands in TF32X3 mode (hi/lo split), and 16-bit / TF32X1 operands whose base or row
+ * pitch is not a multiple of 16 bytes, which no tensor map can describe: by default they are copied once per call
+ * to an aligned pitch ("re-pitch", loader_a/b == 2; nova_b200_operand_prepare does that copy once for a constant
+ * operand), or, with option "repitch" = 0, read in place by loader warps at a fraction of the rate (loader == 1, no
+ * scratch).  Scratch is kept per (device, stream), so calls on different streams never share it; it grows on
+ * demand with cudaMalloc (never synchronising, never freeing a buffer that enqueued work may still read), which is
+ * refused while the stream is being captured: make one call of the same size, or nova_b200_reserve_scratch, before
+ * capturing.  A captured graph stays valid until nova_b200_shutdown. */
 typedef struct nova_b200_gemm_args {
   uint32_t struct_size; /* = sizeof(nova_b200_gemm_args), for ABI evolution */
   int32_t dtype_ab;     /* NOVA_B200_F32 / F16 / BF16: element type of A and B */
@@ -122,7 +131,8 @@ typedef struct nova_b200_gemm_args {
   int64_t batch_stride_a, batch_stride_b, batch_stride_c, batch_stride_r;
 } nova_b200_gemm_args;
 
-/* How a call will be executed; filled by nova_b200_gemm_plan without launching anything. */
+/* How a call will be executed; filled by nova_b200_gemm_plan without launching anything.  The plan is the one a
+ * 148-SM B200 executes (no device is needed to ask for it). */
 typedef struct nova_b200_gemm_plan_info {
   int32_t loader_a;     /* 0 = TMA; unaligned base or pitch: 2 = re-pitched into aligned scratch first, then TMA
                            (the default), 1 = predicated ld.global loader warps (NOVA_B200_REPITCH=0) */
@@ -145,7 +155,41 @@ int32_t nova_b200_shutdown(void);
 const char* nova_b200_last_error_string(void);
 int32_t nova_b200_abi_version(void);
 
-/* The contraction; device pointers; enqueues on `stream`. */
+/* Tuning switches, process-wide.  Each is seeded once from the environment variable NOVA_B200_<NAME> and can be
+ * changed at run time (later calls see the new value; cached plans are dropped):
+ *   "repitch" (1)  unaligned operands: 1 = copy to an aligned pitch in scratch and stream with TMA, 0 = loader warps
+ *   "pair" (-1)    CTA-pair (cta_group::2) kernel: -1 = cost model, 0 = never, 1 = whenever legal
+ *   "block_n" (0)  tile width: 0 = cost model, else 64 / 128 / 256
+ *   "short_k" (1)  eight epilogue warps for K <= 256
+ *   "group_m" (16) raster group height in row blocks
+ *   "prefetch" (-1) L2 prefetch distance of the pair kernel in ring stages: -1 = planner, 0 = off
+ *   "pdl" (1)      launch contractions with programmatic stream serialization (prologue overlaps the previous kernel's tail)
+ *   "plan_cache" (1) reuse plans and tensor maps of repeated calls;  "debug" (0)
+ * No counterpart in the reference (its schedule is fixed at compile time by lowering_config attributes,
+ * lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1487-1577). */
+int32_t nova_b200_set_option(const char* name, int64_t value);
+int32_t nova_b200_get_option(const char* name, int64_t* value_out);
+
+/* Makes sure `stream` of the current device owns at least `bytes` of library scratch (see nova_b200_gemm_args), so
+ * that later calls on it, e.g. under stream capture, need not allocate.  Counterpart in the reference: the
+ * cudaMallocAsync calls its generated host code makes per launch (lib/Transforms/FixGpuLaunch.cpp:49-50). */
+int32_t nova_b200_reserve_scratch(int64_t bytes, void* stream);
+
+/* A constant operand (a weight) whose base or row pitch is not a multiple of 16 bytes, copied ONCE into
+ * library-owned memory with an aligned pitch: pass the returned view to nova_b200_gemm as A or B and the call
+ * streams it with TMA at the full rate without the per-call re-pitch copy.  `src_dev` is [batch, rows, cols]
+ * with row pitch `ld` and batch stride `batch_stride` (elements; 0 = one matrix); rows/cols are those of the
+ * STORED matrix (for B [K, N]: rows = K, cols = N).  The copy is enqueued on `stream`.  This is the compile-time
+ * counterpart of the reference's per-tile PadOperands copy (lib/Transforms/LLVMGPU/Tiling/NovaGPUPadOperands.cpp:34-65):
+ * done once for the operand instead of inside every workgroup tile, and only the pitch is padded, not the extents. */
+typedef struct nova_b200_operand nova_b200_operand;
+int32_t nova_b200_operand_prepare(const void* src_dev, int32_t dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ld,
+                                  int64_t batch_stride, void* stream, nova_b200_operand** out);
+int32_t nova_b200_operand_view(const nova_b200_operand* op, const void** data_dev, int64_t* ld, int64_t* batch_stride);
+void nova_b200_operand_free(nova_b200_operand* op);
+
+/* The contraction; device pointers; enqueues on `stream`.  In a process that sees several devices, operands that
+ * live on another device than the current one are refused (NOVA_B200_ERR_INVALID_ARG) before anything is launched. */
 int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream);
 /* Validation + kernel selection only (no launch); usable without a GPU. */
 int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
@@ -169,7 +213,7 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args);
  *  - Limit: the split needs 8 bytes per element of A and of B (rows padded to a multiple of 4
  *    elements); the array holds 16 MiB of it (e.g. 1024x1024x1024, or batch 4 of 512^3).  Larger
  *    requests return NOVA_B200_ERR_TOO_LARGE; non-f32 or TF32X1 requests return
- *    NOVA_B200_ERR_UNSUPPORTED (they use no scratch: call nova_b200_gemm).
+ *    NOVA_B200_ERR_UNSUPPORTED (with 16-byte-aligned operands they use no scratch in nova_b200_gemm).
  *  - Every GPU on which the library is loaded holds the 16 MiB + 256 B until the process exits.
  *  - The first call on each device resolves the array's device address and the tensor-map encoder
  *    (no allocation, but driver calls): make that first call outside any stream capture.
@@ -177,7 +221,8 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args);
  *    clears the status word and rewrites every scratch byte it reads, so consecutive calls on one
  *    stream are safe; calls that overlap on the GPU (different streams, or this and another process
  *    thread) race on the scratch and give wrong results.
- *  - wait_code_out == NULL: the call only enqueues.  Otherwise it synchronises `stream`, stores the
+ *  - wait_code_out == NULL: the call only enqueues; a wait that gave up is then reported by the next
+ *    nova_b200_device_status.  Otherwise the call clears the status word, synchronises `stream`, stores the
  *    device-side wait code (0 = every bounded wait completed) and returns
  *    NOVA_B200_ERR_DEVICE_TIMEOUT when it is non-zero. */
 int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream, uint32_t* wait_code_out);
@@ -253,8 +298,9 @@ int32_t nova_b200_gather(const void* in_dev, const void* idx_dev, void* out_dev,
                          int64_t post, int64_t n_idx, int32_t idx_dtype, int32_t batched_idx, int32_t elem_bytes,
                          int64_t* bad_count_dev, void* stream);
 
-/* Reads (and clears) the device-side status word of the current device: 0 when every bounded wait
- * inside the kernels completed; otherwise a code naming the wait that gave up.  Synchronises the device. */
+/* Reads (and clears) the device-side status words of the current device (the allocated one and, once
+ * nova_b200_gemm_f32_static has run there, the one inside its static array): 0 when every bounded wait inside the
+ * kernels completed; otherwise a code naming the wait that gave up.  Synchronises the device. */
 int32_t nova_b200_device_status(uint32_t* code_out);
 
 /* ---- memref-descriptor entry points ------------------------------------------------------------
@@ -281,6 +327,14 @@ typedef struct nova_b200_memref3d {
   int64_t strides[3];
 } nova_b200_memref3d;
 
+typedef struct nova_b200_memref4d {
+  void* allocated;
+  void* aligned;
+  int64_t offset;
+  int64_t sizes[4];
+  int64_t strides[4];
+} nova_b200_memref4d;
+
 typedef struct nova_b200_memref1d {
   void* allocated;
   void* aligned;
@@ -296,6 +350,12 @@ int32_t _mlir_ciface_nova_b200_matmul(nova_b200_memref2d* C, nova_b200_memref2d*
 /* C[b] = A[b] * B[b] (linalg.batch_matmul, NovaToLinalg.cpp:1039-1043); ab_dtype inputs, c_dtype output. */
 int32_t _mlir_ciface_nova_b200_batch_matmul(nova_b200_memref3d* C, nova_b200_memref3d* A, nova_b200_memref3d* B,
                                             int32_t ab_dtype, int32_t c_dtype);
+/* Rank-4 batch_matmul: nova.matmul on rank > 3 operands collapses the batch dims to one, runs batch_matmul and
+ * expands the result (NovaToLinalg.cpp:904-989); the collapse is metadata when the two batch dims of an operand
+ * are contiguous with each other (else the outer dim is walked, one batched call per slice).  A batch dim of
+ * size 1 in B broadcasts. */
+int32_t _mlir_ciface_nova_b200_batch_matmul_4d(nova_b200_memref4d* C, nova_b200_memref4d* A, nova_b200_memref4d* B,
+                                               int32_t ab_dtype, int32_t c_dtype);
 /* Y = act(X * W + bias) (nova.linear rank 2, NovaToLinalgGeneric.cpp:1623-1823, + optional activation). */
 int32_t _mlir_ciface_nova_b200_linear(nova_b200_memref2d* Y, nova_b200_memref2d* X, nova_b200_memref2d* W,
                                       nova_b200_memref1d* bias, int32_t dtype, int32_t act);
@@ -334,6 +394,16 @@ int32_t nova_b200_module_plan(const nova_b200_module* m, const char* func, char*
  * are allocated with cudaMallocAsync on `stream` and freed when the call returns (stream-ordered). */
 int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const nova_b200_tensor* args, int32_t n_args,
                              nova_b200_tensor* results, int32_t n_results, void* stream);
+
+/* The dynamic-argument form of the outer entry point: the reference renames a multi-argument `main` to
+ * `_mlir_ciface_main_impl` and emits `_mlir_ciface_main(result*, void** args)` that unpacks the pointer array
+ * (lib/Transforms/GenerateDynamicWrapper.cpp:34-95).  Here: `args[i]` points at the memref descriptor
+ * {allocated, aligned, offset, sizes[R], strides[R]} of argument i of @func and `result` at the descriptor of its
+ * result (several results: their descriptors one after the other, as MLIR packs a struct of memrefs); ranks and
+ * element types come from the function's signature.  Descriptors must be row-major contiguous.  Buffers may be
+ * host or device memory (detected per pointer; host buffers are staged).  Result buffers are caller-provided
+ * (result->aligned != NULL): the library never allocates user-visible outputs.  Synchronises before returning. */
+int32_t nova_b200_module_call_ciface(const nova_b200_module* m, const char* func, void* result, void** args);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

@@ -52,7 +52,7 @@ def _memref(rank: int):
     return MemRef
 
 
-MemRef1D, MemRef2D, MemRef3D = _memref(1), _memref(2), _memref(3)
+MemRef1D, MemRef2D, MemRef3D, MemRef4D = _memref(1), _memref(2), _memref(3), _memref(4)
 
 
 class Tensor(C.Structure):
@@ -65,6 +65,13 @@ PROTOTYPES = {
     "nova_b200_shutdown": (C.c_int32, []),
     "nova_b200_last_error_string": (C.c_char_p, []),
     "nova_b200_abi_version": (C.c_int32, []),
+    "nova_b200_set_option": (C.c_int32, [C.c_char_p, C.c_int64]),
+    "nova_b200_get_option": (C.c_int32, [C.c_char_p, C.POINTER(C.c_int64)]),
+    "nova_b200_reserve_scratch": (C.c_int32, [C.c_int64, C.c_void_p]),
+    "nova_b200_operand_prepare": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                              C.c_void_p, C.POINTER(C.c_void_p)]),
+    "nova_b200_operand_view": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "nova_b200_operand_free": (None, [C.c_void_p]),
     "nova_b200_gemm": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p]),
     "nova_b200_gemm_plan": (C.c_int32, [C.POINTER(GemmArgs), C.POINTER(GemmPlanInfo)]),
     "nova_b200_gemm_host": (C.c_int32, [C.POINTER(GemmArgs)]),
@@ -98,6 +105,9 @@ PROTOTYPES = {
                                                   C.c_int32]),
     "_mlir_ciface_nova_b200_batch_matmul": (C.c_int32, [C.POINTER(MemRef3D), C.POINTER(MemRef3D), C.POINTER(MemRef3D),
                                                         C.c_int32, C.c_int32]),
+    "_mlir_ciface_nova_b200_batch_matmul_4d": (C.c_int32, [C.POINTER(MemRef4D), C.POINTER(MemRef4D), C.POINTER(MemRef4D),
+                                                           C.c_int32, C.c_int32]),
+    "nova_b200_module_call_ciface": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(C.c_void_p)]),
     "_mlir_ciface_nova_b200_linear": (C.c_int32, [C.POINTER(MemRef2D), C.POINTER(MemRef2D), C.POINTER(MemRef2D),
                                                   C.POINTER(MemRef1D), C.c_int32, C.c_int32]),
 }
@@ -128,6 +138,16 @@ def load() -> C.CDLL:
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+def set_option(name: str, value: int) -> None:
+    check(load().nova_b200_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    v = C.c_int64(0)
+    check(load().nova_b200_get_option(name.encode(), C.byref(v)))
+    return int(v.value)
 
 
 def check(status: int) -> None:

@@ -7,6 +7,7 @@
 
 #include <cstring>
 #include <memory>
+#include <vector>
 
 #include "frontend.h"
 #include "runtime.h"
@@ -471,6 +472,87 @@ int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const 
                                    cudaMemcpyDeviceToDevice, ex.stream));
   }
   return NOVA_B200_OK;
+}
+
+int32_t nova_b200_module_call_ciface(const nova_b200_module* m, const char* func, void* result, void** args) {
+  if (!m || !func) return fail(NOVA_B200_ERR_INVALID_ARG, "module_call_ciface: null argument");
+  const fe::Function* f = m->module.find(func);
+  if (!f) return fail(NOVA_B200_ERR_INVALID_ARG, std::string("module_call_ciface: no function @") + func);
+  fe::Plan p;
+  std::string err;
+  if (!fe::plan_function(*f, &p, &err)) return fail(NOVA_B200_ERR_UNSUPPORTED, err);
+  const int32_t n_args = static_cast<int32_t>(f->arg_types.size()), n_results = static_cast<int32_t>(p.results.size());
+  if ((n_args && !args) || (n_results && !result)) return fail(NOVA_B200_ERR_INVALID_ARG, "module_call_ciface: null descriptor list");
+  int32_t st = NOVA_B200_OK;
+  if (!current_context(&st)) return st;
+
+  struct Staged { void* dev = nullptr; void* host = nullptr; size_t bytes = 0; };
+  std::vector<Staged> temps;       // device copies of host buffers (inputs and outputs)
+  std::vector<Staged> copy_back;   // outputs that live in host memory
+  auto cleanup = [&]() { for (Staged& t : temps) cudaFree(t.dev); };
+  auto is_device = [](const void* ptr) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) { cudaGetLastError(); return false; }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+  };
+  // descriptor {allocated, aligned, offset, sizes[R], strides[R]} -> a contiguous row-major tensor on the device
+  auto bind = [&](const int64_t* d, const fe::Type& t, bool is_output, const std::string& what, nova_b200_tensor* out) -> int32_t {
+    const int rank = static_cast<int>(t.shape.size());
+    if (rank > 6) return fail(NOVA_B200_ERR_UNSUPPORTED, what + ": rank > 6");
+    const int64_t* sizes = d + 3;
+    const int64_t* strides = d + 3 + rank;
+    int64_t expect = 1;
+    for (int i = rank - 1; i >= 0; --i) {
+      if (sizes[i] != t.shape[i]) return fail(NOVA_B200_ERR_INVALID_ARG, what + ": descriptor sizes do not match the signature");
+      if (sizes[i] != 1 && strides[i] != expect) return fail(NOVA_B200_ERR_LAYOUT, what + ": descriptor is not row-major contiguous");
+      expect *= sizes[i];
+    }
+    const int es = dtype_bytes(t.dtype);
+    void* aligned = reinterpret_cast<void*>(static_cast<uintptr_t>(d[1]));
+    if (!aligned && t.numel() > 0) return fail(NOVA_B200_ERR_INVALID_ARG, what + ": null buffer (results are caller-provided)");
+    char* ptr = static_cast<char*>(aligned) + d[2] * es;
+    const size_t bytes = static_cast<size_t>(t.numel()) * es;
+    std::memset(out, 0, sizeof(*out));
+    out->dtype = t.dtype;
+    out->rank = rank;
+    for (int i = 0; i < rank; ++i) out->shape[i] = t.shape[i];
+    if (bytes == 0 || is_device(ptr)) {
+      out->data = ptr;
+      return NOVA_B200_OK;
+    }
+    Staged sgd;
+    sgd.host = ptr;
+    sgd.bytes = bytes;
+    NOVA_CUDA_OK(cudaMalloc(&sgd.dev, bytes));
+    temps.push_back(sgd);
+    if (!is_output) NOVA_CUDA_OK(cudaMemcpyAsync(sgd.dev, ptr, bytes, cudaMemcpyHostToDevice, nullptr));
+    else copy_back.push_back(sgd);
+    out->data = sgd.dev;
+    return NOVA_B200_OK;
+  };
+  std::vector<nova_b200_tensor> in(static_cast<size_t>(n_args)), outs(static_cast<size_t>(n_results));
+  for (int32_t i = 0; i < n_args; ++i) {
+    if (!args[i]) { cleanup(); return fail(NOVA_B200_ERR_INVALID_ARG, "module_call_ciface: null argument descriptor"); }
+    st = bind(static_cast<const int64_t*>(args[i]), f->arg_types[i], false, "argument " + std::to_string(i), &in[i]);
+    if (st != NOVA_B200_OK) { cleanup(); return st; }
+  }
+  const int64_t* rd = static_cast<const int64_t*>(result);
+  for (int32_t i = 0; i < n_results; ++i) {
+    auto it = p.types.find(p.results[i]);
+    if (it == p.types.end()) it = p.types.find(p.results[i] + "#0");
+    if (it == p.types.end()) { cleanup(); return fail(NOVA_B200_ERR_INVALID_ARG, "module_call_ciface: untyped result"); }
+    st = bind(rd, it->second, true, "result " + std::to_string(i), &outs[i]);
+    if (st != NOVA_B200_OK) { cleanup(); return st; }
+    rd += 3 + 2 * it->second.shape.size();
+  }
+  st = nova_b200_module_run(m, func, in.data(), n_args, outs.data(), n_results, nullptr);
+  if (st == NOVA_B200_OK) {
+    for (Staged& c : copy_back)
+      if (cudaMemcpyAsync(c.host, c.dev, c.bytes, cudaMemcpyDeviceToHost, nullptr) != cudaSuccess) st = fail(NOVA_B200_ERR_CUDA, "module_call_ciface: copy back failed");
+  }
+  if (cudaStreamSynchronize(nullptr) != cudaSuccess && st == NOVA_B200_OK) st = fail(NOVA_B200_ERR_CUDA, "module_call_ciface: synchronize failed");
+  cleanup();
+  return st;
 }
 
 }  // extern "C"

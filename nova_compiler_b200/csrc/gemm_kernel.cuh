@@ -60,6 +60,7 @@ struct GemmKernelParams {
   const void* residual;
   int64_t ldc, stride_c, ldr, stride_r;
   int32_t act, init, out_dtype, vec_store;
+  int32_t prefetch_dist;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads (0 = none)
   uint32_t* status;
 };
 
@@ -515,6 +516,9 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  // everything above touched only this CTA's shared and tensor memory: it may overlap the previous kernel's tail
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     // ============================================================ TMA producer

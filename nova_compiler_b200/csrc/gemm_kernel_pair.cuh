@@ -107,6 +107,9 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
   if (threadIdx.x == 0) trace_mark(p.trace, 1, kTraceKernel);
+  // everything above touched only the pair's shared and tensor memory: it may overlap the previous kernel's tail
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     // ============================================================ TMA producer (one per CTA)
@@ -116,6 +119,41 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
+      // Optional L2 prefetch cursor, p.prefetch_dist ring stages ahead of the loads (it runs on into the pair's
+      // next tile): pays when operands come cold from HBM and few tiles share a panel; costs L2 request slots
+      // when the panels are already L2-resident, so the launcher decides.
+      int32_t pf_tile = pair;
+      int pf_kb = 0;
+      auto pf_advance = [&]() {
+        if (++pf_kb == p.k_blocks) { pf_kb = 0; pf_tile += num_pairs; }
+      };
+      auto pf_issue = [&]() {
+        if (pf_tile >= p.tiles) return;
+        const TileCoord t = decode_tile(p, pf_tile);
+        const int m0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM;
+        const int n0 = t.n_blk * kPairBlockN + static_cast<int>(rank) * kHalfN;
+        const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
+#pragma unroll
+        for (int sub = 0; sub < kPairSubK; ++sub) {
+          const int k0 = pf_kb * kBlockK + sub * kSubBlockK;
+          if (k0 >= p.K) break;
+          if (!kAMn) {
+            tma_prefetch_3d(&tmap_a, k0, m0, za);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBlockM / kElemsPerRow; ++c) tma_prefetch_3d(&tmap_a, m0 + c * kElemsPerRow, k0, za);
+          }
+          if (!kBMn) {
+            tma_prefetch_3d(&tmap_b, k0, n0, zb);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kHalfN / kElemsPerRow; ++c) tma_prefetch_3d(&tmap_b, n0 + c * kElemsPerRow, k0, zb);
+          }
+        }
+      };
+      const bool prefetch = p.prefetch_dist > 0;
+      if (prefetch)
+        for (int i = 0; i < p.prefetch_dist; ++i) pf_advance();
       for (int32_t tile = pair; ok && tile < p.tiles; tile += num_pairs, ++tile_iter) {
         const TileCoord t = decode_tile(p, tile);
         const int m0 = t.m_blk * kPairBlockM + static_cast<int>(rank) * kBlockM;
@@ -123,6 +161,7 @@ nova_gemm_sm100_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
         long long waited = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          if (prefetch) { pf_issue(); pf_advance(); }
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           const long long w0 = (kTraceEnabled && p.trace) ? clock64() : 0;

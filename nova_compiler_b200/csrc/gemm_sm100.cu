@@ -23,6 +23,7 @@ struct Plan {
   bool pair = false;  // CTA-pair kernel (cta_group::2, 256 x 256 tiles)
   bool short_k = false;  // contraction so short that the epilogue dominates: 8 epilogue warps, 3 stages
   int64_t repitch_a_ld = 0, repitch_b_ld = 0;  // > 0: the operand is first copied to scratch with this pitch
+  int prefetch_dist = 0;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads
 };
 
 constexpr int64_t kMaxExtent = (1ll << 31) - 1;
@@ -99,8 +100,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     // of the operand, then the full-rate TMA kernels).  Measured from 500^3 (11.9 us against 29.2) to
     // 4095 x 11007 x 4097 (0.32 ms against 1.70) that beats reading it in place with the loader warps, which
     // remain for callers that want no scratch traffic: NOVA_B200_REPITCH=0.
-    bool repitch = pi.loader_a || pi.loader_b;
-    if (const char* e = std::getenv("NOVA_B200_REPITCH")) repitch = repitch && std::atoi(e) != 0;
+    const bool repitch = (pi.loader_a || pi.loader_b) && options().repitch.load() != 0;
     if (repitch) {
       const int per_chunk = 16 / es;
       const int64_t a_rows = a->trans_a ? a->K : a->M, a_cols = a->trans_a ? a->M : a->K;
@@ -156,15 +156,13 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   else if (a->N <= 128) block_n = 128;
   else if (both_tma && plan->terms == 1) block_n = cost128 < cost256 ? 128 : 256;
   else if (tiles256 < sms) block_n = 128;  // loader warps: keep every SM's loaders busy
-  if (const char* e = std::getenv("NOVA_B200_BLOCK_N")) {
-    const int v = std::atoi(e);
+  {
+    const int v = static_cast<int>(options().block_n.load());
     if ((v == 128 || v == 256) && plan->terms != 3) { block_n = v; pair = false; }
     if (v == 64 && (plan->terms == 3 || both_tma)) { block_n = v; pair = false; }
-  }
-  if (const char* e = std::getenv("NOVA_B200_PAIR")) {
-    const int v = std::atoi(e);
-    if (v == 0) pair = false;
-    else pair = plan->terms == 1 && both_tma && a->K >= 256;
+    const int pv = static_cast<int>(options().pair.load());
+    if (pv == 0) pair = false;
+    else if (pv > 0) pair = plan->terms == 1 && both_tma && a->K >= 256;
   }
   pi.block_n = block_n;
   const int64_t tiles = block_n == 256 ? tiles256 : (block_n == 128 ? tiles128 : tiles64);
@@ -176,9 +174,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   // K <= 256 with full-width tiles: the mainloop of a tile is at most four k-blocks, the time goes into
   // draining 128 x 256 accumulators, so trade one ring stage for a second set of epilogue warps.
   plan->short_k = !pair && plan->terms == 1 && both_tma && block_n == 256 && a->K <= 256 && pi.store_c == 0;
-  if (const char* e = std::getenv("NOVA_B200_SHORT_K")) {
-    if (std::atoi(e) == 0) plan->short_k = false;
-  }
+  if (options().short_k.load() == 0) plan->short_k = false;
   if (plan->short_k) pi.stages = 3;
   if (pair) {
     pi.block_m = kPairBlockM;
@@ -186,6 +182,8 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     pi.stages = kPairStages;
     pi.tiles = pair_tiles;
     pi.grid = static_cast<int32_t>(2 * (pair_tiles < sms / 2 ? pair_tiles : sms / 2));
+    const int64_t pf = options().prefetch.load();
+    plan->prefetch_dist = pf >= 0 ? static_cast<int>(std::min<int64_t>(pf, 64)) : 0;
   }
   return NOVA_B200_OK;
 }
@@ -206,8 +204,27 @@ int32_t encode_operand_map(DeviceContext* ctx, CUtensorMap* out, const void* bas
   return NOVA_B200_OK;
 }
 
+// Launch with programmatic stream serialization when asked: the kernels call griddepcontrol.wait before their
+// first global access, so letting their prologue (barrier setup, tensor-memory allocation) overlap the tail of
+// the previous kernel in the stream is always safe.
+template <typename Kernel, typename... Args>
+int32_t launch_ex(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  NOVA_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, args...));
+  return NOVA_B200_OK;
+}
+
 template <int kBlockN, int kElemBytes, int kTerms, bool kAMn, bool kBMn, int kStages, bool kLoader, int kEpiWarps>
-int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int grid, cudaStream_t st) {
+int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int grid, cudaStream_t st, bool pdl) {
   using L = GemmSmemLayout<kBlockN, (kTerms == 3 ? 2 : 1), kStages, kEpiWarps>;
   auto kernel = nova_gemm_sm100_kernel<kBlockN, kElemBytes, kTerms, kAMn, kBMn, kStages, kLoader, kEpiWarps>;
   static thread_local int configured_device = -1;
@@ -218,33 +235,31 @@ int32_t launch_instance(const CUtensorMap* maps, const GemmKernelParams& p, int 
     configured_device = dev;
   }
   constexpr int kThreads = kLoader ? kThreadsWithLoader : 32 * (kFirstEpilogueWarp + kEpiWarps);
-  kernel<<<grid, kThreads, L::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
-  NOVA_CUDA_OK(cudaGetLastError());
-  return NOVA_B200_OK;
+  return launch_ex(kernel, grid, kThreads, L::kDynamicBytes, st, pdl, maps[0], maps[1], maps[2], maps[3], maps[4], p);
 }
 
 template <int kBlockN, int kElemBytes, int kTerms, int kStages, bool kLoader, int kEpiWarps>
 int32_t launch_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int grid,
-                      cudaStream_t st) {
+                      cudaStream_t st, bool pdl) {
   if (!a_mn && b_mn)
-    return launch_instance<kBlockN, kElemBytes, kTerms, false, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+    return launch_instance<kBlockN, kElemBytes, kTerms, false, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st, pdl);
   if (!a_mn && !b_mn)
-    return launch_instance<kBlockN, kElemBytes, kTerms, false, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+    return launch_instance<kBlockN, kElemBytes, kTerms, false, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st, pdl);
   if (a_mn && b_mn)
-    return launch_instance<kBlockN, kElemBytes, kTerms, true, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
-  return launch_instance<kBlockN, kElemBytes, kTerms, true, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st);
+    return launch_instance<kBlockN, kElemBytes, kTerms, true, true, kStages, kLoader, kEpiWarps>(maps, p, grid, st, pdl);
+  return launch_instance<kBlockN, kElemBytes, kTerms, true, false, kStages, kLoader, kEpiWarps>(maps, p, grid, st, pdl);
 }
 
 // the loader-warp build only exists for the single-term kernels (the 3xTF32 split re-lays its operands out)
 template <int kBlockN, int kElemBytes, int kStages>
 int32_t launch_single_term(bool loader, bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p,
-                           int grid, cudaStream_t st) {
-  if (loader) return launch_majors<kBlockN, kElemBytes, 1, kStages, true, 4>(a_mn, b_mn, maps, p, grid, st);
-  return launch_majors<kBlockN, kElemBytes, 1, kStages, false, 4>(a_mn, b_mn, maps, p, grid, st);
+                           int grid, cudaStream_t st, bool pdl) {
+  if (loader) return launch_majors<kBlockN, kElemBytes, 1, kStages, true, 4>(a_mn, b_mn, maps, p, grid, st, pdl);
+  return launch_majors<kBlockN, kElemBytes, 1, kStages, false, 4>(a_mn, b_mn, maps, p, grid, st, pdl);
 }
 
 template <int kElemBytes, bool kAMn, bool kBMn, int kEpiWarps>
-int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p, int sm_count, cudaStream_t st) {
+int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p, int sm_count, cudaStream_t st, bool pdl) {
   constexpr int kThreads = 32 * (kFirstEpilogueWarp + kEpiWarps);
   using PairSmem = PairSmemLayout<kEpiWarps>;
   auto kernel = nova_gemm_sm100_pair_kernel<kElemBytes, kAMn, kBMn, kEpiWarps>;
@@ -270,65 +285,57 @@ int32_t launch_pair_instance(const CUtensorMap* maps, const GemmKernelParams& p,
       n = sm_count / 2;
     }
     max_pairs = n < sm_count / 2 ? n : sm_count / 2;
-    if (std::getenv("NOVA_B200_DEBUG")) fprintf(stderr, "[nova_b200] pair kernel: %d resident clusters reported, using %d\n", n, max_pairs);
+    if (options().debug.load()) fprintf(stderr, "[nova_b200] pair kernel: %d resident clusters reported, using %d\n", n, max_pairs);
     configured_device = dev;
   }
   const int pairs = p.tiles < max_pairs ? p.tiles : max_pairs;
-  kernel<<<2 * pairs, kThreads, PairSmem::kDynamicBytes, st>>>(maps[0], maps[1], maps[2], p);
-  NOVA_CUDA_OK(cudaGetLastError());
-  return NOVA_B200_OK;
+  return launch_ex(kernel, 2 * pairs, kThreads, PairSmem::kDynamicBytes, st, pdl, maps[0], maps[1], maps[2], p);
 }
 
 template <int kElemBytes, int kEpiWarps>
 int32_t launch_pair_majors(bool a_mn, bool b_mn, const CUtensorMap* maps, const GemmKernelParams& p, int sm_count,
-                           cudaStream_t st) {
-  if (!a_mn && b_mn) return launch_pair_instance<kElemBytes, false, true, kEpiWarps>(maps, p, sm_count, st);
-  if (!a_mn && !b_mn) return launch_pair_instance<kElemBytes, false, false, kEpiWarps>(maps, p, sm_count, st);
-  if (a_mn && b_mn) return launch_pair_instance<kElemBytes, true, true, kEpiWarps>(maps, p, sm_count, st);
-  return launch_pair_instance<kElemBytes, true, false, kEpiWarps>(maps, p, sm_count, st);
+                           cudaStream_t st, bool pdl) {
+  if (!a_mn && b_mn) return launch_pair_instance<kElemBytes, false, true, kEpiWarps>(maps, p, sm_count, st, pdl);
+  if (!a_mn && !b_mn) return launch_pair_instance<kElemBytes, false, false, kEpiWarps>(maps, p, sm_count, st, pdl);
+  if (a_mn && b_mn) return launch_pair_instance<kElemBytes, true, true, kEpiWarps>(maps, p, sm_count, st, pdl);
+  return launch_pair_instance<kElemBytes, true, false, kEpiWarps>(maps, p, sm_count, st, pdl);
 }
 
-uint32_t env_u32(const char* name, uint32_t dflt) {
-  const char* e = std::getenv(name);
-  return e ? static_cast<uint32_t>(std::strtoul(e, nullptr, 0)) : dflt;
-}
-
-}  // namespace
-
-int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
+// Everything a launch needs, derived from the argument struct.  Building it costs a plan, up to five
+// cuTensorMapEncodeTiled calls and the descriptor arithmetic (several microseconds, more than the kernel of a small
+// contraction), so the last few are kept per host thread and reused while the arguments (pointers included), the
+// device, the tuning options and the scratch buffer are the same.
+struct Prepared {
+  nova_b200_gemm_args key{};
+  const void* key_status = nullptr;  // identifies the device context
+  const void* key_scratch = nullptr;
+  uint32_t key_epoch = 0;
+  bool valid = false;
   Plan plan;
-  int sm = 148;
-  int32_t st = validate_and_plan(args, &plan, sm);
-  if (st != NOVA_B200_OK) return st;
-  if (out) *out = plan.info;
-  return NOVA_B200_OK;
-}
-
-int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream) {
-  Plan plan;
-  int32_t st = validate_and_plan(a, &plan, ctx->sm_count);
-  if (st != NOVA_B200_OK) return st;
-  if (plan.empty) return NOVA_B200_OK;
-  const nova_b200_gemm_plan_info& pi = plan.info;
-
   GemmKernelParams p{};
+  CUtensorMap maps[5];
+  int pre_kernel = 0;  // 0 none, 1 hi/lo split, 2 re-pitch
+  SplitOperand split_a{}, split_b{};
+  RepitchOperand rep_a{}, rep_b{};
+  int pre_blocks = 0;
+};
+constexpr int kPlanCacheEntries = 32;
+
+int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch, Prepared* out) {
+  Plan& plan = out->plan;
+  const nova_b200_gemm_plan_info& pi = plan.info;
+  GemmKernelParams& p = out->p;
+  p = GemmKernelParams{};
   p.M = static_cast<int32_t>(a->M); p.N = static_cast<int32_t>(a->N); p.K = static_cast<int32_t>(a->K);
   p.batch = static_cast<int32_t>(a->batch);
   p.C = a->C; p.bias = a->bias; p.residual = a->residual;
   p.ldc = a->ldc; p.stride_c = a->batch_stride_c; p.ldr = a->ldr; p.stride_r = a->batch_stride_r;
   p.act = a->act; p.init = a->init; p.out_dtype = a->dtype_c;
   p.status = ctx->status_word;
+  out->pre_kernel = 0;
+  if (plan.k_zero) return NOVA_B200_OK;
 
-  if (plan.k_zero) {
-    const int64_t n = a->batch * a->M * a->N;
-    const int grid = static_cast<int>(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
-    if (a->dtype_c == NOVA_B200_BF16) nova_gemm_k0_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
-    else if (a->dtype_c == NOVA_B200_F16) nova_gemm_k0_kernel<__half><<<grid, 256, 0, stream>>>(p);
-    else nova_gemm_k0_kernel<float><<<grid, 256, 0, stream>>>(p);
-    NOVA_CUDA_OK(cudaGetLastError());
-    return NOVA_B200_OK;
-  }
-
+  int32_t st = NOVA_B200_OK;
   const int es = plan.elem_bytes;
   const int block_n = pi.block_n;
   const int block_k = pi.block_k;
@@ -337,7 +344,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   p.n_blocks = static_cast<int32_t>((a->N + block_n - 1) / block_n);
   const int stage_k = plan.pair ? block_k * kPairSubK : block_k;  // K elements consumed per ring stage
   p.k_blocks = static_cast<int32_t>((a->K + stage_k - 1) / stage_k);
-  p.group_m = static_cast<int32_t>(env_u32("NOVA_B200_GROUP_M", 16));
+  p.group_m = static_cast<int32_t>(options().group_m.load());
   if (p.group_m < 1) p.group_m = 1;
   p.tiles = static_cast<int32_t>(pi.tiles);
   p.a_batch_mul = a->batch_stride_a == 0 ? 0 : 1;
@@ -346,6 +353,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   p.A = a->A; p.B = a->B; p.lda = a->lda; p.ldb = a->ldb;
   p.stride_a = a->batch_stride_a; p.stride_b = a->batch_stride_b;
   p.vec_store = pi.store_c == 0 ? 1 : 0;
+  p.prefetch_dist = plan.prefetch_dist;
 
   // tcgen05 instruction descriptor: D=f32 (bits 4-5 = 1), A/B format (bits 7-9 / 10-12: f16=0, bf16=1, tf32=2),
   // A/B major (bits 15/16: 1 = MN-major), N>>3 in bits 17-22, M>>4 in bits 24-28.
@@ -372,7 +380,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   p.a_kstep = plan.a_mn ? umma_k * kSwizzleBytes : 32u;
   p.b_kstep = plan.b_mn ? umma_k * kSwizzleBytes : 32u;
 
-  // operand views (possibly redirected to the hi/lo scratch for 3xTF32)
+  // operand views (possibly redirected to scratch: the hi/lo split of f32 operands, re-pitched copies)
   const int64_t a_rows = a->trans_a ? a->K : a->M, a_cols = a->trans_a ? a->M : a->K;
   const int64_t b_rows = a->trans_b ? a->N : a->K, b_cols = a->trans_b ? a->K : a->N;
   const int64_t a_nb = a->batch_stride_a == 0 ? 1 : a->batch, b_nb = a->batch_stride_b == 0 ? 1 : a->batch;
@@ -380,53 +388,45 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   const void* b_src[2] = {a->B, nullptr};
   int64_t a_ld = a->lda, b_ld = a->ldb, a_bs = a->batch_stride_a, b_bs = a->batch_stride_b;
   if (plan.terms == 3) {
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    st = ensure_scratch(ctx, static_cast<size_t>(pi.scratch_bytes));
-    if (st != NOVA_B200_OK) return st;
     const int64_t a_ldo = (a_cols + 3) & ~3ll, b_ldo = (b_cols + 3) & ~3ll;
-    float* s = static_cast<float*>(ctx->scratch);
+    float* s = static_cast<float*>(scratch);
     float* a_hi = s; float* a_lo = a_hi + a_nb * a_rows * a_ldo;
     float* b_hi = a_lo + a_nb * a_rows * a_ldo; float* b_lo = b_hi + b_nb * b_rows * b_ldo;
-    SplitOperand oa{static_cast<const float*>(a->A), a_hi, a_lo, a_nb * a_rows, a->lda, a->batch_stride_a,
-                    static_cast<int32_t>(a_rows), static_cast<int32_t>(a_cols), static_cast<int32_t>(a_ldo)};
-    SplitOperand ob{static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows, a->ldb, a->batch_stride_b,
-                    static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols), static_cast<int32_t>(b_ldo)};
+    out->split_a = SplitOperand{static_cast<const float*>(a->A), a_hi, a_lo, a_nb * a_rows, a->lda, a->batch_stride_a,
+                                static_cast<int32_t>(a_rows), static_cast<int32_t>(a_cols), static_cast<int32_t>(a_ldo)};
+    out->split_b = SplitOperand{static_cast<const float*>(a->B), b_hi, b_lo, b_nb * b_rows, a->ldb, a->batch_stride_b,
+                                static_cast<int32_t>(b_rows), static_cast<int32_t>(b_cols), static_cast<int32_t>(b_ldo)};
     const int64_t biggest = std::max(a_nb * a_rows * a_ldo, b_nb * b_rows * b_ldo);
     const int64_t want = (biggest / 4 + 255) / 256;  // four elements per thread
-    const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8)));
-    nova_split_tf32_kernel<<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
-    NOVA_CUDA_OK(cudaGetLastError());
+    out->pre_blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8)));
+    out->pre_kernel = 1;
     a_src[0] = a_hi; a_src[1] = a_lo; b_src[0] = b_hi; b_src[1] = b_lo;
     a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;
   } else if (plan.repitch_a_ld > 0 || plan.repitch_b_ld > 0) {
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    st = ensure_scratch(ctx, static_cast<size_t>(pi.scratch_bytes));
-    if (st != NOVA_B200_OK) return st;
-    uint8_t* s = static_cast<uint8_t*>(ctx->scratch);
-    RepitchOperand oa{}, ob{};
+    uint8_t* s = static_cast<uint8_t*>(scratch);
+    out->rep_a = RepitchOperand{};
+    out->rep_b = RepitchOperand{};
     int64_t biggest = 0;
     if (plan.repitch_a_ld > 0) {
-      oa = RepitchOperand{a->A, s, a_nb * a_rows, a->lda, a->batch_stride_a, static_cast<int32_t>(a_rows),
-                          static_cast<int32_t>(a_cols), static_cast<int32_t>(plan.repitch_a_ld)};
+      out->rep_a = RepitchOperand{a->A, s, a_nb * a_rows, a->lda, a->batch_stride_a, static_cast<int32_t>(a_rows),
+                                  static_cast<int32_t>(a_cols), static_cast<int32_t>(plan.repitch_a_ld)};
       a_src[0] = s; a_ld = plan.repitch_a_ld; a_bs = a_rows * a_ld;
       s += (a_nb * a_rows * a_ld * es + 255) / 256 * 256;
       biggest = std::max(biggest, a_nb * a_rows * a_ld * es / 16);
     }
     if (plan.repitch_b_ld > 0) {
-      ob = RepitchOperand{a->B, s, b_nb * b_rows, a->ldb, a->batch_stride_b, static_cast<int32_t>(b_rows),
-                          static_cast<int32_t>(b_cols), static_cast<int32_t>(plan.repitch_b_ld)};
+      out->rep_b = RepitchOperand{a->B, s, b_nb * b_rows, a->ldb, a->batch_stride_b, static_cast<int32_t>(b_rows),
+                                  static_cast<int32_t>(b_cols), static_cast<int32_t>(plan.repitch_b_ld)};
       b_src[0] = s; b_ld = plan.repitch_b_ld; b_bs = b_rows * b_ld;
       biggest = std::max(biggest, b_nb * b_rows * b_ld * es / 16);
     }
     const int64_t want = (biggest + 255) / 256;
-    const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 16)));
-    if (es == 2) nova_repitch_kernel<uint16_t><<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
-    else nova_repitch_kernel<uint32_t><<<dim3(blocks, 2), 256, 0, stream>>>(oa, ob);
-    NOVA_CUDA_OK(cudaGetLastError());
+    out->pre_blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 16)));
+    out->pre_kernel = 2;
   }
 
-  CUtensorMap maps[5];  // A hi, A lo, B hi, B lo, C
-  std::memset(maps, 0, sizeof(maps));
+  CUtensorMap* maps = out->maps;  // A hi, A lo, B hi, B lo, C
+  std::memset(maps, 0, sizeof(out->maps));
   const CUtensorMapDataType tdt = a->dtype_ab == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                 : a->dtype_ab == NOVA_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -449,7 +449,6 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
       if (st != NOVA_B200_OK) return st;
     }
   }
-
   if (p.vec_store) {
     // output boxes: 32 rows x 128 bytes, clipped by the tensor map at M and N
     const int osz = plan.out_bytes;
@@ -460,23 +459,132 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
                             static_cast<uint32_t>(kSwizzleBytes / osz), 32u, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != NOVA_B200_OK) return st;
   }
+  return NOVA_B200_OK;
+}
+
+}  // namespace
+
+// One operand copied to a 16-byte-aligned pitch (the copy nova_b200_operand_prepare keeps for a constant weight).
+int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_t rows, int64_t cols, int64_t ld_in,
+                       int64_t stride_in, int64_t ld_out, int sm_count, cudaStream_t stream) {
+  RepitchOperand o{src, dst, batch * rows, ld_in, stride_in, static_cast<int32_t>(rows), static_cast<int32_t>(cols),
+                   static_cast<int32_t>(ld_out)};
+  RepitchOperand none{};
+  const int64_t want = (batch * rows * ld_out * es / 16 + 255) / 256;
+  const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(sm_count) * 16)));
+  if (es == 2) nova_repitch_kernel<uint16_t><<<dim3(blocks, 1), 256, 0, stream>>>(o, none);
+  else nova_repitch_kernel<uint32_t><<<dim3(blocks, 1), 256, 0, stream>>>(o, none);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
+  Plan plan;
+  int sm = 148;  // the plan a B200 will execute; needs no device
+  int32_t st = validate_and_plan(args, &plan, sm);
+  if (st != NOVA_B200_OK) return st;
+  if (out) *out = plan.info;
+  return NOVA_B200_OK;
+}
+
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream) {
+  static thread_local Prepared cache[kPlanCacheEntries];
+  static thread_local int next_slot = 0;
+  if (!a || a->struct_size != sizeof(nova_b200_gemm_args)) {
+    Plan tmp;
+    return validate_and_plan(a, &tmp, ctx->sm_count);  // reports the argument error
+  }
+  Options& opt = options();
+  const uint32_t epoch = opt.epoch.load();
+  const bool use_cache = opt.plan_cache.load() != 0;
+  Prepared* hit = nullptr;
+  if (use_cache) {
+    for (int i = 0; i < kPlanCacheEntries; ++i) {
+      Prepared& c = cache[i];
+      if (c.valid && c.key_status == ctx->status_word && c.key_epoch == epoch &&
+          std::memcmp(&c.key, a, sizeof(nova_b200_gemm_args)) == 0) {
+        hit = &c;
+        break;
+      }
+    }
+  }
+  Prepared local;
+  Prepared* pr = hit;
+  int32_t st = NOVA_B200_OK;
+  if (!pr) {
+    pr = use_cache ? &cache[next_slot] : &local;
+    pr->valid = false;
+    pr->plan = Plan{};
+    st = validate_and_plan(a, &pr->plan, ctx->sm_count);
+    if (st != NOVA_B200_OK) return st;
+  }
+  const Plan& plan = pr->plan;
+  if (plan.empty) return NOVA_B200_OK;
+  const nova_b200_gemm_plan_info& pi = plan.info;
+  if (!hit) {  // (a hit has the same pointers on the same device: already checked)
+    for (const void* ptr : {a->A, a->B, static_cast<const void*>(a->C)}) {
+      st = check_pointer_device(ctx, ptr, "gemm: an operand");
+      if (st != NOVA_B200_OK) return st;
+    }
+  }
+  void* scratch = nullptr;
+  if (pi.scratch_bytes > 0 && !plan.k_zero) {
+    st = acquire_scratch(ctx, stream, static_cast<size_t>(pi.scratch_bytes), &scratch);
+    if (st != NOVA_B200_OK) return st;
+  }
+  if (!hit || pr->key_scratch != scratch) {
+    pr->valid = false;
+    st = prepare(ctx, a, scratch, pr);
+    if (st != NOVA_B200_OK) return st;
+    pr->key = *a;
+    pr->key_status = ctx->status_word;
+    pr->key_scratch = scratch;
+    pr->key_epoch = epoch;
+    pr->valid = true;
+    if (!hit && use_cache) next_slot = (next_slot + 1) % kPlanCacheEntries;
+  }
+  const GemmKernelParams& p = pr->p;
+  const CUtensorMap* maps = pr->maps;
+  const bool pdl = opt.pdl.load() != 0;
+
+  if (plan.k_zero) {
+    const int64_t n = a->batch * a->M * a->N;
+    const int grid = static_cast<int>(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
+    if (a->dtype_c == NOVA_B200_BF16) nova_gemm_k0_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+    else if (a->dtype_c == NOVA_B200_F16) nova_gemm_k0_kernel<__half><<<grid, 256, 0, stream>>>(p);
+    else nova_gemm_k0_kernel<float><<<grid, 256, 0, stream>>>(p);
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
+  const int es = plan.elem_bytes;
+  if (pr->pre_kernel == 1) {
+    nova_split_tf32_kernel<<<dim3(pr->pre_blocks, 2), 256, 0, stream>>>(pr->split_a, pr->split_b);
+    NOVA_CUDA_OK(cudaGetLastError());
+  } else if (pr->pre_kernel == 2) {
+    if (es == 2) nova_repitch_kernel<uint16_t><<<dim3(pr->pre_blocks, 2), 256, 0, stream>>>(pr->rep_a, pr->rep_b);
+    else nova_repitch_kernel<uint32_t><<<dim3(pr->pre_blocks, 2), 256, 0, stream>>>(pr->rep_a, pr->rep_b);
+    NOVA_CUDA_OK(cudaGetLastError());
+  }
+
+  const int block_n = pi.block_n;
   if (plan.pair) {
     const CUtensorMap pm[3] = {maps[0], maps[2], maps[4]};
     // NOVA_B200_TRACE=<file> (diagnostic builds only): the launch is synchronous and every CTA's role timeline
     // (clock64 samples, see TraceSlot) is written to the file as int64[grid][kTraceTiles][kTraceSlots].
     const char* trace_path = kTraceEnabled ? std::getenv("NOVA_B200_TRACE") : nullptr;
     const size_t trace_bytes = sizeof(long long) * pi.grid * kTraceTiles * kTraceSlots;
+    GemmKernelParams pt = p;
     if (trace_path != nullptr) {
-      NOVA_CUDA_OK(cudaMalloc(&p.trace, trace_bytes));
-      NOVA_CUDA_OK(cudaMemsetAsync(p.trace, 0, trace_bytes, stream));
+      NOVA_CUDA_OK(cudaMalloc(&pt.trace, trace_bytes));
+      NOVA_CUDA_OK(cudaMemsetAsync(pt.trace, 0, trace_bytes, stream));
     }
-    st = es == 2 ? launch_pair_majors<2, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream)
-                 : launch_pair_majors<4, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, p, ctx->sm_count, stream);
+    st = es == 2 ? launch_pair_majors<2, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, pt, ctx->sm_count, stream, pdl)
+                 : launch_pair_majors<4, kPairEpilogueWarps>(plan.a_mn, plan.b_mn, pm, pt, ctx->sm_count, stream, pdl);
     if (trace_path != nullptr) {
       std::vector<long long> host(trace_bytes / sizeof(long long));
       cudaStreamSynchronize(stream);
-      cudaMemcpy(host.data(), p.trace, trace_bytes, cudaMemcpyDeviceToHost);
-      cudaFree(p.trace);
+      cudaMemcpy(host.data(), pt.trace, trace_bytes, cudaMemcpyDeviceToHost);
+      cudaFree(pt.trace);
       if (FILE* f = std::fopen(trace_path, "wb")) {
         std::fwrite(host.data(), 1, trace_bytes, f);
         std::fclose(f);
@@ -487,23 +595,23 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   const bool loader = pi.loader_a == 1 || pi.loader_b == 1;
   const int grid = pi.grid;
   if (plan.terms == 3) {
-    if (block_n == 64) return launch_majors<64, 4, 3, 4, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
-    return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    if (block_n == 64) return launch_majors<64, 4, 3, 4, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
   }
   if (block_n == 64) {  // TMA-only build: narrow tiles are chosen only for operands tensor maps can describe
-    if (es == 2) return launch_majors<64, 2, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
-    return launch_majors<64, 4, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    if (es == 2) return launch_majors<64, 2, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    return launch_majors<64, 4, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
   }
   if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps
-    if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
-    return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
   }
   if (es == 2) {
-    if (block_n == 256) return launch_single_term<256, 2, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
-    return launch_single_term<128, 2, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
+    if (block_n == 256) return launch_single_term<256, 2, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    return launch_single_term<128, 2, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
   }
-  if (block_n == 256) return launch_single_term<256, 4, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
-  return launch_single_term<128, 4, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream);
+  if (block_n == 256) return launch_single_term<256, 4, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+  return launch_single_term<128, 4, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
 }
 
 }  // namespace nova

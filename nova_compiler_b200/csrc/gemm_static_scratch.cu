@@ -71,14 +71,36 @@ int32_t setup_device(int dev, StaticDevice** out) {
 
 }  // namespace
 
+namespace nova {
+// For nova_b200_device_status: reads (and clears) the static array's status word on `dev` if this entry point has
+// been used there, so a caller that only enqueues (wait_code_out == NULL) can still learn that a bounded wait gave
+// up.  The caller has synchronised the device.  Allocates nothing.
+int32_t static_scratch_status(int dev, uint32_t* code_out) {
+  *code_out = 0;
+  if (dev < 0 || dev >= kMaxDevices) return NOVA_B200_OK;
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mu);
+    if (!g_devices[dev].ready) return NOVA_B200_OK;
+    base = g_devices[dev].base;
+  }
+  uint32_t code = 0;
+  NOVA_CUDA_OK(cudaMemcpy(&code, base, 4, cudaMemcpyDeviceToHost));
+  if (code != 0) NOVA_CUDA_OK(cudaMemset(base, 0, 4));
+  *code_out = code;
+  return NOVA_B200_OK;
+}
+}  // namespace nova
+
 extern "C" int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream, uint32_t* wait_code_out) {
   using namespace nova;
   nova_b200_gemm_plan_info info;
   int32_t st = gemm_plan_only(args, &info);
   if (st != NOVA_B200_OK) return st;
   if (args->dtype_ab != NOVA_B200_F32 || args->f32_mode != NOVA_B200_TF32X3)
-    return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm_f32_static: only f32 operands in NOVA_B200_TF32X3 mode use scratch memory; "
-                                           "other contractions allocate nothing through nova_b200_gemm once the device is initialised");
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm_f32_static: only the f32 contraction in NOVA_B200_TF32X3 mode is offered here; 16-bit and "
+                                           "TF32X1 contractions with 16-byte-aligned operands use no scratch in nova_b200_gemm "
+                                           "(unaligned ones are re-pitched into allocated scratch there)");
   if (static_cast<size_t>(info.scratch_bytes) > kScratchBytes)
     return fail(NOVA_B200_ERR_TOO_LARGE,
                 "gemm_f32_static: the hi/lo split of A and B needs " + std::to_string(info.scratch_bytes) +
@@ -96,15 +118,18 @@ extern "C" int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, vo
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left.  The split kernels overwrite every scratch byte the
-  // contraction reads (padding columns included); only the status word has to start from zero.
-  NOVA_CUDA_OK(cudaMemsetAsync(d->base, 0, 4, s));
+  // contraction reads (padding columns included); only the status word has to start from zero, and it does unless
+  // an earlier call's wait gave up and nobody has read the code yet: a call that reports the code itself
+  // (wait_code_out) clears the word first, an enqueue-only call leaves it for nova_b200_device_status.
+  if (wait_code_out) NOVA_CUDA_OK(cudaMemsetAsync(d->base, 0, 4, s));
   DeviceContext ctx;  // a view of the static array in the shape the launcher expects; owns nothing
   ctx.device = dev;
   ctx.sm_count = d->sm_count;
+  ctx.device_count = count;
   ctx.cc_major = 10;
   ctx.status_word = reinterpret_cast<uint32_t*>(d->base);
-  ctx.scratch = d->base + kStatusBytes;
-  ctx.scratch_bytes = kScratchBytes;  // >= the request, so the launcher's grow-on-demand never triggers
+  ctx.fixed_scratch = d->base + kStatusBytes;  // the launcher takes its scratch from here and never allocates
+  ctx.fixed_scratch_bytes = kScratchBytes;
   ctx.encode_tiled = d->encode_tiled;
   st = gemm_launch(&ctx, args, s);
   if (st != NOVA_B200_OK) return st;

@@ -106,6 +106,22 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
+// L2 prefetch of a box (no shared-memory destination, no barrier): the data is on its way to L2 when the
+// load proper is issued some ring stages later.
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// launch_dependents: the next kernel in the stream (if it was launched with programmatic stream serialization) may
+// start its own prologue once every CTA of this grid has passed this point.  wait: blocks until the grids this one
+// depends on have completed and their memory is visible; a no-op for a normally serialised launch.  Every thread of
+// the contraction kernels executes wait before its first global-memory access.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- tensor memory
 // Allocates `cols` (power of two >= 32) TMEM columns; the base address lands in *dst_smem.
 // Must be executed by one full warp.

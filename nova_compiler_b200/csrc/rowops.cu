@@ -855,6 +855,8 @@ int32_t nova_b200_layer_norm(const void* x, const void* gamma, const void* beta,
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_layer_norm: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, y, "nova_b200_layer_norm: the output")) != NOVA_B200_OK) return st;
   return dispatch_row_kernel<0>(x, gamma, beta, y, mean_sum, rstd, rows, D, dtype, ctx->sm_count,
                                 static_cast<cudaStream_t>(stream));
 }
@@ -871,6 +873,8 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_layer_norm_backward: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, dx, "nova_b200_layer_norm_backward: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype);
   const uintptr_t align = reinterpret_cast<uintptr_t>(grad_y) | reinterpret_cast<uintptr_t>(x) |
@@ -893,12 +897,10 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   int resident = !wide ? (max_v >= 4 ? 1 : 2) : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
   const int64_t row_blocks = wide ? (rows + rows_per - 1) / rows_per : rows;
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(row_blocks, static_cast<int64_t>(ctx->sm_count) * resident)));
-  {
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    st = ensure_scratch(ctx, static_cast<size_t>(grid) * 2 * D * sizeof(float));
-    if (st != NOVA_B200_OK) return st;
-  }
-  float* partial = static_cast<float*>(ctx->scratch);
+  void* scratch = nullptr;
+  st = acquire_scratch(ctx, s, static_cast<size_t>(grid) * 2 * D * sizeof(float), &scratch);
+  if (st != NOVA_B200_OK) return st;
+  float* partial = static_cast<float*>(scratch);
 #define NOVA_LNB(T, V, MV)                                                                                             \
   ln_backward_kernel<T, V, MV, (MV) == 1 ? 1024 : kRowThreads><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x),      \
                                                         static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
@@ -942,6 +944,8 @@ int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_softmax: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, y, "nova_b200_softmax: the output")) != NOVA_B200_OK) return st;
   return dispatch_row_kernel<1>(x, nullptr, nullptr, y, nullptr, nullptr, rows, D, dtype, ctx->sm_count,
                                 static_cast<cudaStream_t>(stream));
 }
@@ -959,13 +963,13 @@ int32_t nova_b200_sce(const void* logits, const void* targets, void* softmax_out
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, logits, "nova_b200_sce: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, softmax_out, "nova_b200_sce: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  {
-    std::lock_guard<std::mutex> lock(ctx->mu);
-    st = ensure_scratch(ctx, static_cast<size_t>(std::max<int64_t>(rows, 1)) * 2 * sizeof(float));
-    if (st != NOVA_B200_OK) return st;
-  }
-  float* stats = static_cast<float*>(ctx->scratch);
+  void* scratch = nullptr;
+  st = acquire_scratch(ctx, s, static_cast<size_t>(std::max<int64_t>(rows, 1)) * 2 * sizeof(float), &scratch);
+  if (st != NOVA_B200_OK) return st;
+  float* stats = static_cast<float*>(scratch);
   if (rows > 0 && C > 0) {
     st = dispatch_row_kernel<1>(logits, nullptr, nullptr, softmax_out, nullptr, nullptr, rows, C, dtype, ctx->sm_count, s, stats);
     if (st != NOVA_B200_OK) return st;
@@ -992,6 +996,8 @@ int32_t nova_b200_sce_backward(const void* softmax, const void* targets, void* g
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, softmax, "nova_b200_sce_backward: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, grad, "nova_b200_sce_backward: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype), vec = 16 / es;
   const bool vec_ok = C % vec == 0 && reinterpret_cast<uintptr_t>(softmax) % 16 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0;
@@ -1019,6 +1025,8 @@ int32_t nova_b200_scatter_add(void* inout, const void* idx, const void* src, int
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, src, "nova_b200_scatter_add: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, inout, "nova_b200_scatter_add: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = 256;
   const int grid = grid_for(pre * n_idx * post, threads, ctx->sm_count);
@@ -1046,6 +1054,8 @@ int32_t nova_b200_gather(const void* in, const void* idx, void* out, int64_t pre
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, in, "nova_b200_gather: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, out, "nova_b200_gather: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t row_bytes = post * elem_bytes;
   const uintptr_t align = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
@@ -1079,16 +1089,18 @@ int32_t nova_b200_column_sum(const void* x, void* out, int64_t rows, int64_t col
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_column_sum: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, out, "nova_b200_column_sum: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t col_tiles = (cols + 63) / 64;
   // enough row splits to fill the machine, at most one per 8 rows
   int64_t splits = (static_cast<int64_t>(ctx->sm_count) * 8 + col_tiles - 1) / col_tiles;
   splits = std::max<int64_t>(1, std::min<int64_t>(splits, (rows + 7) / 8));
   splits = std::min<int64_t>(splits, 65535);
-  std::lock_guard<std::mutex> lock(ctx->mu);  // the partial sums live in the per-device scratch
-  st = ensure_scratch(ctx, static_cast<size_t>(splits * cols) * sizeof(float));
+  void* scratch = nullptr;  // the partial sums live in this stream's scratch
+  st = acquire_scratch(ctx, s, static_cast<size_t>(splits * cols) * sizeof(float), &scratch);
   if (st != NOVA_B200_OK) return st;
-  float* partial = static_cast<float*>(ctx->scratch);
+  float* partial = static_cast<float*>(scratch);
   const dim3 grid(static_cast<unsigned>(col_tiles), static_cast<unsigned>(splits));
   const int fgrid = grid_for(cols, 256, ctx->sm_count);
 #define NOVA_COLSUM(T)                                                                                   \
@@ -1114,6 +1126,8 @@ int32_t nova_b200_activation(const void* x, void* y, int64_t n, int32_t dtype, i
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_activation: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, y, "nova_b200_activation: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype), vec = 16 / es;
   const bool vec_ok = n % vec == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
@@ -1136,6 +1150,8 @@ int32_t nova_b200_gelu_backward(const void* go, const void* x, void* y, int64_t 
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "nova_b200_gelu_backward: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, y, "nova_b200_gelu_backward: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype), vec = 16 / es;
   const bool vec_ok = n % vec == 0 && reinterpret_cast<uintptr_t>(go) % 16 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
@@ -1161,6 +1177,8 @@ int32_t nova_b200_add_rowbcast(const void* a, const void* b, void* out, int64_t 
   int32_t st = NOVA_B200_OK;
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, a, "nova_b200_add_rowbcast: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, out, "nova_b200_add_rowbcast: the output")) != NOVA_B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype), vec = 16 / es;
   const bool vec_ok = cols % vec == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&

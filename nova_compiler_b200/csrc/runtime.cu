@@ -2,6 +2,8 @@
 // contraction (device-pointer, host-pointer and memref-descriptor forms).
 #include "runtime.h"
 
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -11,6 +13,9 @@ namespace nova {
 
 int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
 int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream);
+int32_t static_scratch_status(int dev, uint32_t* code_out);
+int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_t rows, int64_t cols, int64_t ld_in,
+                       int64_t stride_in, int64_t ld_out, int sm_count, cudaStream_t stream);
 
 namespace {
 thread_local std::string g_last_error;
@@ -46,6 +51,7 @@ DeviceContext* current_context(int32_t* status_out) {
   }
   auto ctx = std::make_unique<DeviceContext>();
   ctx->device = dev;
+  ctx->device_count = count;
   cudaDeviceProp prop;
   e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) {
@@ -82,10 +88,11 @@ DeviceContext* current_context(int32_t* status_out) {
   return raw;
 }
 
-static int32_t grow(void** buf, size_t* have, size_t want, const char* what) {
+// Staging of the *_host entry points: those calls synchronise before they return, so by the time a later call
+// finds the buffer too small nothing can still be using it.
+static int32_t grow_staging(void** buf, size_t* have, size_t want) {
   if (*have >= want) return NOVA_B200_OK;
   if (*buf) {
-    NOVA_CUDA_OK(cudaDeviceSynchronize());  // earlier launches may still read the old buffer
     NOVA_CUDA_OK(cudaFree(*buf));
     *buf = nullptr;
     *have = 0;
@@ -94,11 +101,78 @@ static int32_t grow(void** buf, size_t* have, size_t want, const char* what) {
   cudaError_t e = cudaMalloc(buf, bytes);
   if (e != cudaSuccess) {
     cudaGetLastError();
-    return fail(NOVA_B200_ERR_CUDA, std::string(what) + ": cudaMalloc of " + std::to_string(bytes) + " bytes failed: " +
+    return fail(NOVA_B200_ERR_CUDA, "staging: cudaMalloc of " + std::to_string(bytes) + " bytes failed: " +
                                         cudaGetErrorString(e));
   }
   *have = bytes;
   return NOVA_B200_OK;
+}
+
+int32_t acquire_scratch(DeviceContext* ctx, cudaStream_t stream, size_t bytes, void** out) {
+  if (ctx->fixed_scratch) {
+    if (bytes > ctx->fixed_scratch_bytes)
+      return fail(NOVA_B200_ERR_TOO_LARGE, "scratch request of " + std::to_string(bytes) + " bytes exceeds the fixed scratch");
+    *out = ctx->fixed_scratch;
+    return NOVA_B200_OK;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceContext::ScratchBuf& buf = ctx->scratch_by_stream[stream];
+  if (buf.bytes < bytes) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(NOVA_B200_ERR_CUDA, "this call needs " + std::to_string(bytes) + " bytes of library scratch on a stream that is "
+                  "being captured; make one such call (or nova_b200_reserve_scratch) on the stream before the capture");
+    // at least double, so the retired buffers of a growing stream sum to less than the live one
+    size_t want = std::max(bytes, 2 * buf.bytes);
+    want = (want + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    void* fresh = nullptr;
+    cudaError_t e = cudaMalloc(&fresh, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(NOVA_B200_ERR_CUDA, "scratch: cudaMalloc of " + std::to_string(want) + " bytes failed: " + cudaGetErrorString(e));
+    }
+    if (buf.ptr) ctx->retired_scratch.push_back(buf.ptr);  // enqueued or captured kernels may still use it
+    buf.ptr = fresh;
+    buf.bytes = want;
+  }
+  *out = buf.ptr;
+  return NOVA_B200_OK;
+}
+
+int32_t check_pointer_device(const DeviceContext* ctx, const void* p, const char* what) {
+  if (!p || ctx->device_count <= 1) return NOVA_B200_OK;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return NOVA_B200_OK;  // not a pointer CUDA knows: the launch itself will report it
+  }
+  if (attr.type == cudaMemoryTypeDevice && attr.device != ctx->device)
+    return fail(NOVA_B200_ERR_INVALID_ARG, std::string(what) + " lives on device " + std::to_string(attr.device) +
+                                               " but the current device is " + std::to_string(ctx->device) +
+                                               ": make the operands' device current before the call");
+  return NOVA_B200_OK;
+}
+
+namespace {
+struct OptionEntry { const char* name; const char* env; std::atomic<int64_t> Options::*field; };
+const OptionEntry kOptionTable[] = {
+    {"repitch", "NOVA_B200_REPITCH", &Options::repitch},     {"pair", "NOVA_B200_PAIR", &Options::pair},
+    {"block_n", "NOVA_B200_BLOCK_N", &Options::block_n},     {"short_k", "NOVA_B200_SHORT_K", &Options::short_k},
+    {"group_m", "NOVA_B200_GROUP_M", &Options::group_m},     {"prefetch", "NOVA_B200_PREFETCH", &Options::prefetch},
+    {"plan_cache", "NOVA_B200_PLAN_CACHE", &Options::plan_cache}, {"debug", "NOVA_B200_DEBUG", &Options::debug},
+    {"pdl", "NOVA_B200_PDL", &Options::pdl},
+};
+}  // namespace
+
+Options& options() {
+  static Options* opts = [] {
+    Options* o = new Options();
+    for (const OptionEntry& e : kOptionTable)
+      if (const char* v = std::getenv(e.env)) (o->*(e.field)).store(std::strtoll(v, nullptr, 0));
+    return o;
+  }();
+  return *opts;
 }
 
 int32_t ensure_host_streams(DeviceContext* ctx) {
@@ -113,8 +187,7 @@ int32_t ensure_host_streams(DeviceContext* ctx) {
   return NOVA_B200_OK;
 }
 
-int32_t ensure_scratch(DeviceContext* ctx, size_t bytes) { return grow(&ctx->scratch, &ctx->scratch_bytes, bytes, "scratch"); }
-int32_t ensure_staging(DeviceContext* ctx, size_t bytes) { return grow(&ctx->staging, &ctx->staging_bytes, bytes, "staging"); }
+int32_t ensure_staging(DeviceContext* ctx, size_t bytes) { return grow_staging(&ctx->staging, &ctx->staging_bytes, bytes); }
 
 }  // namespace nova
 
@@ -150,7 +223,9 @@ int32_t nova_b200_shutdown(void) {
     if (cudaSetDevice(c->device) != cudaSuccess) continue;
     cudaDeviceSynchronize();
     if (c->status_word) cudaFree(c->status_word);
-    if (c->scratch) cudaFree(c->scratch);
+    for (auto& sb : c->scratch_by_stream)
+      if (sb.second.ptr) cudaFree(sb.second.ptr);
+    for (void* r : c->retired_scratch) cudaFree(r);
     if (c->staging) cudaFree(c->staging);
     if (c->s_in) {
       cudaStreamDestroy(c->s_in); cudaStreamDestroy(c->s_comp); cudaStreamDestroy(c->s_out);
@@ -171,6 +246,11 @@ int32_t nova_b200_device_status(uint32_t* code_out) {
   NOVA_CUDA_OK(cudaDeviceSynchronize());
   NOVA_CUDA_OK(cudaMemcpy(&code, ctx->status_word, 4, cudaMemcpyDeviceToHost));
   if (code != 0) NOVA_CUDA_OK(cudaMemset(ctx->status_word, 0, 4));
+  // the static-array entry point keeps its own status word (it may not use allocated memory)
+  uint32_t static_code = 0;
+  st = static_scratch_status(ctx->device, &static_code);
+  if (st != NOVA_B200_OK) return st;
+  if (code == 0) code = static_code;
   if (code_out) *code_out = code;
   if (code != 0)
     return fail(NOVA_B200_ERR_DEVICE_TIMEOUT, "a bounded in-kernel wait gave up, code 0x" + [&] {
@@ -179,6 +259,110 @@ int32_t nova_b200_device_status(uint32_t* code_out) {
       return std::string(b);
     }());
   return NOVA_B200_OK;
+}
+
+int32_t nova_b200_set_option(const char* name, int64_t value) {
+  if (!name) return fail(NOVA_B200_ERR_INVALID_ARG, "set_option: name is null");
+  Options& o = options();
+  for (const OptionEntry& e : kOptionTable) {
+    if (std::strcmp(e.name, name) == 0) {
+      (o.*(e.field)).store(value);
+      o.epoch.fetch_add(1);
+      return NOVA_B200_OK;
+    }
+  }
+  return fail(NOVA_B200_ERR_INVALID_ARG, std::string("set_option: unknown option '") + name + "'");
+}
+
+int32_t nova_b200_get_option(const char* name, int64_t* value_out) {
+  if (!name || !value_out) return fail(NOVA_B200_ERR_INVALID_ARG, "get_option: null argument");
+  Options& o = options();
+  for (const OptionEntry& e : kOptionTable) {
+    if (std::strcmp(e.name, name) == 0) {
+      *value_out = (o.*(e.field)).load();
+      return NOVA_B200_OK;
+    }
+  }
+  return fail(NOVA_B200_ERR_INVALID_ARG, std::string("get_option: unknown option '") + name + "'");
+}
+
+int32_t nova_b200_reserve_scratch(int64_t bytes, void* stream) {
+  if (bytes < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "reserve_scratch: negative size");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  void* unused = nullptr;
+  return bytes == 0 ? NOVA_B200_OK : acquire_scratch(ctx, static_cast<cudaStream_t>(stream), static_cast<size_t>(bytes), &unused);
+}
+
+// ---------------------------------------------------------------- prepared operands
+
+struct nova_b200_operand {
+  void* data = nullptr;
+  int device = -1;
+  int32_t dtype = 0;
+  int64_t batch = 0, rows = 0, cols = 0, ld = 0, batch_stride = 0;
+};
+
+int32_t nova_b200_operand_prepare(const void* src_dev, int32_t dtype, int64_t batch, int64_t rows, int64_t cols, int64_t ld,
+                                  int64_t batch_stride, void* stream, nova_b200_operand** out) {
+  if (!out) return fail(NOVA_B200_ERR_INVALID_ARG, "operand_prepare: out is null");
+  *out = nullptr;
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "operand_prepare: dtype must be f32, f16 or bf16");
+  if (batch < 1 || rows < 1 || cols < 1 || ld < cols || batch_stride < 0 || !src_dev)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "operand_prepare: bad extent, pitch or pointer");
+  if (batch > 1 && batch_stride != 0 && batch_stride < (rows - 1) * ld + cols)
+    return fail(NOVA_B200_ERR_LAYOUT, "operand_prepare: batches overlap");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  st = check_pointer_device(ctx, src_dev, "operand_prepare: the operand");
+  if (st != NOVA_B200_OK) return st;
+  const int es = dtype_bytes(dtype);
+  const int per_chunk = 16 / es;
+  auto op = std::make_unique<nova_b200_operand>();
+  op->device = ctx->device;
+  op->dtype = dtype;
+  op->batch = batch_stride == 0 ? 1 : batch;
+  op->rows = rows;
+  op->cols = cols;
+  op->ld = (cols + per_chunk - 1) / per_chunk * per_chunk;
+  op->batch_stride = op->batch > 1 ? rows * op->ld : 0;
+  const size_t bytes = static_cast<size_t>(op->batch) * rows * op->ld * es;
+  cudaError_t e = cudaMalloc(&op->data, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NOVA_B200_ERR_CUDA, "operand_prepare: cudaMalloc of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e));
+  }
+  st = repitch_launch(src_dev, op->data, es, op->batch, rows, cols, ld, batch_stride, op->ld, ctx->sm_count,
+                      static_cast<cudaStream_t>(stream));
+  if (st != NOVA_B200_OK) {
+    cudaFree(op->data);
+    return st;
+  }
+  *out = op.release();
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_operand_view(const nova_b200_operand* op, const void** data_dev, int64_t* ld, int64_t* batch_stride) {
+  if (!op) return fail(NOVA_B200_ERR_INVALID_ARG, "operand_view: operand is null");
+  if (data_dev) *data_dev = op->data;
+  if (ld) *ld = op->ld;
+  if (batch_stride) *batch_stride = op->batch_stride;
+  return NOVA_B200_OK;
+}
+
+void nova_b200_operand_free(nova_b200_operand* op) {
+  if (!op) return;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(op->device) == cudaSuccess) {
+    cudaDeviceSynchronize();  // kernels that still read the copy
+    cudaFree(op->data);
+  }
+  if (prev >= 0) cudaSetDevice(prev);
+  cudaGetLastError();
+  delete op;
 }
 
 int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
@@ -391,6 +575,52 @@ int32_t _mlir_ciface_nova_b200_batch_matmul(nova_b200_memref3d* C, nova_b200_mem
   g.B = static_cast<char*>(B->aligned) + B->offset * es;
   g.C = static_cast<char*>(C->aligned) + C->offset * os;
   return run_descriptor_gemm(g);
+}
+
+int32_t _mlir_ciface_nova_b200_batch_matmul_4d(nova_b200_memref4d* C, nova_b200_memref4d* A, nova_b200_memref4d* B,
+                                               int32_t ab_dtype, int32_t c_dtype) {
+  if (!C || !A || !B) return fail(NOVA_B200_ERR_INVALID_ARG, "batch_matmul_4d: null descriptor");
+  for (int d = 0; d < 2; ++d) {
+    if (A->sizes[d] != C->sizes[d] || (B->sizes[d] != C->sizes[d] && B->sizes[d] != 1))
+      return fail(NOVA_B200_ERR_INVALID_ARG, "batch_matmul_4d: batch dims do not compose");
+  }
+  // A size-1 batch dim broadcasts: give it stride 0 so the arithmetic below treats every operand alike.
+  auto bstride = [](const nova_b200_memref4d* m, int d, int64_t full) { return (m->sizes[d] == 1 && full > 1) ? 0 : m->strides[d]; };
+  const int64_t b0 = C->sizes[0], b1 = C->sizes[1];
+  // collapsing [b0, b1] to one batch dim is metadata when stride[0] == b1 * stride[1] (or either dim is 1)
+  auto collapses = [&](const nova_b200_memref4d* m) {
+    const int64_t s0 = bstride(m, 0, b0), s1 = bstride(m, 1, b1);
+    return b0 == 1 || b1 == 1 || s0 == b1 * s1;
+  };
+  auto slice3 = [&](const nova_b200_memref4d* m, int64_t i0, bool collapse, int esz) {
+    nova_b200_memref3d r{};
+    const int64_t s0 = bstride(m, 0, b0), s1 = bstride(m, 1, b1);
+    r.allocated = m->allocated;
+    r.aligned = static_cast<char*>(m->aligned) + (m->offset + (collapse ? 0 : i0 * s0)) * esz;
+    r.offset = 0;
+    const bool bcast = m->sizes[0] == 1 && m->sizes[1] == 1 && b0 * b1 > 1;
+    r.sizes[0] = bcast ? 1 : (collapse ? b0 * b1 : b1);
+    r.strides[0] = collapse ? (b1 == 1 ? s0 : s1) : s1;
+    r.sizes[1] = m->sizes[2]; r.sizes[2] = m->sizes[3];
+    r.strides[1] = m->strides[2]; r.strides[2] = m->strides[3];
+    return r;
+  };
+  const int es = dtype_bytes(ab_dtype), os = dtype_bytes(c_dtype);
+  if (es == 0 || os == 0) return fail(NOVA_B200_ERR_UNSUPPORTED, "batch_matmul_4d: dtypes must be f32, f16 or bf16");
+  // an operand that broadcasts along only ONE of the two batch dims cannot be a single strided batch
+  auto mixed = [&](const nova_b200_memref4d* m) { return (m->sizes[0] == 1) != (m->sizes[1] == 1) && b0 > 1 && b1 > 1; };
+  const bool one_call = collapses(C) && collapses(A) && collapses(B) && !mixed(B);
+  if (one_call) {
+    nova_b200_memref3d c3 = slice3(C, 0, true, os), a3 = slice3(A, 0, true, es), bb3 = slice3(B, 0, true, es);
+    return _mlir_ciface_nova_b200_batch_matmul(&c3, &a3, &bb3, ab_dtype, c_dtype);
+  }
+  for (int64_t i0 = 0; i0 < b0; ++i0) {
+    nova_b200_memref3d c3 = slice3(C, i0, false, os), a3 = slice3(A, i0, false, es), bb3 = slice3(B, i0, false, es);
+    if (B->sizes[1] == 1 && b1 > 1) bb3.sizes[0] = 1;
+    int32_t st = _mlir_ciface_nova_b200_batch_matmul(&c3, &a3, &bb3, ab_dtype, c_dtype);
+    if (st != NOVA_B200_OK) return st;
+  }
+  return NOVA_B200_OK;
 }
 
 int32_t _mlir_ciface_nova_b200_linear(nova_b200_memref2d* Y, nova_b200_memref2d* X, nova_b200_memref2d* W,

@@ -4,8 +4,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <map>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "../../include/nova_b200.h"
 
@@ -32,16 +35,25 @@ struct DeviceContext {
   int device = -1;
   int sm_count = 0;
   int cc_major = 0, cc_minor = 0;
+  int device_count = 1;             // visible devices: pointer-ownership checks only run when > 1
   uint32_t* status_word = nullptr;  // device memory, 4 bytes (+ padding)
-  void* scratch = nullptr;          // hi/lo split buffers for the 3xTF32 path
-  size_t scratch_bytes = 0;
+  // Scratch (hi/lo split of f32 operands, re-pitched operand copies, partial sums of the row kernels): one buffer
+  // per STREAM, so calls on different streams never share scratch.  A buffer that has to grow is replaced, and
+  // the old one is kept until nova_b200_shutdown because kernels already enqueued (or captured into a CUDA
+  // graph) may still read it: growing never synchronises and never frees.
+  struct ScratchBuf { void* ptr = nullptr; size_t bytes = 0; };
+  std::map<cudaStream_t, ScratchBuf> scratch_by_stream;
+  std::vector<void*> retired_scratch;
+  // a caller-provided fixed scratch (the static-array entry point): used instead of the pool, never grown
+  void* fixed_scratch = nullptr;
+  size_t fixed_scratch_bytes = 0;
   void* staging = nullptr;          // device staging for the *_host entry points
   size_t staging_bytes = 0;
   EncodeTiledFn encode_tiled = nullptr;
   // the *_host entry points pipeline H2D / kernel / D2H over three streams
   cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
   cudaEvent_t ev_in[kHostChunks] = {}, ev_comp[kHostChunks] = {};
-  std::mutex mu;       // guards scratch
+  std::mutex mu;       // guards the scratch pool
   std::mutex host_mu;  // guards staging (the *_host entry points)
 };
 
@@ -49,8 +61,27 @@ void set_error(const std::string& msg);
 int32_t fail(nova_b200_status st, const std::string& msg);
 // Returns the context of the current device, initialising it on first use; nullptr + error on failure.
 DeviceContext* current_context(int32_t* status_out);
-// Grows ctx->scratch to at least `bytes` (device-synchronising only when it has to reallocate).
-int32_t ensure_scratch(DeviceContext* ctx, size_t bytes);
+// Scratch of at least `bytes` for work enqueued on `stream` (see DeviceContext).  Allocates only when the stream's
+// buffer is too small; refuses (NOVA_B200_ERR_CUDA) to allocate while `stream` is being captured.
+int32_t acquire_scratch(DeviceContext* ctx, cudaStream_t stream, size_t bytes, void** out);
+// NOVA_B200_ERR_INVALID_ARG when `p` is device memory of another device than the current one (only checked in
+// processes that see more than one device).  `what` names the operand in the message.
+int32_t check_pointer_device(const DeviceContext* ctx, const void* p, const char* what);
+
+// Tuning switches.  Seeded once from the environment (NOVA_B200_<NAME>), changed with nova_b200_set_option.
+struct Options {
+  std::atomic<int64_t> repitch{1};    // unaligned operands: 1 = re-pitch copy + TMA, 0 = in-place loader warps
+  std::atomic<int64_t> pair{-1};      // CTA-pair kernel: -1 = cost model, 0 = never, 1 = whenever legal
+  std::atomic<int64_t> block_n{0};    // 0 = cost model, else 64 / 128 / 256
+  std::atomic<int64_t> short_k{1};    // 8 epilogue warps for K <= 256
+  std::atomic<int64_t> group_m{16};   // raster group height in row blocks
+  std::atomic<int64_t> prefetch{-1};  // L2 prefetch distance of the pair kernel in ring stages: -1 = planner, 0 = off
+  std::atomic<int64_t> plan_cache{1}; // reuse plans and tensor maps of repeated calls
+  std::atomic<int64_t> pdl{1};        // launch contractions with programmatic stream serialization
+  std::atomic<int64_t> debug{0};
+  std::atomic<uint32_t> epoch{0};     // bumped by every change: cached plans are keyed on it
+};
+Options& options();
 int32_t ensure_staging(DeviceContext* ctx, size_t bytes);
 int32_t ensure_host_streams(DeviceContext* ctx);
 

@@ -32,6 +32,29 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _on_device(fn):
+    """Runs the wrapped op with its tensors' device current, so the library's per-device context, the tensor maps
+    and torch's current stream all belong to the device that owns the memory; tensors on different devices are
+    refused before anything is launched (the library cannot read another GPU's memory by accident)."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        dev = None
+        for v in list(args) + list(kwargs.values()):
+            if isinstance(v, torch.Tensor) and v.is_cuda:
+                if dev is None:
+                    dev = v.device
+                elif v.device != dev:
+                    raise L.NovaB200Error(L.ERR_INVALID_ARG, f"tensors live on different devices ({dev} and {v.device})")
+        if dev is None or dev.index == torch.cuda.current_device():
+            return fn(*args, **kwargs)
+        with torch.cuda.device(dev):
+            return fn(*args, **kwargs)
+
+    return wrapper
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -61,6 +84,7 @@ def _batch_stride(t: torch.Tensor) -> int:
     return 0 if t.shape[0] == 1 else t.stride(0)
 
 
+@_on_device
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
          out_dtype: Optional[torch.dtype] = None, accumulate_into_out: bool = False,
@@ -195,6 +219,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, *, act: Optiona
     return y.reshape(*x.shape[:-1], w.shape[-1])
 
 
+@_on_device
 def column_sum(x: torch.Tensor) -> torch.Tensor:
     """Sum over all leading dims of x[..., C] -> [C], fp32 accumulation (grad_bias of nova.linear_backward)."""
     _require_cuda(x)
@@ -225,6 +250,7 @@ def linear_backward(grad_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor):
     return grad_input, grad_weight, column_sum(gf)
 
 
+@_on_device
 def _unary(x: torch.Tensor, act: int) -> torch.Tensor:
     _require_cuda(x)
     xc = x.contiguous()
@@ -238,6 +264,7 @@ def gelu(x: torch.Tensor) -> torch.Tensor:
     return _unary(x, L.ACT_GELU_TANH)
 
 
+@_on_device
 def gelu_backward(grad_out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     """nova.gelu_backward: grad_out * d/dx gelu_tanh(x) (NovaGeluBackwardPattern, NovaToLinalgGeneric.cpp:1339-1420)."""
     _require_cuda(grad_out, x)
@@ -254,6 +281,7 @@ def relu(x: torch.Tensor) -> torch.Tensor:
     return _unary(x, L.ACT_RELU)
 
 
+@_on_device
 def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """nova.add where b either has a's shape or broadcasts along rows ([N] or [1,N] against [...,N]),
     the forms next to a contraction (ltest/test_cpu.mlir: 8x10 + 1x10).  Other broadcasts are out of scope."""
@@ -271,6 +299,7 @@ def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_on_device
 def softmax(x: torch.Tensor, dimension: int = -1) -> torch.Tensor:
     """nova.softmax (NovaSoftmaxForwardPattern, NovaToLinalgGeneric.cpp:1427-1534) along `dimension`
     (default -1, negative wraps, :1439-1443).  Non-last dimensions are moved last and back."""
@@ -288,6 +317,7 @@ def softmax(x: torch.Tensor, dimension: int = -1) -> torch.Tensor:
     return y.movedim(-1, dim)
 
 
+@_on_device
 def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
     """nova.layer_norm over the last dim (NovaLayerNormPattern, NovaToLinalgGeneric.cpp:1997-2126).
     Returns (y, mean_sum, rstd): mean_sum is the RAW row sum, as in the reference (:2121-2123)."""
@@ -304,6 +334,7 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor):
     return y, mean_sum, rstd
 
 
+@_on_device
 def layer_norm_backward(grad_y: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, mean_sum: torch.Tensor,
                         rstd: torch.Tensor):
     """nova.layer_norm_backward (NovaLayerNormBackwardPattern, NovaToLinalgGeneric.cpp:2128-2376): returns
@@ -326,6 +357,7 @@ def layer_norm_backward(grad_y: torch.Tensor, x: torch.Tensor, gamma: torch.Tens
     return dx, dgamma, dbeta
 
 
+@_on_device
 def gather(inp: torch.Tensor, indices: torch.Tensor, axis: int = 0, *, return_bad_count: bool = False):
     """nova.gather (NovaGatherOpLowering, NovaToLinalgGeneric.cpp:2372-2472; shapes NovaOps.cpp:1898-1946):
     out[pre..., idx..., post...] = inp[pre..., indices[...], post...].  Leading index dims equal to inp's
@@ -362,6 +394,7 @@ def gather(inp: torch.Tensor, indices: torch.Tensor, axis: int = 0, *, return_ba
     return (out, int(bad.item())) if return_bad_count else out
 
 
+@_on_device
 def sce(logits: torch.Tensor, targets: torch.Tensor, *, return_bad_count: bool = False):
     """nova.sce (NovaSceForwardLowering, NovaToLinalgGeneric.cpp:801-1010): sparse softmax cross-entropy over the
     last dim.  Returns (softmax, loss[1]) as the op does (NovaOps.cpp:1648-1677)."""
@@ -381,6 +414,7 @@ def sce(logits: torch.Tensor, targets: torch.Tensor, *, return_bad_count: bool =
     return (sm, loss, int(bad.item())) if return_bad_count else (sm, loss)
 
 
+@_on_device
 def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1) -> torch.Tensor:
     """nova.sce_backward (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137): (softmax - one_hot) / rows."""
     _require_cuda(softmax_, targets)
@@ -399,6 +433,7 @@ def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1) -
     return g
 
 
+@_on_device
 def scatter_add(inp: torch.Tensor, indices: torch.Tensor, src: torch.Tensor, axis: int = 0, *,
                 return_bad_count: bool = False):
     """nova.scatter_add (NovaScatterAddOpLowering, NovaToLinalg.cpp:1086-1294; verify NovaOps.cpp:1990-2026): a copy

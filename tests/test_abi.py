@@ -84,12 +84,12 @@ def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
     st, info = _plan(lib, _args(1000, 1000, 999))
     assert st == L.OK and (info.loader_a, info.loader_b, info.store_c) == (2, 0, 0)
     assert info.scratch_bytes == (1000 * 1000 * 2 + 255) // 256 * 256
-    # NOVA_B200_REPITCH=0: read in place by the loader warps, no scratch
-    os.environ["NOVA_B200_REPITCH"] = "0"
+    # option "repitch" = 0: read in place by the loader warps, no scratch
+    L.set_option("repitch", 0)
     try:
         st, info = _plan(lib, _args(1000, 1000, 999))
     finally:
-        del os.environ["NOVA_B200_REPITCH"]
+        L.set_option("repitch", 1)
     assert st == L.OK and (info.loader_a, info.loader_b, info.scratch_bytes) == (1, 0, 0)
     # 4095 x 11007 x 4097: every pitch is odd in bytes/16; both operands re-pitched, C written with element stores
     st, info = _plan(lib, _args(4095, 11007, 4097))

@@ -243,12 +243,13 @@ def test_unaligned_pitch_loader_matches_tma_bit_for_bit(cuda, oracle):
     bp = torch.zeros(1, K, 336, device="cuda", dtype=torch.bfloat16); bp[:, :, :N] = b
     cp = torch.zeros(1, M, 336, device="cuda", dtype=torch.bfloat16)
     aligned = ops.gemm(ap[:, :, :K], bp[:, :, :N], out=cp[:, :, :N])
-    os.environ["NOVA_B200_REPITCH"] = "0"  # read in place by the loader warps
+    from nova_compiler_b200 import _lib as L
+    L.set_option("repitch", 0)  # read in place by the loader warps
     try:
         ragged = ops.gemm(a, b)  # pitches 514 B / 666 B: neither is a multiple of 16
         torch.cuda.synchronize()
     finally:
-        del os.environ["NOVA_B200_REPITCH"]
+        L.set_option("repitch", 1)
     assert torch.equal(aligned, ragged)
     check(oracle, to_host(torch, ragged, "bf16"), oracle.gemm(to_host(torch, a, "bf16"), to_host(torch, b, "bf16"),
                                                                dtype_in="bf16"), "bf16")
@@ -258,7 +259,7 @@ def test_unaligned_pitch_loader_matches_tma_bit_for_bit(cuda, oracle):
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (False, True), (True, False), (True, True)])
 def test_unaligned_pitch_repitch_copy_matches_loader_bit_for_bit(cuda, oracle, dt, trans_a, trans_b):
     """An operand no tensor map can describe is read by the loader warps (small contractions) or re-pitched into
-    aligned scratch and streamed with TMA (large ones).  NOVA_B200_REPITCH forces either: same bits, batched,
+    aligned scratch and streamed with TMA (the default).  The option "repitch" forces either: same bits, batched,
     with a batch-shared B, for both operand majors."""
     torch = cuda
     from nova_compiler_b200 import ops, _lib as L
@@ -274,12 +275,12 @@ def test_unaligned_pitch_repitch_copy_matches_loader_bit_for_bit(cuda, oracle, d
     kw = dict(f32_mode=L.TF32X1) if dt == "f32" else {}
     outs = {}
     for mode in ("0", "1"):
-        os.environ["NOVA_B200_REPITCH"] = mode
+        L.set_option("repitch", int(mode))
         try:
             outs[mode] = ops.gemm(a3, b3, act="relu", **kw)
             torch.cuda.synchronize()
         finally:
-            del os.environ["NOVA_B200_REPITCH"]
+            L.set_option("repitch", 1)
     assert torch.equal(outs["0"], outs["1"])
     if dt != "f32":
         want = oracle.gemm(a, b[0], dtype_in=dt, act="relu", trans_a=trans_a, trans_b=trans_b)
