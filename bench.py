@@ -1,18 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the matmul hot path through the C ABI of libnova_b200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--only] [--impl reference]
 
-A step is ONE pass of the contraction over one batch of seeded synthetic input.  The default workload
-is the f16 batch_matmul configuration (batch 32 of 1024^3, fp32 accumulation, f16 output); the other
-configurations are selectable with --workload.  Inputs are resident in HBM for `value`; `e2e` runs the
-same contraction through nova_b200_gemm_host with pinned HOST buffers (H2D + kernel + D2H per step).
-With N > 1 (torchrun, one rank per GPU) the batch index is sharded across ranks with no data-path
-collective: every rank owns a full per-GPU batch (weak scaling) and the slowest rank sets the time.
+A step is ONE pass of a contraction over one batch of seeded synthetic input.  The headline workload is the bf16
+transformer linear layer (X[8192,4096] . W[4096,11008] + bias, GELU-tanh, fp32 accumulation, bf16 out); the same
+JSON line carries a `workloads` object with one sub-record per remaining configuration (f32 512^3, f16 batch 32 x
+1024^3, f16 attention scores 256 x 2048 x 2048 x 128, bf16 16384^3, the two ragged bf16 GEMMs) and per row kernel
+(layer_norm, softmax, gather, layer_norm_backward), each with its own time, roofline fraction and clocks.
+`--workload X` makes X the headline; `--only` drops the sub-records.
 
-`--impl reference` times the reference's own CPU lowering of the same contraction — the single-threaded
-i/j/k loop nest its CPU pipeline emits, restated in oracle/nova_oracle.c — on this machine's host cores,
-on a bounded row sample of the workload.  That is a reported baseline, not the target.
+Inputs are resident in HBM for `value`; `e2e` runs the headline through nova_b200_gemm_host with pinned HOST
+buffers (H2D + kernel + D2H inside the timed region).
+
+With N > 1 (torchrun, one rank per GPU) every workload is ONE GLOBAL PROBLEM partitioned over the ranks with no
+data-path collective: batched contractions by batch index (rank r owns a contiguous range of batches), single
+GEMMs by 64-column-aligned N slabs (every rank holds A and reads its slab of B as a strided view).  value = global
+FLOPs / the slowest rank's device time ("scaling": "strong").  The optional all-gather of the output slabs (NCCL +
+one re-interleave kernel) is timed on its own and reported as `allgather_ms`, outside `value`.
+
+`--impl reference` times the reference's own CPU lowering of the same contraction (the single-threaded i/j/k loop
+nest its CPU pipeline emits, restated in oracle/nova_oracle.c) on this machine's host cores, on a bounded row
+sample of the workload.  That is a reported baseline, not the target.
 
 Rank 0 prints exactly one JSON line.
 """
@@ -32,29 +41,44 @@ sys.path.insert(0, HERE)
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# name -> (description, dtype_ab, dtype_c, batch, M, N, K, epilogue)
+# name -> (description, dtype_ab, dtype_c, batch, M, N, K, epilogue, partition over ranks)
 WORKLOADS = {
-    "c1": ("nova.matmul f32 512x512x512 (3xTF32)", "f32", "f32", 1, 512, 512, 512, None),
-    "c2": ("linalg.batch_matmul f16 B=32 M=N=K=1024, fp32 accumulate, f16 out", "f16", "f16", 32, 1024, 1024, 1024, None),
+    "c1": ("nova.matmul f32 512x512x512 (3xTF32)", "f32", "f32", 1, 512, 512, 512, None, None),
+    "c2": ("linalg.batch_matmul f16 B=32 M=N=K=1024, fp32 accumulate, f16 out", "f16", "f16", 32, 1024, 1024, 1024, None,
+           "batch"),
     "c3": ("linear bf16 X[8192,4096] W[4096,11008] + bias, GELU(tanh), bf16 out", "bf16", "bf16", 1, 8192, 11008, 4096,
-           "bias_gelu"),
-    "c4": ("batch_matmul f16 Q[256,2048,128] K^T[256,128,2048], f16 out", "f16", "f16", 256, 2048, 2048, 128, None),
-    "c4s": ("batch_matmul f16 Q[32,2048,128] K^T[32,128,2048] (C4 at one eighth of the batch, profiling-sized)", "f16", "f16", 32, 2048,
-            2048, 128, None),
-    "c5a": ("GEMM bf16 16384^3", "bf16", "bf16", 1, 16384, 16384, 16384, None),
-    "c5b": ("GEMM bf16 ragged 1000x1000x999", "bf16", "bf16", 1, 1000, 1000, 999, None),
-    "c5c": ("GEMM bf16 ragged 4095x11007x4097", "bf16", "bf16", 1, 4095, 11007, 4097, None),
+           "bias_gelu", "slab"),
+    "c4": ("batch_matmul f16 Q[256,2048,128] K^T[256,128,2048], f16 out", "f16", "f16", 256, 2048, 2048, 128, None, "batch"),
+    "c4s": ("batch_matmul f16 Q[32,2048,128] K^T[32,128,2048] (C4 at one eighth of the batch, profiling-sized)", "f16", "f16",
+            32, 2048, 2048, 128, None, "batch"),
+    "c5a": ("GEMM bf16 16384^3", "bf16", "bf16", 1, 16384, 16384, 16384, None, "slab"),
+    "c5b": ("GEMM bf16 ragged 1000x1000x999", "bf16", "bf16", 1, 1000, 1000, 999, None, None),
+    "c5c": ("GEMM bf16 ragged 4095x11007x4097", "bf16", "bf16", 1, 4095, 11007, 4097, None, None),
 }
-# DRAM bytes one launch moves according to ncu (dram__bytes_read.sum + dram__bytes_write.sum), per workload;
-# see profiles/.  None where no capture exists.
+# default steps of a sub-record (the headline takes --steps)
+SUB_STEPS = {"c1": 400, "c2": 400, "c3": 100, "c4": 60, "c4s": 100, "c5a": 12, "c5b": 400, "c5c": 100}
+# DRAM bytes one launch moves according to ncu (dram__bytes_read.sum + dram__bytes_write.sum), per workload at
+# N = 1; see profiles/.  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
     "c2": 173.7e6,      # 134.3 MB read + 39.4 MB written (part of the 67 MB output is still in L2 at kernel end)
     "c3": 468.5e6,      # 308.0 MB read + 160.5 MB written
     "c4": 8 * 243.4e6,  # captured on 32 of the 256 batches (c4s), scaled by 8: traffic is proportional to batches
+    "c4s": 243.4e6,
     "c5c": 207.7e6,     # the contraction kernel: 140.2 MB read + 67.5 MB written (the re-pitch copy before it: 203.8 MB)
     # row kernels (reads match the inputs exactly; part of each output is still in L2 when the kernel ends)
     "ln": 92.3e6, "ln_bwd": 176.0e6, "softmax": 489.8e6, "sce": 3246.0e6, "sce_bwd": 3252.9e6, "gather": 209.2e6,
 }
+
+# HBM-bound companions of the contraction: name -> (description, dtype, rows, D)
+ROW_WORKLOADS = {
+    "ln": ("nova.layer_norm bf16 [8192, 4096] (the rows that feed the C3 linear)", "bf16", 8192, 4096),
+    "softmax": ("nova.softmax f16 [65536, 2048] (attention-score rows, C4 layout, 32 of its 256 batches)", "f16", 65536, 2048),
+    "gather": ("nova.gather bf16 table [50304, 4096], 16384 i32 ids (embedding lookup)", "bf16", 16384, 4096),
+    "ln_bwd": ("nova.layer_norm_backward bf16 [8192, 4096] (dx, dgamma, dbeta from one read of gy and x)", "bf16", 8192, 4096),
+    "sce": ("nova.sce f32 logits [8192, 50304], i16 targets (softmax + mean loss; the vocabulary rows of ltest/test.mlir)", "f32", 8192, 50304),
+    "sce_bwd": ("nova.sce_backward f32 [8192, 50304]", "f32", 8192, 50304),
+}
+DEFAULT_SUBS = ["c1", "c2", "c4", "c5a", "c5b", "c5c", "ln", "softmax", "gather", "ln_bwd"]
 
 
 def load_peaks():
@@ -66,8 +90,12 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-def algorithmic(w):
-    _, dab, dc, B, M, N, K, epi = WORKLOADS[w]
+def algorithmic(w, batch=None, n=None):
+    """(FLOPs, bytes) of one launch: one read of each input, one write of the output (B shared across the batch
+    counts once per launch).  batch / n override the global extents (a rank's share)."""
+    _, dab, dc, B, M, N, K, epi, _ = WORKLOADS[w]
+    B = B if batch is None else batch
+    N = N if n is None else n
     es = 4 if dab == "f32" else 2
     os_ = 4 if dc == "f32" else 2
     flops = 2.0 * B * M * N * K
@@ -75,29 +103,25 @@ def algorithmic(w):
     return flops, byts
 
 
-def make_inputs_np(w, seed):
-    """Seeded synthetic inputs with the configuration's shapes and distributions (numpy, storage bits)."""
+# ---------------------------------------------------------------------------------------------- reference arm
+
+def make_inputs_np_small(w, rows):
+    """First `rows` of the (batch*M) rows of the workload's A, and the matching B (first batch), seeded."""
     import numpy as np
     from oracle import oracle as O
-    _, dab, dc, B, M, N, K, epi = WORKLOADS[w]
-    rng = np.random.default_rng(seed)
+    _, dab, dc, B, M, N, K, epi, _ = WORKLOADS[w]
+    rng = np.random.default_rng(1234)
+    rows = min(rows, M)
+    scale = 1.0 / np.sqrt(K) if w == "c2" else 1.0
     if w in ("c1", "c5a", "c5b", "c5c"):
-        a = rng.uniform(-1, 1, (B, M, K)).astype(np.float32)
-        b = rng.uniform(-1, 1, (B, K, N)).astype(np.float32)
-    elif w == "c2":
-        a = (rng.normal(size=(B, M, K)) / np.sqrt(K)).astype(np.float32)
-        b = (rng.normal(size=(B, K, N)) / np.sqrt(K)).astype(np.float32)
-    elif w == "c3":
-        a = rng.normal(size=(B, M, K)).astype(np.float32)
-        b = (rng.normal(size=(B, K, N)) * 0.02).astype(np.float32)
+        a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
+        b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
     else:
-        a = rng.normal(size=(B, M, K)).astype(np.float32)
-        b = rng.normal(size=(B, K, N)).astype(np.float32)
+        a = (rng.normal(size=(rows, K)) * scale).astype(np.float32)
+        b = (rng.normal(size=(K, N)) * (0.02 if w == "c3" else scale)).astype(np.float32)
     bias = (rng.normal(size=N) * 0.02).astype(np.float32) if epi else None
     return O.to_bits(a, dab), O.to_bits(b, dab), (O.to_bits(bias, dc) if bias is not None else None)
 
-
-# ---------------------------------------------------------------------------------------------- reference arm
 
 def run_reference(args):
     """The reference's CPU path (restated): scalar i/j/k nest, C re-loaded every k, k unrolled x8, ONE thread
@@ -105,16 +129,16 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    import numpy as np
     from oracle import oracle as O
     w = args.workload
     if w not in WORKLOADS:
         raise SystemExit("--impl reference times the contraction workloads only")
-    desc, dab, dc, B, M, N, K, epi = WORKLOADS[w]
-    # a bounded sample: one batch (c4: narrow K makes rows cheap) and a row slice sized for ~0.3 s per step
+    desc, dab, dc, B, M, N, K, epi, _ = WORKLOADS[w]
+    # a bounded sample: a row slice sized for ~0.3 s per step
     rows = max(1, min(M, int(2.0e8 / (2.0 * N * K))))
     a, b, bias = make_inputs_np_small(w, rows)
     flops = 2.0 * rows * N * K
+
     def step():
         O.gemm_scalar_rows(a, b, dtype_in=dab, dtype_out=dc, bias=bias, act="gelu_tanh" if epi else "none",
                            row_begin=0, row_end=rows)
@@ -130,7 +154,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "batch-matmul/linear TFLOPS", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": dab, "data": "synthetic (seeded)",
+        "scaling": "strong", "vs_baseline": None, "dtype": dab, "data": "synthetic (seeded)",
         "config": {"workload": f"{w}: {desc}", "sample": sample},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": 1, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -141,22 +165,24 @@ def run_reference(args):
     return 0
 
 
-def make_inputs_np_small(w, rows):
-    """First `rows` of the (batch*M) rows of the workload's A, and the matching B (first batch), seeded."""
-    import numpy as np
+def cpu_baseline(w, budget_s=12.0):
+    """The reference's single-threaded CPU nest on a bounded row sample of the same workload (about 10 s)."""
     from oracle import oracle as O
-    _, dab, dc, B, M, N, K, epi = WORKLOADS[w]
-    rng = np.random.default_rng(1234)
-    rows = min(rows, M)
-    scale = 1.0 / np.sqrt(K) if w == "c2" else 1.0
-    if w in ("c1", "c5a", "c5b", "c5c"):
-        a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
-        b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
-    else:
-        a = (rng.normal(size=(rows, K)) * scale).astype(np.float32)
-        b = (rng.normal(size=(K, N)) * (0.02 if w == "c3" else scale)).astype(np.float32)
-    bias = (rng.normal(size=N) * 0.02).astype(np.float32) if epi else None
-    return O.to_bits(a, dab), O.to_bits(b, dab), (O.to_bits(bias, dc) if bias is not None else None)
+    desc, dab, dc, B, M, N, K, epi, _ = WORKLOADS[w]
+    rows = max(1, min(M, int(1.0e8 / (2.0 * N * K)) or 1))
+    a, b, bias = make_inputs_np_small(w, rows)
+    done, t0 = 0, time.perf_counter()
+    while True:
+        O.gemm_scalar_rows(a, b, dtype_in=dab, dtype_out=dc, bias=bias, act="gelu_tanh" if epi else "none",
+                           row_begin=0, row_end=rows)
+        done += rows
+        el = time.perf_counter() - t0
+        if el > budget_s:
+            break
+    tflops = 2.0 * done * N * K / el / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+            "sample": f"{done} output rows (repeats of rows 0..{rows - 1}) of {B * M}, full N and K, {el:.1f} s; "
+                      "single-threaded scalar i/j/k nest as the reference's CPU pipeline emits it; extrapolates linearly"}
 
 
 # ---------------------------------------------------------------------------------------------- clocks
@@ -211,68 +237,125 @@ class ClockSampler(threading.Thread):
 
 # ---------------------------------------------------------------------------------------------- GPU arm
 
-def run_gpu(args):
-    import numpy as np
-    import torch
-    import torch.distributed as dist
-    from nova_compiler_b200 import _lib as L
-    from nova_compiler_b200 import ops
+class Ctx:
+    """Process-wide state of the GPU arm: rank layout, library handle, peaks."""
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        from nova_compiler_b200 import _lib as L
+        self.torch, self.dist, self.L = torch, dist, L
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lib = L.load()
-    L.check(lib.nova_b200_init(local))
+        torch.cuda.set_device(self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        self.lib = L.load()
+        L.check(self.lib.nova_b200_init(self.local))
+        self.peaks, self.peak_src = load_peaks()
+        self.args = args
 
-    w = args.workload
-    desc, dab, dc, B, M, N, K, epi = WORKLOADS[w]
-    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
-    flops, byts = algorithmic(w)
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
 
-    def dev(arr, dt):
-        t = torch.from_numpy(arr)
-        if dt != "f32":
-            t = t.view(torch.int16).view(tdt[dt])
-        return t.cuda()
+    def max_over_ranks(self, v):
+        t = self.torch.tensor([float(v)], device="cuda", dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    # Batch-index sharding: rank r owns global batches [r*B, (r+1)*B); its inputs come from seed 1234 + r.
-    a_np, b_np, bias_np = make_inputs_np(w, 1234 + rank)
+
+def _tdt(torch, name):
+    return {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[name]
+
+
+def make_inputs(ctx, w, batch_range=None):
+    """Seeded device inputs with the configuration's shapes and distributions.  Slab-partitioned workloads use
+    the same seed on every rank (A and B are replicated; a rank reads its slab of B as a strided view);
+    batch-partitioned ones draw only the rank's batches (seed offset by the first batch index)."""
+    torch = ctx.torch
+    _, dab, dc, B, M, N, K, epi, part = WORKLOADS[w]
+    first, count = batch_range if batch_range is not None else (0, B)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234 + first)
+    dt, dtc = _tdt(torch, dab), _tdt(torch, dc)
+
+    def uniform(shape):
+        return (torch.rand(shape, device="cuda", generator=g, dtype=torch.float32) * 2 - 1).to(dt)
+
+    def normal(shape, scale):
+        return (torch.randn(shape, device="cuda", generator=g, dtype=torch.float32) * scale).to(dt)
+
+    if w in ("c1", "c5a", "c5b", "c5c"):
+        a, b = uniform((count, M, K)), uniform((count, K, N))
+    elif w == "c2":
+        a, b = normal((count, M, K), K ** -0.5), normal((count, K, N), K ** -0.5)
+    elif w == "c3":
+        a, b = normal((count, M, K), 1.0), normal((count, K, N), 0.02)
+    else:
+        a, b = normal((count, M, K), 1.0), normal((count, K, N), 1.0)
+    bias = (torch.randn(N, device="cuda", generator=g, dtype=torch.float32) * 0.02).to(dtc) if epi else None
+    return a, b, bias
+
+
+def run_contraction(ctx, w, steps, warmup, headline=False):
+    """One contraction workload: device-resident timing (graph replay unless --no-graph), roofline record, and for
+    the headline the end-to-end and sustained legs."""
+    import numpy as np
+    from nova_compiler_b200 import ops, sharding
+    torch, L, lib, args = ctx.torch, ctx.L, ctx.lib, ctx.args
+    desc, dab, dc, B, M, N, K, epi, part = WORKLOADS[w]
+    world, rank = ctx.world, ctx.rank
+    if world > 1 and part is None:
+        return None  # this workload has no partition the north star names: single-GPU record only
+    # this rank's share of the global problem
+    b0, bcount, n0, ncount = 0, B, 0, N
+    if world > 1 and part == "batch":
+        b0, bcount = sharding.batch_range(B, world, rank)
+    if world > 1 and part == "slab":
+        n0, ncount = sharding.column_slab(N, world, rank)
+    g_flops, g_bytes = algorithmic(w)
+    r_flops, r_bytes = algorithmic(w, batch=bcount, n=ncount)
+
+    a0, b_full, bias_full = make_inputs(ctx, w, (b0, bcount))
     # Rotate over enough buffer sets that consecutive steps never find their operands in the 126 MB L2.
-    n_sets = max(2, min(8, int(np.ceil(3 * 140e6 / byts)) + 1))
+    n_sets = max(2, min(8, int(np.ceil(3 * 140e6 / max(r_bytes, 1))) + 1))
     sets = []
     for i in range(n_sets):
-        a = dev(a_np, dab) if i == 0 else sets[0][0].clone()
-        b = dev(b_np, dab) if i == 0 else sets[0][1].clone()
-        c = torch.empty((B, M, N), dtype=tdt[dc], device="cuda")
-        sets.append((a, b, c))
-    bias = dev(bias_np, dc) if bias_np is not None else None
+        a = a0 if i == 0 else a0.clone()
+        bf = b_full if i == 0 else b_full.clone()
+        bview = bf[:, :, n0:n0 + ncount]  # a column slab is a strided view: the row pitch stays N
+        c = torch.empty((bcount, M, ncount), dtype=_tdt(torch, dc), device="cuda")
+        sets.append((a, bview, c, bf))
+    bias = bias_full[n0:n0 + ncount].contiguous() if bias_full is not None else None
     act = "gelu" if epi else None
 
     def step(i):
-        a, b, c = sets[i % n_sets]
+        a, b, c, _ = sets[i % n_sets]
         ops.gemm(a, b, bias=bias, act=act, out=c)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    if bcount == 0 or ncount == 0:
+        def step(i):  # noqa: F811 - a rank that owns nothing still takes part in the barriers
+            return None
 
-    for i in range(max(args.warmup, 3)):
+    for i in range(max(warmup, 3)):
         step(i)
-    barrier()
-    # The launches of one pass over the buffer sets are captured into a CUDA graph and replayed: the host side
-    # of a call (argument checks, three tensor-map encodings, the launch) costs more than the smallest
-    # workloads' kernels.  EXACTLY args.steps steps run: whole replays, then the remainder as direct calls.
+    ctx.barrier()
+    # The launches of one pass over the buffer sets are captured into a CUDA graph and replayed; EXACTLY `steps`
+    # steps run: whole replays, then the remainder as direct calls.
     graph = None
-    if not args.no_graph:
+    if not args.no_graph and bcount and ncount:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(n_sets):
+                step(i)  # the capturing stream's scratch must exist before the capture
+        side.synchronize()
         with torch.cuda.stream(side):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
@@ -280,151 +363,188 @@ def run_gpu(args):
                     step(i)
         torch.cuda.current_stream().wait_stream(side)
         graph.replay()  # one untimed replay (n_sets more warm-up steps)
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    if graph is not None:
-        for _ in range(args.steps // n_sets):
-            graph.replay()
-        for i in range(args.steps % n_sets):
-            step(i)
-    else:
-        for i in range(args.steps):
-            step(i)
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+
+    def timed(n_steps, use_graph):
+        ctx.barrier()
+        sampler = ClockSampler(ctx.local)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx.barrier()
+        e0.record()
+        if use_graph and graph is not None:
+            for _ in range(n_steps // n_sets):
+                graph.replay()
+            for i in range(n_steps % n_sets):
+                step(i)
+        else:
+            for i in range(n_steps):
+                step(i)
+        e1.record()
+        ctx.barrier()
+        clocks = sampler.stop()
+        return ctx.max_over_ranks(e0.elapsed_time(e1)) / n_steps, clocks
+
+    ms_step, clocks = timed(steps, True)
     status = ops.device_status()
     if status != 0:
         raise SystemExit(f"device status 0x{status:x}: a bounded in-kernel wait gave up")
-    value = world * flops / (ms_step * 1e-3) / 1e12
-    per_gpu = flops / (ms_step * 1e-3) / 1e12
+    value = g_flops / (ms_step * 1e-3) / 1e12          # whole job: the global problem / the slowest rank
+    per_gpu = value / world
 
-    # ---- end to end through the host-buffer C-ABI entry point (pinned host memory)
+    peak, hbm = ctx.peaks["bf16_tflops"], ctx.peaks["hbm_gbs"]
+    bound = "tensor" if (g_flops / g_bytes) * hbm / 1e3 > peak else "hbm"
+    if bound == "tensor":
+        roof = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak}
+    else:
+        gbs = g_bytes / world / (ms_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm}
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get(w) if world == 1 else None,
+                 "peak_source": f"{ctx.peak_src} (cuBLAS bf16 burst / copy bandwidth), per GPU",
+                 "algorithmic_flops_per_launch": r_flops, "algorithmic_bytes_per_launch": r_bytes,
+                 "kernel_ms": ms_step, "frac_of_nominal_bf16_2250": per_gpu / NOMINAL_BF16_TFLOPS})
+
+    # how this rank's call is executed
+    ga = L.GemmArgs()
+    ga.struct_size = C.sizeof(L.GemmArgs)
+    code = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}
+    ga.dtype_ab, ga.dtype_c = code[dab], code[dc]
+    ga.batch, ga.M, ga.N, ga.K = max(bcount, 1), M, max(ncount, 1), K
+    ga.lda, ga.ldb, ga.ldc = K, N, max(ncount, 1)
+    ga.batch_stride_a, ga.batch_stride_b, ga.batch_stride_c = M * K, K * N, M * max(ncount, 1)
+    ga.A, ga.B, ga.C = sets[0][0].data_ptr(), sets[0][1].data_ptr(), sets[0][2].data_ptr()
+    info = L.GemmPlanInfo()
+    L.check(lib.nova_b200_gemm_plan(C.byref(ga), C.byref(info)))
+    launches_per_step = 2 if info.scratch_bytes > 0 else 1
+
+    rec = {
+        "workload": f"{w}: {desc}", "value": value, "unit": "TFLOP/s", "per_gpu": per_gpu, "ms_per_step": ms_step,
+        "steps": steps, "dtype": dab, "roofline": roof, "clocks": clocks, "gpu_launches": launches_per_step * steps,
+        "pct_of_bf16_dense_peak_nominal": 100.0 * per_gpu / NOMINAL_BF16_TFLOPS,
+        "plan": {"tile": [info.block_m, info.block_n, info.block_k], "stages": info.stages, "grid": info.grid,
+                 "tiles": info.tiles, "loader_a": info.loader_a, "loader_b": info.loader_b, "store_c": info.store_c,
+                 "repitch_bytes": int(info.scratch_bytes) if info.loader_a == 2 or info.loader_b == 2 else 0},
+        "l2": f"rotating {n_sets} buffer sets ({n_sets * r_bytes / 1e6:.0f} MB per rank) so operands never sit in L2",
+        "launch": "direct calls" if graph is None else f"CUDA graph of {n_sets} steps, replayed",
+    }
+    if world > 1:
+        rec["partition"] = ({"by": "batch index", "per_rank_batches": [sharding.batch_range(B, world, r)[1] for r in range(world)]}
+                            if part == "batch" else
+                            {"by": "N-column slabs (64-column aligned), A replicated",
+                             "per_rank_columns": [sharding.column_slab(N, world, r)[1] for r in range(world)]})
+    # host cost of a call: the same steps as direct calls (no graph).  Small problems are where it shows.
+    if graph is not None and (w in ("c1", "c5b") or headline) and world == 1:
+        ms_direct, _ = timed(min(steps, 200), False)
+        rec["no_graph_ms_per_step"] = ms_direct
+
+    # the optional exchange: all ranks end with the whole row-major C (NCCL all-gather + one re-interleave kernel)
+    if world > 1 and part == "slab" and not args.no_gather:
+        c_slab = sets[0][2][0]
+        full = sharding.gather_slabs(c_slab, N)  # warm-up (allocations, NCCL channels)
+        ctx.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            full = sharding.gather_slabs(c_slab, N, out=full)
+        e1.record()
+        ctx.barrier()
+        ag_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / reps
+        os_ = 4 if dc == "f32" else 2
+        recv_bytes = M * (N - ncount) * os_
+        rec["allgather_ms"] = ag_ms
+        rec["allgather"] = {"ms": ag_ms, "bytes_received_per_rank": recv_bytes,
+                            "gbs_per_rank": recv_bytes / (ag_ms * 1e-3) / 1e9,
+                            "nvlink_peer_copy_gbs_measured": 770.0,
+                            "how": "NCCL all_gather into [world, M, slab] staging + nova_b200_interleave_slabs; outside `value`"}
+        del full
+
+    if headline:
+        if not args.profile:
+            rec["e2e"] = run_e2e(ctx, w, sets[0], bias, (bcount, ncount), g_flops)
+        if world == 1 and not args.profile and not args.no_sustained and graph is not None:
+            rec["sustained"] = run_sustained(ctx, graph, n_sets, g_flops)
+    del sets, graph
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_e2e(ctx, w, set0, bias, share, g_flops):
+    """The same contraction through nova_b200_gemm_host: this rank's operands in pinned host memory, H2D + kernel +
+    D2H + sync inside the timed region, every step."""
+    torch, L, lib = ctx.torch, ctx.L, ctx.lib
+    desc, dab, dc, B, M, N, K, epi, part = WORKLOADS[w]
+    bcount, ncount = share
+    if bcount == 0 or ncount == 0:
+        ctx.barrier(); ctx.barrier()
+        ctx.max_over_ranks(0.0)
+        return None
+    a, bview, c, _ = set0
+    ha = a.cpu().pin_memory()
+    hb = bview.contiguous().cpu().pin_memory()   # the host side holds the rank's slab of B on its own
+    hc = torch.empty((bcount, M, ncount), dtype=c.dtype).pin_memory()
     g = L.GemmArgs()
     g.struct_size = C.sizeof(L.GemmArgs)
-    g.dtype_ab, g.dtype_c = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}[dab], {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}[dc]
-    g.batch, g.M, g.N, g.K = B, M, N, K
-    g.lda, g.ldb, g.ldc = K, N, N
-    g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = M * K, K * N, M * N
-    ha = torch.from_numpy(a_np).pin_memory()
-    hb = torch.from_numpy(b_np).pin_memory()
-    hc = torch.empty((B, M, N), dtype=torch.float32 if dc == "f32" else torch.int16).pin_memory()
+    code = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}
+    g.dtype_ab, g.dtype_c = code[dab], code[dc]
+    g.batch, g.M, g.N, g.K = bcount, M, ncount, K
+    g.lda, g.ldb, g.ldc = K, ncount, ncount
+    g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = M * K, K * ncount, M * ncount
     g.A, g.B, g.C = ha.data_ptr(), hb.data_ptr(), hc.data_ptr()
-    if bias_np is not None:
-        hbias = torch.from_numpy(bias_np).pin_memory()
+    h2d = ha.numel() * ha.element_size() + hb.numel() * hb.element_size()
+    if bias is not None:
+        hbias = bias.cpu().pin_memory()
         g.bias, g.init, g.act = hbias.data_ptr(), L.INIT_BIAS_ROW, L.ACT_GELU_TANH
-    e2e = None
-    if not args.profile:
-        e2e_steps = max(3, min(args.steps, 20))
-        for _ in range(2):
-            L.check(lib.nova_b200_gemm_host(C.byref(g)))
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            L.check(lib.nova_b200_gemm_host(C.byref(g)))
+        h2d += hbias.numel() * hbias.element_size()
+    d2h = hc.numel() * hc.element_size()
+    e2e_steps = max(3, min(ctx.args.steps, 10))
+    for _ in range(2):
+        L.check(lib.nova_b200_gemm_host(C.byref(g)))
+    ctx.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        L.check(lib.nova_b200_gemm_host(C.byref(g)))
+    torch.cuda.synchronize()
+    own_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    ctx.barrier()
+    e2e_ms = ctx.max_over_ranks(own_ms)
+    return {"value": g_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "pcie_gbs_this_rank": (h2d + d2h) / (own_ms * 1e-3) / 1e9,
+            "api": "nova_b200_gemm_host (pinned host buffers: H2D, kernel, D2H, sync every step); bytes are rank 0's share"}
+
+
+def run_sustained(ctx, graph, n_sets, g_flops, seconds=2.5):
+    """The headline launch looped for seconds (graph replays back to back) with the clocks sampled: the figure to
+    hold against the sustained cuBLAS peak, where the burst number is held against the burst peak."""
+    torch = ctx.torch
+    torch.cuda.synchronize()
+    sampler = ClockSampler(ctx.local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    n = 0
+    e0.record()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(50):
+            graph.replay()
+        n += 50 * n_sets
         torch.cuda.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-        e2e = {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "steps": e2e_steps,
-               "h2d_bytes_per_step": int(a_np.nbytes + b_np.nbytes + (bias_np.nbytes if bias_np is not None else 0)),
-               "d2h_bytes_per_step": int(hc.numel() * hc.element_size()),
-               "api": "nova_b200_gemm_host (pinned host buffers: H2D, kernel, D2H, sync every step)"}
-
-    line = None
-    if rank == 0:
-        peaks, src = load_peaks()
-        peak = peaks["bf16_tflops"]
-        hbm = peaks["hbm_gbs"]
-        ai = flops / byts
-        bound = "tensor" if ai * hbm / 1e3 > peak else "hbm"
-        if bound == "tensor":
-            roof = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak}
-        else:
-            gbs = byts / (ms_step * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm}
-        roof.update({"traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": f"{src} (cuBLAS bf16 burst / copy bandwidth)",
-                     "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": byts,
-                     "kernel_ms": ms_step, "frac_of_nominal_bf16_2250": per_gpu / NOMINAL_BF16_TFLOPS})
-        # the contraction, plus one launch when operands go through scratch first (the f32 hi/lo split, or the
-        # re-pitched copy of operands whose pitch no tensor map can describe)
-        info = L.GemmPlanInfo()
-        L.check(lib.nova_b200_gemm_plan(C.byref(g), C.byref(info)))
-        launches_per_step = 2 if info.scratch_bytes > 0 else 1
-        line = {
-            "metric": "batch-matmul/linear TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": dab, "data": "synthetic (seeded, shapes and distributions of the config)",
-            "config": {"workload": f"{w}: {desc}", "per_gpu_batch": B, "sharding": "batch index, no collective",
-                       "l2": f"rotating {n_sets} buffer sets ({n_sets * byts / 1e6:.0f} MB) so operands never sit in L2",
-                       "accumulate": "fp32",
-                       "launch": "direct calls" if graph is None else f"CUDA graph of {n_sets} steps, replayed"},
-            "impl": "nova_b200", "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-            "roofline": roof, "pct_of_bf16_dense_peak_nominal": 100.0 * per_gpu / NOMINAL_BF16_TFLOPS,
-        }
-        if world == 1 and not args.profile:
-            line["cpu_baseline"] = cpu_baseline(w)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    if line is not None:
-        print(json.dumps(line), flush=True)
-    return 0
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / n
+    tf = g_flops / (ms * 1e-3) / 1e12
+    peak = ctx.peaks["bf16_tflops_sustained"]
+    return {"value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": n, "seconds": e0.elapsed_time(e1) / 1e3,
+            "clocks": clocks, "peak": peak, "frac": tf / peak, "peak_source": f"{ctx.peak_src} (cuBLAS bf16, seconds-long loop)"}
 
 
-def cpu_baseline(w, budget_s=12.0):
-    """The reference's single-threaded CPU nest on a bounded row sample of the same workload (about 10 s)."""
-    from oracle import oracle as O
-    desc, dab, dc, B, M, N, K, epi = WORKLOADS[w]
-    rows = max(1, min(M, int(1.0e8 / (2.0 * N * K)) or 1))
-    a, b, bias = make_inputs_np_small(w, rows)
-    done, t0 = 0, time.perf_counter()
-    while True:
-        O.gemm_scalar_rows(a, b, dtype_in=dab, dtype_out=dc, bias=bias, act="gelu_tanh" if epi else "none",
-                           row_begin=0, row_end=rows)
-        done += rows
-        el = time.perf_counter() - t0
-        if el > budget_s:
-            break
-    tflops = 2.0 * done * N * K / el / 1e12
-    return {"value": tflops, "unit": "TFLOP/s", "cores": 1, "kind": "port",
-            "sample": f"{done} output rows (repeats of rows 0..{rows - 1}) of {B * M}, full N and K, {el:.1f} s; "
-                      "single-threaded scalar i/j/k nest as the reference's CPU pipeline emits it; extrapolates linearly"}
-
-
-# HBM-bound companions of the contraction: name -> (description, dtype, rows, D)
-ROW_WORKLOADS = {
-    "ln": ("nova.layer_norm bf16 [8192, 4096] (the rows that feed the C3 linear)", "bf16", 8192, 4096),
-    "softmax": ("nova.softmax f16 [65536, 2048] (attention-score rows, C4 layout, 32 of its 256 batches)", "f16", 65536, 2048),
-    "gather": ("nova.gather bf16 table [50304, 4096], 16384 i32 ids (embedding lookup)", "bf16", 16384, 4096),
-    "ln_bwd": ("nova.layer_norm_backward bf16 [8192, 4096] (dx, dgamma, dbeta from one read of gy and x)", "bf16", 8192, 4096),
-    "sce": ("nova.sce f32 logits [8192, 50304], i16 targets (softmax + mean loss; the vocabulary rows of ltest/test.mlir)", "f32", 8192, 50304),
-    "sce_bwd": ("nova.sce_backward f32 [8192, 50304]", "f32", 8192, 50304),
-}
-
-
-def run_rowop(args):
+def run_rowop(ctx, w, steps, warmup):
     """HBM roofline of the row-wise kernels: GB/s = (bytes read + bytes written) / event time."""
-    import torch
-    from nova_compiler_b200 import _lib as L
     from nova_compiler_b200 import ops
-    torch.cuda.set_device(0)
-    L.check(L.load().nova_b200_init(0))
-    w = args.workload
+    torch = ctx.torch
     desc, dt, rows, D = ROW_WORKLOADS[w]
-    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dt]
+    tdt = _tdt(torch, dt)
     es = 4 if dt == "f32" else 2
     g = torch.Generator(device="cuda")
     g.manual_seed(1234)
@@ -457,31 +577,90 @@ def run_rowop(args):
         beta = torch.randn(D, device="cuda", generator=g).to(tdt)
         byts = 2 * rows * D * 2 + (2 * D * 2 + 2 * rows * 2 if w == "ln" else 0)
         fn = (lambda i: ops.layer_norm(sets[i % n_sets], gamma, beta)) if w == "ln" else (lambda i: ops.softmax(sets[i % n_sets]))
-    for i in range(max(args.warmup, 3)):
+    for i in range(max(warmup, 3)):
         fn(i)
     torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(ctx.local)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
+    for i in range(steps):
         fn(i)
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
-    peaks, src = load_peaks()
+    ms = e0.elapsed_time(e1) / steps
     gbs = byts / (ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": "row-op HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": dt, "data": "synthetic (seeded)", "impl": "nova_b200", "clocks": clocks,
-        "gpu_launches": args.steps * {"ln_bwd": 2, "sce": 2}.get(w, 1),  # ln_bwd: + column-sum finish; sce: + loss kernel
-        "config": {"workload": f"{w}: {desc}", "l2": f"rotating {n_sets} input sets; outputs are fresh allocations"},
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                     "traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": src, "algorithmic_bytes_per_launch": byts,
-                     "frac_of_nominal_8000": gbs / 8000.0},
-    }), flush=True)
+    del sets
+    torch.cuda.empty_cache()
+    return {
+        "workload": f"{w}: {desc}", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "steps": steps, "dtype": dt,
+        "clocks": clocks, "gpu_launches": steps * {"ln_bwd": 2, "sce": 2}.get(w, 1),  # + column-sum finish / loss kernel
+        "l2": f"rotating {n_sets} input sets; outputs are fresh allocations",
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": ctx.peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / ctx.peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": ctx.peak_src,
+                     "algorithmic_bytes_per_launch": byts, "frac_of_nominal_8000": gbs / 8000.0},
+    }
+
+
+def run_gpu(args):
+    ctx = Ctx(args)
+    head = args.workload
+    if head in ROW_WORKLOADS:
+        rec = run_rowop(ctx, head, args.steps or 100, args.warmup if args.warmup is not None else 5)
+        line = {"metric": "row-op HBM GB/s", "value": rec["value"], "unit": "GB/s", "n_gpus": 1, "steps": rec["steps"],
+                "warmup": max(args.warmup or 5, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": rec["dtype"], "data": "synthetic (seeded)",
+                "impl": "nova_b200", "clocks": rec["clocks"], "gpu_launches": rec["gpu_launches"],
+                "config": {"workload": rec["workload"], "l2": rec["l2"]}, "roofline": rec["roofline"]}
+        print(json.dumps(line), flush=True)
+        return 0
+    steps = args.steps or SUB_STEPS[head]
+    warmup = args.warmup if args.warmup is not None else 10
+    rec = run_contraction(ctx, head, steps, warmup, headline=True)
+    subs = {}
+    if not args.only and not args.profile:
+        for s in DEFAULT_SUBS:
+            if s == head:
+                continue
+            if s in WORKLOADS:
+                r = run_contraction(ctx, s, SUB_STEPS[s], 5)
+            elif ctx.world == 1:
+                r = run_rowop(ctx, s, 60, 5)
+            else:
+                r = None  # row kernels are per-row independent: no multi-GPU partition is reported for them
+            if r is not None:
+                subs[s] = r
+    line = None
+    if ctx.rank == 0:
+        desc = WORKLOADS[head][0]
+        part = WORKLOADS[head][8]
+        line = {
+            "metric": "batch-matmul/linear TFLOPS", "value": rec["value"], "unit": "TFLOP/s", "n_gpus": ctx.world,
+            "steps": steps, "warmup": max(warmup, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": rec["dtype"],
+            "data": "synthetic (seeded, shapes and distributions of the config)",
+            "config": {"workload": f"{head}: {desc}",
+                       "partition": ("one GPU" if ctx.world == 1 else
+                                     ("batch index, no collective" if part == "batch" else
+                                      "N-column slabs of the one global GEMM, A replicated, no collective")),
+                       "l2": rec["l2"], "accumulate": "fp32", "launch": rec["launch"]},
+            "impl": "nova_b200", "clocks": rec["clocks"], "e2e": rec.get("e2e"), "gpu_launches": rec["gpu_launches"],
+            "roofline": rec["roofline"], "pct_of_bf16_dense_peak_nominal": rec["pct_of_bf16_dense_peak_nominal"],
+            "per_gpu": rec["per_gpu"], "plan": rec["plan"],
+        }
+        for k in ("sustained", "allgather_ms", "allgather", "partition", "no_graph_ms_per_step"):
+            if k in rec:
+                line[k] = rec[k]
+        if subs:
+            line["workloads"] = subs
+        if ctx.world == 1 and not args.profile and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(head)
+    if ctx.world > 1:
+        ctx.dist.barrier()
+        ctx.dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
     return 0
 
 
@@ -490,11 +669,15 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(ROW_WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + sorted(ROW_WORKLOADS))
     ap.add_argument("--impl", default="nova_b200", choices=["nova_b200", "reference"])
+    ap.add_argument("--only", action="store_true", help="the headline workload only: no `workloads` sub-records")
     ap.add_argument("--no-graph", action="store_true", help="launch every step with a direct call instead of replaying a CUDA graph")
+    ap.add_argument("--no-gather", action="store_true", help="skip the (separately timed) all-gather of slab-partitioned outputs")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the seconds-long sustained loop of the headline")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profile", action="store_true",
-                    help="device-resident leg only (no end-to-end leg, no CPU baseline): for captures under ncu")
+                    help="device-resident leg of the headline only (no sub-records, end-to-end leg or CPU baseline): for captures under ncu")
     args = ap.parse_args()
     if args.profile:
         args.no_graph = True  # captures under ncu see plain kernel launches
@@ -502,12 +685,6 @@ def main():
         args.steps = args.steps or 10
         args.warmup = args.warmup if args.warmup is not None else 1
         return run_reference(args)
-    if args.workload in ROW_WORKLOADS:
-        args.steps = args.steps or 100
-        args.warmup = args.warmup if args.warmup is not None else 5
-        return run_rowop(args)
-    args.steps = args.steps or (1000 if args.workload in ("c1", "c2", "c5b") else 200)
-    args.warmup = args.warmup if args.warmup is not None else 10
     return run_gpu(args)
 
 

@@ -298,6 +298,16 @@ int32_t nova_b200_gather(const void* in_dev, const void* idx_dev, void* out_dev,
                          int64_t post, int64_t n_idx, int32_t idx_dtype, int32_t batched_idx, int32_t elem_bytes,
                          int64_t* bad_count_dev, void* stream);
 
+/* Multi-GPU, single large GEMM split by N-column slabs: after the ranks' output slabs have been all-gathered into
+ * staging_dev = [world, rows, slab_pitch] (slab r in staging[r], its first width(r) columns valid), writes the
+ * row-major [rows, cols] matrix to out_dev.  The slabs are the partition used throughout: whole `align`-column
+ * units dealt out contiguously over the ranks, the first (units mod world) ranks one unit more, the ragged
+ * remainder in the last non-empty slab.  16-byte copies when every boundary allows, element copies otherwise.
+ * No counterpart in the reference, which has no multi-device code (its #nova.device attribute only separates
+ * host from GPU: lib/Transforms/RemDevAttr.cpp:33-41). */
+int32_t nova_b200_interleave_slabs(const void* staging_dev, void* out_dev, int64_t rows, int64_t cols, int32_t world,
+                                   int64_t slab_pitch, int64_t align, int32_t elem_bytes, void* stream);
+
 /* Reads (and clears) the device-side status words of the current device (the allocated one and, once
  * nova_b200_gemm_f32_static has run there, the one inside its static array): 0 when every bounded wait inside the
  * kernels completed; otherwise a code naming the wait that gave up.  Synchronises the device. */

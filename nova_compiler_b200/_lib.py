@@ -93,6 +93,8 @@ PROTOTYPES = {
     "nova_b200_softmax": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_gather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                      C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "nova_b200_interleave_slabs": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64, C.c_int64,
+                                               C.c_int32, C.c_void_p]),
     "nova_b200_device_status": (C.c_int32, [C.POINTER(C.c_uint32)]),
     "nova_b200_module_parse": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "nova_b200_module_free": (None, [C.c_void_p]),

@@ -53,6 +53,26 @@ __device__ __forceinline__ float row_reduce(float v, float* red_smem) {
   return kMax ? warp_max(r) : warp_sum(r);
 }
 
+// Two values at once, ONE barrier per call: the exchange buffer alternates between calls (`phase`), so a warp
+// writes buffer b only after every thread has passed the barrier of the call before, i.e. after all readers of
+// the call before that (the last user of b) are done.  Lowers the barriers of a layer_norm row from four to one.
+template <int TPR, bool kMax>
+__device__ __forceinline__ void row_reduce2(float& a, float& b, float2 (*red_smem)[8], uint32_t& phase) {
+  a = kMax ? warp_max(a) : warp_sum(a);
+  b = kMax ? warp_max(b) : warp_sum(b);
+  if (TPR == 32) return;
+  constexpr int kWarpsPerRow = TPR / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = (warp / kWarpsPerRow) * kWarpsPerRow;
+  float2* buf = red_smem[phase & 1u];
+  ++phase;
+  if (lane == 0) buf[warp] = make_float2(a, b);
+  __syncthreads();
+  const float2 r = lane < kWarpsPerRow ? buf[first + lane] : (kMax ? make_float2(-INFINITY, -INFINITY) : make_float2(0.0f, 0.0f));
+  a = kMax ? warp_max(r.x) : warp_sum(r.x);
+  b = kMax ? warp_max(r.y) : warp_sum(r.y);
+}
+
 constexpr int kRowThreads = 256;
 constexpr int kLongUnroll = 8;  // vectors a thread keeps in flight when a row is too long for its registers
 
@@ -64,7 +84,9 @@ __global__ void __launch_bounds__(kRowThreads, (VEC > 1 && kMaxV > 0 && kMaxV <=
 row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
            T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t prefetch_next,
            float* __restrict__ row_stats) {  // softmax only, optional: {row max, sum of exp(x - max)} per row
-  __shared__ float red[kRowThreads / 32];
+  __shared__ float2 red2[2][8];
+  static_assert(kRowThreads / 32 == 8, "exchange buffer size");
+  uint32_t red_phase = 0;
   constexpr int kRowsPerCta = kRowThreads / TPR;
   constexpr bool CACHED = kMaxV > 0;
   const int t = threadIdx.x % TPR;
@@ -138,8 +160,8 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
     }
 
     if (kMode == 0) {
-      const float sum = row_reduce<TPR, false>(s0, red);
-      const float sq = row_reduce<TPR, false>(s1, red);
+      row_reduce2<TPR, false>(s0, s1, red2, red_phase);
+      const float sum = s0, sq = s1;
       const float mean = sum * inv_d;
       const float var = sq * inv_d - mean * mean;
       const float rstd = rsqrtf(var + 1e-5f);
@@ -175,7 +197,8 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
         }
       }
     } else {
-      const float m = row_reduce<TPR, true>(s0, red);
+      float m = s0, m_dup = s0;
+      row_reduce2<TPR, true>(m, m_dup, red2, red_phase);
       float part = 0.0f;
       if (!CACHED) part = s0 == -INFINITY ? 0.0f : s1 * __expf(s0 - m);  // this thread's sum, rescaled to the row max
       if (CACHED) {
@@ -188,7 +211,8 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
           }
         }
       }
-      const float s = row_reduce<TPR, false>(part, red);
+      float s = part, s_dup = 0.0f;
+      row_reduce2<TPR, false>(s, s_dup, red2, red_phase);
       if (row_stats != nullptr && active && t == 0) { row_stats[2 * row] = m; row_stats[2 * row + 1] = s; }
       const float recip = 1.0f / fmaxf(s, 1.0e-7f);
       auto emit = [&](int i, const P& in) {
@@ -293,9 +317,11 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
   const int64_t nvec = D / VEC;
   // Measured on B200: rows handled by one warp (no CTA-wide barrier) run best as many short-lived CTAs;
   // rows that need the whole CTA run best as persistent CTAs that prefetch their next row into L2.
-  auto launch_grid = [&](int tpr, int max_v) {
+  // `resident`: CTAs of the chosen instance that fit on one SM.  A persistent grid larger than sm_count * resident
+  // runs as one full wave plus a tail wave that starts late and walks as many rows per CTA.
+  auto launch_grid = [&](int tpr, int max_v, int resident) {
     const int64_t ctas = (rows * tpr + kRowThreads - 1) / kRowThreads;
-    int64_t cap = static_cast<int64_t>(sm_count) * (tpr == 32 ? 32 : 8);
+    int64_t cap = static_cast<int64_t>(sm_count) * (tpr == 32 ? 32 : std::max(1, std::min(resident, 8)));
     if (max_v == 0) {
       // rows too long for registers are read twice: keep the rows in flight within ~64 MB so that the second
       // read finds them in L2 (126 MB) instead of HBM
@@ -304,9 +330,18 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     }
     return static_cast<int>(ctas < cap ? ctas : cap);
   };
-#define NOVA_ROW(TPR_, MAXV_)                                                                             \
-  row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_, MAXV_), kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, \
-                                                                                     d, (TPR_) == 32 ? 0 : 1, stats)
+#define NOVA_ROW(TPR_, MAXV_)                                                                                        \
+  do {                                                                                                               \
+    static int resident_ = 0; /* same on every device this library runs on (one architecture) */                     \
+    if (resident_ == 0 &&                                                                                            \
+        (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_, row_kernel<T, VEC, TPR_, MAXV_, kMode>, kRowThreads, 0) != \
+             cudaSuccess || resident_ <= 0)) {                                                                       \
+      cudaGetLastError();                                                                                            \
+      resident_ = 4;                                                                                                 \
+    }                                                                                                                \
+    row_kernel<T, VEC, TPR_, MAXV_, kMode><<<launch_grid(TPR_, MAXV_, resident_), kRowThreads, 0, st>>>(             \
+        xp, gp, bp, yp, mp, rp, rows, d, (TPR_) == 32 ? 0 : 1, stats);                                               \
+  } while (0)
   // Vectors a thread keeps in registers are kept few (occupancy sets the bytes in flight per SM):
   // longer rows get more threads, not more registers.
   constexpr int kWarpMv = VEC == 1 ? 32 : (kMode == 0 ? 4 : 8);
@@ -619,7 +654,8 @@ __global__ void __launch_bounds__(kMaxThreads)
 ln_backward_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
                         float* __restrict__ partial, int64_t rows, int32_t D) {
-  __shared__ float red[2 * kRowsPer][kMaxThreads / 32];
+  __shared__ float red[2][2 * kRowsPer][kMaxThreads / 32];  // exchange buffer, alternating per trip: one barrier per trip
+  uint32_t trip = 0;
   using P = Pack<T, VEC>;
   const int nvec = D / VEC;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -675,14 +711,17 @@ ln_backward_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const
       s[2 * k + 1] = warp_sum(s2);
     }
     if (nwarps > 1) {
-      __syncthreads();  // the previous trip's readers are done with red
+      // (a warp writes this buffer again two trips on, after the barrier of the trip in between: by then every
+      // reader of this trip is done)
+      float (*buf)[kMaxThreads / 32] = red[trip & 1u];
+      ++trip;
       if (lane == 0) {
 #pragma unroll
-        for (int j = 0; j < 2 * kRowsPer; ++j) red[j][warp] = s[j];
+        for (int j = 0; j < 2 * kRowsPer; ++j) buf[j][warp] = s[j];
       }
       __syncthreads();
 #pragma unroll
-      for (int j = 0; j < 2 * kRowsPer; ++j) s[j] = warp_sum(lane < nwarps ? red[j][lane] : 0.0f);
+      for (int j = 0; j < 2 * kRowsPer; ++j) s[j] = warp_sum(lane < nwarps ? buf[j][lane] : 0.0f);
     }
 #pragma unroll
     for (int k = 0; k < kRowsPer; ++k) {
@@ -842,6 +881,36 @@ int grid_for(int64_t work_items, int threads, int sm_count) {
 }  // namespace nova
 
 using namespace nova;
+
+// ---------------------------------------------------------------- multi-GPU: re-interleave all-gathered column slabs
+//
+// After an all-gather every rank holds the ranks' output slabs one after the other, staging[r] = [rows, wmax] with
+// the first width(r) columns valid.  This kernel writes the row-major [rows, cols] matrix: one thread per 16-byte
+// chunk of the output (element-wise when a slab boundary or the row pitch is not 16-byte aligned), reads and writes
+// both coalesced along rows.
+struct SlabLayout {
+  int32_t world;
+  int64_t start[17];  // slab r covers columns [start[r], start[r + 1])
+};
+
+template <int kUnitBytes>
+__global__ void interleave_slabs_kernel(const uint8_t* __restrict__ staging, uint8_t* __restrict__ out, int64_t rows,
+                                        int64_t units_per_row, int64_t wmax_units, SlabLayout lay) {
+  // everything is counted in units of kUnitBytes (16-byte chunks, or single elements)
+  const int64_t n = rows * units_per_row;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / units_per_row;
+    const int64_t c = i - row * units_per_row;
+    int r = 0;
+    while (r + 1 < lay.world && c >= lay.start[r + 1]) ++r;
+    const uint8_t* src = staging + ((static_cast<int64_t>(r) * rows + row) * wmax_units + (c - lay.start[r])) * kUnitBytes;
+    uint8_t* dst = out + i * kUnitBytes;
+    if (kUnitBytes == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    else if (kUnitBytes == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+    else *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<const uint16_t*>(src);
+  }
+}
 
 extern "C" {
 
@@ -1192,6 +1261,51 @@ int32_t nova_b200_add_rowbcast(const void* a, const void* b, void* out, int64_t 
   else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_ADD(__half, 8); else NOVA_ADD(__half, 1); }
   else { if (vec_ok) NOVA_ADD(__nv_bfloat16, 8); else NOVA_ADD(__nv_bfloat16, 1); }
 #undef NOVA_ADD
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_interleave_slabs(const void* staging, void* out, int64_t rows, int64_t cols, int32_t world,
+                                   int64_t slab_pitch, int64_t align, int32_t elem_bytes, void* stream) {
+  if (rows < 0 || cols < 0 || world < 1 || world > 16 || align < 1 || slab_pitch < 0)
+    return fail(NOVA_B200_ERR_INVALID_ARG, "interleave_slabs: bad extent (1 <= world <= 16)");
+  if (elem_bytes != 2 && elem_bytes != 4) return fail(NOVA_B200_ERR_UNSUPPORTED, "interleave_slabs: 2- or 4-byte elements");
+  if (rows == 0 || cols == 0) return NOVA_B200_OK;
+  if (!staging || !out) return fail(NOVA_B200_ERR_INVALID_ARG, "interleave_slabs: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, staging, "interleave_slabs: the staging buffer")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, out, "interleave_slabs: the output")) != NOVA_B200_OK) return st;
+  // the partition of nova_compiler_b200/sharding.py column_slab: whole `align`-column units dealt out contiguously,
+  // the first (units % world) ranks one unit more, the last non-empty slab takes the ragged remainder
+  SlabLayout lay{};
+  lay.world = world;
+  const int64_t units = (cols + align - 1) / align, base = units / world, extra = units % world;
+  int64_t widest = 0;
+  for (int r = 0; r <= world; ++r) {
+    const int64_t u = r * base + std::min<int64_t>(r, extra);
+    lay.start[r] = std::min<int64_t>(u * align, cols);
+    if (r > 0) widest = std::max(widest, lay.start[r] - lay.start[r - 1]);
+  }
+  if (slab_pitch < widest) return fail(NOVA_B200_ERR_LAYOUT, "interleave_slabs: slab_pitch is narrower than the widest slab");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int per = 16 / elem_bytes;
+  bool vec = (reinterpret_cast<uintptr_t>(staging) | reinterpret_cast<uintptr_t>(out)) % 16 == 0 && cols % per == 0 &&
+             slab_pitch % per == 0;
+  for (int r = 0; r <= world && vec; ++r) vec = lay.start[r] % per == 0;
+  if (vec) {
+    for (int r = 0; r <= world; ++r) lay.start[r] /= per;
+    const int64_t n = rows * (cols / per);
+    interleave_slabs_kernel<16><<<grid_for(n, 256, ctx->sm_count), 256, 0, s>>>(
+        static_cast<const uint8_t*>(staging), static_cast<uint8_t*>(out), rows, cols / per, slab_pitch / per, lay);
+  } else if (elem_bytes == 4) {
+    interleave_slabs_kernel<4><<<grid_for(rows * cols, 256, ctx->sm_count), 256, 0, s>>>(
+        static_cast<const uint8_t*>(staging), static_cast<uint8_t*>(out), rows, cols, slab_pitch, lay);
+  } else {
+    interleave_slabs_kernel<2><<<grid_for(rows * cols, 256, ctx->sm_count), 256, 0, s>>>(
+        static_cast<const uint8_t*>(staging), static_cast<uint8_t*>(out), rows, cols, slab_pitch, lay);
+  }
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }

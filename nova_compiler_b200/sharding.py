@@ -73,23 +73,39 @@ def slab_matmul(a: torch.Tensor, b: torch.Tensor, rank: int, world: int,
     return matmul_fn(a, b[:, start:start + count], **kw), (start, count)
 
 
-def gather_slabs(c_slab: torch.Tensor, n: int, group=None) -> torch.Tensor:
+def gather_slabs(c_slab: torch.Tensor, n: int, group=None, out: Optional[torch.Tensor] = None,
+                 align: int = 64) -> torch.Tensor:
     """All-gathers the ranks' column slabs into the full row-major [M, N] matrix on every rank.
-    Slabs may have different widths (ragged N): they are padded to the widest for the collective."""
+
+    Transport: ONE all-gather (NCCL over NVLink on GPUs, gloo on CPU) into a [world, M, widest] staging buffer;
+    slabs narrower than the widest (ragged N) are padded for the collective.  On GPUs the staging is then
+    re-interleaved into [M, N] by one kernel of the library (nova_b200_interleave_slabs); CPU ranks, which only
+    exercise the partition logic, copy the column blocks with torch.  `out` reuses a previous result's storage."""
     world = dist.get_world_size(group)
     m = c_slab.shape[0]
-    widths = [column_slab(n, world, r)[1] for r in range(world)]
+    widths = [column_slab(n, world, r, align)[1] for r in range(world)]
     wmax = max(widths) if widths else 0
     send = c_slab
-    if c_slab.shape[1] != wmax:
+    if c_slab.shape[1] != wmax or not c_slab.is_contiguous():
         send = c_slab.new_zeros((m, wmax))
         send[:, :c_slab.shape[1]] = c_slab
-    send = send.contiguous()
-    recv: List[torch.Tensor] = [torch.empty_like(send) for _ in range(world)]
-    dist.all_gather(recv, send, group=group)
-    out = c_slab.new_empty((m, n))
+    staging = c_slab.new_empty((world, m, wmax))
+    if c_slab.is_cuda:
+        dist.all_gather_into_tensor(staging, send, group=group)
+    else:
+        dist.all_gather(list(staging.unbind(0)), send, group=group)
+    if out is None:
+        out = c_slab.new_empty((m, n))
+    if c_slab.is_cuda:
+        from . import _lib as L
+        with torch.cuda.device(c_slab.device):
+            L.check(L.load().nova_b200_interleave_slabs(staging.data_ptr(), out.data_ptr(), m, n, world, wmax, align,
+                                                        c_slab.element_size(),
+                                                        torch.cuda.current_stream().cuda_stream))
+        staging.record_stream(torch.cuda.current_stream())
+        return out
     for r in range(world):
-        start, count = column_slab(n, world, r)
+        start, count = column_slab(n, world, r, align)
         if count:
-            out[:, start:start + count] = recv[r][:, :count]
+            out[:, start:start + count] = staging[r][:, :count]
     return out

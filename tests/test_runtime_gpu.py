@@ -1,0 +1,256 @@
+"""Runtime behaviour around the contraction, on a GPU through the C ABI: per-stream scratch (two streams at once),
+graph capture of scratch users, plan cache / launch-mode / prefetch invariance, bytes around an output survive,
+prepared operands, the rank-4 and dynamic-argument entry points, the slab re-interleave kernel."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from test_gemm_gpu import TOL, _tdt, check, rand_bits, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def _gemm_args(L, a, b, c, **kw):
+    g = L.GemmArgs()
+    g.struct_size = C.sizeof(L.GemmArgs)
+    code = {4: L.F32}
+    import torch
+    dt = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+    g.dtype_ab, g.dtype_c = dt[a.dtype], dt[c.dtype]
+    g.batch, g.M, g.K = a.shape
+    g.N = b.shape[2]
+    g.A, g.B, g.C = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    g.lda, g.ldb, g.ldc = a.stride(1), b.stride(1), c.stride(1)
+    g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = a.stride(0), b.stride(0), c.stride(0)
+    for k, v in kw.items():
+        setattr(g, k, v)
+    return g
+
+
+def test_two_streams_run_scratch_users_concurrently(cuda, oracle):
+    """Scratch is per (device, stream): two f32 contractions (hi/lo split in scratch) and two re-pitched bf16
+    ones, enqueued alternately on two streams without any synchronisation between them, all match the oracle."""
+    torch = cuda
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(7)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    cases = []
+    for i, (M, N, K) in enumerate([(384, 512, 640), (512, 384, 768), (300, 333, 257), (203, 141, 275)]):
+        dt = "f32" if i < 2 else "bf16"
+        a = rand_bits(oracle, rng, (1, M, K), dt)
+        b = rand_bits(oracle, rng, (1, K, N), dt)
+        cases.append((dt, a, b, to_dev(torch, a, dt), to_dev(torch, b, dt)))
+    torch.cuda.synchronize()
+    outs = [None] * len(cases)
+    for rep in range(3):  # several rounds in flight on both streams
+        for i, (dt, a, b, ta, tb) in enumerate(cases):
+            with torch.cuda.stream(s1 if i % 2 == 0 else s2):
+                outs[i] = ops.gemm(ta, tb)
+    torch.cuda.synchronize()
+    for (dt, a, b, ta, tb), out in zip(cases, outs):
+        check(oracle, to_host(torch, out, dt), oracle.gemm(a, b, dtype_in=dt), dt)
+    assert ops.device_status() == 0
+
+
+def test_scratch_users_capture_into_a_graph_and_survive_growth(cuda, oracle):
+    """A captured f32 contraction keeps working after a LARGER scratch request on the same stream: growing never
+    frees the buffer the graph holds.  Growth during capture is refused with a clear error instead."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    rng = np.random.default_rng(8)
+    a = rng.uniform(-1, 1, (1, 256, 320)).astype(np.float32)
+    b = rng.uniform(-1, 1, (1, 320, 192)).astype(np.float32)
+    ta, tb = to_dev(torch, a, "f32"), to_dev(torch, b, "f32")
+    out = torch.empty(1, 256, 192, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ops.gemm(ta, tb, out=out)  # the stream's scratch exists before the capture
+    side.synchronize()
+    big_a = torch.zeros(1, 1024, 1024, device="cuda")
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            ops.gemm(ta, tb, out=out)
+            with pytest.raises(L.NovaB200Error) as ei:  # 16 MiB of split buffers: more than the stream owns
+                ops.gemm(big_a, big_a)
+            assert "captured" in str(ei.value)
+    out.zero_()
+    with torch.cuda.stream(side):
+        ops.gemm(big_a, big_a)  # grows the stream's scratch: the graph's buffer must stay alive
+    side.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    check(oracle, to_host(torch, out, "f32"), oracle.gemm(a, b), "f32")
+
+
+def test_launch_modes_and_prefetch_do_not_change_the_result(cuda, oracle):
+    """Plan cache on/off, programmatic dependent launch on/off and the pair kernel's L2 prefetch cursor are
+    scheduling choices: the output bits are the same."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    rng = np.random.default_rng(9)
+    a = to_dev(torch, rand_bits(oracle, rng, (2, 512, 1024), "bf16"), "bf16")
+    b = to_dev(torch, rand_bits(oracle, rng, (2, 1024, 768), "bf16"), "bf16")
+    base = ops.gemm(a, b, act="gelu")
+    torch.cuda.synchronize()
+    info = L.GemmPlanInfo()
+    for opt, val, restore in [("plan_cache", 0, 1), ("pdl", 0, 1), ("prefetch", 3, -1), ("prefetch", 11, -1), ("pair", 0, -1)]:
+        L.set_option(opt, val)
+        try:
+            got = ops.gemm(a, b, act="gelu")
+            got2 = ops.gemm(a, b, act="gelu")  # back to back: the second launch's prologue overlaps the first
+            torch.cuda.synchronize()
+        finally:
+            L.set_option(opt, restore)
+        assert torch.equal(got, base) and torch.equal(got2, base), opt
+    assert L.get_option("prefetch") == -1 and L.get_option("pdl") == 1
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+def test_bytes_around_the_output_survive(cuda, oracle, dt):
+    """C is a window of a larger buffer (ldc > N, rows past M, a gap between batches): every byte outside the
+    window keeps its sentinel.  Ragged extents and an unaligned pitch take the element-store path, aligned ones
+    the TMA-store path."""
+    torch = cuda
+    from nova_compiler_b200 import ops
+    rng = np.random.default_rng(10)
+    for (Bn, M, N, K, ldc, rows_alloc) in [(2, 200, 328, 264, 384, 256), (2, 130, 77, 100, 83, 140), (1, 256, 256, 256, 320, 300)]:
+        a = rand_bits(oracle, rng, (Bn, M, K), dt)
+        b = rand_bits(oracle, rng, (Bn, K, N), dt)
+        buf = torch.full((Bn, rows_alloc, ldc), -7.0, device="cuda", dtype=_tdt(torch, dt))
+        window = buf[:, :M, :N]
+        ops.gemm(to_dev(torch, a, dt), to_dev(torch, b, dt), out=window)
+        torch.cuda.synchronize()
+        check(oracle, to_host(torch, window, dt), oracle.gemm(a, b, dtype_in=dt), dt)
+        mask = torch.ones_like(buf, dtype=torch.bool)
+        mask[:, :M, :N] = False
+        assert torch.all(buf[mask] == -7.0), f"bytes outside the {M}x{N} window of a {rows_alloc}x{ldc} buffer changed"
+
+
+def test_prepared_operand_skips_the_per_call_copy(cuda, oracle, lib):
+    """A weight with an unaligned pitch, prepared once: the call plans as plain TMA (no scratch) and gives the same
+    bits as the default per-call re-pitch."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    rng = np.random.default_rng(11)
+    M, N, K = 320, 527, 448   # B [K, N]: pitch 1054 B, not a multiple of 16
+    a = to_dev(torch, rand_bits(oracle, rng, (1, M, K), "bf16"), "bf16")
+    bh = rand_bits(oracle, rng, (1, K, N), "bf16")
+    b = to_dev(torch, bh, "bf16")
+    want = ops.gemm(a, b)
+    handle = C.c_void_p()
+    L.check(lib.nova_b200_operand_prepare(b.data_ptr(), L.BF16, 1, K, N, N, 0, None, C.byref(handle)))
+    data, ld, bs = C.c_void_p(), C.c_int64(), C.c_int64()
+    L.check(lib.nova_b200_operand_view(handle, C.byref(data), C.byref(ld), C.byref(bs)))
+    assert ld.value == 528 and data.value % 16 == 0
+    out = torch.empty(1, M, N, device="cuda", dtype=torch.bfloat16)
+    g = _gemm_args(L, a, b, out)
+    g.B, g.ldb, g.batch_stride_b = data.value, ld.value, 0
+    info = L.GemmPlanInfo()
+    L.check(lib.nova_b200_gemm_plan(C.byref(g), C.byref(info)))
+    assert (info.loader_b, info.scratch_bytes) == (0, 0)
+    L.check(lib.nova_b200_gemm(C.byref(g), None))
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    lib.nova_b200_operand_free(handle)
+
+
+def test_rank4_descriptor_entry_point(cuda, oracle, lib):
+    """nova.matmul on rank-4 operands = collapse the batch dims, batch_matmul, expand (NovaToLinalg.cpp:904-989):
+    contiguous operands collapse as metadata; a B that broadcasts along one batch dim walks the outer dim."""
+    torch = cuda
+    from nova_compiler_b200 import _lib as L
+    rng = np.random.default_rng(12)
+
+    def desc(t):
+        d = L.MemRef4D()
+        d.allocated = d.aligned = t.data_ptr()
+        d.offset = 0
+        for i in range(4):
+            d.sizes[i], d.strides[i] = t.shape[i], t.stride(i)
+        return d
+
+    for bshape in [(2, 3), (1, 1), (1, 3), (2, 1)]:
+        ah = rand_bits(oracle, rng, (2, 3, 64, 96), "f16")
+        bh = rand_bits(oracle, rng, bshape + (96, 80), "f16")
+        a, b = to_dev(torch, ah, "f16"), to_dev(torch, bh, "f16")
+        c = torch.zeros(2, 3, 64, 80, device="cuda", dtype=torch.float16)
+        L.check(lib._mlir_ciface_nova_b200_batch_matmul_4d(C.byref(desc(c)), C.byref(desc(a)), C.byref(desc(b)), L.F16, L.F16))
+        torch.cuda.synchronize()
+        bb = np.broadcast_to(bh, (2, 3, 96, 80)).reshape(6, 96, 80)
+        want = oracle.gemm(ah.reshape(6, 64, 96), np.ascontiguousarray(bb), dtype_in="f16")
+        check(oracle, to_host(torch, c, "f16").reshape(6, 64, 80), want, "f16")
+
+
+def test_dynamic_argument_entry_point_with_host_buffers(cuda, oracle, lib):
+    """(result*, void** args) in the style of the reference's _mlir_ciface_main wrapper
+    (lib/Transforms/GenerateDynamicWrapper.cpp:34-95), host memrefs in and out as robust_driver.cpp passes them."""
+    from nova_compiler_b200 import _lib as L
+    text = """
+    func.func @main(%a: tensor<16x16xf32>, %b: tensor<16x16xf32>, %c: tensor<16x16xf32>) -> tensor<16x16xf32> {
+      %s = nova.add %a, %b : tensor<16x16xf32>, tensor<16x16xf32>
+      %r = nova.matmul %s, %c : tensor<16x16xf32>, tensor<16x16xf32>
+      return %r : tensor<16x16xf32>
+    }
+    """
+    mod = C.c_void_p()
+    L.check(lib.nova_b200_module_parse(text.encode(), C.byref(mod)))
+    bufs = [np.full((16, 16), v, np.float32) for v in (1.0, 2.0, 1.0)]  # robust_driver.cpp:71-80: (1+2).1 -> 48
+    out = np.zeros((16, 16), np.float32)
+
+    def desc(arr):
+        d = L.MemRef2D()
+        d.allocated = d.aligned = arr.ctypes.data
+        d.offset = 0
+        d.sizes[0], d.sizes[1] = arr.shape
+        d.strides[0], d.strides[1] = arr.shape[1], 1
+        return d
+
+    descs = [desc(x) for x in bufs]
+    rd = desc(out)
+    argv = (C.c_void_p * 3)(*[C.addressof(d) for d in descs])
+    L.check(lib.nova_b200_module_call_ciface(mod, b"main", C.byref(rd), argv))
+    assert np.all(out == np.float32(48.0))
+    lib.nova_b200_module_free(mod)
+
+
+@pytest.mark.parametrize("n,dt", [(1000, "bf16"), (11008, "bf16"), (333, "f32"), (135, "bf16")])
+def test_slab_interleave_kernel(cuda, lib, n, dt):
+    """staging = the ranks' column slabs one after the other (as an all-gather leaves them) -> row-major [M, N]."""
+    torch = cuda
+    from nova_compiler_b200 import _lib as L
+    from nova_compiler_b200.sharding import column_slab
+    world, m = 4, 37
+    tdt = _tdt(torch, dt)
+    full = torch.arange(m * n, device="cuda", dtype=torch.float32).reshape(m, n).remainder(251).to(tdt)
+    widths = [column_slab(n, world, r)[1] for r in range(world)]
+    wmax = max(widths)
+    staging = torch.full((world, m, wmax), -1.0, device="cuda", dtype=tdt)
+    for r in range(world):
+        s, c = column_slab(n, world, r)
+        staging[r, :, :c] = full[:, s:s + c]
+    out = torch.empty(m, n, device="cuda", dtype=tdt)
+    L.check(lib.nova_b200_interleave_slabs(staging.data_ptr(), out.data_ptr(), m, n, world, wmax, 64, out.element_size(), None))
+    torch.cuda.synchronize()
+    assert torch.equal(out, full)
+
+
+def test_operands_on_another_device_are_refused(cuda, lib):
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from nova_compiler_b200 import ops, _lib as L
+    a = torch.zeros(1, 128, 128, device="cuda:1", dtype=torch.bfloat16)
+    out = torch.empty(1, 128, 128, device="cuda:1", dtype=torch.bfloat16)
+    g = _gemm_args(L, a, a, out)
+    torch.cuda.set_device(0)
+    assert lib.nova_b200_gemm(C.byref(g), None) == L.ERR_INVALID_ARG  # cuda:1 memory with cuda:0 current
+    assert b"current device" in lib.nova_b200_last_error_string()
+    res = ops.gemm(a, a)  # the operator layer makes the operands' device current instead
+    assert res.device.index == 1
+    b0 = torch.zeros(1, 128, 128, device="cuda:0", dtype=torch.bfloat16)
+    with pytest.raises(L.NovaB200Error):
+        ops.gemm(a, b0)
+    torch.cuda.synchronize(1)
