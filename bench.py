@@ -78,7 +78,10 @@ ROW_WORKLOADS = {
     "sce": ("nova.sce f32 logits [8192, 50304], i16 targets (softmax + mean loss; the vocabulary rows of ltest/test.mlir)", "f32", 8192, 50304),
     "sce_bwd": ("nova.sce_backward f32 [8192, 50304]", "f32", 8192, 50304),
 }
-DEFAULT_SUBS = ["c1", "c2", "c4", "c5a", "c5b", "c5c", "ln", "softmax", "gather", "ln_bwd"]
+# order: latency-bound and HBM-bound records first, the seconds of dense tensor work (which pull the part into its
+# power cap) last; each record starts after a short idle so that it does not inherit the previous one's clocks
+DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "c2", "c4", "c5c", "c5a"]
+SUB_IDLE_S = 0.75
 
 
 def load_peaks():
@@ -496,7 +499,7 @@ def run_e2e(ctx, w, set0, bias, share, g_flops):
         g.bias, g.init, g.act = hbias.data_ptr(), L.INIT_BIAS_ROW, L.ACT_GELU_TANH
         h2d += hbias.numel() * hbias.element_size()
     d2h = hc.numel() * hc.element_size()
-    e2e_steps = max(3, min(ctx.args.steps, 10))
+    e2e_steps = max(3, min(ctx.args.steps or 10, 10))
     for _ in range(2):
         L.check(lib.nova_b200_gemm_host(C.byref(g)))
     ctx.barrier()
@@ -623,6 +626,8 @@ def run_gpu(args):
         for s in DEFAULT_SUBS:
             if s == head:
                 continue
+            ctx.torch.cuda.synchronize()
+            time.sleep(SUB_IDLE_S)
             if s in WORKLOADS:
                 r = run_contraction(ctx, s, SUB_STEPS[s], 5)
             elif ctx.world == 1:
@@ -641,6 +646,7 @@ def run_gpu(args):
             "scaling": "strong", "vs_baseline": None, "dtype": rec["dtype"],
             "data": "synthetic (seeded, shapes and distributions of the config)",
             "config": {"workload": f"{head}: {desc}",
+                       "sub_records": f"each starts after {SUB_IDLE_S} s of idle; the headline runs first",
                        "partition": ("one GPU" if ctx.world == 1 else
                                      ("batch index, no collective" if part == "batch" else
                                       "N-column slabs of the one global GEMM, A replicated, no collective")),

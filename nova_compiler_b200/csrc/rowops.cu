@@ -197,8 +197,9 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
         }
       }
     } else {
-      float m = s0, m_dup = s0;
-      row_reduce2<TPR, true>(m, m_dup, red2, red_phase);
+      float m = s0, m_dup = 0.0f;
+      if (TPR == 32) m = warp_max(m);
+      else row_reduce2<TPR, true>(m, m_dup, red2, red_phase);
       float part = 0.0f;
       if (!CACHED) part = s0 == -INFINITY ? 0.0f : s1 * __expf(s0 - m);  // this thread's sum, rescaled to the row max
       if (CACHED) {
@@ -212,7 +213,8 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
         }
       }
       float s = part, s_dup = 0.0f;
-      row_reduce2<TPR, false>(s, s_dup, red2, red_phase);
+      if (TPR == 32) s = warp_sum(s);
+      else row_reduce2<TPR, false>(s, s_dup, red2, red_phase);
       if (row_stats != nullptr && active && t == 0) { row_stats[2 * row] = m; row_stats[2 * row + 1] = s; }
       const float recip = 1.0f / fmaxf(s, 1.0e-7f);
       auto emit = [&](int i, const P& in) {
