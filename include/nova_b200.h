@@ -56,7 +56,8 @@ typedef enum nova_b200_dtype {
   NOVA_B200_BF16 = 2,
   NOVA_B200_I16 = 3, /* index types for gather; i16 is zero-extended like the reference */
   NOVA_B200_I32 = 4,
-  NOVA_B200_I64 = 5
+  NOVA_B200_I64 = 5,
+  NOVA_B200_I1 = 6   /* one byte per element, 0 or 1: results of nova.compare in the textual front-end only */
 } nova_b200_dtype;
 
 /* Fused consumers of the contraction, as classified by the reference's isEpilogue
@@ -249,6 +250,15 @@ int32_t nova_b200_gelu_backward(const void* grad_out_dev, const void* x_dev, voi
  * operand (NovaToLinalg.cpp:115-194; the `[1,10]` bias of ltest/test_cpu.mlir). */
 int32_t nova_b200_add_rowbcast(const void* a_dev, const void* b_dev, void* out_dev, int64_t rows, int64_t cols,
                                int32_t b_is_full, int32_t dtype, void* stream);
+
+/* out = a (op) b, elementwise with numpy-style, right-aligned broadcasting: nova.add / nova.sub / nova.mul
+ * (NovaToLinalgElementwiseConverter, NovaToLinalg.cpp:115-194; operand broadcast :154-168; result shape
+ * lib/Dialect/nova/Broadcast.cpp:9-52).  `shape` is the OUTPUT shape (rank <= 6, contiguous row-major);
+ * a_strides / b_strides are element strides per output dim, 0 where the operand has extent 1 and stretches.
+ * Same-dtype float operands only (the reference's f16+bf16 -> f32 promotion is out of scope). */
+typedef enum nova_b200_binary_op { NOVA_B200_BIN_ADD = 0, NOVA_B200_BIN_SUB = 1, NOVA_B200_BIN_MUL = 2 } nova_b200_binary_op;
+int32_t nova_b200_binary(const void* a_dev, const void* b_dev, void* out_dev, int32_t rank, const int64_t* shape,
+                         const int64_t* a_strides, const int64_t* b_strides, int32_t op, int32_t dtype, void* stream);
 
 /* out[c] = sum over rows of x[r, c], fp32 accumulation: the bias gradient of nova.linear_backward, a column sum
  * over the flattened batch*M rows (NovaLinearBackwardPattern, NovaToLinalgGeneric.cpp:1970-1985).  x is

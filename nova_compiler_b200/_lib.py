@@ -15,11 +15,13 @@ OK, ERR_INVALID_ARG, ERR_LAYOUT, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_D
 STATUS_NAMES = ["OK", "ERR_INVALID_ARG", "ERR_LAYOUT", "ERR_UNSUPPORTED", "ERR_CUDA", "ERR_NO_DEVICE",
                 "ERR_DEVICE_TIMEOUT", "ERR_TOO_LARGE"]
 # nova_b200_dtype
-F32, F16, BF16, I16, I32, I64 = range(6)
+F32, F16, BF16, I16, I32, I64, I1 = range(7)
 # nova_b200_act
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_TANH_GRAD = range(4)
 # nova_b200_acc_init
 INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_FROM_C, INIT_BIAS_AND_RESIDUAL = range(5)
+# nova_b200_binary_op
+BIN_ADD, BIN_SUB, BIN_MUL = range(3)
 # nova_b200_f32_mode
 TF32X3, TF32X1 = range(2)
 
@@ -87,6 +89,8 @@ PROTOTYPES = {
     "nova_b200_gelu_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_add_rowbcast": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                            C.c_int32, C.c_void_p]),
+    "nova_b200_binary": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                     C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_void_p]),
     "nova_b200_layer_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_column_sum": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),

@@ -30,7 +30,10 @@ struct Op {
   std::vector<std::string> index_operands;  // nova.gather [%idx]
   int num_ins = 0;                    // linalg ops: operands[0..num_ins) are ins
   std::map<std::string, int64_t> attrs;  // axis, dimension, axes1, axes2
-  double fvalue = 0.0;                // arith.constant
+  std::map<std::string, std::vector<int64_t>> int_lists;  // dimension = [0, 1]
+  std::string kind_attr;              // nova.reduce<sum>, nova.compare<gt>: the text between the angle brackets
+  bool from_generic = false;          // a linalg.generic bias / ReLU consumer rewritten into the nova op it came from
+  double fvalue = 0.0;                // arith.constant, nova.constant (splat)
   std::vector<Type> operand_types;    // as written after ':'
   std::vector<Type> result_types;     // as written after '->' (may be empty: inferred)
   int line = 0;

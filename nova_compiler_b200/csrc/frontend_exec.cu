@@ -72,6 +72,53 @@ __global__ void cast_kernel(const Tin* __restrict__ x, Tout* __restrict__ y, int
     y[i] = static_cast<Tout>(static_cast<float>(x[i]));  // extf / truncf (round to nearest even)
 }
 
+// i1 (one byte, 0 / 1) -> float
+template <typename Tout>
+__global__ void cast_i1_kernel(const uint8_t* __restrict__ x, Tout* __restrict__ y, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    y[i] = static_cast<Tout>(x[i] ? 1.0f : 0.0f);
+}
+
+// out[i] = a (cmp) b with right-aligned broadcasting (strides 0 on stretched dims), kind: eq ne lt le gt ge
+template <typename T>
+__global__ void compare_kernel(const T* __restrict__ a, const T* __restrict__ b, uint8_t* __restrict__ out, Strided6 sa,
+                               Strided6 sb, int64_t n, int kind) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t rem = i, oa = 0, ob = 0;
+#pragma unroll
+    for (int d = 5; d >= 0; --d) {
+      const int64_t q = rem / sa.shape[d], r = rem - q * sa.shape[d];
+      oa += r * sa.strides[d];
+      ob += r * sb.strides[d];
+      rem = q;
+    }
+    const float x = static_cast<float>(a[oa]), y = static_cast<float>(b[ob]);
+    const bool v = kind == 0 ? x == y : kind == 1 ? x != y : kind == 2 ? x < y : kind == 3 ? x <= y : kind == 4 ? x > y : x >= y;
+    out[i] = v ? 1 : 0;
+  }
+}
+
+// out[0] = mean over all n elements of (a - b)^2: one CTA, fp32 accumulation in a fixed order (the loss scalar of the
+// training-step fixtures; a few thousand elements)
+template <typename T>
+__global__ void __launch_bounds__(1024) mse_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n) {
+  __shared__ float part[1024];
+  float acc = 0.0f;
+  for (int64_t i = threadIdx.x; i < n; i += 1024) {
+    const float d = static_cast<float>(a[i]) - static_cast<float>(b[i]);
+    acc = fmaf(d, d, acc);
+  }
+  part[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = 512; s > 0; s >>= 1) {
+    if (static_cast<int>(threadIdx.x) < s) part[threadIdx.x] += part[threadIdx.x + s];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] = static_cast<T>(part[0] / static_cast<float>(n));
+}
+
 template <typename T>
 __global__ void fill_kernel(T* __restrict__ y, float v, int64_t n) {
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
@@ -138,6 +185,7 @@ struct Exec {
     const uint8_t* src = static_cast<const uint8_t*>(v.ptr);
     uint8_t* dst = static_cast<uint8_t*>(out->ptr);
     switch (dtype_bytes(v.dtype)) {
+      case 1: strided_copy_kernel<1><<<grid_for(n), 256, 0, stream>>>(src, dst, s, n); break;
       case 2: strided_copy_kernel<2><<<grid_for(n), 256, 0, stream>>>(src, dst, s, n); break;
       case 4: strided_copy_kernel<4><<<grid_for(n), 256, 0, stream>>>(src, dst, s, n); break;
       default: strided_copy_kernel<8><<<grid_for(n), 256, 0, stream>>>(src, dst, s, n); break;
@@ -298,9 +346,26 @@ struct Exec {
       st = nova_b200_layer_norm_backward(in[0].ptr, in[1].ptr, in[2].ptr, in[3].ptr, in[4].ptr, out[0].ptr, out[1].ptr,
                                          out[2].ptr, in[1].numel() / std::max<int64_t>(D, 1), D, in[1].dtype, stream);
     } else if (k == "gelu_backward") st = nova_b200_gelu_backward(in[0].ptr, in[1].ptr, out[0].ptr, n, in[0].dtype, stream);
-    else if (k == "add") {
-      const int64_t cols = in[0].shape.back();
-      st = nova_b200_add_rowbcast(in[0].ptr, in[1].ptr, out[0].ptr, n / cols, cols, in[1].numel() == n ? 1 : 0, in[0].dtype, stream);
+    else if (k == "binary") {
+      // right-aligned broadcast: an operand dim of extent 1 (or a missing leading dim) gets stride 0
+      const std::vector<int64_t>& os = out[0].shape;
+      const int r = static_cast<int>(os.size());
+      if (r > 6) return fail(NOVA_B200_ERR_UNSUPPORTED, "front-end: elementwise op of rank > 6");
+      int64_t shp[6], sa[6], sb[6];
+      auto strides_for = [&](const Value& v, int64_t* dst) {
+        const int pad = r - static_cast<int>(v.shape.size());
+        for (int d = 0; d < r; ++d) dst[d] = (d < pad || v.shape[d - pad] == 1) ? 0 : v.strides[d - pad];
+      };
+      for (int d = 0; d < r; ++d) shp[d] = os[d];
+      strides_for(in[0], sa);
+      strides_for(in[1], sb);
+      st = nova_b200_binary(in[0].ptr, in[1].ptr, out[0].ptr, r, shp, sa, sb, static_cast<int32_t>(s.attrs.at("op")), in[0].dtype, stream);
+    } else if (k == "reduce_sum") {
+      const int64_t lead = s.attrs.at("lead");
+      int64_t rows = 1;
+      for (int64_t i = 0; i < lead; ++i) rows *= in[0].shape[i];
+      const int64_t cols = n / std::max<int64_t>(rows, 1);
+      st = nova_b200_column_sum(in[0].ptr, out[0].ptr, rows, cols, in[0].dtype, stream);
     } else if (k == "column_sum") {
       const int64_t cols = in[0].shape.back();
       st = nova_b200_column_sum(in[0].ptr, out[0].ptr, n / std::max<int64_t>(cols, 1), cols, in[0].dtype, stream);
@@ -333,6 +398,43 @@ struct Exec {
       for (size_t i = batched ? batch_dims : 0; i < idx.shape.size(); ++i) n_idx *= idx.shape[i];
       st = nova_b200_gather(x.ptr, idx.ptr, out[0].ptr, pre, x.shape[axis], post, n_idx, idx.dtype, batched ? 1 : 0,
                             dtype_bytes(x.dtype), nullptr, stream);
+    } else if (k == "compare") {
+      const std::vector<int64_t>& os = out[0].shape;
+      const int r = static_cast<int>(os.size());
+      if (r > 6) return fail(NOVA_B200_ERR_UNSUPPORTED, "front-end: compare of rank > 6");
+      Strided6 sa, sb;
+      auto fill6 = [&](const Value& v, Strided6* dst) {
+        const int pad_out = 6 - r, pad_v = r - static_cast<int>(v.shape.size());
+        for (int d = 0; d < 6; ++d) {
+          const int od = d - pad_out;  // index into the output shape
+          dst->shape[d] = od < 0 ? 1 : os[od];
+          const int vd = od - pad_v;
+          dst->strides[d] = (od < 0 || vd < 0 || v.shape[vd] == 1) ? 0 : v.strides[vd];
+        }
+      };
+      fill6(in[0], &sa);
+      fill6(in[1], &sb);
+      const int64_t m = out[0].numel();
+      const int kind = static_cast<int>(s.attrs.at("op"));
+      uint8_t* o = static_cast<uint8_t*>(out[0].ptr);
+      if (in[0].dtype == NOVA_B200_F32) compare_kernel<float><<<grid_for(m), 256, 0, stream>>>(static_cast<const float*>(in[0].ptr), static_cast<const float*>(in[1].ptr), o, sa, sb, m, kind);
+      else if (in[0].dtype == NOVA_B200_F16) compare_kernel<__half><<<grid_for(m), 256, 0, stream>>>(static_cast<const __half*>(in[0].ptr), static_cast<const __half*>(in[1].ptr), o, sa, sb, m, kind);
+      else compare_kernel<__nv_bfloat16><<<grid_for(m), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in[0].ptr), static_cast<const __nv_bfloat16*>(in[1].ptr), o, sa, sb, m, kind);
+      NOVA_CUDA_OK(cudaGetLastError());
+      st = NOVA_B200_OK;
+    } else if (k == "mse") {
+      if (in[0].dtype == NOVA_B200_F32) mse_kernel<float><<<1, 1024, 0, stream>>>(static_cast<const float*>(in[0].ptr), static_cast<const float*>(in[1].ptr), static_cast<float*>(out[0].ptr), n);
+      else if (in[0].dtype == NOVA_B200_F16) mse_kernel<__half><<<1, 1024, 0, stream>>>(static_cast<const __half*>(in[0].ptr), static_cast<const __half*>(in[1].ptr), static_cast<__half*>(out[0].ptr), n);
+      else mse_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(in[0].ptr), static_cast<const __nv_bfloat16*>(in[1].ptr), static_cast<__nv_bfloat16*>(out[0].ptr), n);
+      NOVA_CUDA_OK(cudaGetLastError());
+      st = NOVA_B200_OK;
+    } else if (k == "cast" && in[0].dtype == NOVA_B200_I1) {
+      const uint8_t* x = static_cast<const uint8_t*>(in[0].ptr);
+      if (out[0].dtype == NOVA_B200_F32) cast_i1_kernel<float><<<grid_for(n), 256, 0, stream>>>(x, static_cast<float*>(out[0].ptr), n);
+      else if (out[0].dtype == NOVA_B200_F16) cast_i1_kernel<__half><<<grid_for(n), 256, 0, stream>>>(x, static_cast<__half*>(out[0].ptr), n);
+      else cast_i1_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, stream>>>(x, static_cast<__nv_bfloat16*>(out[0].ptr), n);
+      NOVA_CUDA_OK(cudaGetLastError());
+      st = NOVA_B200_OK;
     } else if (k == "cast") {
       const int32_t di = in[0].dtype, dout = out[0].dtype;
 #define NOVA_CAST(TI, TO) cast_kernel<TI, TO><<<grid_for(n), 256, 0, stream>>>(static_cast<const TI*>(in[0].ptr), static_cast<TO*>(out[0].ptr), n)
@@ -346,7 +448,7 @@ struct Exec {
 #undef NOVA_CAST
       NOVA_CUDA_OK(cudaGetLastError());
       st = NOVA_B200_OK;
-    } else if (k == "fill") {
+    } else if (k == "fill" || k == "constant") {
       const int64_t m = out[0].numel();
       if (out[0].dtype == NOVA_B200_F32) fill_kernel<float><<<grid_for(m), 256, 0, stream>>>(static_cast<float*>(out[0].ptr), static_cast<float>(s.fvalue), m);
       else if (out[0].dtype == NOVA_B200_F16) fill_kernel<__half><<<grid_for(m), 256, 0, stream>>>(static_cast<__half*>(out[0].ptr), static_cast<float>(s.fvalue), m);

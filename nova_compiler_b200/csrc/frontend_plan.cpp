@@ -28,6 +28,7 @@ const char* dtype_name(int32_t d) {
     case NOVA_B200_I16: return "i16";
     case NOVA_B200_I32: return "i32";
     case NOVA_B200_I64: return "i64";
+    case NOVA_B200_I1: return "i1";
     default: return "?";
   }
 }
@@ -236,12 +237,54 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
       if (in.size() != 2 || !is_float(in[1]->dtype) || in[0]->dtype != in[1]->dtype || !(in[0]->shape == in[1]->shape))
         return c.fail(op, "expects grad_out and input of one float type and shape");
       set(0, *in[1]);
-    } else if (n == "nova.add") {
+    } else if (n == "nova.add" || n == "nova.sub" || n == "nova.mul") {
+      // numpy broadcasting, right-aligned (inference: NovaOps.cpp:20-138 -> Broadcast.cpp:9-52)
       if (in.size() != 2) return c.fail(op, "expects two operands");
       if (in[0]->dtype != in[1]->dtype || !is_float(in[0]->dtype)) return c.fail(op, "mixed or non-float dtypes are outside the supported subset");
-      if (in[0]->shape == in[1]->shape || is_row_broadcast(*in[0], *in[1])) set(0, *in[0]);
-      else if (is_row_broadcast(*in[1], *in[0])) set(0, *in[1]);
-      else return c.fail(op, "only same-shape or row-broadcast operands are supported");
+      Type t;
+      t.dtype = in[0]->dtype;
+      if (!broadcast_batch(in[0]->shape, in[1]->shape, &t.shape)) return c.fail(op, "operand shapes do not broadcast");
+      set(0, t);
+    } else if (n == "nova.compare") {
+      // elementwise comparison with broadcasting -> i1 (CompareOp::inferReturnTypes, NovaOps.cpp:1006-1040)
+      static const char* kinds[] = {"eq", "ne", "lt", "le", "gt", "ge"};
+      bool known = false;
+      for (const char* k : kinds) known = known || op.kind_attr == k;
+      if (in.size() != 2 || !known) return c.fail(op, "expects compare<eq|ne|lt|le|gt|ge> of two operands");
+      if (in[0]->dtype != in[1]->dtype || !is_float(in[0]->dtype)) return c.fail(op, "mixed or non-float dtypes are outside the supported subset");
+      Type t;
+      t.dtype = NOVA_B200_I1;
+      if (!broadcast_batch(in[0]->shape, in[1]->shape, &t.shape)) return c.fail(op, "operand shapes do not broadcast");
+      set(0, t);
+    } else if (n == "nova.mse") {
+      // mean over every element of (lhs - rhs)^2 -> tensor<1> (NovaMseForwardLowering, NovaToLinalgGeneric.cpp:367-428)
+      if (in.size() != 2 || !is_float(in[0]->dtype) || in[0]->dtype != in[1]->dtype || !(in[0]->shape == in[1]->shape))
+        return c.fail(op, "expects two float tensors of one type and shape");
+      Type t;
+      t.dtype = in[0]->dtype;
+      t.shape = {1};
+      set(0, t);
+    } else if (n == "nova.constant") {
+      // {value = dense<v> : T} : T  -- a splat; the written type is the result type
+      if (!in.empty() || op.operand_types.empty()) return c.fail(op, "expects `{value = dense<v> : T} : T`");
+      if (!is_float(op.operand_types[0].dtype)) return c.fail(op, "only float splat constants are supported");
+      set(0, op.operand_types[0]);
+    } else if (n == "nova.reduce") {
+      // sum over the LEADING dims `dimension = [0, .., k-1]`, reduced dims dropped (ReduceOp, NovaOps.td:191-230): the
+      // gradient accumulations of the backward graphs (ltest/test.mlir:45, ltest/testing.mlir:21-33)
+      if (in.size() != 1 || !is_float(in[0]->dtype)) return c.fail(op, "expects one float tensor");
+      if (op.kind_attr != "sum") return c.fail(op, "only reduce<sum> is inside the supported subset");
+      if (op.attrs.count("keepdims") && op.attrs.at("keepdims") != 0) return c.fail(op, "keepdims is outside the supported subset");
+      auto it = op.int_lists.find("dimension");
+      if (it == op.int_lists.end() || it->second.empty()) return c.fail(op, "expects `dimension = [0, ..]`");
+      const std::vector<int64_t>& dims = it->second;
+      if (dims.size() >= in[0]->shape.size() + 0 && dims.size() > in[0]->shape.size()) return c.fail(op, "too many dimensions");
+      for (size_t k = 0; k < dims.size(); ++k)
+        if (dims[k] != static_cast<int64_t>(k)) return c.fail(op, "only the leading dimensions can be reduced");
+      Type t;
+      t.dtype = in[0]->dtype;
+      t.shape.assign(in[0]->shape.begin() + dims.size(), in[0]->shape.end());
+      set(0, t);
     } else if (n == "nova.layer_norm") {
       if (in.size() != 3) return c.fail(op, "expects input, gamma, beta");
       const Type& x = *in[0];
@@ -296,8 +339,9 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
       set(0, t);
     } else if (n == "nova.cast") {
       if (in.size() != 1 || op.result_types.empty()) return c.fail(op, "expects `%x : Tin -> Tout`");
-      if (!is_float(in[0]->dtype) || !is_float(op.result_types[0].dtype) || op.result_types[0].shape != in[0]->shape)
-        return c.fail(op, "only float-to-float casts of equal shape are supported");
+      if (!(is_float(in[0]->dtype) || in[0]->dtype == NOVA_B200_I1) || !is_float(op.result_types[0].dtype) ||
+          op.result_types[0].shape != in[0]->shape)
+        return c.fail(op, "only float-to-float and i1-to-float casts of equal shape are supported");
       set(0, op.result_types[0]);
     } else if (n == "nova.to_device" || n == "bufferization.to_tensor") {
       if (in.size() != 1) return c.fail(op, "expects one operand");
@@ -469,10 +513,23 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.gelu_backward") {
       s.kind = "gelu_backward";
       s.inputs = op.operands; s.outputs = op.results;
-    } else if (n == "nova.add") {
-      s.kind = "add";
+    } else if (n == "nova.add" || n == "nova.sub" || n == "nova.mul") {
+      s.kind = "binary";
+      s.attrs["op"] = n == "nova.add" ? NOVA_B200_BIN_ADD : (n == "nova.sub" ? NOVA_B200_BIN_SUB : NOVA_B200_BIN_MUL);
       s.inputs = op.operands; s.outputs = op.results;
-      if (!(c.type_of(op.operands[0])->shape == c.type_of(op.results[0])->shape)) std::swap(s.inputs[0], s.inputs[1]);
+    } else if (n == "nova.compare") {
+      static const char* kinds[] = {"eq", "ne", "lt", "le", "gt", "ge"};
+      s.kind = "compare";
+      for (int k = 0; k < 6; ++k)
+        if (op.kind_attr == kinds[k]) s.attrs["op"] = k;
+      s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.mse") {
+      s.kind = "mse"; s.inputs = op.operands; s.outputs = op.results;
+    } else if (n == "nova.constant") {
+      s.kind = "constant"; s.fvalue = op.fvalue; s.outputs = op.results;
+    } else if (n == "nova.reduce") {
+      s.kind = "reduce_sum"; s.attrs["lead"] = static_cast<int64_t>(op.int_lists.at("dimension").size());
+      s.inputs = op.operands; s.outputs = op.results;
     } else if (n == "nova.softmax") { s.kind = "softmax"; s.inputs = op.operands; s.outputs = op.results; }
     else if (n == "nova.layer_norm") {
       s.kind = "layer_norm"; s.inputs = op.operands;

@@ -508,6 +508,35 @@ __global__ void add_rowbcast_kernel(const T* __restrict__ a, const T* __restrict
   }
 }
 
+// out = a (op) b with numpy-style broadcasting over up to six dims: every operand carries one element stride per
+// output dim, 0 where it broadcasts.  The launcher collapses dims first, so the common shapes (equal shapes, a
+// bias along the rows, one scalar, a batch of equal slices) arrive as at most two dims with unit or zero strides
+// and the index arithmetic is one division per element; only odd broadcasts walk all six.
+struct BinaryDims {
+  int32_t rank;
+  int64_t shape[6], sa[6], sb[6];
+};
+
+template <typename T, int kOp>
+__global__ void binary_broadcast_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n,
+                                        BinaryDims d) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t rem = i, oa = 0, ob = 0;
+#pragma unroll 1
+    for (int k = d.rank - 1; k > 0; --k) {
+      const int64_t q = rem / d.shape[k], r = rem - q * d.shape[k];
+      oa += r * d.sa[k];
+      ob += r * d.sb[k];
+      rem = q;
+    }
+    oa += rem * d.sa[0];
+    ob += rem * d.sb[0];
+    const float x = ld_f32<T>(a[oa]), y = ld_f32<T>(b[ob]);
+    out[i] = st_f32<T>(kOp == 0 ? x + y : (kOp == 1 ? x - y : x * y));
+  }
+}
+
 // Column sums of x[rows, cols] (the bias gradient of nova.linear_backward).  Pass 1: CTA (cx, ry) owns 64
 // columns and every gridDim.y-th block of 32 rows; a warp reads one row segment of 64 columns (128 B of
 // 16-bit data) per step, so loads are coalesced, and accumulates in fp32; the 8 warps' partials meet in shared
@@ -1263,6 +1292,56 @@ int32_t nova_b200_add_rowbcast(const void* a, const void* b, void* out, int64_t 
   else if (dtype == NOVA_B200_F16) { if (vec_ok) NOVA_ADD(__half, 8); else NOVA_ADD(__half, 1); }
   else { if (vec_ok) NOVA_ADD(__nv_bfloat16, 8); else NOVA_ADD(__nv_bfloat16, 1); }
 #undef NOVA_ADD
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_binary(const void* a, const void* b, void* out, int32_t rank, const int64_t* shape,
+                         const int64_t* a_strides, const int64_t* b_strides, int32_t op, int32_t dtype, void* stream) {
+  if (rank < 0 || rank > 6) return fail(NOVA_B200_ERR_UNSUPPORTED, "binary: rank must be 0..6");
+  if (op < NOVA_B200_BIN_ADD || op > NOVA_B200_BIN_MUL) return fail(NOVA_B200_ERR_INVALID_ARG, "binary: unknown op");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "binary: dtype must be f32, f16 or bf16");
+  if (rank > 0 && (!shape || !a_strides || !b_strides)) return fail(NOVA_B200_ERR_INVALID_ARG, "binary: null shape or strides");
+  int64_t n = 1;
+  for (int i = 0; i < rank; ++i) {
+    if (shape[i] < 0 || a_strides[i] < 0 || b_strides[i] < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "binary: negative extent or stride");
+    n *= shape[i];
+  }
+  if (n == 0) return NOVA_B200_OK;
+  if (!a || !b || !out) return fail(NOVA_B200_ERR_INVALID_ARG, "binary: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, a, "binary: an input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, out, "binary: the output")) != NOVA_B200_OK) return st;
+  // drop size-1 dims, then merge neighbours that both operands walk like one dim
+  BinaryDims d{};
+  for (int i = 0; i < rank; ++i) {
+    if (shape[i] == 1) continue;
+    const int64_t sa = a_strides[i], sb = b_strides[i];
+    if (d.rank > 0) {
+      const int k = d.rank - 1;
+      if (d.sa[k] == sa * shape[i] && d.sb[k] == sb * shape[i]) {  // (0 == 0 * n merges two broadcast dims too)
+        d.shape[k] *= shape[i]; d.sa[k] = sa; d.sb[k] = sb;
+        continue;
+      }
+    }
+    d.shape[d.rank] = shape[i]; d.sa[d.rank] = sa; d.sb[d.rank] = sb;
+    ++d.rank;
+  }
+  if (d.rank == 0) { d.rank = 1; d.shape[0] = 1; d.sa[0] = d.sb[0] = 0; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n, 256, ctx->sm_count);
+#define NOVA_BIN(T)                                                                                                      \
+  do {                                                                                                                   \
+    if (op == NOVA_B200_BIN_ADD) binary_broadcast_kernel<T, 0><<<grid, 256, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n, d); \
+    else if (op == NOVA_B200_BIN_SUB) binary_broadcast_kernel<T, 1><<<grid, 256, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n, d); \
+    else binary_broadcast_kernel<T, 2><<<grid, 256, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), n, d); \
+  } while (0)
+  if (dtype == NOVA_B200_F32) NOVA_BIN(float);
+  else if (dtype == NOVA_B200_F16) NOVA_BIN(__half);
+  else NOVA_BIN(__nv_bfloat16);
+#undef NOVA_BIN
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }

@@ -90,6 +90,7 @@ inline int dtype_bytes(int32_t dt) {
     case NOVA_B200_F32: case NOVA_B200_I32: return 4;
     case NOVA_B200_F16: case NOVA_B200_BF16: case NOVA_B200_I16: return 2;
     case NOVA_B200_I64: return 8;
+    case NOVA_B200_I1: return 1;
     default: return 0;
   }
 }

@@ -28,7 +28,7 @@ def _torch_dtypes():
     if _TORCH_DT is None:
         import torch
         _TORCH_DT = {L.F32: torch.float32, L.F16: torch.float16, L.BF16: torch.bfloat16, L.I16: torch.int16,
-                     L.I32: torch.int32, L.I64: torch.int64}
+                     L.I32: torch.int32, L.I64: torch.int64, L.I1: torch.uint8}
     return _TORCH_DT
 
 

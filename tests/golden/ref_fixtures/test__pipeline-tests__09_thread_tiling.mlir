@@ -1,0 +1,37 @@
+// Test: nova-gpu-apply-tiling-level-thread
+// Verifies that the M/N parallel dimensions of linalg.matmul are tiled into
+// an scf.for loop with step 4.
+//
+// RUN: nova-opt %s \
+// RUN:   -nova-tile-and-distribute \
+// RUN:   -canonicalize -cse \
+// RUN:   -nova-gpu-pad-operands \
+// RUN:   -canonicalize -cse \
+// RUN:   -nova-gpu-promote-matmul-operands \
+// RUN:   -canonicalize -cse \
+// RUN:   -nova-gpu-apply-tiling-level-reduction \
+// RUN:   -canonicalize -cse \
+// RUN:   -nova-gpu-apply-tiling-level-thread \
+// RUN:   -canonicalize -cse \
+// RUN: | FileCheck %s
+
+// CHECK-LABEL: func.func @thread_tiling_test
+// CHECK:       scf.forall
+// K-tiling loop
+// CHECK:         scf.for {{.*}} step %c32
+// Thread-tiling loop
+// CHECK:           scf.for {{.*}} step %c4
+// CHECK:             scf.for {{.*}} step %c4
+// CHECK:               linalg.matmul
+
+func.func @thread_tiling_test(
+    %arg0: tensor<100x300xf32>,
+    %arg1: tensor<300x200xf32>) -> tensor<100x200xf32> {
+  %cst = arith.constant 0.000000e+00 : f32
+  %empty = tensor.empty() : tensor<100x200xf32>
+  %fill = linalg.fill ins(%cst : f32) outs(%empty : tensor<100x200xf32>) -> tensor<100x200xf32>
+  %result = linalg.matmul
+      ins(%arg0, %arg1 : tensor<100x300xf32>, tensor<300x200xf32>)
+      outs(%fill : tensor<100x200xf32>) -> tensor<100x200xf32>
+  return %result : tensor<100x200xf32>
+}
