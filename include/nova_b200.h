@@ -194,6 +194,17 @@ void nova_b200_operand_free(nova_b200_operand* op);
 int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream);
 /* Validation + kernel selection only (no launch); usable without a GPU. */
 int32_t nova_b200_gemm_plan(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
+/* nova_b200_gemm with every field passed as a scalar: the form compiled IR calls.  The lowering pass
+ * (mlir/ConvertNovaContractionsToB200Calls.cpp) emits `func.call @nova_b200_gemm_flat(...)` with the operands'
+ * aligned pointers as i64 (memref.extract_aligned_pointer_as_index, the pointer FixGpuLaunch takes from descriptor
+ * field 1: lib/Transforms/FixGpuLaunch.cpp:245-246) and the extents, pitches and enums as i64 / i32 constants; no
+ * struct has to be laid out in IR and the element type does not appear in the callee's signature.  `stream` is the
+ * cudaStream_t as an integer (0 = default stream).  Returns a nova_b200_status. */
+int32_t nova_b200_gemm_flat(int64_t A, int64_t B, int64_t C, int64_t bias, int64_t residual, int64_t batch, int64_t M,
+                            int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                            int64_t batch_stride_a, int64_t batch_stride_b, int64_t batch_stride_c, int64_t batch_stride_r,
+                            int32_t dtype_ab, int32_t dtype_c, int32_t trans_a, int32_t trans_b, int32_t act, int32_t init,
+                            int32_t f32_mode, int64_t stream);
 /* Same contraction with HOST pointers for A, B, C, bias, residual: stages them through
  * library-owned device buffers (H2D, kernel, D2H) and synchronises before returning.  This is the
  * form the reference's host harnesses use (driver.cpp:22-40: host descriptors in, result out). */

@@ -75,6 +75,7 @@ PROTOTYPES = {
     "nova_b200_operand_view": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "nova_b200_operand_free": (None, [C.c_void_p]),
     "nova_b200_gemm": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p]),
+    "nova_b200_gemm_flat": (C.c_int32, [C.c_int64] * 17 + [C.c_int32] * 7 + [C.c_int64]),
     "nova_b200_gemm_plan": (C.c_int32, [C.POINTER(GemmArgs), C.POINTER(GemmPlanInfo)]),
     "nova_b200_gemm_host": (C.c_int32, [C.POINTER(GemmArgs)]),
     "nova_b200_gemm_f32_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),

@@ -169,7 +169,8 @@ struct Exec {
     return p.types.at(h == std::string::npos ? n : n.substr(0, h));
   }
   // a contiguous row-major version of v (a copy only when v is a strided view)
-  int32_t make_contiguous(const Value& v, Value* out) {
+  int32_t make_contiguous(const Value& v_in, Value* out) {
+    const Value v = v_in;  // callers pass the same object as input and output
     if (v.contiguous()) { *out = v; out->strides = row_major(v.shape); return NOVA_B200_OK; }
     if (v.shape.size() > 6) return fail(NOVA_B200_ERR_UNSUPPORTED, "front-end: strided copy of rank > 6");
     Type t; t.dtype = v.dtype; t.shape = v.shape;

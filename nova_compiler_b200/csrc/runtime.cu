@@ -379,6 +379,27 @@ int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream) {
   return gemm_launch(ctx, args, static_cast<cudaStream_t>(stream));
 }
 
+int32_t nova_b200_gemm_flat(int64_t A, int64_t B, int64_t C, int64_t bias, int64_t residual, int64_t batch, int64_t M,
+                            int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                            int64_t batch_stride_a, int64_t batch_stride_b, int64_t batch_stride_c, int64_t batch_stride_r,
+                            int32_t dtype_ab, int32_t dtype_c, int32_t trans_a, int32_t trans_b, int32_t act, int32_t init,
+                            int32_t f32_mode, int64_t stream) {
+  nova_b200_gemm_args g{};
+  g.struct_size = sizeof(g);
+  g.dtype_ab = dtype_ab; g.dtype_c = dtype_c; g.trans_a = trans_a; g.trans_b = trans_b;
+  g.act = act; g.init = init; g.f32_mode = f32_mode;
+  g.batch = batch; g.M = M; g.N = N; g.K = K;
+  g.A = reinterpret_cast<const void*>(static_cast<intptr_t>(A));
+  g.B = reinterpret_cast<const void*>(static_cast<intptr_t>(B));
+  g.C = reinterpret_cast<void*>(static_cast<intptr_t>(C));
+  g.bias = reinterpret_cast<const void*>(static_cast<intptr_t>(bias));
+  g.residual = reinterpret_cast<const void*>(static_cast<intptr_t>(residual));
+  g.lda = lda; g.ldb = ldb; g.ldc = ldc; g.ldr = ldr;
+  g.batch_stride_a = batch_stride_a; g.batch_stride_b = batch_stride_b; g.batch_stride_c = batch_stride_c;
+  g.batch_stride_r = batch_stride_r;
+  return nova_b200_gemm(&g, reinterpret_cast<void*>(static_cast<intptr_t>(stream)));
+}
+
 int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   nova_b200_gemm_plan_info info;
   int32_t st = gemm_plan_only(args, &info);
