@@ -542,6 +542,66 @@ def run_sustained(ctx, graph, n_sets, g_flops, seconds=2.5):
             "clocks": clocks, "peak": peak, "frac": tf / peak, "peak_source": f"{ctx.peak_src} (cuBLAS bf16, seconds-long loop)"}
 
 
+def run_ln_fold(ctx, steps=60):
+    """nova.layer_norm feeding the headline linear + GELU: the two-kernel form (layer_norm writes y, the contraction
+    reads it) against the folded form (row statistics in one read of x, the contraction consumes x itself).  Both
+    timed as graph replays over rotating input sets; the record is the block's time, not a TFLOP/s figure."""
+    from nova_compiler_b200 import ops
+    torch = ctx.torch
+    _, dab, dc, B, M, N, K, epi, _ = WORKLOADS["c3"]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234)
+    dt = _tdt(torch, dab)
+    n_sets = 3
+    xs = [(torch.randn(M, K, device="cuda", generator=g)).to(dt) for _ in range(n_sets)]
+    w = (torch.randn(K, N, device="cuda", generator=g) * 0.02).to(dt)
+    bias = (torch.randn(N, device="cuda", generator=g) * 0.02).to(dt)
+    gamma = (1.0 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(dt)
+    beta = (0.1 * torch.randn(K, device="cuda", generator=g)).to(dt)
+    outs = [torch.empty(M, N, device="cuda", dtype=dt) for _ in range(n_sets)]
+    folded = ops.LnFoldedLinear(w, gamma, beta, bias)
+
+    def unfused(i):
+        y, _, _ = ops.layer_norm(xs[i % n_sets], gamma, beta)
+        ops.gemm(y[None], w[None], bias=bias, act="gelu", out=outs[i % n_sets][None])
+
+    def fused(i):
+        folded(xs[i % n_sets], act="gelu", out=outs[i % n_sets])
+
+    res = {}
+    for name, fn in (("layer_norm_then_linear_ms", unfused), ("folded_ms", fused)):
+        for i in range(n_sets):
+            fn(i)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for i in range(n_sets):
+                fn(i)
+        side.synchronize()
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(n_sets):
+                    fn(i)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        time.sleep(SUB_IDLE_S)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps // n_sets):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / (steps // n_sets * n_sets)
+        del graph
+    es = 2
+    res.update({"workload": "nova.layer_norm [8192, 4096] bf16 -> linear 4096 x 11008 + bias + GELU (the C3 block with its producer)",
+                "hbm_bytes_saved_per_step": 2 * M * K * es - M * 8,
+                "note": "folded: y is never written or read; kernels per step 2 (row statistics, contraction) in both forms"})
+    return res
+
+
 def run_rowop(ctx, w, steps, warmup):
     """HBM roofline of the row-wise kernels: GB/s = (bytes read + bytes written) / event time."""
     from nova_compiler_b200 import ops
@@ -583,12 +643,36 @@ def run_rowop(ctx, w, steps, warmup):
     for i in range(max(warmup, 3)):
         fn(i)
     torch.cuda.synchronize()
+    # one pass over the input sets captured into a CUDA graph and replayed, as for the contractions: the metric is
+    # the kernels' HBM rate, and the host side of a call (allocations of the outputs, the ctypes call) is of the
+    # same order as these kernels
+    graph = None
+    if not ctx.args.no_graph:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for i in range(n_sets):
+                fn(i)
+        side.synchronize()
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(n_sets):
+                    fn(i)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
     sampler = ClockSampler(ctx.local)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        fn(i)
+    if graph is not None:
+        for _ in range(steps // n_sets):
+            graph.replay()
+        for i in range(steps % n_sets):
+            fn(i)
+    else:
+        for i in range(steps):
+            fn(i)
     e1.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
@@ -599,7 +683,8 @@ def run_rowop(ctx, w, steps, warmup):
     return {
         "workload": f"{w}: {desc}", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "steps": steps, "dtype": dt,
         "clocks": clocks, "gpu_launches": steps * {"ln_bwd": 2, "sce": 2}.get(w, 1),  # + column-sum finish / loss kernel
-        "l2": f"rotating {n_sets} input sets; outputs are fresh allocations",
+        "l2": f"rotating {n_sets} input sets",
+        "launch": "direct calls" if graph is None else f"CUDA graph of {n_sets} steps, replayed",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": ctx.peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / ctx.peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(w), "peak_source": ctx.peak_src,
                      "algorithmic_bytes_per_launch": byts, "frac_of_nominal_8000": gbs / 8000.0},
@@ -636,6 +721,10 @@ def run_gpu(args):
                 r = None  # row kernels are per-row independent: no multi-GPU partition is reported for them
             if r is not None:
                 subs[s] = r
+    ln_fold = None
+    if not args.only and not args.profile and ctx.world == 1 and head == "c3":
+        time.sleep(SUB_IDLE_S)
+        ln_fold = run_ln_fold(ctx)
     line = None
     if ctx.rank == 0:
         desc = WORKLOADS[head][0]
@@ -660,6 +749,8 @@ def run_gpu(args):
                 line[k] = rec[k]
         if subs:
             line["workloads"] = subs
+        if ln_fold is not None:
+            line["ln_fold"] = ln_fold
         if ctx.world == 1 and not args.profile and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(head)
     if ctx.world > 1:

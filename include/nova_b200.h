@@ -81,8 +81,12 @@ typedef enum nova_b200_acc_init {
   NOVA_B200_INIT_BIAS_ROW = 1,      /* bias[N], broadcast along rows                         */
   NOVA_B200_INIT_RESIDUAL_FULL = 2, /* residual[batch, M, N] (own pitch and batch stride)     */
   NOVA_B200_INIT_FROM_C = 3,        /* C holds the initial accumulator and is overwritten     */
-  NOVA_B200_INIT_BIAS_AND_RESIDUAL = 4 /* bias[N] + residual[batch, M, N]: the "out + x + b_down" generic after
+  NOVA_B200_INIT_BIAS_AND_RESIDUAL = 4, /* bias[N] + residual[batch, M, N]: the "out + x + b_down" generic after
                                         * the FFN-down contraction (docs/SelectLoweringStrategy_Report.md rows 15, 25) */
+  NOVA_B200_INIT_LN_FOLD = 5           /* the contraction consumes a layer-normalised A without it ever being written:
+                                        * C = act( rstd_i * (A.W' - mean_i * c_j) + d_j ), see nova_b200_ln_fold_prepare.
+                                        * `bias` then points at fp32 {c[N], d[N]} and `residual` at fp32 {mean, rstd}[M]
+                                        * (both from the library's own routines); batch must be 1 */
 } nova_b200_acc_init;
 
 typedef enum nova_b200_f32_mode {
@@ -165,6 +169,9 @@ int32_t nova_b200_abi_version(void);
  *   "group_m" (16) raster group height in row blocks
  *   "prefetch" (-1) L2 prefetch distance of the pair kernel in ring stages: -1 = planner, 0 = off
  *   "pdl" (1)      launch contractions with programmatic stream serialization (prologue overlaps the previous kernel's tail)
+ *   "ring_rows" (1) layer_norm rows of a few KB stream through a shared-memory ring filled by bulk copies; 2 = the
+ *                  backward kernel as well (slower than its register form where measured); 0 = register kernels only
+ *   "ring_stages" / "ring_ctas" (0) ring depth and CTAs per SM of those kernels, 0 = built-in choice (tuning)
  *   "plan_cache" (1) reuse plans and tensor maps of repeated calls;  "debug" (0)
  * No counterpart in the reference (its schedule is fixed at compile time by lowering_config attributes,
  * lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1487-1577). */
@@ -238,6 +245,28 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args);
  *    device-side wait code (0 = every bounded wait completed) and returns
  *    NOVA_B200_ERR_DEVICE_TIMEOUT when it is non-zero. */
 int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream, uint32_t* wait_code_out);
+
+/* Layer norm folded into the contraction that consumes it (the reference fuses LN-apply into the FFN-up
+ * contraction's scf.forall as a prologue: isPrologue, lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1898-1917;
+ * docs/TileAndDistribute_Report.md:50-60).  With y = (x - mean) * rstd * gamma + beta (NovaLayerNormPattern,
+ * NovaToLinalgGeneric.cpp:2103-2116):
+ *     (y . W + b)_ij = rstd_i * ( (x . W')_ij - mean_i * c_j ) + d_j,
+ *     W' = diag(gamma) . W (rounded to the operand dtype),  c_j = sum_k W'_kj,  d_j = sum_k beta_k W_kj + b_j,
+ * so the tensor cores read x itself, y is never written to or read from HBM, and the normalisation costs two
+ * fused multiply-adds per output element in the epilogue.
+ *   nova_b200_ln_fold_prepare: once per (weight, gamma, beta, bias): writes W' [K, N] (pitch N, dtype) to wprime_dev and
+ *     fp32 {c[N], d[N]} to cd_dev (2 * N floats).  bias_dev may be NULL.
+ *   nova_b200_row_stats: per call, one read of x [rows, D]: fp32 {mean_i, rstd_i} (eps 1e-5, as the reference) to
+ *     stats_dev (2 * rows floats).
+ *   then nova_b200_gemm with A = x, B = W', init = NOVA_B200_INIT_LN_FOLD, bias = cd_dev, residual = stats_dev.
+ * Rounding: the unfused order rounds y to the operand dtype before the contraction, this one rounds gamma * W
+ * instead; the two results differ from each other by about sqrt(2) operand roundings (f16 ~3e-4, bf16 ~2.5e-3
+ * relative Frobenius) while each is equally close to the exact value.  The identity loses digits when |mean| is
+ * much larger than the row's standard deviation (the two terms cancel), as any E[x^2]-E[x]^2 style formula does. */
+int32_t nova_b200_ln_fold_prepare(const void* w_dev, const void* gamma_dev, const void* beta_dev, const void* bias_dev,
+                                  void* wprime_dev, float* cd_dev, int64_t K, int64_t N, int64_t ldw, int32_t dtype,
+                                  void* stream);
+int32_t nova_b200_row_stats(const void* x_dev, float* stats_dev, int64_t rows, int64_t D, int32_t dtype, void* stream);
 
 /* y = act(x), n elements, standalone nova.gelu / nova.relu (NovaToLinalgGeneric.cpp:1277-1337,
  * NovaToLinalg.cpp:1053-1084) for graphs where the activation is not adjacent to a contraction. */

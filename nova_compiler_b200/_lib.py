@@ -19,7 +19,7 @@ F32, F16, BF16, I16, I32, I64, I1 = range(7)
 # nova_b200_act
 ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_TANH_GRAD = range(4)
 # nova_b200_acc_init
-INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_FROM_C, INIT_BIAS_AND_RESIDUAL = range(5)
+INIT_ZERO, INIT_BIAS_ROW, INIT_RESIDUAL_FULL, INIT_FROM_C, INIT_BIAS_AND_RESIDUAL, INIT_LN_FOLD = range(6)
 # nova_b200_binary_op
 BIN_ADD, BIN_SUB, BIN_MUL = range(3)
 # nova_b200_f32_mode
@@ -92,6 +92,9 @@ PROTOTYPES = {
                                            C.c_int32, C.c_void_p]),
     "nova_b200_binary": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64),
                                      C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_void_p]),
+    "nova_b200_ln_fold_prepare": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                              C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "nova_b200_row_stats": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_layer_norm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "nova_b200_column_sum": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),

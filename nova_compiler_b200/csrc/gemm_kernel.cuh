@@ -198,6 +198,26 @@ __device__ __forceinline__ void epilogue_math(const GemmKernelParams& p, const u
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]);
   const int32_t ncols = min(32, p.N - col0);
+  if (p.init == NOVA_B200_INIT_LN_FOLD) {
+    // layer norm folded into the contraction: v = rstd_i * (acc - mean_i * c_j) + d_j, all in fp32
+    const float* c = reinterpret_cast<const float*>(p.bias) + col0;
+    const float* d = c + p.N;
+    const float2 st = row_ok ? __ldg(reinterpret_cast<const float2*>(p.residual) + row) : make_float2(0.0f, 0.0f);
+    if (ncols == 32 && ((reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d)) & 15u) == 0u) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 cq = __ldg(reinterpret_cast<const float4*>(c + j)), dq = __ldg(reinterpret_cast<const float4*>(d + j));
+        v[j] = fmaf(st.y, fmaf(-st.x, cq.x, v[j]), dq.x);
+        v[j + 1] = fmaf(st.y, fmaf(-st.x, cq.y, v[j + 1]), dq.y);
+        v[j + 2] = fmaf(st.y, fmaf(-st.x, cq.z, v[j + 2]), dq.z);
+        v[j + 3] = fmaf(st.y, fmaf(-st.x, cq.w, v[j + 3]), dq.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) v[j] = fmaf(st.y, fmaf(-st.x, __ldg(c + j), v[j]), __ldg(d + j));
+    }
+  }
   if (p.init == NOVA_B200_INIT_BIAS_ROW || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) {
     const OutT* b = reinterpret_cast<const OutT*>(p.bias) + col0;
 #pragma unroll
@@ -802,6 +822,7 @@ __global__ void nova_gemm_k0_kernel(GemmKernelParams p) {
     const int64_t c = i - b * per_batch - r * p.N;
     OutT* dst = reinterpret_cast<OutT*>(p.C) + b * p.stride_c + r * p.ldc + c;
     float v = 0.0f;
+    if (p.init == NOVA_B200_INIT_LN_FOLD) v = reinterpret_cast<const float*>(p.bias)[p.N + c];  // K == 0: only d_j is left
     if (p.init == NOVA_B200_INIT_BIAS_ROW || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL)
       v = to_f32<OutT>(reinterpret_cast<const OutT*>(p.bias)[c]);
     if (p.init == NOVA_B200_INIT_RESIDUAL_FULL || p.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL)

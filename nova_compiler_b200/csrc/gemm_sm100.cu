@@ -37,8 +37,15 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
   if (!is_float_dtype(a->dtype_c)) return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: dtype_c must be f32, f16 or bf16");
   if (a->act < NOVA_B200_ACT_NONE || a->act > NOVA_B200_ACT_GELU_TANH_GRAD)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown activation");
-  if (a->init < NOVA_B200_INIT_ZERO || a->init > NOVA_B200_INIT_BIAS_AND_RESIDUAL)
+  if (a->init < NOVA_B200_INIT_ZERO || a->init > NOVA_B200_INIT_LN_FOLD)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown accumulator init");
+  if (a->init == NOVA_B200_INIT_LN_FOLD) {
+    if (a->batch > 1) return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm: INIT_LN_FOLD takes one matrix (flatten batch into rows)");
+    if (a->act == NOVA_B200_ACT_GELU_TANH_GRAD) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: INIT_LN_FOLD excludes ACT_GELU_TANH_GRAD");
+    if (!a->bias || !a->residual)
+      return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: INIT_LN_FOLD needs bias = fp32 {c, d} and residual = fp32 row statistics");
+    if (reinterpret_cast<uintptr_t>(a->residual) % 8 != 0) return fail(NOVA_B200_ERR_LAYOUT, "gemm: row statistics must be 8-byte aligned");
+  }
   if (a->f32_mode != NOVA_B200_TF32X3 && a->f32_mode != NOVA_B200_TF32X1)
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: unknown f32_mode");
   if (a->batch < 0 || a->M < 0 || a->N < 0 || a->K < 0)

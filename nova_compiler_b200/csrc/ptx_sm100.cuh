@@ -106,6 +106,14 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
+// Untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, size a multiple of 16),
+// completion counted on `bar` in bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // L2 prefetch of a box (no shared-memory destination, no barrier): the data is on its way to L2 when the
 // load proper is issued some ring stages later.
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z) {

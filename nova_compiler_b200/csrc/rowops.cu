@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "ptx_sm100.cuh"
 #include "runtime.h"
 
 namespace nova {
@@ -74,7 +75,8 @@ __device__ __forceinline__ void row_reduce2(float& a, float& b, float2 (*red_sme
 }
 
 constexpr int kRowThreads = 256;
-constexpr int kLongUnroll = 8;  // vectors a thread keeps in flight when a row is too long for its registers
+constexpr int kLongUnroll = 8;
+inline bool ring_rows_enabled() { return options().ring_rows.load() != 0; }  // vectors a thread keeps in flight when a row is too long for its registers
 
 // kMode 0: layer_norm, kMode 1: softmax.  kMaxV > 0: a thread keeps up to kMaxV vectors of its row in
 // registers (the row fits TPR * kMaxV vectors); kMaxV == 0: two passes over global memory.  kMaxV is
@@ -244,6 +246,271 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
   }
 }
 
+// cudaFuncSetAttribute + the occupancy query cost microseconds each: done once per (kernel instance, ring size)
+// and host thread, not per call.
+template <typename Kernel>
+int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
+  struct Entry { size_t smem; int resident; };
+  static thread_local Entry cache[4] = {};
+  static thread_local int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].smem == smem) return cache[i].resident;
+  int resident = 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, threads, smem) != cudaSuccess || resident <= 0) {
+    cudaGetLastError();
+    return 0;
+  }
+  cache[used < 4 ? used++ : 3] = Entry{smem, resident};
+  return resident;
+}
+
+// ---------------------------------------------------------------- layer_norm rows through a shared-memory ring
+//
+// For rows of a few KB (one 256-thread CTA per row) the register-cached kernels above are latency-bound: a CTA's
+// loads, reduction and stores of one row are serial, and the bytes in flight per SM are what its resident CTAs
+// hold in registers.  Here the rows of a persistent CTA stream through a ring of kStages shared-memory slots
+// filled by bulk copies (cp.async.bulk, completion counted on an mbarrier): kStages - 1 rows per CTA are in flight
+// while one is being reduced, no registers are held for them, and a row costs ONE CTA barrier (the pair reduction,
+// after which the slot is free and thread 0 refills it at once).  y is written straight from registers.
+//
+// Waits are bounded: a thread that gives up records kStatusRowRingWait, raises the CTA's abort flag BEFORE the
+// row's barrier and every thread leaves after it, so the decision is uniform; in-flight copies are then given time to land.
+constexpr uint32_t kStatusRowRingWait = 0x201;
+constexpr uint32_t kRingSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void ring_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
+  for (uint32_t it = 0; it < kRingSpinLimit; ++it)
+    if (mbar_try_wait(bar, parity)) return;
+  *abort_flag = 1u;
+  atomicCAS(status, 0u, kStatusRowRingWait);
+}
+
+constexpr int kRingMaxStages = 8;
+
+template <typename T, int kMaxV>
+__global__ void __launch_bounds__(kRowThreads)
+ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+               T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t kStages,
+               uint32_t* status) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  using P = Pack<T, VEC>;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full[kRingMaxStages];
+  __shared__ float2 red2[2][8];
+  __shared__ uint32_t abort_smem;
+  volatile uint32_t* abort_flag = &abort_smem;
+  uint32_t red_phase = 0;
+  const int t = threadIdx.x;
+  const int nvec = D / VEC;
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * sizeof(T);
+  const float inv_d = 1.0f / static_cast<float>(D);
+  if (t == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    abort_smem = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const int64_t step = gridDim.x;
+  if (t == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      const int64_t r = blockIdx.x + s * step;
+      if (r < rows) {
+        mbar_arrive_expect_tx(smem_u32(&full[s]), row_bytes);
+        bulk_load(smem_u32(ring + static_cast<size_t>(s) * row_bytes), x + r * D, row_bytes, smem_u32(&full[s]));
+      }
+    }
+  }
+  // short rows keep their gamma / beta vectors in registers; longer ones re-read them (L1 / L2 hits) to stay at
+  // a register count that lets several CTAs share an SM
+  constexpr bool kPreload = kMaxV <= 2;
+  P g[kPreload ? kMaxV : 1], b[kPreload ? kMaxV : 1];
+  if (kPreload) {
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kRowThreads;
+      if (i < nvec) { g[k] = reinterpret_cast<const P*>(gamma)[i]; b[k] = reinterpret_cast<const P*>(beta)[i]; }
+    }
+  }
+  uint32_t it = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += step, ++it) {
+    const int s = it % kStages;
+    ring_wait(smem_u32(&full[s]), (it / kStages) & 1u, abort_flag, status);
+    const P* slot = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * row_bytes);
+    P cache[kMaxV];
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kRowThreads;
+      if (i < nvec) {
+        cache[k] = slot[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float v = ld_f32<T>(cache[k].e[e]);
+          s0 += v;
+          s1 += v * v;
+        }
+      }
+    }
+    row_reduce2<kRowThreads, false>(s0, s1, red2, red_phase);  // one barrier: every thread has read the slot
+    if (*abort_flag != 0u) break;                              // (raised before the barrier: all threads see it)
+    if (t == 0) {
+      const int64_t nr = row + kStages * step;
+      if (nr < rows) {
+        mbar_arrive_expect_tx(smem_u32(&full[s]), row_bytes);
+        bulk_load(smem_u32(ring + static_cast<size_t>(s) * row_bytes), x + nr * D, row_bytes, smem_u32(&full[s]));
+      }
+    }
+    const float mean = s0 * inv_d;
+    const float rstd = rsqrtf(s1 * inv_d - mean * mean + 1e-5f);
+    if (t == 0) {
+      if (mean_sum) mean_sum[row] = st_f32<T>(s0);
+      if (rstd_out) rstd_out[row] = st_f32<T>(rstd);
+    }
+    P* yr = reinterpret_cast<P*>(y + row * D);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kRowThreads;
+      if (i < nvec) {
+        const P gk = kPreload ? g[kPreload ? k : 0] : reinterpret_cast<const P*>(gamma)[i];
+        const P bk = kPreload ? b[kPreload ? k : 0] : reinterpret_cast<const P*>(beta)[i];
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          o.e[e] = st_f32<T>((ld_f32<T>(cache[k].e[e]) - mean) * rstd * ld_f32<T>(gk.e[e]) + ld_f32<T>(bk.e[e]));
+        yr[i] = o;
+      }
+    }
+  }
+  if (*abort_flag != 0u && t == 0)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // let copies still in flight land before the CTA's memory is reused
+  __syncthreads();
+}
+
+// layer_norm_backward the same way: a slot holds one row of grad_y and one of x (two bulk copies, one barrier
+// phase); a thread owns the same vectors of every row, so dgamma / dbeta accumulate in its registers and leave as
+// one partial row per CTA; the next row's mean and rstd are fetched a row ahead.
+template <typename T, int kMaxV, int kThreads>
+__global__ void __launch_bounds__(kThreads)
+ln_backward_ring_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
+                        const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
+                        float* __restrict__ partial, int64_t rows, int32_t D, int32_t kStages, uint32_t* status) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  using P = Pack<T, VEC>;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full[kRingMaxStages];
+  __shared__ float2 red2[2][kThreads / 32];
+  __shared__ uint32_t abort_smem;
+  volatile uint32_t* abort_flag = &abort_smem;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  constexpr int kWarps = kThreads / 32;
+  const int nvec = D / VEC;
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * sizeof(T);
+  const float inv_d = 1.0f / static_cast<float>(D);
+  if (t == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    abort_smem = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const int64_t step = gridDim.x;
+  auto fill = [&](int s, int64_t r) {
+    const uint32_t bar = smem_u32(&full[s]);
+    uint8_t* dst = ring + static_cast<size_t>(s) * 2 * row_bytes;
+    mbar_arrive_expect_tx(bar, 2 * row_bytes);
+    bulk_load(smem_u32(dst), gy + r * D, row_bytes, bar);
+    bulk_load(smem_u32(dst + row_bytes), x + r * D, row_bytes, bar);
+  };
+  if (t == 0)
+    for (int s = 0; s < kStages; ++s)
+      if (blockIdx.x + s * step < rows) fill(s, blockIdx.x + s * step);
+  P gam[kMaxV];
+  float dg[kMaxV][VEC], db[kMaxV][VEC];
+#pragma unroll
+  for (int k = 0; k < kMaxV; ++k) {
+    const int i = t + k * kThreads;
+    if (i < nvec) gam[k] = reinterpret_cast<const P*>(gamma)[i];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) dg[k][e] = db[k][e] = 0.0f;
+  }
+  float mean_next = 0.0f, rs_next = 0.0f;
+  if (static_cast<int64_t>(blockIdx.x) < rows) {
+    mean_next = ld_f32<T>(mean_sum[blockIdx.x]) * inv_d;
+    rs_next = ld_f32<T>(rstd[blockIdx.x]);
+  }
+  uint32_t it = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += step, ++it) {
+    const int s = it % kStages;
+    const float mean = mean_next, rs = rs_next;
+    if (row + step < rows) {
+      mean_next = ld_f32<T>(mean_sum[row + step]) * inv_d;
+      rs_next = ld_f32<T>(rstd[row + step]);
+    }
+    ring_wait(smem_u32(&full[s]), (it / kStages) & 1u, abort_flag, status);
+    const P* sg = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * 2 * row_bytes);
+    const P* sx = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * 2 * row_bytes + row_bytes);
+    P pg[kMaxV], px[kMaxV];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kThreads;
+      if (i < nvec) {
+        pg[k] = sg[i];
+        px[k] = sx[i];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float g = ld_f32<T>(pg[k].e[e]);
+          const float xhat = (ld_f32<T>(px[k].e[e]) - mean) * rs;
+          const float gyg = g * ld_f32<T>(gam[k].e[e]);
+          s1 += gyg;
+          s2 = fmaf(gyg, xhat, s2);
+          dg[k][e] = fmaf(g, xhat, dg[k][e]);
+          db[k][e] += g;
+        }
+      }
+    }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    float2* buf = red2[it & 1u];  // alternating exchange buffer: one barrier per row
+    if (lane == 0) buf[warp] = make_float2(s1, s2);
+    __syncthreads();
+    if (*abort_flag != 0u) break;
+    if (t == 0 && row + kStages * step < rows) fill(s, row + kStages * step);  // every thread has read the slot
+    const float2 r2 = lane < kWarps ? buf[lane] : make_float2(0.0f, 0.0f);
+    const float m1 = warp_sum(r2.x) * inv_d, m2 = warp_sum(r2.y) * inv_d;
+    P* dxr = reinterpret_cast<P*>(dx + row * D);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kThreads;
+      if (i < nvec) {
+        P o;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float xhat = (ld_f32<T>(px[k].e[e]) - mean) * rs;
+          const float gyg = ld_f32<T>(pg[k].e[e]) * ld_f32<T>(gam[k].e[e]);
+          o.e[e] = st_f32<T>(((gyg - m1) - xhat * m2) * rs);
+        }
+        dxr[i] = o;
+      }
+    }
+  }
+  if (*abort_flag != 0u && t == 0)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  __syncthreads();
+  float* pdg = partial + static_cast<size_t>(blockIdx.x) * 2 * D;
+  float* pdb = pdg + D;
+#pragma unroll
+  for (int k = 0; k < kMaxV; ++k) {
+    const int i = t + k * kThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { pdg[i * VEC + e] = dg[k][e]; pdb[i * VEC + e] = db[k][e]; }
+    }
+  }
+}
+
 // softmax of rows too long for registers but not for shared memory (up to 220 KB, e.g. a 50304-entry f32
 // vocabulary row): one 1024-thread CTA per SM stages its row in shared memory while it takes the running
 // max / sum (four 16-byte loads in flight per thread), then normalises out of shared memory.  HBM sees the row
@@ -308,7 +575,7 @@ softmax_smem_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, in
 
 template <typename T, int VEC, int kMode>
 int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
-                          int64_t rows, int64_t D, int sm_count, cudaStream_t st, float* stats) {
+                          int64_t rows, int64_t D, int sm_count, cudaStream_t st, float* stats, uint32_t* status) {
   const T* xp = static_cast<const T*>(x);
   const T* gp = static_cast<const T*>(gamma);
   const T* bp = static_cast<const T*>(beta);
@@ -347,6 +614,31 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
   // Vectors a thread keeps in registers are kept few (occupancy sets the bytes in flight per SM):
   // longer rows get more threads, not more registers.
   constexpr int kWarpMv = VEC == 1 ? 32 : (kMode == 0 ? 4 : 8);
+  // layer_norm rows of 2 KB .. 32 KB: the shared-memory ring (bulk copies, one barrier per row)
+  if (kMode == 0 && VEC > 1 && status != nullptr && nvec > 32 * kWarpMv && nvec <= kRowThreads * 8 && ring_rows_enabled()) {
+    const size_t row_bytes = static_cast<size_t>(D) * sizeof(T);
+    // Two slots per CTA: one row landing while one is reduced.  With four CTAs per SM that already keeps HBM busy, and
+    // deeper rings measured SLOWER on [8192, 4096] bf16 (2 slots 5.05 TB/s, 4: 4.87, 6: 4.53): more rows in flight
+    // from every SM scatter the DRAM accesses.
+    int stages = 2;
+    if (const int64_t o = options().ring_stages.load(); o >= 2 && o <= kRingMaxStages) stages = static_cast<int>(o);
+#define NOVA_LN_RING(MAXV_)                                                                                          \
+    do {                                                                                                             \
+      auto kernel = ln_ring_kernel<T, MAXV_>;                                                                        \
+      const size_t smem = stages * row_bytes;                                                                        \
+      int resident = ring_resident_ctas(kernel, kRowThreads, smem);                                                  \
+      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, "layer_norm: the ring kernel cannot be configured");       \
+      if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);      \
+      const int grid = static_cast<int>(std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * resident));         \
+      kernel<<<grid, kRowThreads, smem, st>>>(xp, gp, bp, yp, mp, rp, rows, d, stages, status);                      \
+    } while (0)
+    if (nvec <= kRowThreads * 2) NOVA_LN_RING(2);
+    else if (nvec <= kRowThreads * 4) NOVA_LN_RING(4);
+    else NOVA_LN_RING(8);
+#undef NOVA_LN_RING
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
   if (VEC == 1) {
     // scalar path (row length or base not 16-byte friendly)
     if (nvec <= 32 * kWarpMv) NOVA_ROW(32, kWarpMv);
@@ -375,22 +667,23 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
 
 template <int kMode>
 int32_t dispatch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
-                            int64_t rows, int64_t D, int32_t dtype, int sm_count, cudaStream_t st, float* stats = nullptr) {
+                            int64_t rows, int64_t D, int32_t dtype, int sm_count, cudaStream_t st, float* stats = nullptr,
+                            uint32_t* status = nullptr) {
   const int es = dtype_bytes(dtype);
   const int vec = 16 / es;
   auto aligned16 = [](const void* p) { return p == nullptr || reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec_ok = D % vec == 0 && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   switch (dtype) {
     case NOVA_B200_F32:
-      return vec_ok ? launch_row_kernel<float, 4, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
-                    : launch_row_kernel<float, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
+      return vec_ok ? launch_row_kernel<float, 4, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status)
+                    : launch_row_kernel<float, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status);
     case NOVA_B200_F16:
-      return vec_ok ? launch_row_kernel<__half, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
-                    : launch_row_kernel<__half, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
+      return vec_ok ? launch_row_kernel<__half, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status)
+                    : launch_row_kernel<__half, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status);
     case NOVA_B200_BF16:
       return vec_ok
-                 ? launch_row_kernel<__nv_bfloat16, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats)
-                 : launch_row_kernel<__nv_bfloat16, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats);
+                 ? launch_row_kernel<__nv_bfloat16, 8, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status)
+                 : launch_row_kernel<__nv_bfloat16, 1, kMode>(x, gamma, beta, y, mean_sum, rstd, rows, D, sm_count, st, stats, status);
     default:
       return fail(NOVA_B200_ERR_UNSUPPORTED, "row op: dtype must be f32, f16 or bf16");
   }
@@ -913,6 +1206,67 @@ int grid_for(int64_t work_items, int threads, int sm_count) {
 
 using namespace nova;
 
+// ---------------------------------------------------------------- layer norm folded into a contraction
+//
+// Per row {mean, rstd} in fp32 from ONE read of x (the layer_norm reduction without its output pass): a warp
+// per row, 16-byte loads, eight in flight per lane.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) row_stats_kernel(const T* __restrict__ x, float2* __restrict__ stats, int64_t rows, int32_t D) {
+  using P = Pack<T, VEC>;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int nvec = D / VEC;
+  for (int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
+    const P* xr = reinterpret_cast<const P*>(x + row * D);
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int i0 = lane; i0 < nvec; i0 += 32 * 8) {
+      P pk[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i0 + u * 32 < nvec) pk[u] = xr[i0 + u * 32];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (i0 + u * 32 < nvec) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float v = ld_f32<T>(pk[u].e[e]);
+            s0 += v;
+            s1 = fmaf(v, v, s1);
+          }
+        }
+      }
+    }
+    s0 = warp_sum(s0);
+    s1 = warp_sum(s1);
+    if (lane == 0) {
+      const float inv_d = 1.0f / static_cast<float>(D);
+      const float mean = s0 * inv_d;
+      stats[row] = make_float2(mean, rsqrtf(s1 * inv_d - mean * mean + 1e-5f));
+    }
+  }
+}
+
+// W'[k, j] = round(gamma[k] * W[k, j]);  c[j] = sum_k W'[k, j];  d[j] = sum_k beta[k] * W[k, j] (+ bias[j]).
+// One thread per column (coalesced along j), k ascending: a fixed summation order.  Runs once per weight.
+template <typename T>
+__global__ void ln_fold_prepare_kernel(const T* __restrict__ w, const T* __restrict__ gamma, const T* __restrict__ beta,
+                                       const T* __restrict__ bias, T* __restrict__ wprime, float* __restrict__ cd, int64_t K,
+                                       int64_t N, int64_t ldw) {
+  const int64_t j = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (j >= N) return;
+  float c = 0.0f, d = bias ? ld_f32<T>(bias[j]) : 0.0f;
+#pragma unroll 8
+  for (int64_t k = 0; k < K; ++k) {
+    const float wv = ld_f32<T>(w[k * ldw + j]);
+    const T wp = st_f32<T>(ld_f32<T>(gamma[k]) * wv);
+    wprime[k * N + j] = wp;
+    c += ld_f32<T>(wp);
+    d = fmaf(ld_f32<T>(beta[k]), wv, d);
+  }
+  cd[j] = c;
+  cd[N + j] = d;
+}
+
 // ---------------------------------------------------------------- multi-GPU: re-interleave all-gathered column slabs
 //
 // After an all-gather every rank holds the ranks' output slabs one after the other, staging[r] = [rows, wmax] with
@@ -958,7 +1312,7 @@ int32_t nova_b200_layer_norm(const void* x, const void* gamma, const void* beta,
   if ((st = check_pointer_device(ctx, x, "nova_b200_layer_norm: the input")) != NOVA_B200_OK) return st;
   if ((st = check_pointer_device(ctx, y, "nova_b200_layer_norm: the output")) != NOVA_B200_OK) return st;
   return dispatch_row_kernel<0>(x, gamma, beta, y, mean_sum, rstd, rows, D, dtype, ctx->sm_count,
-                                static_cast<cudaStream_t>(stream));
+                                static_cast<cudaStream_t>(stream), nullptr, ctx->status_word);
 }
 
 int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const void* gamma, const void* mean_sum,
@@ -986,6 +1340,53 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
                 "layer_norm_backward: rows longer than 2048 sixteen-byte vectors (or 2048 elements when unaligned)");
   // One vector per thread (64 registers, 2048 resident threads per SM) for rows of up to 1024 vectors; longer rows
   // keep 2-8 vectors per thread in 256-thread CTAs.  Threads: a multiple of 32 covering the row.
+  // rows of 2 KB .. 16 KB whose pointers allow bulk copies: the shared-memory ring kernel
+  // (measured slower than the register kernels below on [8192, 4096] bf16, 2.3 against 3.0 TB/s, whatever the ring
+  // depth or the CTAs per SM, so it is off unless asked for: option "ring_rows" = 2)
+  if (vec > 1 && nvec >= 128 && nvec <= 1024 && options().ring_rows.load() == 2 &&
+      reinterpret_cast<uintptr_t>(dx) % 16 == 0) {
+    const size_t row_bytes = static_cast<size_t>(D) * es;
+    int grid = 0;
+    float* partial = nullptr;
+    // two CTAs per SM share ~192 KB of ring: as many (grad_y, x) row slots per CTA as fit in 96 KB (2..8)
+    int stages = static_cast<int>(std::max<size_t>(2, std::min<size_t>(kRingMaxStages, (96u << 10) / (2 * row_bytes))));
+    if (const int64_t o = options().ring_stages.load(); o >= 2 && o <= kRingMaxStages) stages = static_cast<int>(o);
+#define NOVA_LNB_RING(T, MAXV_)                                                                                       \
+    do {                                                                                                              \
+      auto kernel = ln_backward_ring_kernel<T, MAXV_, 512>;                                                           \
+      const size_t smem = stages * 2 * row_bytes;                                                                     \
+      int resident = ring_resident_ctas(kernel, 512, smem);                                                           \
+      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, "layer_norm_backward: the ring kernel cannot be configured"); \
+      if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);       \
+      grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows, static_cast<int64_t>(ctx->sm_count) * resident))); \
+      void* scratch = nullptr;                                                                                        \
+      st = acquire_scratch(ctx, s, static_cast<size_t>(grid) * 2 * D * sizeof(float), &scratch);                      \
+      if (st != NOVA_B200_OK) return st;                                                                              \
+      partial = static_cast<float*>(scratch);                                                                         \
+      kernel<<<grid, 512, smem, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), static_cast<const T*>(gamma), \
+                                     static_cast<const T*>(mean_sum), static_cast<const T*>(rstd), static_cast<T*>(dx), partial, \
+                                     rows, static_cast<int32_t>(D), stages, ctx->status_word);                        \
+    } while (0)
+#define NOVA_LNB_RING_T(T)                                            \
+    do {                                                              \
+      if (nvec <= 512) NOVA_LNB_RING(T, 1); else NOVA_LNB_RING(T, 2); \
+    } while (0)
+    if (dtype == NOVA_B200_F32) NOVA_LNB_RING_T(float);
+    else if (dtype == NOVA_B200_F16) NOVA_LNB_RING_T(__half);
+    else NOVA_LNB_RING_T(__nv_bfloat16);
+#undef NOVA_LNB_RING_T
+#undef NOVA_LNB_RING
+    NOVA_CUDA_OK(cudaGetLastError());
+    const int fin_grid = static_cast<int>((D + 31) / 32);
+    if (dtype == NOVA_B200_F32)
+      ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
+    else if (dtype == NOVA_B200_F16)
+      ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
+    else
+      ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
   const bool wide = nvec <= 1024;
   const int threads = static_cast<int>(wide ? (nvec + 31) / 32 * 32 : kRowThreads);
   const int per_thread = static_cast<int>((nvec + threads - 1) / threads);
@@ -1342,6 +1743,54 @@ int32_t nova_b200_binary(const void* a, const void* b, void* out, int32_t rank, 
   else if (dtype == NOVA_B200_F16) NOVA_BIN(__half);
   else NOVA_BIN(__nv_bfloat16);
 #undef NOVA_BIN
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_row_stats(const void* x, float* stats, int64_t rows, int64_t D, int32_t dtype, void* stream) {
+  if (rows < 0 || D < 1) return fail(NOVA_B200_ERR_INVALID_ARG, "row_stats: bad extent");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "row_stats: dtype must be f32, f16 or bf16");
+  if (D > (1ll << 30)) return fail(NOVA_B200_ERR_TOO_LARGE, "row_stats: D exceeds 2^30");
+  if (rows == 0) return NOVA_B200_OK;
+  if (!x || !stats) return fail(NOVA_B200_ERR_INVALID_ARG, "row_stats: null pointer");
+  if (reinterpret_cast<uintptr_t>(stats) % 8 != 0) return fail(NOVA_B200_ERR_LAYOUT, "row_stats: stats must be 8-byte aligned");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, x, "row_stats: the input")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, stats, "row_stats: the output")) != NOVA_B200_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int es = dtype_bytes(dtype), vec = 16 / es;
+  const bool vec_ok = D % vec == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((rows + 7) / 8, static_cast<int64_t>(ctx->sm_count) * 8)));
+  float2* out = reinterpret_cast<float2*>(stats);
+  const int32_t d = static_cast<int32_t>(D);
+  if (dtype == NOVA_B200_F32) { if (vec_ok) row_stats_kernel<float, 4><<<grid, 256, 0, s>>>(static_cast<const float*>(x), out, rows, d); else row_stats_kernel<float, 1><<<grid, 256, 0, s>>>(static_cast<const float*>(x), out, rows, d); }
+  else if (dtype == NOVA_B200_F16) { if (vec_ok) row_stats_kernel<__half, 8><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), out, rows, d); else row_stats_kernel<__half, 1><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), out, rows, d); }
+  else { if (vec_ok) row_stats_kernel<__nv_bfloat16, 8><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), out, rows, d); else row_stats_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), out, rows, d); }
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_ln_fold_prepare(const void* w, const void* gamma, const void* beta, const void* bias, void* wprime, float* cd,
+                                  int64_t K, int64_t N, int64_t ldw, int32_t dtype, void* stream) {
+  if (K < 1 || N < 1 || ldw < N) return fail(NOVA_B200_ERR_INVALID_ARG, "ln_fold_prepare: bad extent or pitch");
+  if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "ln_fold_prepare: dtype must be f32, f16 or bf16");
+  if (!w || !gamma || !beta || !wprime || !cd) return fail(NOVA_B200_ERR_INVALID_ARG, "ln_fold_prepare: null pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  if ((st = check_pointer_device(ctx, w, "ln_fold_prepare: the weight")) != NOVA_B200_OK) return st;
+  if ((st = check_pointer_device(ctx, wprime, "ln_fold_prepare: the output")) != NOVA_B200_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>((N + 127) / 128);
+#define NOVA_PREP(T)                                                                                                  \
+  ln_fold_prepare_kernel<T><<<grid, 128, 0, s>>>(static_cast<const T*>(w), static_cast<const T*>(gamma), static_cast<const T*>(beta), \
+                                                 static_cast<const T*>(bias), static_cast<T*>(wprime), cd, K, N, ldw)
+  if (dtype == NOVA_B200_F32) NOVA_PREP(float);
+  else if (dtype == NOVA_B200_F16) NOVA_PREP(__half);
+  else NOVA_PREP(__nv_bfloat16);
+#undef NOVA_PREP
   NOVA_CUDA_OK(cudaGetLastError());
   return NOVA_B200_OK;
 }

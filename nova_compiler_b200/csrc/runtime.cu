@@ -162,6 +162,9 @@ const OptionEntry kOptionTable[] = {
     {"group_m", "NOVA_B200_GROUP_M", &Options::group_m},     {"prefetch", "NOVA_B200_PREFETCH", &Options::prefetch},
     {"plan_cache", "NOVA_B200_PLAN_CACHE", &Options::plan_cache}, {"debug", "NOVA_B200_DEBUG", &Options::debug},
     {"pdl", "NOVA_B200_PDL", &Options::pdl},
+    {"ring_rows", "NOVA_B200_RING_ROWS", &Options::ring_rows},
+    {"ring_stages", "NOVA_B200_RING_STAGES", &Options::ring_stages},
+    {"ring_ctas", "NOVA_B200_RING_CTAS", &Options::ring_ctas},
 };
 }  // namespace
 
@@ -405,6 +408,8 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   int32_t st = gemm_plan_only(args, &info);
   if (st != NOVA_B200_OK) return st;
   if (args->batch == 0 || args->M == 0 || args->N == 0) return NOVA_B200_OK;
+  if (args->init == NOVA_B200_INIT_LN_FOLD)
+    return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm_host: INIT_LN_FOLD takes device-resident statistics and folded weights; use nova_b200_gemm");
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
   const nova_b200_gemm_args& a = *args;

@@ -76,8 +76,11 @@ struct Options {
   std::atomic<int64_t> short_k{1};    // 8 epilogue warps for K <= 256
   std::atomic<int64_t> group_m{16};   // raster group height in row blocks
   std::atomic<int64_t> prefetch{-1};  // L2 prefetch distance of the pair kernel in ring stages: -1 = planner, 0 = off
+  std::atomic<int64_t> ring_stages{0}; // ring depth of those kernels: 0 = chosen from the row size, else 2..8 (tuning)
+  std::atomic<int64_t> ring_ctas{0};   // their CTAs per SM: 0 = as many as fit (tuning)
   std::atomic<int64_t> plan_cache{1}; // reuse plans and tensor maps of repeated calls
   std::atomic<int64_t> pdl{1};        // launch contractions with programmatic stream serialization
+  std::atomic<int64_t> ring_rows{1};  // layer_norm (forward / backward) rows of a few KB through the shared-memory ring kernels
   std::atomic<int64_t> debug{0};
   std::atomic<uint32_t> epoch{0};     // bumped by every change: cached plans are keyed on it
 };

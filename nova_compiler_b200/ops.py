@@ -219,6 +219,57 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, *, act: Optiona
     return y.reshape(*x.shape[:-1], w.shape[-1])
 
 
+class LnFoldedLinear:
+    """nova.layer_norm + nova.linear (+ activation) as ONE contraction over the un-normalised input: the weight is
+    folded once (W' = diag(gamma) W, c = column sums of W', d = beta^T W + bias; nova_b200_ln_fold_prepare), each call
+    takes the row statistics in one read of x (nova_b200_row_stats) and runs the contraction with
+    NOVA_B200_INIT_LN_FOLD.  The normalised tensor is never written.  The counterpart of the LN-apply prologue
+    the reference fuses into the FFN-up contraction (NovaKernelConfig.cpp:1898-1917)."""
+
+    def __init__(self, w: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        _require_cuda(w, gamma, beta, bias)
+        if w.dim() != 2 or w.stride(1) != 1:
+            raise L.NovaB200Error(L.ERR_LAYOUT, "weight must be [K, N] with unit inner stride")
+        K, N = w.shape
+        if gamma.numel() != K or beta.numel() != K or (bias is not None and bias.numel() != N):
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "gamma / beta must hold K elements, bias N")
+        for t in (gamma, beta, bias):
+            if t is not None and t.dtype != w.dtype:
+                raise L.NovaB200Error(L.ERR_UNSUPPORTED, "mixed dtypes are out of scope")
+        self.K, self.N, self.dtype = K, N, w.dtype
+        with torch.cuda.device(w.device):
+            self.wprime = torch.empty((K, N), dtype=w.dtype, device=w.device)
+            self.cd = torch.empty((2, N), dtype=torch.float32, device=w.device)
+            g, b = gamma.contiguous().reshape(-1), beta.contiguous().reshape(-1)
+            bb = bias.contiguous().reshape(-1) if bias is not None else None
+            L.check(L.load().nova_b200_ln_fold_prepare(w.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                                       bb.data_ptr() if bb is not None else None, self.wprime.data_ptr(),
+                                                       self.cd.data_ptr(), K, N, w.stride(0), _dt(w), _stream()))
+
+    def __call__(self, x: torch.Tensor, act: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x)
+        if x.dtype != self.dtype or x.shape[-1] != self.K:
+            raise L.NovaB200Error(L.ERR_INVALID_ARG, "input must be [..., K] of the weight's dtype")
+        xc = x.contiguous()
+        rows = xc.numel() // self.K
+        with torch.cuda.device(xc.device):
+            stats = torch.empty((rows, 2), dtype=torch.float32, device=xc.device)
+            L.check(L.load().nova_b200_row_stats(xc.data_ptr(), stats.data_ptr(), rows, self.K, _dt(xc), _stream()))
+            if out is None:
+                out = torch.empty((rows, self.N), dtype=self.dtype, device=xc.device)
+            g = L.GemmArgs()
+            g.struct_size = C.sizeof(L.GemmArgs)
+            g.dtype_ab = g.dtype_c = _dt(xc)
+            g.batch, g.M, g.N, g.K = 1, rows, self.N, self.K
+            g.A, g.B, g.C = xc.data_ptr(), self.wprime.data_ptr(), out.data_ptr()
+            g.lda, g.ldb, g.ldc = self.K, self.N, out.stride(-2)
+            g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = rows * self.K, 0, rows * out.stride(-2)
+            g.init, g.act = L.INIT_LN_FOLD, _ACT[act]
+            g.bias, g.residual = self.cd.data_ptr(), stats.data_ptr()
+            L.check(L.load().nova_b200_gemm(C.byref(g), _stream()))
+        return out.reshape(*x.shape[:-1], self.N)
+
+
 @_on_device
 def column_sum(x: torch.Tensor) -> torch.Tensor:
     """Sum over all leading dims of x[..., C] -> [C], fp32 accumulation (grad_bias of nova.linear_backward)."""

@@ -254,3 +254,41 @@ def test_operands_on_another_device_are_refused(cuda, lib):
     with pytest.raises(L.NovaB200Error):
         ops.gemm(a, b0)
     torch.cuda.synchronize(1)
+
+
+@pytest.mark.parametrize("dt,tol_pair,tol_truth", [("f16", 1e-3, 1.0e-3), ("bf16", 4e-3, 5e-3), ("f32", 1e-5, 1e-5)])
+def test_layer_norm_folded_into_the_contraction(cuda, oracle, dt, tol_pair, tol_truth):
+    """LN-apply fused into the FFN-up contraction (isPrologue, NovaKernelConfig.cpp:1898-1917) in its algebraic
+    form: rstd_i * (x.W' - mean_i c_j) + d_j.  Against the unfused layer_norm -> linear+GELU pair (which rounds the
+    normalised tensor to the operand dtype) the difference is about two operand roundings: <= 1e-3 for f16,
+    <= 4e-3 for bf16, <= 1e-5 for f32; against float64 the fused result is as close as the unfused one."""
+    torch = cuda
+    from nova_compiler_b200 import ops
+    g = torch.Generator(device="cuda")
+    g.manual_seed(21)
+    tdt = _tdt(torch, dt)
+    rows, K, N = 333, 512, 328
+    x = (torch.randn(rows, K, device="cuda", generator=g) + 0.3).to(tdt)
+    w = (torch.randn(K, N, device="cuda", generator=g) * 0.05).to(tdt)
+    gamma = (1.0 + 0.2 * torch.randn(K, device="cuda", generator=g)).to(tdt)
+    beta = (0.1 * torch.randn(K, device="cuda", generator=g)).to(tdt)
+    bias = (0.1 * torch.randn(N, device="cuda", generator=g)).to(tdt)
+    y, _, _ = ops.layer_norm(x, gamma, beta)
+    unfused = ops.linear(y, w, bias, act="gelu")
+    folded = ops.LnFoldedLinear(w, gamma, beta, bias)
+    fused = folded(x, act="gelu")
+    torch.cuda.synchronize()
+    d = torch.float64
+    truth = torch.nn.functional.gelu(
+        torch.nn.functional.layer_norm(x.to(d), (K,), gamma.to(d), beta.to(d), eps=1e-5) @ w.to(d) + bias.to(d), approximate="tanh")
+    rel = lambda a, b: float((a.to(d) - b.to(d)).norm() / b.to(d).norm())
+    assert rel(fused, unfused) <= tol_pair, rel(fused, unfused)
+    assert rel(fused, truth) <= tol_truth and rel(fused, truth) <= 1.5 * rel(unfused, truth) + 1e-6, (rel(fused, truth), rel(unfused, truth))
+    # the statistics entry point on its own
+    stats = torch.empty(rows, 2, device="cuda")
+    from nova_compiler_b200 import _lib as L
+    L.check(L.load().nova_b200_row_stats(x.data_ptr(), stats.data_ptr(), rows, K, {"f16": L.F16, "bf16": L.BF16, "f32": L.F32}[dt], None))
+    torch.cuda.synchronize()
+    xm = x.to(d).mean(dim=1)
+    xv = x.to(d).var(dim=1, unbiased=False)
+    assert rel(stats[:, 0], xm) <= 1e-5 and rel(stats[:, 1], (xv + 1e-5).rsqrt()) <= 1e-5
