@@ -246,22 +246,40 @@ row_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __rest
   }
 }
 
-// cudaFuncSetAttribute + the occupancy query cost microseconds each: done once per (kernel instance, ring size)
-// and host thread, not per call.
+// cudaFuncSetAttribute + the occupancy query cost microseconds each: the attribute is raised once per kernel instance
+// (to the most any ring may ask for), the occupancy is looked up once per ring size, per host thread.
+constexpr size_t kRingMaxBytes = 200u << 10;
+
+// (keyed on the kernel's address: instances that differ only in a template argument share one function-pointer type)
 template <typename Kernel>
 int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
-  struct Entry { size_t smem; int resident; };
-  static thread_local Entry cache[4] = {};
+  struct Entry { const void* fn; size_t smem; int resident; };
+  static thread_local Entry cache[32] = {};
   static thread_local int used = 0;
-  for (int i = 0; i < used; ++i)
+  const void* fn = reinterpret_cast<const void*>(kernel);
+  if (smem > kRingMaxBytes) { set_error("ring of " + std::to_string(smem) + " bytes exceeds the limit"); return 0; }
+  bool configured = false;
+  for (int i = 0; i < used; ++i) {
+    if (cache[i].fn != fn) continue;
+    configured = true;
     if (cache[i].smem == smem) return cache[i].resident;
+  }
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingMaxBytes));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      set_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+      return 0;
+    }
+  }
   int resident = 0;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, threads, smem) != cudaSuccess || resident <= 0) {
+  const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kernel, threads, smem);
+  if (e != cudaSuccess || resident <= 0) {
     cudaGetLastError();
+    set_error(std::string("occupancy query: ") + cudaGetErrorString(e) + ", resident " + std::to_string(resident) + ", smem " + std::to_string(smem));
     return 0;
   }
-  cache[used < 4 ? used++ : 3] = Entry{smem, resident};
+  cache[used < 32 ? used++ : 31] = Entry{fn, smem, resident};
   return resident;
 }
 
@@ -279,11 +297,19 @@ int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
 constexpr uint32_t kStatusRowRingWait = 0x201;
 constexpr uint32_t kRingSpinLimit = 1u << 24;
 
+// One lane per warp polls (these kernels are bound by instruction issue, and 32 lanes spinning on one barrier are
+// 32 times the instructions); the warp reconverges on __syncwarp, which also orders the lanes' later reads of the slot
+// after the observed completion.
 __device__ __forceinline__ void ring_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t* status) {
-  for (uint32_t it = 0; it < kRingSpinLimit; ++it)
-    if (mbar_try_wait(bar, parity)) return;
-  *abort_flag = 1u;
-  atomicCAS(status, 0u, kStatusRowRingWait);
+  if ((threadIdx.x & 31) == 0) {
+    bool done = false;
+    for (uint32_t it = 0; it < kRingSpinLimit && !done; ++it) done = mbar_try_wait(bar, parity);
+    if (!done) {
+      *abort_flag = 1u;
+      atomicCAS(status, 0u, kStatusRowRingWait);
+    }
+  }
+  __syncwarp();
 }
 
 constexpr int kRingMaxStages = 8;
@@ -392,7 +418,7 @@ ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
 // phase); a thread owns the same vectors of every row, so dgamma / dbeta accumulate in its registers and leave as
 // one partial row per CTA; the next row's mean and rstd are fetched a row ahead.
 template <typename T, int kMaxV, int kThreads>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, kMaxV == 1 ? 2 : 1)
 ln_backward_ring_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
                         const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
                         float* __restrict__ partial, int64_t rows, int32_t D, int32_t kStages, uint32_t* status) {
@@ -451,19 +477,22 @@ ln_backward_ring_kernel(const T* __restrict__ gy, const T* __restrict__ x, const
     ring_wait(smem_u32(&full[s]), (it / kStages) & 1u, abort_flag, status);
     const P* sg = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * 2 * row_bytes);
     const P* sx = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * 2 * row_bytes + row_bytes);
-    P pg[kMaxV], px[kMaxV];
+    // xhat and gy * gamma stay in registers as floats across the row's barrier: the second half of the row is then
+    // three operations per element instead of a second round of conversions
+    float xh[kMaxV][VEC], gg[kMaxV][VEC];
     float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
     for (int k = 0; k < kMaxV; ++k) {
       const int i = t + k * kThreads;
       if (i < nvec) {
-        pg[k] = sg[i];
-        px[k] = sx[i];
+        const P pg = sg[i], px = sx[i];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float g = ld_f32<T>(pg[k].e[e]);
-          const float xhat = (ld_f32<T>(px[k].e[e]) - mean) * rs;
+          const float g = ld_f32<T>(pg.e[e]);
+          const float xhat = (ld_f32<T>(px.e[e]) - mean) * rs;
           const float gyg = g * ld_f32<T>(gam[k].e[e]);
+          xh[k][e] = xhat;
+          gg[k][e] = gyg;
           s1 += gyg;
           s2 = fmaf(gyg, xhat, s2);
           dg[k][e] = fmaf(g, xhat, dg[k][e]);
@@ -487,11 +516,7 @@ ln_backward_ring_kernel(const T* __restrict__ gy, const T* __restrict__ x, const
       if (i < nvec) {
         P o;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float xhat = (ld_f32<T>(px[k].e[e]) - mean) * rs;
-          const float gyg = ld_f32<T>(pg[k].e[e]) * ld_f32<T>(gam[k].e[e]);
-          o.e[e] = st_f32<T>(((gyg - m1) - xhat * m2) * rs);
-        }
+        for (int e = 0; e < VEC; ++e) o.e[e] = st_f32<T>(((gg[k][e] - m1) - xh[k][e] * m2) * rs);
         dxr[i] = o;
       }
     }
@@ -627,7 +652,7 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
       auto kernel = ln_ring_kernel<T, MAXV_>;                                                                        \
       const size_t smem = stages * row_bytes;                                                                        \
       int resident = ring_resident_ctas(kernel, kRowThreads, smem);                                                  \
-      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, "layer_norm: the ring kernel cannot be configured");       \
+      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, std::string("layer_norm: the ring kernel cannot be configured: ") + nova_b200_last_error_string()); \
       if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);      \
       const int grid = static_cast<int>(std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * resident));         \
       kernel<<<grid, kRowThreads, smem, st>>>(xp, gp, bp, yp, mp, rp, rows, d, stages, status);                      \
@@ -1356,7 +1381,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
       auto kernel = ln_backward_ring_kernel<T, MAXV_, 512>;                                                           \
       const size_t smem = stages * 2 * row_bytes;                                                                     \
       int resident = ring_resident_ctas(kernel, 512, smem);                                                           \
-      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, "layer_norm_backward: the ring kernel cannot be configured"); \
+      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, std::string("layer_norm_backward: the ring kernel cannot be configured: ") + nova_b200_last_error_string()); \
       if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);       \
       grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(rows, static_cast<int64_t>(ctx->sm_count) * resident))); \
       void* scratch = nullptr;                                                                                        \

@@ -10,11 +10,22 @@ pytestmark = pytest.mark.gpu
 
 from test_gemm_gpu import GOLD, TOL, _tdt, check, rand_bits, to_dev, to_host  # noqa: E402
 
-ROW_SHAPES = [(64, 384), (33, 1000), (16, 4096), (5, 8192), (3, 10000), (7, 37), (1, 1), (300, 2048)]
+ROW_SHAPES = [(64, 384), (33, 1000), (16, 4096), (5, 8192), (3, 10000), (7, 37), (1, 1), (300, 2048), (3100, 2048)]
 
 
+@pytest.mark.parametrize("ring", [1, 0])
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
-def test_layer_norm(cuda, oracle, dt):
+def test_layer_norm(cuda, oracle, dt, ring):
+    """`ring`: rows of a few KB through the shared-memory ring kernel (1, the default) or the register kernels (0)."""
+    from nova_compiler_b200 import ops, _lib as L0
+    L0.set_option("ring_rows", ring)
+    try:
+        _layer_norm_cases(cuda, oracle, dt)
+    finally:
+        L0.set_option("ring_rows", 1)
+
+
+def _layer_norm_cases(cuda, oracle, dt):
     from nova_compiler_b200 import ops
     rng = np.random.default_rng(1)
     for rows, D in ROW_SHAPES:
@@ -157,10 +168,21 @@ def test_column_sum_and_backward_ops(cuda, oracle, dt):
     check(oracle, to_host(cuda, gbm, dt), oracle.gemm(np.ascontiguousarray(x[0].T), go[0], dtype_in=dt), dt)
 
 
+@pytest.mark.parametrize("ring", [1, 2, 0])
 @pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
-def test_layer_norm_backward(cuda, oracle, dt):
+def test_layer_norm_backward(cuda, oracle, dt, ring):
     """dx, dgamma, dbeta from the saved (mean_sum, rstd) of the forward; vectorised and element-wise row shapes,
-    one to many rows per CTA; fp32 arithmetic rounded once, as the oracle's compute_f32 mode."""
+    one to many rows per CTA; fp32 arithmetic rounded once, as the oracle's compute_f32 mode.  `ring`: the default
+    kernels (1), the shared-memory-ring backward kernel as well (2), register kernels only (0)."""
+    from nova_compiler_b200 import ops, _lib as L0
+    L0.set_option("ring_rows", ring)
+    try:
+        _layer_norm_backward_cases(cuda, oracle, dt)
+    finally:
+        L0.set_option("ring_rows", 1)
+
+
+def _layer_norm_backward_cases(cuda, oracle, dt):
     from nova_compiler_b200 import ops
     rng = np.random.default_rng(6)
     for rows, D in [(64, 384), (8192, 384), (33, 1000), (700, 4096), (5, 8192), (7, 37), (1, 1), (300, 2048), (40, 16384)]:
