@@ -460,6 +460,29 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
                             "nvlink_peer_copy_gbs_measured": 770.0,
                             "how": "NCCL all_gather into [world, M, slab] staging + nova_b200_interleave_slabs; outside `value`"}
         del full
+        # the fused form: the contraction's epilogue stores its slab into every rank's matrix (nova_b200_gemm_push);
+        # a step is the whole exchange + contraction, to hold against ms_per_step + allgather_ms
+        if (N * os_) % 16 == 0 and all(sharding.column_slab(N, world, r)[1] * os_ % 16 == 0 for r in range(world)):
+            pm = sharding.PeerMatrix(M, N, _tdt(torch, dc))
+            a2, b2 = sets[0][0][0], sets[0][3][0]
+            for _ in range(3):
+                sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
+            ctx.barrier()
+            reps = max(5, min(steps, 30))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
+            e1.record()
+            ctx.barrier()
+            push_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / reps
+            rec["allgather_fused"] = {
+                "ms_per_step": push_ms, "value": g_flops / (push_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "bytes_sent_per_rank": M * ncount * os_ * (world - 1),
+                "how": "nova_b200_gemm_push: the epilogue stores every output box into the peers' matrices (plain stores over "
+                       "NVLink), direct calls back to back; the whole C is on every rank when the step ends"}
+            pm.close()
+            del pm
 
     if headline:
         if not args.profile:
@@ -744,7 +767,7 @@ def run_gpu(args):
             "roofline": rec["roofline"], "pct_of_bf16_dense_peak_nominal": rec["pct_of_bf16_dense_peak_nominal"],
             "per_gpu": rec["per_gpu"], "plan": rec["plan"],
         }
-        for k in ("sustained", "allgather_ms", "allgather", "partition", "no_graph_ms_per_step"):
+        for k in ("sustained", "allgather_ms", "allgather", "allgather_fused", "partition", "no_graph_ms_per_step"):
             if k in rec:
                 line[k] = rec[k]
         if subs:

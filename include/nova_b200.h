@@ -358,6 +358,24 @@ int32_t nova_b200_gather(const void* in_dev, const void* idx_dev, void* out_dev,
 int32_t nova_b200_interleave_slabs(const void* staging_dev, void* out_dev, int64_t rows, int64_t cols, int32_t world,
                                    int64_t slab_pitch, int64_t align, int32_t elem_bytes, void* stream);
 
+/* Multi-GPU, one process per GPU: the contraction whose epilogue ALSO stores every finished output box into the
+ * matrices of up to 7 peer GPUs (plain 16-byte stores to peer-mapped addresses over NVLink; no TMA, no multicast, no
+ * peer loads), so that a GEMM split by N-column slabs leaves the whole C on every GPU without a separate all-gather:
+ * rank r passes C = its own full matrix + its slab's column offset and peer_c[i] = the same position in peer i's
+ * matrix (same pitch and batch stride).  The transfer overlaps the contraction tile by tile; the peers may read
+ * their matrices once every rank's kernel has completed and the ranks have met (a barrier or any collective enqueued
+ * after the call on each rank's stream).  Needs C 16-byte aligned (base, pitch, batch stride) and N * element size a
+ * multiple of 16.  No counterpart in the reference (single device).
+ *
+ * Peer-mapped addresses across processes: nova_b200_peer_buffer_alloc allocates device memory and fills a 64-byte
+ * handle that another process of the same machine turns into an address in ITS address space with
+ * nova_b200_peer_buffer_open (CUDA IPC; peer access is enabled on first use).  Close before the owner frees. */
+int32_t nova_b200_gemm_push(const nova_b200_gemm_args* args, void* const* peer_c, int32_t n_peers, void* stream);
+int32_t nova_b200_peer_buffer_alloc(int64_t bytes, void** ptr_out, unsigned char handle_out[64]);
+int32_t nova_b200_peer_buffer_open(const unsigned char handle[64], void** ptr_out);
+int32_t nova_b200_peer_buffer_close(void* opened_ptr);
+int32_t nova_b200_peer_buffer_free(void* owned_ptr);
+
 /* Reads (and clears) the device-side status words of the current device (the allocated one and, once
  * nova_b200_gemm_f32_static has run there, the one inside its static array): 0 when every bounded wait inside the
  * kernels completed; otherwise a code naming the wait that gave up.  Synchronises the device. */

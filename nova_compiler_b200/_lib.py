@@ -76,6 +76,11 @@ PROTOTYPES = {
     "nova_b200_operand_free": (None, [C.c_void_p]),
     "nova_b200_gemm": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p]),
     "nova_b200_gemm_flat": (C.c_int32, [C.c_int64] * 17 + [C.c_int32] * 7 + [C.c_int64]),
+    "nova_b200_gemm_push": (C.c_int32, [C.POINTER(GemmArgs), C.POINTER(C.c_void_p), C.c_int32, C.c_void_p]),
+    "nova_b200_peer_buffer_alloc": (C.c_int32, [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]),
+    "nova_b200_peer_buffer_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "nova_b200_peer_buffer_close": (C.c_int32, [C.c_void_p]),
+    "nova_b200_peer_buffer_free": (C.c_int32, [C.c_void_p]),
     "nova_b200_gemm_plan": (C.c_int32, [C.POINTER(GemmArgs), C.POINTER(GemmPlanInfo)]),
     "nova_b200_gemm_host": (C.c_int32, [C.POINTER(GemmArgs)]),
     "nova_b200_gemm_f32_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),

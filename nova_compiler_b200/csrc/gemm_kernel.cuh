@@ -36,6 +36,7 @@ static constexpr int kFirstEpilogueWarp = 2;
 static constexpr int kFirstLoaderWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
 static constexpr int kThreadsTma = 32 * kFirstLoaderWarp;                      // 192
 static constexpr int kThreadsWithLoader = 32 * (kFirstLoaderWarp + kNumLoaderWarps);  // 448
+static constexpr int kMaxPushPeers = 7;      // the other GPUs of an 8-GPU box
 
 struct GemmKernelParams {
   int32_t M, N, K, batch;
@@ -62,6 +63,10 @@ struct GemmKernelParams {
   int32_t act, init, out_dtype, vec_store;
   int32_t prefetch_dist;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads (0 = none)
   uint32_t* status;
+  // multi-GPU push: every finished output box is also stored into these peers' matrices (same pitch and batch
+  // stride as C), with plain 16-byte stores over NVLink
+  int32_t n_peers;
+  void* peer_c[kMaxPushPeers];
 };
 
 // kOpTerms: operand copies per stage (2 = hi and lo halves of the 3xTF32 split, else 1)
@@ -291,6 +296,31 @@ __device__ __forceinline__ void epilogue_stage(uint8_t* box, const float (&v)[32
   }
 }
 
+// The staged box (32 rows x 128 B, swizzled) once more, into every peer GPU's copy of the output: lane l stores the
+// 16-byte chunks l, l + 32, ... (chunk = row * 8 + position in the row), so a warp instruction covers four whole
+// 128-byte row segments; plain st.global to peer-mapped addresses (no TMA, no multicast).  The host guarantees
+// 16-byte-aligned pitches and N a multiple of the chunk width, so a chunk is either whole or absent.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_push_box(const GemmKernelParams& p, const uint8_t* box, int lane, int32_t batch,
+                                                  int32_t row0, int32_t col0) {
+  constexpr int kPerChunk = 16 / static_cast<int>(sizeof(OutT));
+  uint4 v[8];
+  int64_t off[8];  // element offset of each chunk in the output, -1 when it lies outside
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = lane + 32 * i, r = idx >> 3, c = idx & 7;
+    const int32_t row = row0 + r, col = col0 + c * kPerChunk;
+    v[i] = *reinterpret_cast<const uint4*>(box + r * kSwizzleBytes + ((c ^ (r & 7)) << 4));
+    off[i] = (row < p.M && col < p.N) ? static_cast<int64_t>(batch) * p.stride_c + static_cast<int64_t>(row) * p.ldc + col : -1;
+  }
+  for (int peer = 0; peer < p.n_peers; ++peer) {
+    OutT* base = reinterpret_cast<OutT*>(p.peer_c[peer]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (off[i] >= 0) *reinterpret_cast<uint4*>(base + off[i]) = v[i];
+  }
+}
+
 // One epilogue warp drains kCols columns of its 32 accumulator rows, one 128-byte-wide box at a time.
 // kBoxes staging boxes per warp: with two, the TMA store of one box overlaps the whole of the next; with
 // one, it overlaps only the next box's first tensor-memory load and its arithmetic.
@@ -341,6 +371,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const C
         tma_store_3d(tmap_c, smem_u32(box), col0, row0, batch);  // rows >= M and columns >= N are clipped
         tma_store_commit();
       }
+      if (p.n_peers > 0) epilogue_push_box<OutT>(p, box, lane, batch, row0, col0);
       if (waits) waits[4] += clock64() - t1;
     } else {
       __syncwarp();

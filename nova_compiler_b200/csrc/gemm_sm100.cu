@@ -494,7 +494,8 @@ int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info
   return NOVA_B200_OK;
 }
 
-int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream) {
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream, void* const* peers,
+                    int32_t n_peers) {
   static thread_local Prepared cache[kPlanCacheEntries];
   static thread_local int next_slot = 0;
   if (!a || a->struct_size != sizeof(nova_b200_gemm_args)) {
@@ -550,7 +551,21 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     pr->valid = true;
     if (!hit && use_cache) next_slot = (next_slot + 1) % kPlanCacheEntries;
   }
-  const GemmKernelParams& p = pr->p;
+  GemmKernelParams pushed;
+  if (n_peers > 0) {
+    // every output box also goes to the peers: needs the TMA-store epilogue (aligned C) and whole 16-byte chunks
+    if (plan.k_zero || pi.store_c != 0 || (a->N * plan.out_bytes) % 16 != 0)
+      return fail(NOVA_B200_ERR_LAYOUT, "gemm_push: C must be 16-byte aligned (base, pitch, batch stride), N * element size a multiple of 16, K > 0");
+    if (n_peers > kMaxPushPeers || !peers) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm_push: at most 7 peers");
+    pushed = pr->p;
+    pushed.n_peers = n_peers;
+    for (int i = 0; i < n_peers; ++i) {
+      if (!peers[i] || reinterpret_cast<uintptr_t>(peers[i]) % 16 != 0)
+        return fail(NOVA_B200_ERR_INVALID_ARG, "gemm_push: a peer pointer is null or not 16-byte aligned");
+      pushed.peer_c[i] = peers[i];
+    }
+  }
+  const GemmKernelParams& p = n_peers > 0 ? pushed : pr->p;
   const CUtensorMap* maps = pr->maps;
   const bool pdl = opt.pdl.load() != 0;
 

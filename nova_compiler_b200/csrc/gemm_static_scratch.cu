@@ -14,7 +14,8 @@
 
 namespace nova {
 int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
-int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream);
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream, void* const* peers = nullptr,
+                    int32_t n_peers = 0);
 }  // namespace nova
 
 namespace {

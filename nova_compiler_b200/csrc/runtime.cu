@@ -12,7 +12,8 @@
 namespace nova {
 
 int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
-int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream);
+int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream, void* const* peers = nullptr,
+                    int32_t n_peers = 0);
 int32_t static_scratch_status(int dev, uint32_t* code_out);
 int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_t rows, int64_t cols, int64_t ld_in,
                        int64_t stride_in, int64_t ld_out, int sm_count, cudaStream_t stream);
@@ -380,6 +381,63 @@ int32_t nova_b200_gemm(const nova_b200_gemm_args* args, void* stream) {
   DeviceContext* ctx = current_context(&st);
   if (!ctx) return st;
   return gemm_launch(ctx, args, static_cast<cudaStream_t>(stream));
+}
+
+int32_t nova_b200_gemm_push(const nova_b200_gemm_args* args, void* const* peer_c, int32_t n_peers, void* stream) {
+  if (n_peers < 0 || (n_peers > 0 && !peer_c)) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm_push: bad peer list");
+  nova_b200_gemm_plan_info info;
+  int32_t st = gemm_plan_only(args, &info);
+  if (st != NOVA_B200_OK) return st;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  return gemm_launch(ctx, args, static_cast<cudaStream_t>(stream), peer_c, n_peers);
+}
+
+int32_t nova_b200_peer_buffer_alloc(int64_t bytes, void** ptr_out, unsigned char handle_out[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  if (bytes <= 0 || !ptr_out || !handle_out) return fail(NOVA_B200_ERR_INVALID_ARG, "peer_buffer_alloc: bad argument");
+  int32_t st = NOVA_B200_OK;
+  if (!current_context(&st)) return st;
+  void* p = nullptr;
+  NOVA_CUDA_OK(cudaMalloc(&p, static_cast<size_t>(bytes)));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(p);
+    return fail(NOVA_B200_ERR_CUDA, std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+  }
+  std::memcpy(handle_out, &h, 64);
+  *ptr_out = p;
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_peer_buffer_open(const unsigned char handle[64], void** ptr_out) {
+  if (!handle || !ptr_out) return fail(NOVA_B200_ERR_INVALID_ARG, "peer_buffer_open: bad argument");
+  int32_t st = NOVA_B200_OK;
+  if (!current_context(&st)) return st;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NOVA_B200_ERR_CUDA, std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+  }
+  *ptr_out = p;
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_peer_buffer_close(void* opened_ptr) {
+  if (!opened_ptr) return NOVA_B200_OK;
+  NOVA_CUDA_OK(cudaIpcCloseMemHandle(opened_ptr));
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_peer_buffer_free(void* owned_ptr) {
+  if (!owned_ptr) return NOVA_B200_OK;
+  NOVA_CUDA_OK(cudaFree(owned_ptr));
+  return NOVA_B200_OK;
 }
 
 int32_t nova_b200_gemm_flat(int64_t A, int64_t B, int64_t C, int64_t bias, int64_t residual, int64_t batch, int64_t M,

@@ -109,3 +109,85 @@ def gather_slabs(c_slab: torch.Tensor, n: int, group=None, out: Optional[torch.T
         if count:
             out[:, start:start + count] = staging[r][:, :count]
     return out
+
+
+class PeerMatrix:
+    """A row-major [rows, cols] matrix on every rank that the other ranks of the box can store into: the landing
+    place of a slab-partitioned GEMM whose epilogue pushes its columns to all GPUs (nova_b200_gemm_push).
+
+    Each rank allocates its matrix through the library (plain device memory with a CUDA IPC handle), the 64-byte
+    handles travel through the process group, and every rank opens the others' matrices in its own address space.
+    `local` is this rank's matrix as a torch tensor; `peer_ptrs` are the other ranks' base addresses as seen from here.
+    One process per GPU on one machine."""
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self._L, self._lib = L, L.load()
+        self.rows, self.cols, self.dtype, self.group = rows, cols, dtype, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        es = torch.empty((), dtype=dtype).element_size()
+        self.nbytes = rows * cols * es
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        L.check(self._lib.nova_b200_peer_buffer_alloc(self.nbytes, C.byref(ptr), handle))
+        self.ptr = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.peer_ptrs, self._opened = {}, []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                continue
+            p = C.c_void_p()
+            L.check(self._lib.nova_b200_peer_buffer_open(h, C.byref(p)))
+            self.peer_ptrs[r] = p.value
+            self._opened.append(p.value)
+
+        class _Raw:  # an integer view of the allocation; reinterpreted as `dtype` below
+            __cuda_array_interface__ = {"shape": (rows, cols), "typestr": {1: "|u1", 2: "<i2", 4: "<i4"}[es],
+                                        "data": (self.ptr, False), "version": 2}
+        self._raw = _Raw()
+        self.local = torch.as_tensor(self._raw, device=torch.device("cuda", torch.cuda.current_device())).view(dtype)
+
+    def close(self):
+        """Every rank stops using the peers' matrices, then the owners free them."""
+        if getattr(self, "ptr", None) is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            self._lib.nova_b200_peer_buffer_close(p)
+        dist.barrier(group=self.group)
+        self.local = None
+        self._lib.nova_b200_peer_buffer_free(self.ptr)
+        self.ptr = None
+
+
+def slab_matmul_push(a: torch.Tensor, b: torch.Tensor, out: "PeerMatrix", *, bias: Optional[torch.Tensor] = None,
+                     act: Optional[str] = None) -> Tuple[int, int]:
+    """This rank's column slab of C = act(A @ B + bias), written by the contraction's epilogue into `out.local` AND
+    into every peer's matrix (plain stores over NVLink, overlapped with the contraction).  The whole C is valid on
+    every rank once all ranks have passed a collective enqueued after this call (e.g. `dist.barrier()`).
+    Returns this rank's (first column, width)."""
+    import ctypes as C
+    from . import _lib as L, ops
+    rank, world = out.rank, out.world
+    start, count = column_slab(b.shape[1], world, rank)
+    if count == 0:
+        return start, 0
+    n = b.shape[1]
+    es = out.local.element_size()
+    bias_slab = bias[start:start + count].contiguous() if bias is not None else None
+    g = L.GemmArgs()
+    g.struct_size = C.sizeof(L.GemmArgs)
+    g.dtype_ab, g.dtype_c = ops._dt(a), ops._DT[out.dtype]
+    g.batch, g.M, g.N, g.K = 1, a.shape[0], count, a.shape[1]
+    g.A, g.lda = a.data_ptr(), a.stride(0)
+    g.B, g.ldb = b.data_ptr() + start * b.element_size(), b.stride(0)      # the slab of B is a view: pitch stays N
+    g.C, g.ldc = out.ptr + start * es, n
+    g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = a.shape[0] * a.stride(0), 0, a.shape[0] * n
+    g.act = ops._ACT[act]
+    if bias_slab is not None:
+        g.init, g.bias = L.INIT_BIAS_ROW, bias_slab.data_ptr()
+    peers = (C.c_void_p * max(len(out.peer_ptrs), 1))(*[p + start * es for _, p in sorted(out.peer_ptrs.items())])
+    L.check(L.load().nova_b200_gemm_push(C.byref(g), peers, len(out.peer_ptrs), ops._stream()))
+    return start, count

@@ -37,6 +37,20 @@ def _worker(rank, world, port, tmp):
     bits = lambda t: t.contiguous().cpu().view(torch.int16).numpy().view(np.uint16)
     want = O.gemm(bits(a), bits(b), dtype_in="bf16")
     ok = ok and O.rel_fro(O.from_bits(bits(gathered), "bf16"), O.from_bits(want, "bf16")) <= 1e-3
+    # the same slabs pushed by the contraction's epilogue into every rank's matrix (no all-gather)
+    pm = sharding.PeerMatrix(a.shape[0], b.shape[1] + 24, torch.bfloat16)   # 1024 columns: slabs stay 16-byte aligned
+    bw = torch.zeros(384, 1024, device="cuda", dtype=torch.bfloat16)
+    bw[:, :1000] = b
+    bias = (torch.rand(1024, device="cuda", generator=g) - 0.5).to(torch.bfloat16)
+    pm.local.fill_(-3.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sharding.slab_matmul_push(a, bw, pm, bias=bias, act="gelu")
+    torch.cuda.synchronize()
+    dist.barrier()                      # every rank's kernel has completed: the whole matrix is here
+    whole_w = ops.linear(a, bw, bias, act="gelu")
+    ok = ok and torch.equal(pm.local, whole_w)
+    pm.close()
     ok = ok and ops.device_status() == 0
     with open(os.path.join(tmp, f"rank{rank}.txt"), "w") as f:
         f.write("ok" if ok else "FAILED")
