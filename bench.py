@@ -60,8 +60,8 @@ SUB_STEPS = {"c1": 400, "c2": 400, "c3": 100, "c4": 60, "c4s": 100, "c5a": 12, "
 # DRAM bytes one launch moves according to ncu (dram__bytes_read.sum + dram__bytes_write.sum), per workload at
 # N = 1; see profiles/.  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "c2": 173.7e6,      # 134.3 MB read + 39.4 MB written (part of the 67 MB output is still in L2 at kernel end)
-    "c3": 468.5e6,      # 308.0 MB read + 160.5 MB written
+    "c2": 173.3e6,      # 134.3 MB read + 39.0 MB written (part of the 67 MB output is still in L2 at kernel end)
+    "c3": 466.7e6,      # 306.1 MB read + 160.7 MB written
     "c4": 8 * 243.4e6,  # captured on 32 of the 256 batches (c4s), scaled by 8: traffic is proportional to batches
     "c4s": 243.4e6,
     "c5c": 207.7e6,     # the contraction kernel: 140.2 MB read + 67.5 MB written (the re-pitch copy before it: 203.8 MB)
