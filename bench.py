@@ -54,9 +54,11 @@ WORKLOADS = {
     "c5a": ("GEMM bf16 16384^3", "bf16", "bf16", 1, 16384, 16384, 16384, None, "slab"),
     "c5b": ("GEMM bf16 ragged 1000x1000x999", "bf16", "bf16", 1, 1000, 1000, 999, None, None),
     "c5c": ("GEMM bf16 ragged 4095x11007x4097", "bf16", "bf16", 1, 4095, 11007, 4097, None, None),
+    "c5cp": ("GEMM bf16 ragged 4095x11007x4097 with B (the weight) prepared once: only A is re-pitched per call", "bf16", "bf16", 1,
+             4095, 11007, 4097, None, None),
 }
 # default steps of a sub-record (the headline takes --steps)
-SUB_STEPS = {"c1": 400, "c2": 400, "c3": 100, "c4": 60, "c4s": 100, "c5a": 12, "c5b": 400, "c5c": 100}
+SUB_STEPS = {"c1": 400, "c2": 400, "c3": 100, "c4": 60, "c4s": 100, "c5a": 12, "c5b": 400, "c5c": 100, "c5cp": 100}
 # DRAM bytes one launch moves according to ncu (dram__bytes_read.sum + dram__bytes_write.sum), per workload at
 # N = 1; see profiles/.  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
@@ -80,7 +82,7 @@ ROW_WORKLOADS = {
 }
 # order: latency-bound and HBM-bound records first, the seconds of dense tensor work (which pull the part into its
 # power cap) last; each record starts after a short idle so that it does not inherit the previous one's clocks
-DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "c2", "c4", "c5c", "c5a"]
+DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "c2", "c4", "c5c", "c5cp", "c5a"]
 SUB_IDLE_S = 0.75
 
 
@@ -116,7 +118,7 @@ def make_inputs_np_small(w, rows):
     rng = np.random.default_rng(1234)
     rows = min(rows, M)
     scale = 1.0 / np.sqrt(K) if w == "c2" else 1.0
-    if w in ("c1", "c5a", "c5b", "c5c"):
+    if w in ("c1", "c5a", "c5b", "c5c", "c5cp"):
         a = rng.uniform(-1, 1, (rows, K)).astype(np.float32)
         b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
     else:
@@ -294,7 +296,7 @@ def make_inputs(ctx, w, batch_range=None):
     def normal(shape, scale):
         return (torch.randn(shape, device="cuda", generator=g, dtype=torch.float32) * scale).to(dt)
 
-    if w in ("c1", "c5a", "c5b", "c5c"):
+    if w in ("c1", "c5a", "c5b", "c5c", "c5cp"):
         a, b = uniform((count, M, K)), uniform((count, K, N))
     elif w == "c2":
         a, b = normal((count, M, K), K ** -0.5), normal((count, K, N), K ** -0.5)
@@ -329,9 +331,13 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
     # Rotate over enough buffer sets that consecutive steps never find their operands in the 126 MB L2.
     n_sets = max(2, min(8, int(np.ceil(3 * 140e6 / max(r_bytes, 1))) + 1))
     sets = []
+    prepared = []
     for i in range(n_sets):
         a = a0 if i == 0 else a0.clone()
         bf = b_full if i == 0 else b_full.clone()
+        if w == "c5cp":  # the weight copied once to an aligned pitch, outside the timed region
+            prepared.append(ops.PreparedOperand(bf[0]))
+            bf = prepared[-1].tensor[None]
         bview = bf[:, :, n0:n0 + ncount]  # a column slab is a strided view: the row pitch stays N
         c = torch.empty((bcount, M, ncount), dtype=_tdt(torch, dc), device="cuda")
         sets.append((a, bview, c, bf))
@@ -341,6 +347,25 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
     def step(i):
         a, b, c, _ = sets[i % n_sets]
         ops.gemm(a, b, bias=bias, act=act, out=c)
+
+    # the same calls with the argument structs built once, as a compiled caller holds them: what a direct
+    # (un-graphed) call costs through the C ABI itself, without the Python operator layer
+    abi_args = []
+    for a_, b_, c_, _ in sets:
+        ga_ = L.GemmArgs()
+        ga_.struct_size = C.sizeof(L.GemmArgs)
+        ga_.dtype_ab = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}[dab]
+        ga_.dtype_c = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}[dc]
+        ga_.batch, ga_.M, ga_.N, ga_.K = max(bcount, 1), M, max(ncount, 1), K
+        ga_.A, ga_.B, ga_.C = a_.data_ptr(), b_.data_ptr(), c_.data_ptr()
+        ga_.lda, ga_.ldb, ga_.ldc = K, b_.stride(1), max(ncount, 1)
+        ga_.batch_stride_a, ga_.batch_stride_b, ga_.batch_stride_c = M * K, K * b_.stride(1), M * max(ncount, 1)
+        if bias is not None:
+            ga_.init, ga_.bias, ga_.act = L.INIT_BIAS_ROW, bias.data_ptr(), L.ACT_GELU_TANH
+        abi_args.append(ga_)
+
+    def step_abi(i):
+        L.check(lib.nova_b200_gemm(C.byref(abi_args[i % n_sets]), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
 
     if bcount == 0 or ncount == 0:
         def step(i):  # noqa: F811 - a rank that owns nothing still takes part in the barriers
@@ -367,7 +392,8 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
         torch.cuda.current_stream().wait_stream(side)
         graph.replay()  # one untimed replay (n_sets more warm-up steps)
 
-    def timed(n_steps, use_graph):
+    def timed(n_steps, use_graph, fn=None):
+        fn = fn or step
         ctx.barrier()
         sampler = ClockSampler(ctx.local)
         sampler.start()
@@ -378,10 +404,10 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
             for _ in range(n_steps // n_sets):
                 graph.replay()
             for i in range(n_steps % n_sets):
-                step(i)
+                fn(i)
         else:
             for i in range(n_steps):
-                step(i)
+                fn(i)
         e1.record()
         ctx.barrier()
         clocks = sampler.stop()
@@ -412,8 +438,8 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
     code = {"f32": L.F32, "f16": L.F16, "bf16": L.BF16}
     ga.dtype_ab, ga.dtype_c = code[dab], code[dc]
     ga.batch, ga.M, ga.N, ga.K = max(bcount, 1), M, max(ncount, 1), K
-    ga.lda, ga.ldb, ga.ldc = K, N, max(ncount, 1)
-    ga.batch_stride_a, ga.batch_stride_b, ga.batch_stride_c = M * K, K * N, M * max(ncount, 1)
+    ga.lda, ga.ldb, ga.ldc = K, sets[0][1].stride(1), max(ncount, 1)
+    ga.batch_stride_a, ga.batch_stride_b, ga.batch_stride_c = M * K, K * sets[0][1].stride(1), M * max(ncount, 1)
     ga.A, ga.B, ga.C = sets[0][0].data_ptr(), sets[0][1].data_ptr(), sets[0][2].data_ptr()
     info = L.GemmPlanInfo()
     L.check(lib.nova_b200_gemm_plan(C.byref(ga), C.byref(info)))
@@ -436,8 +462,9 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
                              "per_rank_columns": [sharding.column_slab(N, world, r)[1] for r in range(world)]})
     # host cost of a call: the same steps as direct calls (no graph).  Small problems are where it shows.
     if graph is not None and (w in ("c1", "c5b") or headline) and world == 1:
-        ms_direct, _ = timed(min(steps, 200), False)
+        ms_direct, _ = timed(min(steps, 200), False, step_abi)
         rec["no_graph_ms_per_step"] = ms_direct
+        rec["no_graph"] = "the same steps as direct nova_b200_gemm calls (argument structs built once), no CUDA graph"
 
     # the optional exchange: all ranks end with the whole row-major C (NCCL all-gather + one re-interleave kernel)
     if world > 1 and part == "slab" and not args.no_gather:
@@ -463,26 +490,10 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
         # the fused form: the contraction's epilogue stores its slab into every rank's matrix (nova_b200_gemm_push);
         # a step is the whole exchange + contraction, to hold against ms_per_step + allgather_ms
         if (N * os_) % 16 == 0 and all(sharding.column_slab(N, world, r)[1] * os_ % 16 == 0 for r in range(world)):
-            pm = sharding.PeerMatrix(M, N, _tdt(torch, dc))
-            a2, b2 = sets[0][0][0], sets[0][3][0]
-            for _ in range(3):
-                sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
-            ctx.barrier()
-            reps = max(5, min(steps, 30))
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
-            e1.record()
-            ctx.barrier()
-            push_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / reps
-            rec["allgather_fused"] = {
-                "ms_per_step": push_ms, "value": g_flops / (push_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "bytes_sent_per_rank": M * ncount * os_ * (world - 1),
-                "how": "nova_b200_gemm_push: the epilogue stores every output box into the peers' matrices (plain stores over "
-                       "NVLink), direct calls back to back; the whole C is on every rank when the step ends"}
-            pm.close()
-            del pm
+            try:
+                rec["allgather_fused"] = run_fused_push(ctx, sets[0], bias_full, act, M, N, ncount, os_, g_flops, steps, _tdt(torch, dc))
+            except Exception as exc:  # peer mapping unavailable on this machine: the record says so, the run goes on
+                rec["allgather_fused"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
     if headline:
         if not args.profile:
@@ -490,8 +501,37 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
         if world == 1 and not args.profile and not args.no_sustained and graph is not None:
             rec["sustained"] = run_sustained(ctx, graph, n_sets, g_flops)
     del sets, graph
+    for pr in prepared:
+        pr.free()
     torch.cuda.empty_cache()
     return rec
+
+
+def run_fused_push(ctx, set0, bias_full, act, M, N, ncount, os_, g_flops, steps, out_dtype):
+    """The slab contraction whose epilogue stores into every rank's matrix (nova_b200_gemm_push): a step is the whole
+    contraction + exchange, to hold against ms_per_step + allgather_ms."""
+    from nova_compiler_b200 import sharding
+    torch = ctx.torch
+    pm = sharding.PeerMatrix(M, N, out_dtype)
+    try:
+        a2, b2 = set0[0][0], set0[3][0]
+        for _ in range(3):
+            sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
+        ctx.barrier()
+        reps = max(5, min(steps, 30))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            sharding.slab_matmul_push(a2, b2, pm, bias=bias_full, act=act)
+        e1.record()
+        ctx.barrier()
+        push_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / reps
+    finally:
+        pm.close()
+    return {"ms_per_step": push_ms, "value": g_flops / (push_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "bytes_sent_per_rank": M * ncount * os_ * (ctx.world - 1),
+            "how": "nova_b200_gemm_push: the epilogue stores every output box into the peers' matrices (plain stores over "
+                   "NVLink), direct calls back to back; the whole C is on every rank when the step ends"}
 
 
 def run_e2e(ctx, w, set0, bias, share, g_flops):

@@ -219,6 +219,45 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, *, act: Optiona
     return y.reshape(*x.shape[:-1], w.shape[-1])
 
 
+class PreparedOperand:
+    """A constant 2-D operand (a weight) whose row pitch no tensor map can describe, copied ONCE to a 16-byte-aligned
+    pitch (nova_b200_operand_prepare).  `tensor` is a [rows, cols] strided view of the copy: pass it to gemm / matmul /
+    linear in place of the original and the call streams it with TMA without the per-call re-pitch copy."""
+
+    def __init__(self, t: torch.Tensor):
+        _require_cuda(t)
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise L.NovaB200Error(L.ERR_LAYOUT, "a prepared operand is a 2-D tensor with unit inner stride")
+        self._lib = L.load()
+        self._h = C.c_void_p()
+        rows, cols = t.shape
+        with torch.cuda.device(t.device):
+            L.check(self._lib.nova_b200_operand_prepare(t.data_ptr(), _dt(t), 1, rows, cols, t.stride(0), 0, _stream(),
+                                                        C.byref(self._h)))
+            data, ld, bs = C.c_void_p(), C.c_int64(), C.c_int64()
+            L.check(self._lib.nova_b200_operand_view(self._h, C.byref(data), C.byref(ld), C.byref(bs)))
+            es = t.element_size()
+
+            class _Raw:  # integer view of the library-owned copy, reinterpreted as t's dtype below
+                __cuda_array_interface__ = {"shape": (rows, ld.value), "typestr": {2: "<i2", 4: "<i4"}[es],
+                                            "data": (data.value, False), "version": 2}
+            self._raw = _Raw()
+            full = torch.as_tensor(self._raw, device=t.device).view(t.dtype)
+        self.tensor = full[:, :cols]
+
+    def free(self):
+        if self._h:
+            self.tensor = None
+            self._lib.nova_b200_operand_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class LnFoldedLinear:
     """nova.layer_norm + nova.linear (+ activation) as ONE contraction over the un-normalised input: the weight is
     folded once (W' = diag(gamma) W, c = column sums of W', d = beta^T W + bias; nova_b200_ln_fold_prepare), each call

@@ -155,6 +155,12 @@ def test_prepared_operand_skips_the_per_call_copy(cuda, oracle, lib):
     torch.cuda.synchronize()
     assert torch.equal(out, want)
     lib.nova_b200_operand_free(handle)
+    # the operator-level wrapper: a strided torch view of the library-owned copy
+    prep = ops.PreparedOperand(b[0])
+    assert prep.tensor.shape == (K, N) and prep.tensor.stride(0) == 528 and torch.equal(prep.tensor, b[0])
+    assert torch.equal(ops.gemm(a, prep.tensor[None]), want)
+    torch.cuda.synchronize()
+    prep.free()
 
 
 def test_rank4_descriptor_entry_point(cuda, oracle, lib):
