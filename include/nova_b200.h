@@ -142,7 +142,7 @@ typedef struct nova_b200_gemm_plan_info {
   int32_t loader_a;     /* 0 = TMA; unaligned base or pitch: 2 = re-pitched into aligned scratch first, then TMA
                            (the default), 1 = predicated ld.global loader warps (NOVA_B200_REPITCH=0) */
   int32_t loader_b;
-  int32_t store_c;      /* 0 = TMA stores of swizzled 32x128-byte boxes, 1 = element stores (unaligned C) */
+  int32_t store_c;      /* 0 = TMA stores of swizzled 32x128-byte boxes, 1 = element stores (unaligned C, or rows that end inside a 16-byte chunk) */
   int32_t block_m, block_n, block_k;
   int32_t stages;
   int32_t grid;         /* persistent CTAs launched */
@@ -172,6 +172,8 @@ int32_t nova_b200_abi_version(void);
  *   "ring_rows" (1) layer_norm rows of a few KB stream through a shared-memory ring filled by bulk copies; 2 = the
  *                  backward kernel as well (slower than its register form where measured); 0 = register kernels only
  *   "ring_stages" / "ring_ctas" (0) ring depth and CTAs per SM of those kernels, 0 = built-in choice (tuning)
+ *   "host_tiles" (0) nova_b200_gemm_host on one large product: 0 = tiles of about 2048 x 2048 released in a growing
+ *                  square, -1 = row blocks only, rows * 100 + cols = that many row blocks and column slabs (tuning)
  *   "plan_cache" (1) reuse plans and tensor maps of repeated calls;  "debug" (0)
  * No counterpart in the reference (its schedule is fixed at compile time by lowering_config attributes,
  * lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1487-1577). */

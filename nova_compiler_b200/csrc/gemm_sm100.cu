@@ -126,8 +126,10 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     }
   }
   const int osz = plan->out_bytes;
+  // The TMA-store epilogue writes whole 16-byte chunks: a row whose last chunk is partial (N * element size not a
+  // multiple of 16) inside a wider buffer would have the bytes after column N overwritten, so it takes element stores.
   const bool c_vec = reinterpret_cast<uintptr_t>(a->C) % 16 == 0 && (a->ldc * osz) % 16 == 0 &&
-                     (a->batch <= 1 || (a->batch_stride_c * osz) % 16 == 0);
+                     (a->N * osz) % 16 == 0 && (a->batch <= 1 || (a->batch_stride_c * osz) % 16 == 0);
   pi.store_c = c_vec ? 0 : 1;
 
   pi.block_m = kBlockM;

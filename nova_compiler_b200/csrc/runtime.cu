@@ -166,6 +166,7 @@ const OptionEntry kOptionTable[] = {
     {"ring_rows", "NOVA_B200_RING_ROWS", &Options::ring_rows},
     {"ring_stages", "NOVA_B200_RING_STAGES", &Options::ring_stages},
     {"ring_ctas", "NOVA_B200_RING_CTAS", &Options::ring_ctas},
+    {"host_tiles", "NOVA_B200_HOST_TILES", &Options::host_tiles},
 };
 }  // namespace
 
@@ -184,7 +185,7 @@ int32_t ensure_host_streams(DeviceContext* ctx) {
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking));
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_comp, cudaStreamNonBlocking));
   NOVA_CUDA_OK(cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking));
-  for (int i = 0; i < kHostChunks; ++i) {
+  for (int i = 0; i < kHostEvents; ++i) {
     NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
     NOVA_CUDA_OK(cudaEventCreateWithFlags(&ctx->ev_comp[i], cudaEventDisableTiming));
   }
@@ -233,7 +234,7 @@ int32_t nova_b200_shutdown(void) {
     if (c->staging) cudaFree(c->staging);
     if (c->s_in) {
       cudaStreamDestroy(c->s_in); cudaStreamDestroy(c->s_comp); cudaStreamDestroy(c->s_out);
-      for (int i = 0; i < kHostChunks; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
+      for (int i = 0; i < kHostEvents; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
     }
   }
   g_contexts.clear();
@@ -500,6 +501,87 @@ int32_t nova_b200_gemm_host(const nova_b200_gemm_args* args) {
   const bool by_batch = a.batch > 1 && a.batch_stride_a != 0 && a.batch_stride_c != 0 &&
                         (!reads_residual(a.init, a.act) || a.batch_stride_r != 0);
   const bool by_rows = a.batch == 1 && !a.trans_a && a.M >= 512 && a.K > 0;
+  // One large matrix product: tiles of (row block of A and C) x (column slab of B and C).  The device-to-host copy of
+  // C is the longest leg (C3: 180 MB against 157 MB in), so the first result tile should leave as early as possible:
+  // after ONE row block of A and ONE column slab of B have arrived, not after the whole of B.  From then on the
+  // two PCIe directions run concurrently.  Slabs are strided on both sides: 2-D copies.
+  const int64_t tiles_opt = options().host_tiles.load();
+  const bool by_tiles = tiles_opt >= 0 && by_rows && !a.trans_b && a.N >= 2048 && a.init != NOVA_B200_INIT_FROM_C &&
+                        reinterpret_cast<uintptr_t>(dB) % 16 == 0 && (a.ldb * es) % 16 == 0;
+  if (by_tiles) {
+    st = ensure_host_streams(ctx);
+    if (st != NOVA_B200_OK) return st;
+    cudaStream_t s_in = ctx->s_in, s_comp = ctx->s_comp, s_out = ctx->s_out;
+    const int64_t row_units = (a.M + 255) / 256, col_units = (a.N + 63) / 64;
+    // tiles of about 2048 x 2048: large enough that a strided copy runs at the link's rate and that the distinct tile
+    // shapes stay within the plan cache, small enough that the first results leave early
+    int rb = static_cast<int>(std::clamp<int64_t>((a.M + 1024) / 2048, 1, kHostChunks));
+    int cb = static_cast<int>(std::clamp<int64_t>((a.N + 1024) / 2048, 1, kHostChunks));
+    while (rb * cb > 30) (rb >= cb ? rb : cb) -= 1;
+    if (tiles_opt % 10000 > 0) {
+      rb = static_cast<int>(std::clamp<int64_t>(tiles_opt % 10000 / 100, 1, std::min<int64_t>(row_units, kHostChunks)));
+      cb = static_cast<int>(std::clamp<int64_t>(tiles_opt % 100, 1, std::min<int64_t>(col_units, kHostChunks)));
+    }
+    if (bias_bytes) NOVA_CUDA_OK(cudaMemcpyAsync(dBias, a.bias, bias_bytes, cudaMemcpyHostToDevice, s_in));
+    // Tile order: growing square.  Step s brings row block s and column slab s and releases the tiles whose larger
+    // index is s, so the bytes of C that may leave grow quadratically with the bytes that have arrived and the
+    // device-to-host direction is busy long before the last operand byte is in.  (Slab by slab the first rb tiles each
+    // wait for a row block of A, and the outbound link idles.)  Option host_tiles >= 10000: slab by slab.
+    std::vector<std::pair<int, int>> order;
+    order.reserve(static_cast<size_t>(rb) * cb);
+    if (tiles_opt >= 10000) {
+      for (int j = 0; j < cb; ++j)
+        for (int i = 0; i < rb; ++i) order.emplace_back(i, j);
+    } else {
+      for (int s2 = 0; s2 < std::max(rb, cb); ++s2) {
+        if (s2 < cb)
+          for (int i = 0; i <= std::min(s2, rb - 1); ++i) order.emplace_back(i, s2);
+        if (s2 < rb)
+          for (int j = 0; j < std::min(s2, cb); ++j) order.emplace_back(s2, j);
+      }
+    }
+    bool a_in[kHostChunks] = {}, b_in[kHostChunks] = {};
+    int e = 0;
+    for (const auto& [i, j] : order) {
+      const int64_t c0 = col_units * j / cb * 64, c1 = std::min<int64_t>(col_units * (j + 1) / cb * 64, a.N);
+      const int64_t r0 = row_units * i / rb * 256, r1 = std::min<int64_t>(row_units * (i + 1) / rb * 256, a.M);
+      const int64_t ncols = c1 - c0, nrows = r1 - r0;
+      if (!b_in[j]) {
+        NOVA_CUDA_OK(cudaMemcpy2DAsync(dB + c0 * es, a.ldb * es, static_cast<const char*>(a.B) + c0 * es, a.ldb * es,
+                                       ncols * es, a.K, cudaMemcpyHostToDevice, s_in));
+        b_in[j] = true;
+      }
+      if (!a_in[i]) {
+        NOVA_CUDA_OK(cudaMemcpy2DAsync(dA + r0 * a.lda * es, a.lda * es, static_cast<const char*>(a.A) + r0 * a.lda * es,
+                                       a.lda * es, a.K * es, nrows, cudaMemcpyHostToDevice, s_in));
+        a_in[i] = true;
+      }
+      if (r_bytes)
+        NOVA_CUDA_OK(cudaMemcpy2DAsync(dR + (r0 * a.ldr + c0) * os, a.ldr * os,
+                                       static_cast<const char*>(a.residual) + (r0 * a.ldr + c0) * os, a.ldr * os, ncols * os,
+                                       nrows, cudaMemcpyHostToDevice, s_in));
+      NOVA_CUDA_OK(cudaEventRecord(ctx->ev_in[e], s_in));
+      NOVA_CUDA_OK(cudaStreamWaitEvent(s_comp, ctx->ev_in[e], 0));
+      nova_b200_gemm_args d = a;
+      d.M = nrows;
+      d.N = ncols;
+      d.A = dA + r0 * a.lda * es;
+      d.B = dB + c0 * es;
+      d.C = dC + (r0 * a.ldc + c0) * os;
+      d.bias = dBias + c0 * os;
+      d.residual = dR + (r0 * a.ldr + c0) * os;
+      st = gemm_launch(ctx, &d, s_comp);
+      if (st != NOVA_B200_OK) { cudaDeviceSynchronize(); return st; }
+      NOVA_CUDA_OK(cudaEventRecord(ctx->ev_comp[e], s_comp));
+      NOVA_CUDA_OK(cudaStreamWaitEvent(s_out, ctx->ev_comp[e], 0));
+      NOVA_CUDA_OK(cudaMemcpy2DAsync(static_cast<char*>(a.C) + (r0 * a.ldc + c0) * os, a.ldc * os, dC + (r0 * a.ldc + c0) * os,
+                                     a.ldc * os, ncols * os, nrows, cudaMemcpyDeviceToHost, s_out));
+      ++e;
+    }
+    NOVA_CUDA_OK(cudaStreamSynchronize(s_out));
+    NOVA_CUDA_OK(cudaStreamSynchronize(s_in));
+    return NOVA_B200_OK;
+  }
   if ((by_batch || by_rows) && a.K > 0) {
     st = ensure_host_streams(ctx);
     if (st != NOVA_B200_OK) return st;

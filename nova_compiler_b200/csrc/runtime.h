@@ -28,7 +28,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static constexpr int kHostChunks = 8;   // pipeline depth of the *_host entry points
+static constexpr int kHostChunks = 8;   // chunks per dimension of the *_host entry points
+static constexpr int kHostEvents = kHostChunks * kHostChunks;  // one event pair per (row block, column slab) tile
 
 // Per-device state.  One instance per CUDA device the process touched through this library.
 struct DeviceContext {
@@ -52,7 +53,7 @@ struct DeviceContext {
   EncodeTiledFn encode_tiled = nullptr;
   // the *_host entry points pipeline H2D / kernel / D2H over three streams
   cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
-  cudaEvent_t ev_in[kHostChunks] = {}, ev_comp[kHostChunks] = {};
+  cudaEvent_t ev_in[kHostEvents] = {}, ev_comp[kHostEvents] = {};
   std::mutex mu;       // guards the scratch pool
   std::mutex host_mu;  // guards staging (the *_host entry points)
 };
@@ -81,6 +82,7 @@ struct Options {
   std::atomic<int64_t> plan_cache{1}; // reuse plans and tensor maps of repeated calls
   std::atomic<int64_t> pdl{1};        // launch contractions with programmatic stream serialization
   std::atomic<int64_t> ring_rows{1};  // layer_norm (forward / backward) rows of a few KB through the shared-memory ring kernels
+  std::atomic<int64_t> host_tiles{0}; // host pipeline of one large product: 0 = built-in, -1 = row blocks only, else rows * 100 + cols
   std::atomic<int64_t> debug{0};
   std::atomic<uint32_t> epoch{0};     // bumped by every change: cached plans are keyed on it
 };

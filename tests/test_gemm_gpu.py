@@ -472,6 +472,32 @@ def test_gemm_host_pipeline_carries_epilogue_operands(cuda, oracle, lib, shape):
         check(oracle, c, want, "bf16")
 
 
+@pytest.mark.parametrize("N", [2504, 2500])
+def test_gemm_host_tiled_pipeline_writes_only_its_window(cuda, oracle, lib, N):
+    """One large product from host memory is cut into (row block) x (column slab) tiles so that results start
+    flowing back before all of B has arrived; the slabs are strided 2-D copies on both sides.  Ragged extents,
+    bias + residual, and a host C that is a window of a larger buffer whose other bytes must survive."""
+    from nova_compiler_b200 import _lib as L
+    rng = np.random.default_rng(47)
+    M, K, ldc = 1100, 200, 2600   # N = 2500: B's pitch is not 16-byte aligned, so row blocks only
+    a = oracle.to_bits(rng.normal(size=(M, K)).astype(np.float32), "bf16")
+    b = oracle.to_bits(rng.normal(size=(K, N)).astype(np.float32) / 8, "bf16")
+    bias = oracle.to_bits(rng.normal(size=N).astype(np.float32), "bf16")
+    res = oracle.to_bits(rng.normal(size=(M, N)).astype(np.float32), "bf16")
+    cbuf = np.full((M + 3, ldc), 0x4321, np.uint16)
+    g = L.GemmArgs()
+    g.struct_size = C.sizeof(L.GemmArgs)
+    g.dtype_ab = g.dtype_c = L.BF16
+    g.batch, g.M, g.N, g.K = 1, M, N, K
+    g.lda, g.ldb, g.ldc, g.ldr = K, N, ldc, N
+    g.A, g.B, g.C = a.ctypes.data, b.ctypes.data, cbuf.ctypes.data
+    g.bias, g.residual, g.init, g.act = bias.ctypes.data, res.ctypes.data, L.INIT_BIAS_AND_RESIDUAL, L.ACT_RELU
+    L.check(lib.nova_b200_gemm_host(C.byref(g)))
+    want = oracle.gemm(a, b, dtype_in="bf16", bias=bias, residual=res, act="relu")
+    check(oracle, np.ascontiguousarray(cbuf[:M, :N]), want, "bf16")
+    assert np.all(cbuf[:M, N:] == 0x4321) and np.all(cbuf[M:] == 0x4321)
+
+
 def test_nova_matmul_rank_rules(cuda, oracle):
     """nova.matmul shape rules (MatmulOp::inferReturnTypes, NovaOps.cpp:1116-1285)."""
     torch = cuda

@@ -116,7 +116,8 @@ def test_bytes_around_the_output_survive(cuda, oracle, dt):
     torch = cuda
     from nova_compiler_b200 import ops
     rng = np.random.default_rng(10)
-    for (Bn, M, N, K, ldc, rows_alloc) in [(2, 200, 328, 264, 384, 256), (2, 130, 77, 100, 83, 140), (1, 256, 256, 256, 320, 300)]:
+    for (Bn, M, N, K, ldc, rows_alloc) in [(2, 200, 328, 264, 384, 256), (2, 130, 77, 100, 83, 140), (1, 256, 256, 256, 320, 300),
+                                            (2, 200, 250, 128, 256, 210)]:   # aligned pitch, rows end inside a 16-byte chunk
         a = rand_bits(oracle, rng, (Bn, M, K), dt)
         b = rand_bits(oracle, rng, (Bn, K, N), dt)
         buf = torch.full((Bn, rows_alloc, ldc), -7.0, device="cuda", dtype=_tdt(torch, dt))
