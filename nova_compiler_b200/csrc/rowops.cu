@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "ptx_sm100.cuh"
 #include "runtime.h"
@@ -1097,6 +1098,186 @@ ln_backward_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const
   }
 }
 
+// ---- two elements per instruction: sm_100's packed fp32 pipe (fma/add/mul on float2) halves the issue slots of the
+// arithmetic, which is what bounds these kernels (their DRAM traffic is already the algorithmic minimum).
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+// Pair `P` of a 16-byte vector of T as two floats (16-bit types: one 32-bit word; float: two words).
+template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v);
+#define NOVA_WORD(v, i) ((i) == 0 ? (v).x : (i) == 1 ? (v).y : (i) == 2 ? (v).z : (v).w)
+template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v) {
+  if constexpr (sizeof(T) == 4) {
+    return make_float2(__uint_as_float(NOVA_WORD(v, 2 * P)), __uint_as_float(NOVA_WORD(v, 2 * P + 1)));
+  } else if constexpr (std::is_same<T, __half>::value) {
+    const uint32_t w = NOVA_WORD(v, P);
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  } else {
+    const uint32_t w = NOVA_WORD(v, P);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+}
+#undef NOVA_WORD
+// Two floats rounded to T, as the 32-bit word (16-bit types) they occupy in a vector.
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float2 v) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 h = __float22half2_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    const __nv_bfloat162 h = __float22bfloat162_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+
+// Sums N (a power of two, <= 32) values over the warp in N - 1 + log2(32 / N) shuffles instead of 5 N: each
+// exchange step halves the values a lane still carries (the lane keeps one half of the set and hands the other to its
+// partner).  Returns the complete sum number `j` (also returned), the same in the 32 / N lanes that share it.
+template <int N>
+__device__ __forceinline__ float warp_multi_sum(float (&v)[N], int lane, int& j) {
+  int off = 16;
+  j = 0;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = up ? v[i] : v[i + n / 2];
+      const float keep = up ? v[i + n / 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+    j += up ? n / 2 : 0;
+    off >>= 1;
+  }
+#pragma unroll
+  for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+  return v[0];
+}
+
+// layer_norm_backward for rows of one 16-byte vector per thread (at most kThreads vectors), kRowsPer rows per trip,
+// in packed fp32 arithmetic.  Per trip: 2 kRowsPer vector loads in flight, the first half of the arithmetic
+//   xhat = x rstd - mean rstd,  gg = gy gamma,  s1 += gg,  s2 += gg xhat,  dgamma += gy xhat,  dbeta += gy
+// (six packed operations per element pair), ONE exchange of the 2 kRowsPer row sums (shuffle tree that halves the
+// carried values, one shared-memory round, one barrier), then dx = gg rstd - xhat (s2/D) rstd - (s1/D) rstd as two
+// packed fmas from the xhat and gg kept in registers.  Rows past the end and threads past the row load zeros and so
+// add nothing anywhere.
+template <typename T, int kRowsPer, int kThreads>
+__global__ void __launch_bounds__(kThreads, 1)
+ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
+                          const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
+                          float* __restrict__ partial, int64_t rows, int32_t D) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), NP = VEC / 2, NS = 2 * kRowsPer, kSlots = 16;
+  static_assert(kThreads / 32 <= kSlots && NS * kSlots / 4 <= 32, "one float4 of warp partials per lane");
+  __shared__ __align__(16) float red[2][NS][kSlots];  // [trip parity][sum][warp]; slots of absent warps stay zero
+  const int nvec = D / VEC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool mine = static_cast<int>(threadIdx.x) < nvec;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  for (int i = threadIdx.x; i < 2 * NS * kSlots; i += blockDim.x) (&red[0][0][0])[i] = 0.0f;
+  __syncthreads();
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  const uint4 gam_raw = mine ? reinterpret_cast<const uint4*>(gamma)[threadIdx.x] : zero4;
+  float2 gam[NP], dg[NP], db[NP];
+  gam[0] = pair_of<T, 0>(gam_raw);
+  gam[1] = pair_of<T, 1>(gam_raw);
+  if constexpr (NP == 4) { gam[2] = pair_of<T, 2>(gam_raw); gam[3] = pair_of<T, 3>(gam_raw); }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) dg[p] = db[p] = make_float2(0.0f, 0.0f);
+  uint32_t trip = 0;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPer;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * kRowsPer; r0 < rows; r0 += step) {
+    uint4 pg[kRowsPer], px[kRowsPer];
+    float rs[kRowsPer], nmr[kRowsPer];
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      const bool live = mine && r < rows;
+      pg[k] = live ? reinterpret_cast<const uint4*>(gy + r * D)[threadIdx.x] : zero4;
+      px[k] = live ? reinterpret_cast<const uint4*>(x + r * D)[threadIdx.x] : zero4;
+    }
+    if (mine && (threadIdx.x & 7) == 0) {  // the trip after this one into L2, one request per 128-byte line
+#pragma unroll
+      for (int k = 0; k < kRowsPer; ++k) {
+        const int64_t r = r0 + step + k;
+        if (r < rows) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(gy + r * D) + threadIdx.x));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(x + r * D) + threadIdx.x));
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      const bool live = r < rows;
+      rs[k] = live ? ld_f32<T>(rstd[r]) : 0.0f;
+      nmr[k] = live ? -ld_f32<T>(mean_sum[r]) * inv_d * rs[k] : 0.0f;
+    }
+    float2 kxh[kRowsPer][NP], kgg[kRowsPer][NP];
+    float s[NS];
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      float2 s1 = make_float2(0.0f, 0.0f), s2 = make_float2(0.0f, 0.0f);
+      const float2 rs2 = splat2(rs[k]), nmr2 = splat2(nmr[k]);
+      auto first_half = [&](int p, float2 g2, float2 x2) {
+        const float2 xh = __ffma2_rn(x2, rs2, nmr2);
+        const float2 gg = __fmul2_rn(g2, gam[p]);
+        s1 = __fadd2_rn(s1, gg);
+        s2 = __ffma2_rn(gg, xh, s2);
+        dg[p] = __ffma2_rn(g2, xh, dg[p]);
+        db[p] = __fadd2_rn(db[p], g2);
+        kxh[k][p] = xh;
+        kgg[k][p] = gg;
+      };
+      first_half(0, pair_of<T, 0>(pg[k]), pair_of<T, 0>(px[k]));
+      first_half(1, pair_of<T, 1>(pg[k]), pair_of<T, 1>(px[k]));
+      if constexpr (NP == 4) {
+        first_half(2, pair_of<T, 2>(pg[k]), pair_of<T, 2>(px[k]));
+        first_half(3, pair_of<T, 3>(pg[k]), pair_of<T, 3>(px[k]));
+      }
+      s[2 * k] = s1.x + s1.y;
+      s[2 * k + 1] = s2.x + s2.y;
+    }
+    // exchange: (a warp writes this buffer again two trips on, after the barrier of the trip in between: by then
+    // every reader of this trip is done)
+    float (*buf)[kSlots] = red[trip & 1u];
+    ++trip;
+    int j;
+    const float mine_sum = warp_multi_sum<NS>(s, lane, j);
+    if ((lane & (32 / NS - 1)) == 0) buf[j][warp] = mine_sum;
+    __syncthreads();
+    // lane l adds four warps' partials of sum l / 4; two more exchanges complete it in the four lanes 4j .. 4j + 3
+    float4 q = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (lane < NS * kSlots / 4) q = reinterpret_cast<const float4*>(&buf[0][0])[lane];
+    float t = (q.x + q.y) + (q.z + q.w);
+    t += __shfl_xor_sync(0xffffffffu, t, 1);
+    t += __shfl_xor_sync(0xffffffffu, t, 2);
+#pragma unroll
+    for (int k = 0; k < kRowsPer; ++k) {
+      const int64_t r = r0 + k;
+      const float m1 = __shfl_sync(0xffffffffu, t, 8 * k) * inv_d, m2 = __shfl_sync(0xffffffffu, t, 8 * k + 4) * inv_d;
+      const float2 a2 = splat2(rs[k]), b2 = splat2(-m2 * rs[k]), c2 = splat2(-m1 * rs[k]);
+      uint4 o;
+      if constexpr (NP == 4) {
+        o.x = pack_pair<T>(__ffma2_rn(kxh[k][0], b2, __ffma2_rn(kgg[k][0], a2, c2)));
+        o.y = pack_pair<T>(__ffma2_rn(kxh[k][1], b2, __ffma2_rn(kgg[k][1], a2, c2)));
+        o.z = pack_pair<T>(__ffma2_rn(kxh[k][2], b2, __ffma2_rn(kgg[k][2], a2, c2)));
+        o.w = pack_pair<T>(__ffma2_rn(kxh[k][3], b2, __ffma2_rn(kgg[k][3], a2, c2)));
+      } else {
+        const float2 lo = __ffma2_rn(kxh[k][0], b2, __ffma2_rn(kgg[k][0], a2, c2));
+        const float2 hi = __ffma2_rn(kxh[k][1], b2, __ffma2_rn(kgg[k][1], a2, c2));
+        o = make_uint4(__float_as_uint(lo.x), __float_as_uint(lo.y), __float_as_uint(hi.x), __float_as_uint(hi.y));
+      }
+      if (mine && r < rows) reinterpret_cast<uint4*>(dx + r * D)[threadIdx.x] = o;
+    }
+  }
+  if (mine) {
+    float* pdg = partial + static_cast<size_t>(blockIdx.x) * 2 * D + threadIdx.x * VEC;
+    float* pdb = pdg + D;
+#pragma unroll
+    for (int p = 0; p < NP; p += 2) {
+      reinterpret_cast<float4*>(pdg)[p / 2] = make_float4(dg[p].x, dg[p].y, dg[p + 1].x, dg[p + 1].y);
+      reinterpret_cast<float4*>(pdb)[p / 2] = make_float4(db[p].x, db[p].y, db[p + 1].x, db[p + 1].y);
+    }
+  }
+}
+
 // dgamma[c] = sum over CTAs of partial[cta][0][c], dbeta[c] likewise from [cta][1][c]; several CTA slices per
 // column are combined through shared memory so that short D still fills the machine.
 template <typename T>
@@ -1420,6 +1601,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   // rows of up to 512 vectors: four rows per trip in one 128-register CTA per SM (measured best of 1, 2, 4 rows
   // per trip and of one or two CTAs per SM on [8192, 4096] bf16)
   const int rows_per = threads <= 512 ? 4 : 1;
+  const bool packed = options().ring_rows.load() != 0;  // 0: the scalar-arithmetic form of the same schedule
   int resident = !wide ? (max_v >= 4 ? 1 : 2) : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
   const int64_t row_blocks = wide ? (rows + rows_per - 1) / rows_per : rows;
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(row_blocks, static_cast<int64_t>(ctx->sm_count) * resident)));
@@ -1437,9 +1619,15 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
                                                               static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
                                                               static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
                                                               static_cast<int32_t>(D))
+#define NOVA_LNB_PACKED(T)                                                                                            \
+  ln_backward_packed_kernel<T, 4, 512><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
+                                                               static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
+                                                               static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
+                                                               static_cast<int32_t>(D))
 #define NOVA_LNB_MV(T, V)                                                                       \
   do {                                                                                          \
-    if (wide && rows_per == 4) NOVA_LNB_ROWS(T, V, 4, 512);                                     \
+    if (wide && rows_per == 4 && V > 1 && packed) NOVA_LNB_PACKED(T);                           \
+    else if (wide && rows_per == 4) NOVA_LNB_ROWS(T, V, 4, 512);                                \
     else if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);             \
     else if (max_v == 4) NOVA_LNB(T, V, 4); else NOVA_LNB(T, V, 8);                             \
   } while (0)
@@ -1447,6 +1635,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   else if (dtype == NOVA_B200_F16) { if (vec > 1) NOVA_LNB_MV(__half, 8); else NOVA_LNB_MV(__half, 1); }
   else { if (vec > 1) NOVA_LNB_MV(__nv_bfloat16, 8); else NOVA_LNB_MV(__nv_bfloat16, 1); }
 #undef NOVA_LNB_MV
+#undef NOVA_LNB_PACKED
 #undef NOVA_LNB_ROWS
 #undef NOVA_LNB
   NOVA_CUDA_OK(cudaGetLastError());
