@@ -298,6 +298,101 @@ int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
 constexpr uint32_t kStatusRowRingWait = 0x201;
 constexpr uint32_t kRingSpinLimit = 1u << 24;
 
+// ---- two elements per instruction: sm_100's packed fp32 pipe (fma/add/mul on float2) halves the issue slots of the
+// arithmetic, which is what bounds these kernels (their DRAM traffic is already the algorithmic minimum).
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+// Pair `P` of a 16-byte vector of T as two floats (16-bit types: one 32-bit word; float: two words).
+template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v);
+#define NOVA_WORD(v, i) ((i) == 0 ? (v).x : (i) == 1 ? (v).y : (i) == 2 ? (v).z : (v).w)
+template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v) {
+  if constexpr (sizeof(T) == 4) {
+    return make_float2(__uint_as_float(NOVA_WORD(v, 2 * P)), __uint_as_float(NOVA_WORD(v, 2 * P + 1)));
+  } else if constexpr (std::is_same<T, __half>::value) {
+    const uint32_t w = NOVA_WORD(v, P);
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  } else {
+    const uint32_t w = NOVA_WORD(v, P);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+}
+#undef NOVA_WORD
+// Two floats rounded to T, as the 32-bit word (16-bit types) they occupy in a vector.
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float2 v) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 h = __float22half2_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    const __nv_bfloat162 h = __float22bfloat162_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+
+// Sums N (a power of two, <= 32) values over the warp in N - 1 + log2(32 / N) shuffles instead of 5 N: each
+// exchange step halves the values a lane still carries (the lane keeps one half of the set and hands the other to its
+// partner).  Returns the complete sum number `j` (also returned), the same in the 32 / N lanes that share it.
+template <int N>
+__device__ __forceinline__ float warp_multi_sum(float (&v)[N], int lane, int& j) {
+  int off = 16;
+  j = 0;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1) {
+    const bool up = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = up ? v[i] : v[i + n / 2];
+      const float keep = up ? v[i + n / 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+    j += up ? n / 2 : 0;
+    off >>= 1;
+  }
+#pragma unroll
+  for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+  return v[0];
+}
+
+// f(p, pair p of `v` as two floats) for every element pair of a 16-byte vector of T.
+template <typename T, typename F>
+__device__ __forceinline__ void for_pairs(const uint4& v, F&& f) {
+  f(0, pair_of<T, 0>(v));
+  f(1, pair_of<T, 1>(v));
+  if constexpr (sizeof(T) == 2) {
+    f(2, pair_of<T, 2>(v));
+    f(3, pair_of<T, 3>(v));
+  }
+}
+// Pair `p` of the 16-byte vector assembled in `w`, rounded to T.
+template <typename T>
+__device__ __forceinline__ void put_pair(uint32_t (&w)[4], int p, float2 v) {
+  if constexpr (sizeof(T) == 4) {
+    w[2 * p] = __float_as_uint(v.x);
+    w[2 * p + 1] = __float_as_uint(v.y);
+  } else {
+    w[p] = pack_pair<T>(v);
+  }
+}
+
+// Two sums over the 256 threads of a CTA with one barrier (exchange buffer alternating per call, as row_reduce2):
+// the warp stage halves the carried values after the first exchange (6 shuffles instead of 10).
+__device__ __forceinline__ void cta256_sum2(float& a, float& b, float2 (*red_smem)[8], uint32_t& phase) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float v[2] = {a, b};
+  int j;
+  const float m = warp_multi_sum<2>(v, lane, j);
+  float* buf = reinterpret_cast<float*>(red_smem[phase & 1u]);
+  ++phase;
+  if ((lane & 15) == 0) buf[2 * warp + j] = m;
+  __syncthreads();
+  float2 r = reinterpret_cast<const float2*>(buf)[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    r.x += __shfl_xor_sync(0xffffffffu, r.x, o);
+    r.y += __shfl_xor_sync(0xffffffffu, r.y, o);
+  }
+  a = r.x;
+  b = r.y;
+}
+
 // One lane per warp polls (these kernels are bound by instruction issue, and 32 lanes spinning on one barrier are
 // 32 times the instructions); the warp reconverges on __syncwarp, which also orders the lanes' later reads of the slot
 // after the observed completion.
@@ -321,10 +416,9 @@ ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
                T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D, int32_t kStages,
                uint32_t* status) {
   constexpr int VEC = 16 / static_cast<int>(sizeof(T));
-  using P = Pack<T, VEC>;
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full[kRingMaxStages];
-  __shared__ float2 red2[2][8];
+  __shared__ __align__(16) float2 red2[2][8];
   __shared__ uint32_t abort_smem;
   volatile uint32_t* abort_flag = &abort_smem;
   uint32_t red_phase = 0;
@@ -349,39 +443,43 @@ ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
       }
     }
   }
-  // short rows keep their gamma / beta vectors in registers; longer ones re-read them (L1 / L2 hits) to stay at
-  // a register count that lets several CTAs share an SM
+  // short rows keep their gamma / beta vectors in registers (as floats: no conversion per row); longer ones re-read
+  // them (L1 / L2 hits) to stay at a register count that lets several CTAs share an SM.  Arithmetic is packed fp32.
   constexpr bool kPreload = kMaxV <= 2;
-  P g[kPreload ? kMaxV : 1], b[kPreload ? kMaxV : 1];
+  constexpr int NP = VEC / 2;
+  float2 gf[kPreload ? kMaxV : 1][NP], bf[kPreload ? kMaxV : 1][NP];
   if (kPreload) {
 #pragma unroll
     for (int k = 0; k < kMaxV; ++k) {
       const int i = t + k * kRowThreads;
-      if (i < nvec) { g[k] = reinterpret_cast<const P*>(gamma)[i]; b[k] = reinterpret_cast<const P*>(beta)[i]; }
+      const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+      const uint4 gr = i < nvec ? reinterpret_cast<const uint4*>(gamma)[i] : zero4;
+      const uint4 br = i < nvec ? reinterpret_cast<const uint4*>(beta)[i] : zero4;
+      for_pairs<T>(gr, [&](int p, float2 v) { gf[kPreload ? k : 0][p] = v; });
+      for_pairs<T>(br, [&](int p, float2 v) { bf[kPreload ? k : 0][p] = v; });
     }
   }
   uint32_t it = 0;
   for (int64_t row = blockIdx.x; row < rows; row += step, ++it) {
     const int s = it % kStages;
     ring_wait(smem_u32(&full[s]), (it / kStages) & 1u, abort_flag, status);
-    const P* slot = reinterpret_cast<const P*>(ring + static_cast<size_t>(s) * row_bytes);
-    P cache[kMaxV];
-    float s0 = 0.0f, s1 = 0.0f;
+    const uint4* slot = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(s) * row_bytes);
+    uint4 cache[kMaxV];
+    float2 a0 = make_float2(0.0f, 0.0f), a1 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int k = 0; k < kMaxV; ++k) {
       const int i = t + k * kRowThreads;
       if (i < nvec) {
         cache[k] = slot[i];
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float v = ld_f32<T>(cache[k].e[e]);
-          s0 += v;
-          s1 += v * v;
-        }
+        for_pairs<T>(cache[k], [&](int, float2 v) {
+          a0 = __fadd2_rn(a0, v);
+          a1 = __ffma2_rn(v, v, a1);
+        });
       }
     }
-    row_reduce2<kRowThreads, false>(s0, s1, red2, red_phase);  // one barrier: every thread has read the slot
-    if (*abort_flag != 0u) break;                              // (raised before the barrier: all threads see it)
+    float s0 = a0.x + a0.y, s1 = a1.x + a1.y;
+    cta256_sum2(s0, s1, red2, red_phase);   // one barrier: every thread has read the slot
+    if (*abort_flag != 0u) break;           // (raised before the barrier: all threads see it)
     if (t == 0) {
       const int64_t nr = row + kStages * step;
       if (nr < rows) {
@@ -395,18 +493,27 @@ ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
       if (mean_sum) mean_sum[row] = st_f32<T>(s0);
       if (rstd_out) rstd_out[row] = st_f32<T>(rstd);
     }
-    P* yr = reinterpret_cast<P*>(y + row * D);
+    const float2 rs2 = splat2(rstd), nm2 = splat2(-mean * rstd);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
 #pragma unroll
     for (int k = 0; k < kMaxV; ++k) {
       const int i = t + k * kRowThreads;
       if (i < nvec) {
-        const P gk = kPreload ? g[kPreload ? k : 0] : reinterpret_cast<const P*>(gamma)[i];
-        const P bk = kPreload ? b[kPreload ? k : 0] : reinterpret_cast<const P*>(beta)[i];
-        P o;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e)
-          o.e[e] = st_f32<T>((ld_f32<T>(cache[k].e[e]) - mean) * rstd * ld_f32<T>(gk.e[e]) + ld_f32<T>(bk.e[e]));
-        yr[i] = o;
+        uint32_t w[4];
+        if (kPreload) {
+          for_pairs<T>(cache[k], [&](int p, float2 v) {
+            put_pair<T>(w, p, __ffma2_rn(__ffma2_rn(v, rs2, nm2), gf[kPreload ? k : 0][p], bf[kPreload ? k : 0][p]));
+          });
+        } else {
+          const uint4 gr = reinterpret_cast<const uint4*>(gamma)[i], br = reinterpret_cast<const uint4*>(beta)[i];
+          float2 gk[NP], bk[NP];
+          for_pairs<T>(gr, [&](int p, float2 v) { gk[p] = v; });
+          for_pairs<T>(br, [&](int p, float2 v) { bk[p] = v; });
+          for_pairs<T>(cache[k], [&](int p, float2 v) {
+            put_pair<T>(w, p, __ffma2_rn(__ffma2_rn(v, rs2, nm2), gk[p], bk[p]));
+          });
+        }
+        yr[i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }
@@ -1098,59 +1205,6 @@ ln_backward_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const
   }
 }
 
-// ---- two elements per instruction: sm_100's packed fp32 pipe (fma/add/mul on float2) halves the issue slots of the
-// arithmetic, which is what bounds these kernels (their DRAM traffic is already the algorithmic minimum).
-__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
-// Pair `P` of a 16-byte vector of T as two floats (16-bit types: one 32-bit word; float: two words).
-template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v);
-#define NOVA_WORD(v, i) ((i) == 0 ? (v).x : (i) == 1 ? (v).y : (i) == 2 ? (v).z : (v).w)
-template <typename T, int P> __device__ __forceinline__ float2 pair_of(const uint4& v) {
-  if constexpr (sizeof(T) == 4) {
-    return make_float2(__uint_as_float(NOVA_WORD(v, 2 * P)), __uint_as_float(NOVA_WORD(v, 2 * P + 1)));
-  } else if constexpr (std::is_same<T, __half>::value) {
-    const uint32_t w = NOVA_WORD(v, P);
-    return __half22float2(*reinterpret_cast<const __half2*>(&w));
-  } else {
-    const uint32_t w = NOVA_WORD(v, P);
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-  }
-}
-#undef NOVA_WORD
-// Two floats rounded to T, as the 32-bit word (16-bit types) they occupy in a vector.
-template <typename T> __device__ __forceinline__ uint32_t pack_pair(float2 v) {
-  if constexpr (std::is_same<T, __half>::value) {
-    const __half2 h = __float22half2_rn(v);
-    return *reinterpret_cast<const uint32_t*>(&h);
-  } else {
-    const __nv_bfloat162 h = __float22bfloat162_rn(v);
-    return *reinterpret_cast<const uint32_t*>(&h);
-  }
-}
-
-// Sums N (a power of two, <= 32) values over the warp in N - 1 + log2(32 / N) shuffles instead of 5 N: each
-// exchange step halves the values a lane still carries (the lane keeps one half of the set and hands the other to its
-// partner).  Returns the complete sum number `j` (also returned), the same in the 32 / N lanes that share it.
-template <int N>
-__device__ __forceinline__ float warp_multi_sum(float (&v)[N], int lane, int& j) {
-  int off = 16;
-  j = 0;
-#pragma unroll
-  for (int n = N; n > 1; n >>= 1) {
-    const bool up = (lane & off) != 0;
-#pragma unroll
-    for (int i = 0; i < n / 2; ++i) {
-      const float send = up ? v[i] : v[i + n / 2];
-      const float keep = up ? v[i + n / 2] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-    j += up ? n / 2 : 0;
-    off >>= 1;
-  }
-#pragma unroll
-  for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
-  return v[0];
-}
-
 // layer_norm_backward for rows of one 16-byte vector per thread (at most kThreads vectors), kRowsPer rows per trip,
 // in packed fp32 arithmetic.  Per trip: 2 kRowsPer vector loads in flight, the first half of the arithmetic
 //   xhat = x rstd - mean rstd,  gg = gy gamma,  s1 += gg,  s2 += gg xhat,  dgamma += gy xhat,  dbeta += gy
@@ -1158,8 +1212,8 @@ __device__ __forceinline__ float warp_multi_sum(float (&v)[N], int lane, int& j)
 // carried values, one shared-memory round, one barrier), then dx = gg rstd - xhat (s2/D) rstd - (s1/D) rstd as two
 // packed fmas from the xhat and gg kept in registers.  Rows past the end and threads past the row load zeros and so
 // add nothing anywhere.
-template <typename T, int kRowsPer, int kThreads>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int kRowsPer, int kThreads, int kMinCtas>
+__global__ void __launch_bounds__(kThreads, kMinCtas)
 ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
                           const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
                           float* __restrict__ partial, int64_t rows, int32_t D) {
@@ -1597,12 +1651,16 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   const int threads = static_cast<int>(wide ? (nvec + 31) / 32 * 32 : kRowThreads);
   const int per_thread = static_cast<int>((nvec + threads - 1) / threads);
   const int max_v = per_thread <= 1 ? 1 : per_thread <= 2 ? 2 : per_thread <= 4 ? 4 : 8;
-  // few persistent CTAs: every CTA ends with 2*D floats of column sums that the finish kernel has to read back
-  // rows of up to 512 vectors: four rows per trip in one 128-register CTA per SM (measured best of 1, 2, 4 rows
-  // per trip and of one or two CTAs per SM on [8192, 4096] bf16)
-  const int rows_per = threads <= 512 ? 4 : 1;
-  const bool packed = options().ring_rows.load() != 0;  // 0: the scalar-arithmetic form of the same schedule
-  int resident = !wide ? (max_v >= 4 ? 1 : 2) : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
+  // few persistent CTAs: every CTA ends with 2*D floats of column sums that the finish kernel has to read back.
+  // Rows of up to 512 vectors, vectorised: the packed-arithmetic kernel, two rows per trip in 64 registers so that
+  // 1024 threads are resident per SM (measured on [8192, 4096] bf16: 47.2 us; four rows per trip in one 128-register
+  // CTA per SM, option "ring_ctas" = 1: 48.6 us; the scalar-arithmetic form, option "ring_rows" = 0: 67.8 us).
+  const bool packed = wide && vec > 1 && threads <= 512 && options().ring_rows.load() != 0;
+  const bool two_ctas = packed && options().ring_ctas.load() != 1;
+  const int rows_per = threads <= 512 ? (two_ctas ? 2 : 4) : 1;
+  int resident = !wide ? (max_v >= 4 ? 1 : 2)
+                       : two_ctas ? std::max(2, std::min(8, 1024 / threads))
+                                  : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
   const int64_t row_blocks = wide ? (rows + rows_per - 1) / rows_per : rows;
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(row_blocks, static_cast<int64_t>(ctx->sm_count) * resident)));
   void* scratch = nullptr;
@@ -1620,13 +1678,19 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
                                                               static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
                                                               static_cast<int32_t>(D))
 #define NOVA_LNB_PACKED(T)                                                                                            \
-  ln_backward_packed_kernel<T, 4, 512><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
+  ln_backward_packed_kernel<T, 4, 512, 1><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
+                                                               static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
+                                                               static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
+                                                               static_cast<int32_t>(D))
+#define NOVA_LNB_PACKED2(T)                                                                                           \
+  ln_backward_packed_kernel<T, 2, 512, 2><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
                                                                static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
                                                                static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
                                                                static_cast<int32_t>(D))
 #define NOVA_LNB_MV(T, V)                                                                       \
   do {                                                                                          \
-    if (wide && rows_per == 4 && V > 1 && packed) NOVA_LNB_PACKED(T);                           \
+    if (two_ctas && V > 1) NOVA_LNB_PACKED2(T);                                                 \
+    else if (wide && rows_per == 4 && V > 1 && packed) NOVA_LNB_PACKED(T);                      \
     else if (wide && rows_per == 4) NOVA_LNB_ROWS(T, V, 4, 512);                                \
     else if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);             \
     else if (max_v == 4) NOVA_LNB(T, V, 4); else NOVA_LNB(T, V, 8);                             \
@@ -1636,6 +1700,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   else { if (vec > 1) NOVA_LNB_MV(__nv_bfloat16, 8); else NOVA_LNB_MV(__nv_bfloat16, 1); }
 #undef NOVA_LNB_MV
 #undef NOVA_LNB_PACKED
+#undef NOVA_LNB_PACKED2
 #undef NOVA_LNB_ROWS
 #undef NOVA_LNB
   NOVA_CUDA_OK(cudaGetLastError());
