@@ -393,6 +393,72 @@ __device__ __forceinline__ void cta256_sum2(float& a, float& b, float2 (*red_sme
   b = r.y;
 }
 
+// softmax of rows that fit one warp's registers (at most 32 * kMaxV 16-byte vectors), one warp per row, no CTA barrier.
+// exp(x - max) is evaluated ONCE per element and kept in fp32 registers for the normalisation (the special-function
+// unit retires 16 results per SM and cycle: two evaluations per element would cost more than the row's HBM time), the
+// row maximum is taken on the packed 16-bit words, and the remaining arithmetic is packed fp32.  Lanes past the row
+// carry -inf (exp gives 0) so that no arithmetic is predicated.
+template <typename T, int kMaxV>
+__global__ void __launch_bounds__(kRowThreads)
+softmax_warp_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int32_t D, float* __restrict__ row_stats) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), NP = VEC / 2, kRowsPerCta = kRowThreads / 32;
+  const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
+  const int nvec = D / VEC;
+  const uint32_t ninf = sizeof(T) == 4 ? 0xff800000u : std::is_same<T, __half>::value ? 0xfc00fc00u : 0xff80ff80u;
+  const uint4 fill = make_uint4(ninf, ninf, ninf, ninf);
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + sub; row < rows; row += step) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+    uint4 cache[kMaxV];
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) cache[k] = lane + 32 * k < nvec ? xr[lane + 32 * k] : fill;
+    float m;
+    if constexpr (sizeof(T) == 4) {
+      m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < kMaxV; ++k)
+        m = fmaxf(fmaxf(m, fmaxf(__uint_as_float(cache[k].x), __uint_as_float(cache[k].y))),
+                  fmaxf(__uint_as_float(cache[k].z), __uint_as_float(cache[k].w)));
+    } else {
+      using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+      auto as2 = [](uint32_t w) { return *reinterpret_cast<const T2*>(&w); };
+      T2 mm = as2(ninf);
+#pragma unroll
+      for (int k = 0; k < kMaxV; ++k)
+        mm = __hmax2(__hmax2(mm, __hmax2(as2(cache[k].x), as2(cache[k].y))), __hmax2(as2(cache[k].z), as2(cache[k].w)));
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(&mm);
+      const float2 f = pair_of<T, 0>(make_uint4(w, 0u, 0u, 0u));
+      m = fmaxf(f.x, f.y);
+    }
+    m = warp_max(m);
+    const float2 neg_m = splat2(-m), log2e = splat2(1.4426950408889634f);
+    float2 e[kMaxV][NP];
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      for_pairs<T>(cache[k], [&](int p, float2 v) {
+        const float2 a = __fmul2_rn(__fadd2_rn(v, neg_m), log2e);
+        float2 r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(a.x));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(a.y));
+        e[k][p] = r;
+        acc = __fadd2_rn(acc, r);
+      });
+    }
+    const float total = warp_sum(acc.x + acc.y);
+    if (row_stats != nullptr && lane == 0) { row_stats[2 * row] = m; row_stats[2 * row + 1] = total; }
+    const float2 recip = splat2(1.0f / fmaxf(total, 1.0e-7f));
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      uint32_t w[4];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) put_pair<T>(w, p, __fmul2_rn(e[k][p], recip));
+      if (lane + 32 * k < nvec) yr[lane + 32 * k] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // One lane per warp polls (these kernels are bound by instruction issue, and 32 lanes spinning on one barrier are
 // 32 times the instructions); the warp reconverges on __syncwarp, which also orders the lanes' later reads of the slot
 // after the observed completion.
@@ -769,6 +835,16 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     else if (nvec <= kRowThreads * 4) NOVA_LN_RING(4);
     else NOVA_LN_RING(8);
 #undef NOVA_LN_RING
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
+  if (kMode == 1 && VEC > 1 && nvec <= 32 * 8 && ring_rows_enabled()) {
+    // one warp per row, many short-lived CTAs (see the note on launch_grid)
+    const int64_t ctas = (rows + kRowThreads / 32 - 1) / (kRowThreads / 32);
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(ctas, static_cast<int64_t>(sm_count) * 32)));
+    if (nvec <= 32 * 2) softmax_warp_kernel<T, 2><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
+    else if (nvec <= 32 * 4) softmax_warp_kernel<T, 4><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
+    else softmax_warp_kernel<T, 8><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
     NOVA_CUDA_OK(cudaGetLastError());
     return NOVA_B200_OK;
   }
