@@ -1302,6 +1302,7 @@ ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, con
   const float inv_d = 1.0f / static_cast<float>(D);
   for (int i = threadIdx.x; i < 2 * NS * kSlots; i += blockDim.x) (&red[0][0][0])[i] = 0.0f;
   __syncthreads();
+  griddep_launch_dependents();  // the finish kernel may be scheduled as SMs free up; it waits for this grid's end
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
   const uint4 gam_raw = mine ? reinterpret_cast<const uint4*>(gamma)[threadIdx.x] : zero4;
   float2 gam[NP], dg[NP], db[NP];
@@ -1415,6 +1416,7 @@ __global__ void ln_backward_finish_kernel(const float* __restrict__ partial, int
                                           T* __restrict__ dgamma, T* __restrict__ dbeta) {
   __shared__ float sh[2][32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;  // blockDim = (32, 32)
+  griddep_wait();  // launched while the kernel that writes `partial` is still running (programmatic serialization)
   float a = 0.0f, b = 0.0f;
   if (c < D)
   {
@@ -1555,6 +1557,23 @@ __global__ void __launch_bounds__(256) row_stats_kernel(const T* __restrict__ x,
   for (int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < rows; row += warps) {
     const P* xr = reinterpret_cast<const P*>(x + row * D);
     float s0 = 0.0f, s1 = 0.0f;
+    if constexpr (VEC > 1) {  // packed fp32 arithmetic; vectors past the row are zeros and add nothing
+      const uint4* xv = reinterpret_cast<const uint4*>(xr);
+      float2 a0 = make_float2(0.0f, 0.0f), a1 = make_float2(0.0f, 0.0f);
+      for (int i0 = lane; i0 < nvec; i0 += 32 * 8) {
+        uint4 pk[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) pk[u] = i0 + u * 32 < nvec ? xv[i0 + u * 32] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          for_pairs<T>(pk[u], [&](int, float2 v) {
+            a0 = __fadd2_rn(a0, v);
+            a1 = __ffma2_rn(v, v, a1);
+          });
+      }
+      s0 = a0.x + a0.y;
+      s1 = a1.x + a1.y;
+    } else {
     for (int i0 = lane; i0 < nvec; i0 += 32 * 8) {
       P pk[8];
 #pragma unroll
@@ -1571,6 +1590,7 @@ __global__ void __launch_bounds__(256) row_stats_kernel(const T* __restrict__ x,
           }
         }
       }
+    }
     }
     s0 = warp_sum(s0);
     s1 = warp_sum(s1);
@@ -1632,6 +1652,34 @@ __global__ void interleave_slabs_kernel(const uint8_t* __restrict__ staging, uin
     else *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<const uint16_t*>(src);
   }
 }
+
+namespace {
+// The finish kernel is launched with programmatic stream serialization: it is scheduled while the main kernel's last
+// CTAs still run and blocks in griddepcontrol.wait until that grid has ended, so its launch latency is off the
+// critical path.  (Kernels that never call launch_dependents release their dependents when they end: the attribute
+// is safe after any of the main kernels.)
+template <typename T>
+int32_t launch_finish_t(const float* partial, int n_partials, int64_t D, void* dgamma, void* dbeta, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((D + 31) / 32), 1, 1);
+  cfg.blockDim = dim3(32, 32, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = options().pdl.load() != 0 ? 1 : 0;
+  NOVA_CUDA_OK(cudaLaunchKernelEx(&cfg, ln_backward_finish_kernel<T>, partial, static_cast<int32_t>(n_partials),
+                                  static_cast<int32_t>(D), static_cast<T*>(dgamma), static_cast<T*>(dbeta)));
+  return NOVA_B200_OK;
+}
+int32_t launch_ln_backward_finish(const float* partial, int n_partials, int64_t D, int32_t dtype, void* dgamma, void* dbeta,
+                                  cudaStream_t s) {
+  if (dtype == NOVA_B200_F32) return launch_finish_t<float>(partial, n_partials, D, dgamma, dbeta, s);
+  if (dtype == NOVA_B200_F16) return launch_finish_t<__half>(partial, n_partials, D, dgamma, dbeta, s);
+  return launch_finish_t<__nv_bfloat16>(partial, n_partials, D, dgamma, dbeta, s);
+}
+}  // namespace
 
 extern "C" {
 
@@ -1713,15 +1761,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
 #undef NOVA_LNB_RING_T
 #undef NOVA_LNB_RING
     NOVA_CUDA_OK(cudaGetLastError());
-    const int fin_grid = static_cast<int>((D + 31) / 32);
-    if (dtype == NOVA_B200_F32)
-      ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
-    else if (dtype == NOVA_B200_F16)
-      ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
-    else
-      ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
-    NOVA_CUDA_OK(cudaGetLastError());
-    return NOVA_B200_OK;
+    return launch_ln_backward_finish(partial, grid, D, dtype, dgamma, dbeta, s);
   }
   const bool wide = nvec <= 1024;
   const int threads = static_cast<int>(wide ? (nvec + 31) / 32 * 32 : kRowThreads);
@@ -1780,15 +1820,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
 #undef NOVA_LNB_ROWS
 #undef NOVA_LNB
   NOVA_CUDA_OK(cudaGetLastError());
-  const int fin_grid = static_cast<int>((D + 31) / 32);
-  if (dtype == NOVA_B200_F32)
-    ln_backward_finish_kernel<float><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<float*>(dgamma), static_cast<float*>(dbeta));
-  else if (dtype == NOVA_B200_F16)
-    ln_backward_finish_kernel<__half><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
-  else
-    ln_backward_finish_kernel<__nv_bfloat16><<<fin_grid, dim3(32, 32), 0, s>>>(partial, grid, static_cast<int32_t>(D), static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta));
-  NOVA_CUDA_OK(cudaGetLastError());
-  return NOVA_B200_OK;
+  return launch_ln_backward_finish(partial, grid, D, dtype, dgamma, dbeta, s);
 }
 
 int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32_t dtype, void* stream) {
