@@ -775,6 +775,9 @@ struct SplitOperand {
 };
 
 __global__ void nova_split_tf32_kernel(const SplitOperand oa, const SplitOperand ob) {
+  // the contraction that consumes this scratch is launched with programmatic serialization: let its prologue
+  // (barriers, tensor-memory allocation) start now; it waits for this whole grid before its first global access
+  griddep_launch_dependents();
   const SplitOperand& o = blockIdx.y == 0 ? oa : ob;
   // four output columns per thread (ld_out is a multiple of 4 and the scratch is 16-byte aligned); the input is
   // read as one float4 when its row start allows, else element-wise
@@ -823,6 +826,7 @@ struct RepitchOperand {
 template <typename ElemT>
 __global__ void nova_repitch_kernel(const RepitchOperand oa, const RepitchOperand ob) {
   constexpr int kPerChunk = 16 / static_cast<int>(sizeof(ElemT));
+  griddep_launch_dependents();  // as in nova_split_tf32_kernel
   const RepitchOperand& o = blockIdx.y == 0 ? oa : ob;
   const int32_t chunks_per_row = o.ld_out / kPerChunk;
   const int64_t n = o.rows_total * chunks_per_row;
