@@ -82,7 +82,7 @@ ROW_WORKLOADS = {
 }
 # order: latency-bound and HBM-bound records first, the seconds of dense tensor work (which pull the part into its
 # power cap) last; each record starts after a short idle so that it does not inherit the previous one's clocks
-DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "c2", "c4", "c5c", "c5cp", "c5a"]
+DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "sce", "sce_bwd", "c2", "c4", "c5c", "c5cp", "c5a"]
 SUB_IDLE_S = 0.75
 
 

@@ -772,6 +772,188 @@ softmax_smem_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, in
   }
 }
 
+// softmax of vocabulary-sized rows (up to 224 KB): the row lives in shared memory, filled in 16 KB chunks by bulk copies
+// (cp.async.bulk, completion counted per chunk on an mbarrier); thread t owns vector t of every chunk.
+//   pass A  waits for the chunks as they land and takes the maximum;
+//   pass B  e = exp(x - max), summed; fp32 rows keep e in place of x (one evaluation per element); the first four chunks
+//           move to registers and are handed back at once;
+//   pass C  writes e / sum and hands the other chunks back (a barrier the 32 warps arrive on); thread 0 refills every
+//           chunk that has been handed back with the same chunk of the CTA's NEXT row.
+// So the next row streams in while this one is still being summed and written: the SM reads and writes at the same time
+// instead of alternating a load phase, two reductions and a store phase.  All waits are bounded; a wait that gives up raises the
+// CTA's abort flag, which every thread tests after the row's first reduction barrier.
+constexpr int kStreamChunkBytes = 16384;
+constexpr int kStreamMaxChunks = 14;
+constexpr uint32_t kStatusSoftmaxStreamWait = 0x202;
+
+template <typename T>
+__global__ void __launch_bounds__(kSmemRowThreads)
+softmax_stream_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int32_t D, float* __restrict__ row_stats,
+                      uint32_t* status) {
+  extern __shared__ __align__(128) uint8_t stream_row[];
+  __shared__ __align__(8) uint64_t full[kStreamMaxChunks];
+  __shared__ __align__(8) uint64_t consumed[kStreamMaxChunks];
+  __shared__ float red[2][kSmemRowThreads / 32];
+  __shared__ uint32_t abort_smem;
+  volatile uint32_t* abort_flag = &abort_smem;
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  constexpr bool kKeepExp = sizeof(T) == 4;
+  constexpr int kRegChunks = 4;   // 16 registers per thread
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int nvec = D / VEC;
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * sizeof(T);
+  const int nchunks = (row_bytes + kStreamChunkBytes - 1) / kStreamChunkBytes;
+  auto chunk_bytes = [&](int c) { return c + 1 < nchunks ? static_cast<uint32_t>(kStreamChunkBytes) : row_bytes - static_cast<uint32_t>(c) * kStreamChunkBytes; };
+  if (t == 0) {
+    for (int c = 0; c < nchunks; ++c) {
+      mbar_init(smem_u32(&full[c]), 1);
+      mbar_init(smem_u32(&consumed[c]), kSmemRowThreads / 32);
+    }
+    abort_smem = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  auto fill = [&](int64_t row, int c) {  // thread 0 only
+    mbar_arrive_expect_tx(smem_u32(&full[c]), chunk_bytes(c));
+    bulk_load(smem_u32(stream_row + static_cast<size_t>(c) * kStreamChunkBytes),
+              reinterpret_cast<const uint8_t*>(x + row * D) + static_cast<size_t>(c) * kStreamChunkBytes, chunk_bytes(c),
+              smem_u32(&full[c]));
+  };
+  // one polling lane per warp; gives up when the limit is reached or another thread already has
+  auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+    if (lane == 0) {
+      bool done = false;
+      for (uint32_t spin = 0; spin < kRingSpinLimit && !done; ++spin) {
+        done = mbar_try_wait(smem_u32(bar), parity);
+        if (!done && (spin & 1023u) == 1023u && *abort_flag != 0u) break;
+      }
+      if (!done) {
+        *abort_flag = 1u;
+        atomicCAS(status, 0u, kStatusSoftmaxStreamWait);
+      }
+    }
+    __syncwarp();
+  };
+  uint32_t red_phase = 0;
+  auto block_reduce = [&](float v, bool is_max) {  // one barrier: the exchange buffer alternates between calls
+    v = is_max ? warp_max(v) : warp_sum(v);
+    float* buf = red[red_phase & 1u];
+    ++red_phase;
+    if (lane == 0) buf[warp] = v;
+    __syncthreads();
+    const float r = buf[lane];  // 32 warps
+    return is_max ? warp_max(r) : warp_sum(r);
+  };
+  if (t == 0 && blockIdx.x < rows)
+    for (int c = 0; c < nchunks; ++c) fill(blockIdx.x, c);
+  const float2 log2e = splat2(1.4426950408889634f);
+  uint32_t it = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
+    const uint32_t ph = it & 1u;
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+    // ---- pass A
+    float m = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) {
+      wait_on(&full[c], ph);
+      const int i = c * (kStreamChunkBytes / 16) + t;
+      if (i < nvec) {
+        const uint4 v = reinterpret_cast<const uint4*>(stream_row)[i];
+        for_pairs<T>(v, [&](int, float2 f) { m = fmaxf(m, fmaxf(f.x, f.y)); });
+      }
+    }
+    const float row_max = block_reduce(m, true);
+    if (*abort_flag != 0u) break;  // raised before that barrier by whoever gave up: uniform
+    // ---- pass B
+    const float2 neg_max = splat2(-row_max);
+    const int64_t next = row + gridDim.x;
+    int refill = 0;  // thread 0: chunks of the next row requested so far
+    auto hand_back = [&](int c) {   // every lane is done with chunk c of this row
+      if (next >= rows) return;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&consumed[c]));
+      // thread 0 refills whatever the 32 warps have handed back so far, without waiting: a producer that blocked here
+      // would fall a chunk further behind the other warps at every step and delay the whole next row
+      if (t == 0)
+        while (refill < c && mbar_test_wait(smem_u32(&consumed[refill]), ph)) fill(next, refill++);
+    };
+    auto exp_of = [&](float2 f) {
+      const float2 a = __fmul2_rn(__fadd2_rn(f, neg_max), log2e);
+      float2 e;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(a.x));
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(a.y));
+      return e;
+    };
+    float2 acc = make_float2(0.0f, 0.0f);
+    // The first kRegChunks chunks leave shared memory here (four measured best: 667 us on [8192, 50304] f32; six 670, eight 702, none 707): their e (fp32 rows) or x (16-bit rows) stays in registers
+    // for pass C, so they are handed back at once and the next row's copies run during this pass and the reduction
+    // after it, when the SM would otherwise move no bytes at all.
+    uint4 kept[kRegChunks];
+#pragma unroll
+    for (int c = 0; c < kRegChunks; ++c) {
+      if (c < nchunks) {
+        const int i = c * (kStreamChunkBytes / 16) + t;
+        kept[c] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < nvec) {
+          const uint4 v = reinterpret_cast<const uint4*>(stream_row)[i];
+          uint32_t w[4];
+          for_pairs<T>(v, [&](int p, float2 f) {
+            const float2 e = exp_of(f);
+            acc = __fadd2_rn(acc, e);
+            if (kKeepExp) put_pair<T>(w, p, e);
+          });
+          kept[c] = kKeepExp ? make_uint4(w[0], w[1], w[2], w[3]) : v;
+        }
+        hand_back(c);
+      }
+    }
+    for (int c = kRegChunks; c < nchunks; ++c) {
+      const int i = c * (kStreamChunkBytes / 16) + t;
+      if (i < nvec) {
+        const uint4 v = reinterpret_cast<const uint4*>(stream_row)[i];
+        uint32_t w[4];
+        for_pairs<T>(v, [&](int p, float2 f) {
+          const float2 e = exp_of(f);
+          acc = __fadd2_rn(acc, e);
+          if (kKeepExp) put_pair<T>(w, p, e);
+        });
+        if (kKeepExp) reinterpret_cast<uint4*>(stream_row)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    // this thread's writes of e (the only generic-proxy writes to the row) are ordered before the bulk copies that will
+    // refill those chunks: once per row, ahead of the barrier below and of every hand-back in pass C
+    if (kKeepExp) fence_proxy_async_smem();
+    const float total = block_reduce(acc.x + acc.y, false);
+    if (row_stats != nullptr && t == 0) { row_stats[2 * row] = row_max; row_stats[2 * row + 1] = total; }
+    const float2 recip = splat2(1.0f / fmaxf(total, 1.0e-7f));
+    // ---- pass C
+    auto emit = [&](int i, const uint4& v) {
+      uint32_t w[4];
+      for_pairs<T>(v, [&](int p, float2 f) { put_pair<T>(w, p, __fmul2_rn(kKeepExp ? f : exp_of(f), recip)); });
+      yr[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    };
+#pragma unroll
+    for (int c = 0; c < kRegChunks; ++c) {
+      const int i = c * (kStreamChunkBytes / 16) + t;
+      if (c < nchunks && i < nvec) emit(i, kept[c]);
+    }
+    for (int c = kRegChunks; c < nchunks; ++c) {
+      const int i = c * (kStreamChunkBytes / 16) + t;
+      if (i < nvec) emit(i, reinterpret_cast<const uint4*>(stream_row)[i]);
+      hand_back(c);
+    }
+    if (next < rows && warp == 0) {   // the rest, in order, now waiting (the other warps are at most a chunk away)
+      for (int c = __shfl_sync(0xffffffffu, refill, 0); c < nchunks; ++c) {
+        wait_on(&consumed[c], ph);
+        if (t == 0 && *abort_flag == 0u) fill(next, c);
+      }
+    }
+  }
+  if (*abort_flag != 0u && t == 0)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // let copies still in flight land before the CTA's memory is reused
+  __syncthreads();
+}
+
 template <typename T, int VEC, int kMode>
 int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, void* y, void* mean_sum, void* rstd,
                           int64_t rows, int64_t D, int sm_count, cudaStream_t st, float* stats, uint32_t* status) {
@@ -861,7 +1043,17 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     else if (nvec <= kRowThreads * 4) NOVA_ROW(kRowThreads, 4);
     else if (nvec <= kRowThreads * 8) NOVA_ROW(kRowThreads, 8);
     else if (nvec <= kRowThreads * 16) NOVA_ROW(kRowThreads, 16);
-    else if (kMode == 1 && D * static_cast<int64_t>(sizeof(T)) <= kSmemRowBytes) {
+    else if (kMode == 1 && status != nullptr && ring_rows_enabled() && D * static_cast<int64_t>(sizeof(T)) <= kSmemRowBytes) {
+      auto kernel = softmax_stream_kernel<T>;
+      const int smem = static_cast<int>((D * sizeof(T) + kStreamChunkBytes - 1) / kStreamChunkBytes) * kStreamChunkBytes;
+      static bool configured = false;  // same on every device this library runs on (one architecture)
+      if (!configured) {
+        NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamMaxChunks * kStreamChunkBytes));
+        configured = true;
+      }
+      const int grid = static_cast<int>(rows < sm_count ? rows : sm_count);
+      kernel<<<grid, kSmemRowThreads, smem, st>>>(xp, yp, rows, d, stats, status);
+    } else if (kMode == 1 && D * static_cast<int64_t>(sizeof(T)) <= kSmemRowBytes) {
       auto kernel = softmax_smem_kernel<T, VEC>;
       const int smem = static_cast<int>(D * sizeof(T));
       NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemRowBytes));
@@ -1835,7 +2027,7 @@ int32_t nova_b200_softmax(const void* x, void* y, int64_t rows, int64_t D, int32
   if ((st = check_pointer_device(ctx, x, "nova_b200_softmax: the input")) != NOVA_B200_OK) return st;
   if ((st = check_pointer_device(ctx, y, "nova_b200_softmax: the output")) != NOVA_B200_OK) return st;
   return dispatch_row_kernel<1>(x, nullptr, nullptr, y, nullptr, nullptr, rows, D, dtype, ctx->sm_count,
-                                static_cast<cudaStream_t>(stream));
+                                static_cast<cudaStream_t>(stream), nullptr, ctx->status_word);
 }
 
 static bool is_index_dtype(int32_t dt) { return dt == NOVA_B200_I16 || dt == NOVA_B200_I32 || dt == NOVA_B200_I64; }
@@ -1859,7 +2051,8 @@ int32_t nova_b200_sce(const void* logits, const void* targets, void* softmax_out
   if (st != NOVA_B200_OK) return st;
   float* stats = static_cast<float*>(scratch);
   if (rows > 0 && C > 0) {
-    st = dispatch_row_kernel<1>(logits, nullptr, nullptr, softmax_out, nullptr, nullptr, rows, C, dtype, ctx->sm_count, s, stats);
+    st = dispatch_row_kernel<1>(logits, nullptr, nullptr, softmax_out, nullptr, nullptr, rows, C, dtype, ctx->sm_count, s, stats,
+                                ctx->status_word);
     if (st != NOVA_B200_OK) return st;
   }
   const int64_t loss_rows = C > 0 ? rows : 0;

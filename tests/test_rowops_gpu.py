@@ -56,6 +56,24 @@ def test_softmax(cuda, oracle, dt):
         if dt == "f32":
             e = np.exp(x.astype(np.float64) - x.astype(np.float64).max(-1, keepdims=True))
             assert oracle.rel_fro(y, e / e.sum(-1, keepdims=True)) <= 2e-6
+    # more vocabulary rows than SMs: every CTA of the streaming kernel takes several rows, so the chunks of its next
+    # row are copied in over the row it is still writing; ragged last chunk (50304 * 4 B = 12 chunks + 4.6 KB).  Checked
+    # against float64 on every row, and against the kernel that stages one row at a time.
+    from nova_compiler_b200 import _lib as L
+    for rows, D in [(470, 50304 if dt == "f32" else 100352), (301, 8200)]:
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
+        xd = to_dev(cuda, x, dt)
+        y = ops.softmax(xd)
+        xf = oracle.from_bits(x, dt).astype(np.float64)
+        e = np.exp(xf - xf.max(-1, keepdims=True))
+        assert oracle.rel_fro(oracle.from_bits(to_host(cuda, y, dt), dt), e / e.sum(-1, keepdims=True)) <= (2e-6 if dt == "f32" else 3e-3)
+        assert ops.device_status() == 0
+        L.set_option("ring_rows", 0)
+        try:
+            y0 = ops.softmax(xd)
+        finally:
+            L.set_option("ring_rows", 1)
+        assert oracle.rel_fro(oracle.from_bits(to_host(cuda, y, dt), dt), oracle.from_bits(to_host(cuda, y0, dt), dt)) <= (1e-6 if dt == "f32" else 3e-3)
     # non-last dimension and the attention-score layout
     x = rand_bits(oracle, rng, (4, 96, 50), "f32", "normal")
     y = ops.softmax(to_dev(cuda, x, "f32"), dimension=1)
