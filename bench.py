@@ -68,13 +68,14 @@ NCU_TRAFFIC_BYTES = {
     "c4s": 243.4e6,
     "c5c": 207.7e6,     # the contraction kernel: 140.2 MB read + 67.5 MB written (the re-pitch copy before it: 203.8 MB)
     # row kernels (reads match the inputs exactly; part of each output is still in L2 when the kernel ends)
-    "ln": 92.3e6, "ln_bwd": 176.0e6, "softmax": 489.8e6, "sce": 3246.0e6, "sce_bwd": 3252.9e6, "gather": 209.2e6,
+    "ln": 88.6e6, "ln_bwd": 182.1e6, "softmax": 488.6e6, "sce": 3246.0e6, "sce_bwd": 3252.9e6, "gather": 209.2e6,
 }
 
 # HBM-bound companions of the contraction: name -> (description, dtype, rows, D)
 ROW_WORKLOADS = {
     "ln": ("nova.layer_norm bf16 [8192, 4096] (the rows that feed the C3 linear)", "bf16", 8192, 4096),
     "softmax": ("nova.softmax f16 [65536, 2048] (attention-score rows, C4 layout, 32 of its 256 batches)", "f16", 65536, 2048),
+    "softmax8k": ("nova.softmax f16 [16384, 8192] (score rows of an 8192-token context)", "f16", 16384, 8192),
     "gather": ("nova.gather bf16 table [50304, 4096], 16384 i32 ids (embedding lookup)", "bf16", 16384, 4096),
     "ln_bwd": ("nova.layer_norm_backward bf16 [8192, 4096] (dx, dgamma, dbeta from one read of gy and x)", "bf16", 8192, 4096),
     "sce": ("nova.sce f32 logits [8192, 50304], i16 targets (softmax + mean loss; the vocabulary rows of ltest/test.mlir)", "f32", 8192, 50304),
@@ -82,7 +83,7 @@ ROW_WORKLOADS = {
 }
 # order: latency-bound and HBM-bound records first, the seconds of dense tensor work (which pull the part into its
 # power cap) last; each record starts after a short idle so that it does not inherit the previous one's clocks
-DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "gather", "ln_bwd", "sce", "sce_bwd", "c2", "c4", "c5c", "c5cp", "c5a"]
+DEFAULT_SUBS = ["c1", "c5b", "ln", "softmax", "softmax8k", "gather", "ln_bwd", "sce", "sce_bwd", "c2", "c4", "c5c", "c5cp", "c5a"]
 SUB_IDLE_S = 0.75
 
 

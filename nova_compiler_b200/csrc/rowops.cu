@@ -588,6 +588,124 @@ ln_ring_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __
   __syncthreads();
 }
 
+// One value over the 256 threads of a CTA, one barrier (exchange buffer alternating per call).
+template <bool kMax>
+__device__ __forceinline__ float cta256_reduce1(float v, float (*buf)[8], uint32_t& phase) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  v = kMax ? warp_max(v) : warp_sum(v);
+  float* b = buf[phase & 1u];
+  ++phase;
+  if (lane == 0) b[warp] = v;
+  __syncthreads();
+  float r = b[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) {
+    const float q = __shfl_xor_sync(0xffffffffu, r, o);
+    r = kMax ? fmaxf(r, q) : r + q;
+  }
+  return r;
+}
+
+// softmax rows of 4-32 KB through the same ring as ln_ring_kernel: a persistent 256-thread CTA, row slots filled by
+// bulk copies, the row's vectors in registers after the first read.  Two CTA barriers per row (maximum, sum); the slot
+// is refilled after the first.  exp is evaluated once per element where the values fit in registers as floats (fp32
+// rows; 16-bit rows of up to 512 vectors), else once for the sum and once for the output; packed fp32 arithmetic.
+template <typename T, int kMaxV>
+__global__ void __launch_bounds__(kRowThreads)
+softmax_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int32_t D, int32_t kStages,
+                    float* __restrict__ row_stats, uint32_t* status) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), NP = VEC / 2;
+  constexpr bool kKeep = sizeof(T) == 4 || kMaxV <= 2;
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full[kRingMaxStages];
+  __shared__ float red[2][8];
+  __shared__ uint32_t abort_smem;
+  volatile uint32_t* abort_flag = &abort_smem;
+  uint32_t red_phase = 0;
+  const int t = threadIdx.x;
+  const int nvec = D / VEC;
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * sizeof(T);
+  if (t == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    abort_smem = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const int64_t step = gridDim.x;
+  if (t == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      const int64_t r = blockIdx.x + s * step;
+      if (r < rows) {
+        mbar_arrive_expect_tx(smem_u32(&full[s]), row_bytes);
+        bulk_load(smem_u32(ring + static_cast<size_t>(s) * row_bytes), x + r * D, row_bytes, smem_u32(&full[s]));
+      }
+    }
+  }
+  const uint32_t ninf = sizeof(T) == 4 ? 0xff800000u : std::is_same<T, __half>::value ? 0xfc00fc00u : 0xff80ff80u;
+  const uint4 fill = make_uint4(ninf, ninf, ninf, ninf);  // vectors past the row: exp gives 0
+  const float2 log2e = splat2(1.4426950408889634f);
+  uint32_t it = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += step, ++it) {
+    const int s = it % kStages;
+    ring_wait(smem_u32(&full[s]), (it / kStages) & 1u, abort_flag, status);
+    const uint4* slot = reinterpret_cast<const uint4*>(ring + static_cast<size_t>(s) * row_bytes);
+    uint4 cache[kMaxV];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kRowThreads;
+      cache[k] = i < nvec ? slot[i] : fill;
+      for_pairs<T>(cache[k], [&](int, float2 f) { m = fmaxf(m, fmaxf(f.x, f.y)); });
+    }
+    m = cta256_reduce1<true>(m, red, red_phase);   // every thread has read the slot
+    if (*abort_flag != 0u) break;                  // (raised before the barrier: all threads see it)
+    if (t == 0) {
+      const int64_t nr = row + kStages * step;
+      if (nr < rows) {
+        mbar_arrive_expect_tx(smem_u32(&full[s]), row_bytes);
+        bulk_load(smem_u32(ring + static_cast<size_t>(s) * row_bytes), x + nr * D, row_bytes, smem_u32(&full[s]));
+      }
+    }
+    const float2 neg_m = splat2(-m);
+    auto exp_of = [&](float2 f) {
+      const float2 a = __fmul2_rn(__fadd2_rn(f, neg_m), log2e);
+      float2 e;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(a.x));
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(a.y));
+      return e;
+    };
+    float2 e[kKeep ? kMaxV : 1][NP];
+    float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k)
+      for_pairs<T>(cache[k], [&](int p, float2 f) {
+        const float2 v = exp_of(f);
+        acc = __fadd2_rn(acc, v);
+        if (kKeep) e[kKeep ? k : 0][p] = v;
+      });
+    const float total = cta256_reduce1<false>(acc.x + acc.y, red, red_phase);
+    if (row_stats != nullptr && t == 0) { row_stats[2 * row] = m; row_stats[2 * row + 1] = total; }
+    const float2 recip = splat2(1.0f / fmaxf(total, 1.0e-7f));
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = t + k * kRowThreads;
+      uint32_t w[4];
+      if (kKeep) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) put_pair<T>(w, p, __fmul2_rn(e[kKeep ? k : 0][p], recip));
+      } else {
+        for_pairs<T>(cache[k], [&](int p, float2 f) { put_pair<T>(w, p, __fmul2_rn(exp_of(f), recip)); });
+      }
+      if (i < nvec) yr[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (*abort_flag != 0u && t == 0)
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);  // let copies still in flight land before the CTA's memory is reused
+  __syncthreads();
+}
+
 // layer_norm_backward the same way: a slot holds one row of grad_y and one of x (two bulk copies, one barrier
 // phase); a thread owns the same vectors of every row, so dgamma / dbeta accumulate in its registers and leave as
 // one partial row per CTA; the next row's mean and rstd are fetched a row ahead.
@@ -1028,6 +1146,27 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     if (nvec <= 32 * 2) softmax_warp_kernel<T, 2><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
     else if (nvec <= 32 * 4) softmax_warp_kernel<T, 4><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
     else softmax_warp_kernel<T, 8><<<grid, kRowThreads, 0, st>>>(xp, yp, rows, d, stats);
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
+  if (kMode == 1 && VEC > 1 && status != nullptr && nvec > 32 * 8 && nvec <= kRowThreads * 8 && ring_rows_enabled()) {
+    const size_t row_bytes = static_cast<size_t>(D) * sizeof(T);
+    int stages = 2;
+    if (const int64_t o = options().ring_stages.load(); o >= 2 && o <= kRingMaxStages) stages = static_cast<int>(o);
+#define NOVA_SM_RING(MAXV_)                                                                                          \
+    do {                                                                                                             \
+      auto kernel = softmax_ring_kernel<T, MAXV_>;                                                                   \
+      const size_t smem = stages * row_bytes;                                                                        \
+      int resident = ring_resident_ctas(kernel, kRowThreads, smem);                                                  \
+      if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, std::string("softmax: the ring kernel cannot be configured: ") + nova_b200_last_error_string()); \
+      if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);      \
+      const int grid = static_cast<int>(std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * resident));         \
+      kernel<<<grid, kRowThreads, smem, st>>>(xp, yp, rows, d, stages, stats, status);                               \
+    } while (0)
+    if (nvec <= kRowThreads * 2) NOVA_SM_RING(2);
+    else if (nvec <= kRowThreads * 4) NOVA_SM_RING(4);
+    else NOVA_SM_RING(8);
+#undef NOVA_SM_RING
     NOVA_CUDA_OK(cudaGetLastError());
     return NOVA_B200_OK;
   }

@@ -47,6 +47,12 @@ def test_softmax(cuda, oracle, dt):
         x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
         y = ops.softmax(to_dev(cuda, x, dt))
         check(oracle, to_host(cuda, y, dt), oracle.softmax(x, dt, compute_f32=True), dt)
+    # rows of 4-32 KB, more of them than resident CTAs: the ring kernel refills its slots while rows are in flight
+    for rows, D in [(2100, 4608), (1900, 2560)]:
+        x = rand_bits(oracle, rng, (rows, D), dt, "normal", 3.0)
+        y = ops.softmax(to_dev(cuda, x, dt))
+        check(oracle, to_host(cuda, y, dt), oracle.softmax(x, dt, compute_f32=True), dt)
+        assert ops.device_status() == 0
     # rows beyond the register cache: staged in shared memory (up to 220 KB) or read twice (longer).  The oracle adds
     # the exponentials one by one in fp32, which drifts ~4e-5 over such rows; f32 is also checked against float64.
     for rows, D in [(4, 50304), (2, 70000)]:
