@@ -459,6 +459,62 @@ softmax_warp_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, in
   }
 }
 
+// layer_norm of rows that fit one warp's registers (at most 32 * kMaxV 16-byte vectors; 2 KB for kMaxV = 4), one warp
+// per row, no CTA barrier, packed fp32 arithmetic; the row's two sums cross the warp in one six-shuffle tree.  gamma
+// and beta are re-read per row (L1 hits): a warp's registers hold the row, not the parameters.
+template <typename T, int kMaxV>
+__global__ void __launch_bounds__(kRowThreads)
+ln_warp_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+               T* __restrict__ mean_sum, T* __restrict__ rstd_out, int64_t rows, int32_t D) {
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), kRowsPerCta = kRowThreads / 32;
+  const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
+  const int nvec = D / VEC;
+  const float inv_d = 1.0f / static_cast<float>(D);
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+  const uint4* b4 = reinterpret_cast<const uint4*>(beta);
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + sub; row < rows; row += step) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+    uint4 cache[kMaxV];
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) cache[k] = lane + 32 * k < nvec ? xr[lane + 32 * k] : zero4;  // zeros add nothing
+    float2 a0 = make_float2(0.0f, 0.0f), a1 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k)
+      for_pairs<T>(cache[k], [&](int, float2 v) {
+        a0 = __fadd2_rn(a0, v);
+        a1 = __ffma2_rn(v, v, a1);
+      });
+    float v2[2] = {a0.x + a0.y, a1.x + a1.y};
+    int j;
+    const float mine = warp_multi_sum<2>(v2, lane, j);   // lanes 0-15 hold the sum, lanes 16-31 the sum of squares
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+    const float s0 = j == 0 ? mine : other, s1 = j == 0 ? other : mine;
+    const float mean = s0 * inv_d;
+    const float rstd = rsqrtf(s1 * inv_d - mean * mean + 1e-5f);
+    if (lane == 0) {
+      if (mean_sum) mean_sum[row] = st_f32<T>(s0);
+      if (rstd_out) rstd_out[row] = st_f32<T>(rstd);
+    }
+    const float2 rs2 = splat2(rstd), nm2 = splat2(-mean * rstd);
+#pragma unroll
+    for (int k = 0; k < kMaxV; ++k) {
+      const int i = lane + 32 * k;
+      if (i < nvec) {
+        const uint4 gr = g4[i], br = b4[i];
+        float2 gk[VEC / 2], bk[VEC / 2];
+        for_pairs<T>(gr, [&](int p, float2 v) { gk[p] = v; });
+        for_pairs<T>(br, [&](int p, float2 v) { bk[p] = v; });
+        uint32_t w[4];
+        for_pairs<T>(cache[k], [&](int p, float2 v) { put_pair<T>(w, p, __ffma2_rn(__ffma2_rn(v, rs2, nm2), gk[p], bk[p])); });
+        yr[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
+
 // One lane per warp polls (these kernels are bound by instruction issue, and 32 lanes spinning on one barrier are
 // 32 times the instructions); the warp reconverges on __syncwarp, which also orders the lanes' later reads of the slot
 // after the observed completion.
@@ -1139,6 +1195,16 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     NOVA_CUDA_OK(cudaGetLastError());
     return NOVA_B200_OK;
   }
+  if (kMode == 0 && VEC > 1 && nvec <= 32 * 4 && ring_rows_enabled()) {
+    // one warp per row, many short-lived CTAs (see the note on launch_grid)
+    const int64_t ctas = (rows + kRowThreads / 32 - 1) / (kRowThreads / 32);
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(ctas, static_cast<int64_t>(sm_count) * 32)));
+    if (nvec <= 32) ln_warp_kernel<T, 1><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+    else if (nvec <= 64) ln_warp_kernel<T, 2><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+    else ln_warp_kernel<T, 4><<<grid, kRowThreads, 0, st>>>(xp, gp, bp, yp, mp, rp, rows, d);
+    NOVA_CUDA_OK(cudaGetLastError());
+    return NOVA_B200_OK;
+  }
   if (kMode == 1 && VEC > 1 && nvec <= 32 * 8 && ring_rows_enabled()) {
     // one warp per row, many short-lived CTAs (see the note on launch_grid)
     const int64_t ctas = (rows + kRowThreads / 32 - 1) / (kRowThreads / 32);
@@ -1625,8 +1691,10 @@ __global__ void __launch_bounds__(kThreads, kMinCtas)
 ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ gamma,
                           const T* __restrict__ mean_sum, const T* __restrict__ rstd, T* __restrict__ dx,
                           float* __restrict__ partial, int64_t rows, int32_t D) {
-  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), NP = VEC / 2, NS = 2 * kRowsPer, kSlots = 16;
-  static_assert(kThreads / 32 <= kSlots && NS * kSlots / 4 <= 32, "one float4 of warp partials per lane");
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T)), NP = VEC / 2, NS = 2 * kRowsPer;
+  constexpr int kSlots = kThreads > 512 ? 32 : 16;  // warps whose partials one sum collects
+  constexpr int kLanesPerSum = kSlots / 4;          // lanes that each add one float4 of them
+  static_assert(kThreads / 32 <= kSlots && NS * kLanesPerSum <= 32, "one float4 of warp partials per lane");
   __shared__ __align__(16) float red[2][NS][kSlots];  // [trip parity][sum][warp]; slots of absent warps stay zero
   const int nvec = D / VEC;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1705,16 +1773,18 @@ ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, con
     const float mine_sum = warp_multi_sum<NS>(s, lane, j);
     if ((lane & (32 / NS - 1)) == 0) buf[j][warp] = mine_sum;
     __syncthreads();
-    // lane l adds four warps' partials of sum l / 4; two more exchanges complete it in the four lanes 4j .. 4j + 3
+    // lane l adds four warps' partials of sum l / kLanesPerSum; log2(kLanesPerSum) more exchanges complete it in the
+    // lanes j kLanesPerSum .. (j + 1) kLanesPerSum - 1
     float4 q = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (lane < NS * kSlots / 4) q = reinterpret_cast<const float4*>(&buf[0][0])[lane];
+    if (lane < NS * kLanesPerSum) q = reinterpret_cast<const float4*>(&buf[0][0])[lane];
     float t = (q.x + q.y) + (q.z + q.w);
-    t += __shfl_xor_sync(0xffffffffu, t, 1);
-    t += __shfl_xor_sync(0xffffffffu, t, 2);
+#pragma unroll
+    for (int o = 1; o < kLanesPerSum; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
 #pragma unroll
     for (int k = 0; k < kRowsPer; ++k) {
       const int64_t r = r0 + k;
-      const float m1 = __shfl_sync(0xffffffffu, t, 8 * k) * inv_d, m2 = __shfl_sync(0xffffffffu, t, 8 * k + 4) * inv_d;
+      const float m1 = __shfl_sync(0xffffffffu, t, 2 * k * kLanesPerSum) * inv_d;
+      const float m2 = __shfl_sync(0xffffffffu, t, (2 * k + 1) * kLanesPerSum) * inv_d;
       const float2 a2 = splat2(rs[k]), b2 = splat2(-m2 * rs[k]), c2 = splat2(-m1 * rs[k]);
       uint4 o;
       if constexpr (NP == 4) {
@@ -2104,10 +2174,12 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
   // 1024 threads are resident per SM (measured on [8192, 4096] bf16: 47.2 us; four rows per trip in one 128-register
   // CTA per SM, option "ring_ctas" = 1: 48.6 us; the scalar-arithmetic form, option "ring_rows" = 0: 67.8 us).
   const bool packed = wide && vec > 1 && threads <= 512 && options().ring_rows.load() != 0;
+  const bool packed_wide = wide && vec > 1 && threads > 512 && options().ring_rows.load() != 0;  // one 1024-thread CTA per SM
   const bool two_ctas = packed && options().ring_ctas.load() != 1;
   const int rows_per = threads <= 512 ? (two_ctas ? 2 : 4) : 1;
   int resident = !wide ? (max_v >= 4 ? 1 : 2)
-                       : two_ctas ? std::max(2, std::min(8, 1024 / threads))
+                       : packed_wide ? 1
+                       : two_ctas ? std::max(2, std::min(16, 1024 / threads))
                                   : (rows_per == 4 ? std::max(1, std::min(4, 512 / threads)) : std::max(1, 2048 / threads));
   const int64_t row_blocks = wide ? (rows + rows_per - 1) / rows_per : rows;
   const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(row_blocks, static_cast<int64_t>(ctx->sm_count) * resident)));
@@ -2135,9 +2207,15 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
                                                                static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
                                                                static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
                                                                static_cast<int32_t>(D))
+#define NOVA_LNB_PACKED_WIDE(T)                                                                                       \
+  ln_backward_packed_kernel<T, 1, 1024, 1><<<grid, threads, 0, s>>>(static_cast<const T*>(grad_y), static_cast<const T*>(x), \
+                                                               static_cast<const T*>(gamma), static_cast<const T*>(mean_sum), \
+                                                               static_cast<const T*>(rstd), static_cast<T*>(dx), partial, rows, \
+                                                               static_cast<int32_t>(D))
 #define NOVA_LNB_MV(T, V)                                                                       \
   do {                                                                                          \
-    if (two_ctas && V > 1) NOVA_LNB_PACKED2(T);                                                 \
+    if (packed_wide && V > 1) NOVA_LNB_PACKED_WIDE(T);                                          \
+    else if (two_ctas && V > 1) NOVA_LNB_PACKED2(T);                                            \
     else if (wide && rows_per == 4 && V > 1 && packed) NOVA_LNB_PACKED(T);                      \
     else if (wide && rows_per == 4) NOVA_LNB_ROWS(T, V, 4, 512);                                \
     else if (max_v == 1) NOVA_LNB(T, V, 1); else if (max_v == 2) NOVA_LNB(T, V, 2);             \
@@ -2149,6 +2227,7 @@ int32_t nova_b200_layer_norm_backward(const void* grad_y, const void* x, const v
 #undef NOVA_LNB_MV
 #undef NOVA_LNB_PACKED
 #undef NOVA_LNB_PACKED2
+#undef NOVA_LNB_PACKED_WIDE
 #undef NOVA_LNB_ROWS
 #undef NOVA_LNB
   NOVA_CUDA_OK(cudaGetLastError());
