@@ -254,14 +254,16 @@ constexpr size_t kRingMaxBytes = 200u << 10;
 // (keyed on the kernel's address: instances that differ only in a template argument share one function-pointer type)
 template <typename Kernel>
 int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
-  struct Entry { const void* fn; size_t smem; int resident; };
+  struct Entry { const void* fn; int device; size_t smem; int resident; };
   static thread_local Entry cache[32] = {};
   static thread_local int used = 0;
   const void* fn = reinterpret_cast<const void*>(kernel);
   if (smem > kRingMaxBytes) { set_error("ring of " + std::to_string(smem) + " bytes exceeds the limit"); return 0; }
-  bool configured = false;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); set_error("cudaGetDevice failed"); return 0; }
+  bool configured = false;  // (a function attribute belongs to one device's copy of the kernel)
   for (int i = 0; i < used; ++i) {
-    if (cache[i].fn != fn) continue;
+    if (cache[i].fn != fn || cache[i].device != device) continue;
     configured = true;
     if (cache[i].smem == smem) return cache[i].resident;
   }
@@ -280,7 +282,7 @@ int ring_resident_ctas(Kernel kernel, int threads, size_t smem) {
     set_error(std::string("occupancy query: ") + cudaGetErrorString(e) + ", resident " + std::to_string(resident) + ", smem " + std::to_string(smem));
     return 0;
   }
-  cache[used < 32 ? used++ : 31] = Entry{fn, smem, resident};
+  cache[used < 32 ? used++ : 31] = Entry{fn, device, smem, resident};
   return resident;
 }
 
@@ -1252,10 +1254,12 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     else if (kMode == 1 && status != nullptr && ring_rows_enabled() && D * static_cast<int64_t>(sizeof(T)) <= kSmemRowBytes) {
       auto kernel = softmax_stream_kernel<T>;
       const int smem = static_cast<int>((D * sizeof(T) + kStreamChunkBytes - 1) / kStreamChunkBytes) * kStreamChunkBytes;
-      static bool configured = false;  // same on every device this library runs on (one architecture)
-      if (!configured) {
+      static thread_local int configured_device = -1;  // (a function attribute belongs to one device's copy of the kernel)
+      int device = 0;
+      NOVA_CUDA_OK(cudaGetDevice(&device));
+      if (configured_device != device) {
         NOVA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamMaxChunks * kStreamChunkBytes));
-        configured = true;
+        configured_device = device;
       }
       const int grid = static_cast<int>(rows < sm_count ? rows : sm_count);
       kernel<<<grid, kSmemRowThreads, smem, st>>>(xp, yp, rows, d, stats, status);

@@ -261,6 +261,23 @@ def test_operands_on_another_device_are_refused(cuda, lib):
     with pytest.raises(L.NovaB200Error):
         ops.gemm(a, b0)
     torch.cuda.synchronize(1)
+    # kernels that ask for more than 48 KB of dynamic shared memory are configured per device: the same process, first
+    # device 0 then device 1, must get the same rows from both
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(5)
+    x = torch.randn(300, 4096, generator=gen).to(torch.bfloat16)
+    wide = torch.randn(20, 50304, generator=gen)
+    gam = torch.randn(4096, generator=gen).to(torch.bfloat16)
+    got = []
+    for dev in (0, 1):
+        d = f"cuda:{dev}"
+        y = ops.layer_norm(x.to(d), gam.to(d), gam.to(d))[0]
+        sm = ops.softmax(wide.to(d))
+        sm2 = ops.softmax(x.to(d))
+        got.append((y.cpu(), sm.cpu(), sm2.cpu()))
+    for u, v in zip(got[0], got[1]):
+        assert torch.equal(u, v)
+    torch.cuda.set_device(0)
 
 
 @pytest.mark.parametrize("dt,tol_pair,tol_truth", [("f16", 1e-3, 1.0e-3), ("bf16", 4e-3, 5e-3), ("f32", 1e-5, 1e-5)])
