@@ -169,11 +169,15 @@ int32_t nova_b200_abi_version(void);
  *   "group_m" (16) raster group height in row blocks
  *   "prefetch" (-1) L2 prefetch distance of the pair kernel in ring stages: -1 = planner, 0 = off
  *   "pdl" (1)      launch contractions with programmatic stream serialization (prologue overlaps the previous kernel's tail)
- *   "ring_rows" (1) layer_norm rows of a few KB stream through a shared-memory ring filled by bulk copies; 2 = the
- *                  backward kernel as well (slower than its register form where measured); 0 = register kernels only
- *   "ring_stages" / "ring_ctas" (0) ring depth and CTAs per SM of those kernels, 0 = built-in choice (tuning)
+ *   "ring_rows" (1) the row kernels (layer_norm forward / backward, softmax, row statistics) in packed fp32 arithmetic,
+ *                  rows of a few KB streamed through shared memory by bulk copies; 0 = their scalar-arithmetic
+ *                  predecessors (register kernels only; for A/B runs and cross-checks); 2 = also the shared-memory-ring
+ *                  form of the layer_norm backward kernel (slower than the default where measured)
+ *   "ring_stages" / "ring_ctas" (0) ring depth and CTAs per SM of those kernels, 0 = built-in choice (tuning;
+ *                  "ring_ctas" = 1 also selects the four-rows-per-trip form of the layer_norm backward kernel)
  *   "host_tiles" (0) nova_b200_gemm_host on one large product: 0 = tiles of about 2048 x 2048 released in a growing
- *                  square, -1 = row blocks only, rows * 100 + cols = that many row blocks and column slabs (tuning)
+ *                  square, -1 = row blocks only, rows * 100 + cols = that many row blocks and column slabs, + 10000 = slab
+ *                  by slab instead of the growing square (tuning)
  *   "plan_cache" (1) reuse plans and tensor maps of repeated calls;  "debug" (0)
  * No counterpart in the reference (its schedule is fixed at compile time by lowering_config attributes,
  * lib/Transforms/LLVMGPU/Config/NovaKernelConfig.cpp:1487-1577). */
