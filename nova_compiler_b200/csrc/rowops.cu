@@ -1221,13 +1221,18 @@ int32_t launch_row_kernel(const void* x, const void* gamma, const void* beta, vo
     const size_t row_bytes = static_cast<size_t>(D) * sizeof(T);
     int stages = 2;
     if (const int64_t o = options().ring_stages.load(); o >= 2 && o <= kRingMaxStages) stages = static_cast<int>(o);
+    // CTAs per SM, measured (fraction of the copy bandwidth with 2 / 3 / 4 resident): rows of 8 KB 0.68 / 0.84 / 0.80,
+    // of 16 KB 0.97 / 0.83 / 0.81 (f16) and 0.91 / 0.87 / 0.87 (f32), of 32 KB 0.83 / 0.79 / -: more rows in flight
+    // than that only scatter the DRAM accesses
+    const int best_ctas = row_bytes <= (8u << 10) ? 3 : 2;
 #define NOVA_SM_RING(MAXV_)                                                                                          \
     do {                                                                                                             \
       auto kernel = softmax_ring_kernel<T, MAXV_>;                                                                   \
       const size_t smem = stages * row_bytes;                                                                        \
       int resident = ring_resident_ctas(kernel, kRowThreads, smem);                                                  \
       if (resident <= 0) return fail(NOVA_B200_ERR_CUDA, std::string("softmax: the ring kernel cannot be configured: ") + nova_b200_last_error_string()); \
-      if (const int64_t o = options().ring_ctas.load(); o >= 1 && o < resident) resident = static_cast<int>(o);      \
+      if (const int64_t o = options().ring_ctas.load(); o >= 1) resident = std::min(resident, static_cast<int>(o));  \
+      else resident = std::min(resident, best_ctas);                                                                 \
       const int grid = static_cast<int>(std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * resident));         \
       kernel<<<grid, kRowThreads, smem, st>>>(xp, yp, rows, d, stages, stats, status);                               \
     } while (0)
