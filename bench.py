@@ -666,6 +666,73 @@ def run_ln_fold(ctx, steps=60):
     return res
 
 
+def run_graph_step(ctx, steps=20):
+    """The reference's own GPT training-step graph (ltest/test.mlir: 8 x 1024 tokens, width 384, vocabulary 50304, f32:
+    embedding gathers, a pre-norm FFN block, the vocabulary contraction, sparse cross entropy and the whole backward
+    down to the embedding scatter-adds) run through the textual front-end, i.e. through the same C-ABI calls the
+    lowering pass would emit.  The record is the step time; nothing is skipped or cached between steps."""
+    from nova_compiler_b200.frontend import Module
+    torch = ctx.torch
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tests", "golden", "ref_fixtures", "ltest__test.mlir")
+    if not os.path.exists(path):
+        return None
+    m = Module(open(path).read())
+    arg_sig, _ = m.signature("main")
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234)
+    V, T = 50304, 1024
+    args = []
+    for i, (dt, shape) in enumerate(arg_sig):
+        if i in (0, 1):
+            args.append(torch.randint(0, V, shape, device="cuda", generator=g).to(torch.int16))
+        elif i in (2, 15):
+            args.append(torch.arange(T, device="cuda", dtype=torch.int64).reshape(shape))
+        elif i < 14:
+            args.append((torch.rand(shape, device="cuda", generator=g) * 2 - 1) * 0.05 + (1.0 if i in (5, 11) else 0.0))
+        else:
+            args.append(torch.zeros(shape, device="cuda"))
+    for _ in range(3):
+        m.run("main", *args)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        m.run("main", *args)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    # the same step captured once into a CUDA graph (its intermediates become the graph's own allocations) and replayed
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            m.run("main", *args)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                m.run("main", *args)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        graph_ms = e0.elapsed_time(e1) / steps
+        del graph
+    except Exception as exc:  # capture is an extra: report why it was not possible
+        graph_ms = f"not captured: {type(exc).__name__}: {str(exc)[:120]}"
+        torch.cuda.synchronize()
+    plan = m.plan("main").splitlines()[1:]
+    kinds = [line.split()[0] for line in plan if line.strip()]
+    flops = 2.0 * 8192 * 384 * 50304 * 3 + 2.0 * 8192 * 384 * 1536 * 2 * 3   # vocabulary and FFN contractions, forward + two backward each
+    return {"workload": "ltest/test.mlir main: GPT training step, f32 (3xTF32 contractions), through nova_b200_module_run",
+            "ms_per_step": ms, "graph_replay_ms_per_step": graph_ms, "steps": steps, "calls_per_step": len(kinds), "contractions_per_step": kinds.count("gemm"),
+            "contraction_tflops": flops / (ms * 1e-3) / 1e12,
+            "note": "direct calls (no CUDA graph), intermediates from cudaMallocAsync; contraction_tflops counts only the 2MNK of the nine contractions"}
+
+
 def run_rowop(ctx, w, steps, warmup):
     """HBM roofline of the row-wise kernels: GB/s = (bytes read + bytes written) / event time."""
     from nova_compiler_b200 import ops
@@ -786,9 +853,12 @@ def run_gpu(args):
             if r is not None:
                 subs[s] = r
     ln_fold = None
+    graph_step = None
     if not args.only and not args.profile and ctx.world == 1 and head == "c3":
         time.sleep(SUB_IDLE_S)
         ln_fold = run_ln_fold(ctx)
+        time.sleep(SUB_IDLE_S)
+        graph_step = run_graph_step(ctx)
     line = None
     if ctx.rank == 0:
         desc = WORKLOADS[head][0]
@@ -815,6 +885,8 @@ def run_gpu(args):
             line["workloads"] = subs
         if ln_fold is not None:
             line["ln_fold"] = ln_fold
+        if graph_step is not None:
+            line["graph_step"] = graph_step
         if ctx.world == 1 and not args.profile and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(head)
     if ctx.world > 1:

@@ -336,6 +336,11 @@ int32_t nova_b200_sce(const void* logits_dev, const void* targets_dev, void* sof
  * grad[r, c] = (softmax[r, c] - (c == target[r])) * (1 / rows). */
 int32_t nova_b200_sce_backward(const void* softmax_dev, const void* targets_dev, void* grad_dev, int64_t rows, int64_t C,
                                int32_t dtype, int32_t idx_dtype, void* stream);
+/* The same followed by a multiplication with one scalar (the incoming gradient of the loss: `nova.mul %grad, %cst` after
+ * nova.sce_backward in the reference's training graphs, ltest/test.mlir:43-45), in the same pass over the logits-sized
+ * tensor: grad = (softmax - onehot) * ((1 / rows) * scale). */
+int32_t nova_b200_sce_backward_scaled(const void* softmax_dev, const void* targets_dev, void* grad_dev, int64_t rows,
+                                      int64_t C, int32_t dtype, int32_t idx_dtype, float scale, void* stream);
 
 /* nova.scatter_add (NovaScatterAddOpLowering, NovaToLinalg.cpp:1086-1294) IN PLACE on the canonical view
  * inout[pre, axis_len, post], idx[n_idx], src[pre, n_idx, post]: inout[p, idx[i], q] += src[p, i, q] with atomic

@@ -89,6 +89,8 @@ PROTOTYPES = {
                                   C.c_int32, C.c_void_p, C.c_void_p]),
     "nova_b200_sce_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                            C.c_int32, C.c_void_p]),
+    "nova_b200_sce_backward_scaled": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
+                                                  C.c_int32, C.c_float, C.c_void_p]),
     "nova_b200_scatter_add": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "nova_b200_layer_norm_backward": (C.c_int32, [C.c_void_p] * 8 + [C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),

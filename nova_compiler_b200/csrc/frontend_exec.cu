@@ -330,7 +330,8 @@ struct Exec {
       const int64_t Cn = in[0].shape.back();
       const int64_t rows = in[0].numel() / std::max<int64_t>(Cn, 1);
       if (k == "sce") st = nova_b200_sce(in[0].ptr, in[1].ptr, out[0].ptr, out[1].ptr, rows, Cn, in[0].dtype, in[1].dtype, nullptr, stream);
-      else st = nova_b200_sce_backward(in[0].ptr, in[1].ptr, out[0].ptr, rows, Cn, in[0].dtype, in[1].dtype, stream);
+      else st = nova_b200_sce_backward_scaled(in[0].ptr, in[1].ptr, out[0].ptr, rows, Cn, in[0].dtype, in[1].dtype,
+                                              s.attrs.count("scaled") ? static_cast<float>(s.fvalue) : 1.0f, stream);
     } else if (k == "scatter_add") {
       const int64_t r = static_cast<int64_t>(in[0].shape.size());
       int64_t axis = s.attrs.count("axis") ? s.attrs.at("axis") : 0;

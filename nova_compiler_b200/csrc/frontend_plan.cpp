@@ -507,6 +507,24 @@ bool plan_function(const Function& f, Plan* out, std::string* error) {
     } else if (n == "nova.sce" || n == "nova.sce_backward" || n == "nova.scatter_add") {
       s.kind = n.substr(5);
       s.inputs = op.operands; s.outputs = op.results;
+      if (n == "nova.sce_backward") {
+        // grad * (one-element constant), its only use: the multiplication joins the pass that writes grad (an
+        // all-parallel consumer of a root, which the reference's tile-and-fuse pipeline fuses as well: isEpilogue,
+        // NovaKernelConfig.cpp:1876-1895)
+        const Op* u = single_user(op.results[0]);
+        if (u && u->name == "nova.mul" && u->operands.size() == 2 && u->operands[0] != u->operands[1]) {
+          const std::string& other = u->operands[0] == op.results[0] ? u->operands[1] : u->operands[0];
+          const Op* cst = c.producer.count(other) ? c.producer[other] : nullptr;
+          const Type* ct = c.type_of(other);
+          if (cst && (cst->name == "nova.constant" || cst->name == "arith.constant") && ct && ct->numel() == 1) {
+            s.attrs["scaled"] = 1;
+            s.fvalue = cst->fvalue;
+            s.outputs = u->results;
+            s.note = "nova.sce_backward + nova.mul by %" + other;
+            c.absorbed.insert(u);
+          }
+        }
+      }
     } else if (n == "nova.layer_norm_backward") {
       s.kind = "layer_norm_backward";
       s.inputs = op.operands; s.outputs = op.results;

@@ -2297,6 +2297,11 @@ int32_t nova_b200_sce(const void* logits, const void* targets, void* softmax_out
 
 int32_t nova_b200_sce_backward(const void* softmax, const void* targets, void* grad, int64_t rows, int64_t C, int32_t dtype,
                                int32_t idx_dtype, void* stream) {
+  return nova_b200_sce_backward_scaled(softmax, targets, grad, rows, C, dtype, idx_dtype, 1.0f, stream);
+}
+
+int32_t nova_b200_sce_backward_scaled(const void* softmax, const void* targets, void* grad, int64_t rows, int64_t C,
+                                      int32_t dtype, int32_t idx_dtype, float scale, void* stream) {
   if (rows < 0 || C < 0) return fail(NOVA_B200_ERR_INVALID_ARG, "sce_backward: negative extent");
   if (!is_float_dtype(dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce_backward: dtype must be f32, f16 or bf16");
   if (!is_index_dtype(idx_dtype)) return fail(NOVA_B200_ERR_UNSUPPORTED, "sce_backward: target dtype must be i16, i32 or i64");
@@ -2310,7 +2315,8 @@ int32_t nova_b200_sce_backward(const void* softmax, const void* targets, void* g
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int es = dtype_bytes(dtype), vec = 16 / es;
   const bool vec_ok = C % vec == 0 && reinterpret_cast<uintptr_t>(softmax) % 16 == 0 && reinterpret_cast<uintptr_t>(grad) % 16 == 0;
-  const float inv_n = static_cast<float>(1.0 / static_cast<double>(rows));
+  // one multiplier per element: (1 / rows) rounded to fp32 as the reference's constant is, times the caller's scale
+  const float inv_n = static_cast<float>(1.0 / static_cast<double>(rows)) * scale;
   const int threads = 256;
   const int grid = grid_for(vec_ok ? rows * C / vec : rows * C, threads, ctx->sm_count);
 #define NOVA_SCEB(T, V)                                                                                                  \

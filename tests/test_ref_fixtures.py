@@ -68,6 +68,7 @@ def test_plan_of_the_gpt_step():
     kinds = [line.split()[0] for line in p.splitlines()[1:]]
     assert kinds.count("gemm") == 9 and kinds.count("layer_norm_backward") == 2 and kinds.count("scatter_add") == 2
     assert "reduce_sum (%37)" in p and kinds.count("store_to_arg") == 12
+    assert "[nova.sce_backward + nova.mul by %27]" in p   # the loss gradient's scalar joins the pass that writes dlogits
     p = Module(_text("ltest__testing.mlir")).plan("main")
     kinds = [line.split()[0] for line in p.splitlines()[1:]]
     assert "gemm init=bias_row(%6) act=none" in p and kinds.count("reduce_sum") == 4 and "compare" in kinds and "mse" in kinds
