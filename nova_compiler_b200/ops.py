@@ -505,8 +505,9 @@ def sce(logits: torch.Tensor, targets: torch.Tensor, *, return_bad_count: bool =
 
 
 @_on_device
-def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1) -> torch.Tensor:
-    """nova.sce_backward (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137): (softmax - one_hot) / rows."""
+def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1, scale: float = 1.0) -> torch.Tensor:
+    """nova.sce_backward (NovaSceBackwardLowering, NovaToLinalgGeneric.cpp:1012-1137): (softmax - one_hot) / rows;
+    `scale` is a following multiplication by one scalar (the loss gradient) done in the same pass."""
     _require_cuda(softmax_, targets)
     if dim not in (-1, softmax_.dim() - 1):
         raise L.NovaB200Error(L.ERR_UNSUPPORTED, "sce_backward: the class dimension must be the last one")
@@ -518,8 +519,8 @@ def sce_backward(softmax_: torch.Tensor, targets: torch.Tensor, dim: int = -1) -
     if t.numel() != rows:
         raise L.NovaB200Error(L.ERR_INVALID_ARG, "sce_backward: one target per row")
     g = torch.empty_like(p)
-    L.check(L.load().nova_b200_sce_backward(p.data_ptr(), t.data_ptr(), g.data_ptr(), rows, Cn, _dt(p), _IDX[t.dtype],
-                                            _stream()))
+    L.check(L.load().nova_b200_sce_backward_scaled(p.data_ptr(), t.data_ptr(), g.data_ptr(), rows, Cn, _dt(p), _IDX[t.dtype],
+                                                   float(scale), _stream()))
     return g
 
 

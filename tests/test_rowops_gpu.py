@@ -262,6 +262,12 @@ def test_sce_forward_and_backward(cuda, oracle, dt):
         g = ops.sce_backward(sm, t_dev)
         wg = oracle.sce_backward(to_host(torch, sm, dt), t.view(np.int16) if it == np.uint16 else t, dt, compute_f32=True)
         check(oracle, to_host(torch, g, dt), wg, dt, tol=TOL[dt] if dt != "f32" else 1e-6)
+        # the loss gradient's scalar folded into the same pass: the oracle's gradient times that scalar, rounded once
+        gs = ops.sce_backward(sm, t_dev, scale=-2.5)
+        pf = oracle.from_bits(to_host(torch, sm, dt), dt).astype(np.float32).reshape(rows, C)
+        pf[np.arange(rows), t.astype(np.int64)] -= np.float32(1.0)
+        want = oracle.to_bits((pf * (np.float32(1.0 / rows) * np.float32(-2.5))).reshape(sm.shape), dt)
+        check(oracle, to_host(torch, gs, dt), want, dt, tol=TOL[dt] if dt != "f32" else 1e-6)
     # an out-of-range target: counted, contributes x[target] = 0
     x = rand_bits(oracle, rng, (5, 16), dt, "normal")
     t = np.array([1, 99, 3, 0, 15], dtype=np.int32)
