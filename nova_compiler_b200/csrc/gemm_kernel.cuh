@@ -845,6 +845,47 @@ __global__ void nova_repitch_kernel(const RepitchOperand oa, const RepitchOperan
   }
 }
 
+// Second half of a K-split product: C[m, n] = round(act(init + sum over ranges of partial[s][m][n])), the ranges added in
+// ascending order, init / activation exactly as the contraction's own epilogue applies them.
+struct SplitKReduce {
+  const float* partial;   // [ranges][M][ldp]
+  void* C;
+  const void* bias;
+  const void* residual;
+  int64_t M, N, ldp, ldc, ldr;
+  int32_t ranges, init, act, out_dtype;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(256) nova_splitk_reduce_kernel(const SplitKReduce r) {
+  griddep_wait();  // launched with programmatic serialization behind the contraction that writes the partials
+  const int64_t n = r.M * r.N;
+  const int64_t plane = r.M * r.ldp;
+  OutT* c = static_cast<OutT*>(r.C);
+  const OutT* bias = static_cast<const OutT*>(r.bias);
+  const OutT* res = static_cast<const OutT*>(r.residual);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / r.N, col = i - m * r.N;
+    const float* pp = r.partial + m * r.ldp + col;
+    float v = pp[0];
+    for (int32_t s = 1; s < r.ranges; ++s) v += pp[s * plane];
+    if (r.init == NOVA_B200_INIT_LN_FOLD) {
+      // v = rstd_m * (acc - mean_m * c_n) + d_n: bias = the fp32 arrays c then d, residual = {mean, rstd} per row
+      const float* cd = static_cast<const float*>(r.bias);
+      const float2 st = static_cast<const float2*>(r.residual)[m];
+      v = fmaf(st.y, fmaf(-st.x, cd[col], v), cd[r.N + col]);
+    }
+    if (r.init == NOVA_B200_INIT_BIAS_ROW || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(bias[col]);
+    if (r.init == NOVA_B200_INIT_RESIDUAL_FULL || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(res[m * r.ldr + col]);
+    if (r.init == NOVA_B200_INIT_FROM_C) v += to_f32<OutT>(c[m * r.ldc + col]);
+    if (r.act == NOVA_B200_ACT_RELU) v = fmaxf(v, 0.0f);
+    else if (r.act == NOVA_B200_ACT_GELU_TANH) v = gelu_tanh_f32(v);
+    else if (r.act == NOVA_B200_ACT_GELU_TANH_GRAD) v *= gelu_tanh_grad_f32(to_f32<OutT>(res[m * r.ldr + col]));
+    c[m * r.ldc + col] = from_f32<OutT>(v);
+  }
+}
+
 // C = act(init) for K == 0 (an empty contraction leaves the accumulator at its initial value).
 template <typename OutT>
 __global__ void nova_gemm_k0_kernel(GemmKernelParams p) {

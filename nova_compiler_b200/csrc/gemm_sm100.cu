@@ -24,11 +24,16 @@ struct Plan {
   bool short_k = false;  // contraction so short that the epilogue dominates: 8 epilogue warps, 3 stages
   int64_t repitch_a_ld = 0, repitch_b_ld = 0;  // > 0: the operand is first copied to scratch with this pitch
   int prefetch_dist = 0;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads
+  // K split into this many equal ranges that run as the batches of one launch and are summed (in a fixed order) by a
+  // second kernel that also applies the epilogue: for products with too few output tiles to fill the GPU
+  int split_k = 1;
+  int64_t split_ldp = 0;         // pitch of one partial matrix (floats)
+  int64_t split_offset = 0;      // byte offset of the partials in the stream's scratch
 };
 
 constexpr int64_t kMaxExtent = (1ll << 31) - 1;
 
-int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count) {
+int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count, bool allow_split_k = true) {
   if (!a) return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: args is null");
   if (a->struct_size != sizeof(nova_b200_gemm_args))
     return fail(NOVA_B200_ERR_INVALID_ARG, "gemm: struct_size does not match this library's nova_b200_gemm_args");
@@ -194,6 +199,47 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     const int64_t pf = options().prefetch.load();
     plan->prefetch_dist = pf >= 0 ? static_cast<int>(std::min<int64_t>(pf, 64)) : 0;
   }
+  // Split K: one matrix product whose output tiles fill less than a quarter of the SMs (weight gradients: small M and
+  // N, K = the token count; the small f32 product), or whose last wave is mostly empty while K is very long.  The K
+  // ranges run as the batches of the same kernel into fp32 partials in scratch; nova_splitk_reduce_kernel adds them in
+  // range order and applies init / activation / rounding exactly once.  Results differ from the unsplit product in the
+  // last bits (the fp32 additions associate differently); option "split_k": -1 = this rule, 0 = never, n >= 2 = n ranges.
+  {
+    const int64_t opt = options().split_k.load();
+    const int64_t stage_k = pi.block_k;
+    const int64_t kb = (a->K + stage_k - 1) / stage_k;
+    const int64_t tiles = pi.tiles;
+    int64_t want = 1;
+    if (allow_split_k && opt != 0 && a->batch == 1 && !pair && both_tma && a->K % stage_k == 0 && tiles > 0) {
+      if (opt >= 2) want = opt;
+      else if (tiles * 4 <= sms && kb >= 16) want = std::min<int64_t>(8, sms / tiles);
+      else if (kb >= 256 && tiles < 4 * sms) {
+        const double eff1 = static_cast<double>(tiles) / (waves(tiles, sms) * sms);
+        if (eff1 < 0.72) {
+          double best = eff1 + 0.1;
+          for (int64_t sp = 2; sp <= 4; ++sp) {
+            const double e = static_cast<double>(tiles * sp) / (waves(tiles * sp, sms) * sms);
+            if (e > best) { best = e; want = sp; }
+          }
+        }
+      }
+      // f32 through 3xTF32: the tensor core adds every product group into its fp32 accumulator with truncation, a bias
+      // that grows with the length of the chain (measured: relative error ~7e-9 x K, 5.7e-5 at K = 8192, where cuBLAS
+      // fp32 has 5e-7).  Ranges of at most 1024 keep one chain short; the partials are then added with rounding.
+      if (opt < 0 && plan->terms == 3) want = std::max<int64_t>(want, (a->K + 1023) / 1024);
+    }
+    int64_t sp = std::min<int64_t>(want, 16);
+    while (sp > 1 && (kb % sp != 0 || kb / sp < 4)) --sp;
+    if (sp > 1) {
+      plan->split_k = static_cast<int>(sp);
+      plan->split_ldp = (a->N + 3) & ~3ll;
+      plan->split_offset = (pi.scratch_bytes + 255) / 256 * 256;
+      pi.scratch_bytes = plan->split_offset + sp * a->M * plan->split_ldp * 4;
+      pi.tiles = tiles * sp;
+      pi.grid = static_cast<int32_t>(pi.tiles < sms ? pi.tiles : sms);
+      pi.store_c = 0;  // the kernel writes the aligned partials; the reduce kernel writes C
+    }
+  }
   return NOVA_B200_OK;
 }
 
@@ -319,6 +365,7 @@ struct Prepared {
   const void* key_status = nullptr;  // identifies the device context
   const void* key_scratch = nullptr;
   uint32_t key_epoch = 0;
+  bool key_allow_split = true;
   bool valid = false;
   Plan plan;
   GemmKernelParams p{};
@@ -327,6 +374,7 @@ struct Prepared {
   SplitOperand split_a{}, split_b{};
   RepitchOperand rep_a{}, rep_b{};
   int pre_blocks = 0;
+  SplitKReduce splitk{};
 };
 constexpr int kPlanCacheEntries = 32;
 
@@ -434,6 +482,29 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
     out->pre_kernel = 2;
   }
 
+  // Split K: range s of K becomes batch s of the launch.  A K-major operand moves along its columns (batch stride =
+  // the range length), an MN-major one along its rows; the output is the fp32 partial [s, M, ldp] in scratch, written
+  // with no init and no activation.
+  int64_t a_rows_v = a_rows, a_cols_v = a_cols, b_rows_v = b_rows, b_cols_v = b_cols, a_nb_v = a_nb, b_nb_v = b_nb;
+  out->splitk = SplitKReduce{};
+  if (plan.split_k > 1) {
+    const int64_t sp = plan.split_k, ks = a->K / sp;
+    p.K = static_cast<int32_t>(ks);
+    p.k_blocks = static_cast<int32_t>((ks + stage_k - 1) / stage_k);
+    p.batch = static_cast<int32_t>(sp);
+    p.a_batch_mul = p.b_batch_mul = 1;
+    if (plan.a_mn) { a_rows_v = ks; a_bs = ks * a_ld; } else { a_cols_v = ks; a_bs = ks; }
+    if (plan.b_mn) { b_rows_v = ks; b_bs = ks * b_ld; } else { b_cols_v = ks; b_bs = ks; }
+    a_nb_v = b_nb_v = sp;
+    float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + plan.split_offset);
+    out->splitk = SplitKReduce{partial, a->C, a->bias, a->residual, a->M, a->N, plan.split_ldp, a->ldc, a->ldr,
+                               static_cast<int32_t>(sp), a->init, a->act, a->dtype_c};
+    p.C = partial; p.ldc = plan.split_ldp; p.stride_c = a->M * plan.split_ldp;
+    p.bias = nullptr; p.residual = nullptr; p.init = NOVA_B200_INIT_ZERO; p.act = NOVA_B200_ACT_NONE;
+    p.out_dtype = NOVA_B200_F32;
+    p.vec_store = 1;
+  }
+
   CUtensorMap* maps = out->maps;  // A hi, A lo, B hi, B lo, C
   std::memset(maps, 0, sizeof(out->maps));
   const CUtensorMapDataType tdt = a->dtype_ab == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -445,20 +516,26 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
   };
   for (int t = 0; t < (plan.terms == 3 ? 2 : 1); ++t) {
     if (pi.loader_a != 1) {
-      st = encode_operand_map(ctx, &maps[t], a_src[t], es, tdt, a_rows, a_cols, a_ld, a_nb, a_bs, chunk,
+      st = encode_operand_map(ctx, &maps[t], a_src[t], es, tdt, a_rows_v, a_cols_v, a_ld, a_nb_v, a_bs, chunk,
                               plan.a_mn ? static_cast<uint32_t>(block_k) : static_cast<uint32_t>(kBlockM),
                               swizzle_for(plan.a_mn));
       if (st != NOVA_B200_OK) return st;
     }
     if (pi.loader_b != 1) {
-      st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows, b_cols, b_ld, b_nb, b_bs, chunk,
+      st = encode_operand_map(ctx, &maps[2 + t], b_src[t], es, tdt, b_rows_v, b_cols_v, b_ld, b_nb_v, b_bs, chunk,
                               plan.b_mn ? static_cast<uint32_t>(block_k)
                                         : static_cast<uint32_t>(plan.pair ? block_n / 2 : block_n),  // a pair CTA loads half of N
                               swizzle_for(plan.b_mn));
       if (st != NOVA_B200_OK) return st;
     }
   }
-  if (p.vec_store) {
+  if (p.vec_store && plan.split_k > 1) {
+    // (columns N .. ldp of a partial row may be written by the last 16-byte chunk: they are padding)
+    st = encode_operand_map(ctx, &maps[4], p.C, 4, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->M, plan.split_ldp, plan.split_ldp,
+                            plan.split_k, a->M * plan.split_ldp, static_cast<uint32_t>(kSwizzleBytes / 4), 32u,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NOVA_B200_OK) return st;
+  } else if (p.vec_store) {
     // output boxes: 32 rows x 128 bytes, clipped by the tensor map at M and N
     const int osz = plan.out_bytes;
     const CUtensorMapDataType cdt = a->dtype_c == NOVA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -487,10 +564,10 @@ int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_
   return NOVA_B200_OK;
 }
 
-int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out) {
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out, bool allow_split_k) {
   Plan plan;
   int sm = 148;  // the plan a B200 will execute; needs no device
-  int32_t st = validate_and_plan(args, &plan, sm);
+  int32_t st = validate_and_plan(args, &plan, sm, allow_split_k);
   if (st != NOVA_B200_OK) return st;
   if (out) *out = plan.info;
   return NOVA_B200_OK;
@@ -507,11 +584,14 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   Options& opt = options();
   const uint32_t epoch = opt.epoch.load();
   const bool use_cache = opt.plan_cache.load() != 0;
+  // (the push epilogue stores finished boxes of C; a K-split product finishes in the reduce kernel: never split those)
+  // (nor with the fixed scratch of the no-allocation entry point, whose size is promised in terms of A and B alone)
+  const bool allow_split = n_peers == 0 && ctx->fixed_scratch == nullptr;
   Prepared* hit = nullptr;
   if (use_cache) {
     for (int i = 0; i < kPlanCacheEntries; ++i) {
       Prepared& c = cache[i];
-      if (c.valid && c.key_status == ctx->status_word && c.key_epoch == epoch &&
+      if (c.valid && c.key_status == ctx->status_word && c.key_epoch == epoch && c.key_allow_split == allow_split &&
           std::memcmp(&c.key, a, sizeof(nova_b200_gemm_args)) == 0) {
         hit = &c;
         break;
@@ -525,7 +605,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     pr = use_cache ? &cache[next_slot] : &local;
     pr->valid = false;
     pr->plan = Plan{};
-    st = validate_and_plan(a, &pr->plan, ctx->sm_count);
+    st = validate_and_plan(a, &pr->plan, ctx->sm_count, allow_split);
     if (st != NOVA_B200_OK) return st;
   }
   const Plan& plan = pr->plan;
@@ -550,6 +630,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     pr->key_status = ctx->status_word;
     pr->key_scratch = scratch;
     pr->key_epoch = epoch;
+    pr->key_allow_split = allow_split;
     pr->valid = true;
     if (!hit && use_cache) next_slot = (next_slot + 1) % kPlanCacheEntries;
   }
@@ -618,24 +699,45 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   }
   const bool loader = pi.loader_a == 1 || pi.loader_b == 1;
   const int grid = pi.grid;
-  if (plan.terms == 3) {
-    if (block_n == 64) return launch_majors<64, 4, 3, 4, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-    return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+  auto launch_single_cta = [&]() -> int32_t {
+    if (plan.terms == 3) {
+      if (block_n == 64) return launch_majors<64, 4, 3, 4, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+      return launch_majors<128, 4, 3, 3, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    }
+    if (block_n == 64) {  // TMA-only build: narrow tiles are chosen only for operands tensor maps can describe
+      if (es == 2) return launch_majors<64, 2, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+      return launch_majors<64, 4, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    }
+    if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps
+      if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+      return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    }
+    if (es == 2) {
+      if (block_n == 256) return launch_single_term<256, 2, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+      return launch_single_term<128, 2, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    }
+    if (block_n == 256) return launch_single_term<256, 4, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+    return launch_single_term<128, 4, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+  };
+  st = launch_single_cta();
+  if (st != NOVA_B200_OK || plan.split_k <= 1) return st;
+  {
+    const SplitKReduce& r = pr->splitk;
+    cudaLaunchConfig_t cfg = {};
+    const int64_t want = (r.M * r.N + 255) / 256;
+    cfg.gridDim = dim3(static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8))), 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (r.out_dtype == NOVA_B200_BF16) NOVA_CUDA_OK(cudaLaunchKernelEx(&cfg, nova_splitk_reduce_kernel<__nv_bfloat16>, r));
+    else if (r.out_dtype == NOVA_B200_F16) NOVA_CUDA_OK(cudaLaunchKernelEx(&cfg, nova_splitk_reduce_kernel<__half>, r));
+    else NOVA_CUDA_OK(cudaLaunchKernelEx(&cfg, nova_splitk_reduce_kernel<float>, r));
   }
-  if (block_n == 64) {  // TMA-only build: narrow tiles are chosen only for operands tensor maps can describe
-    if (es == 2) return launch_majors<64, 2, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-    return launch_majors<64, 4, 1, 8, false, 4>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-  }
-  if (plan.short_k) {  // 256-wide tiles, three stages, eight epilogue warps
-    if (es == 2) return launch_majors<256, 2, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-    return launch_majors<256, 4, 1, 3, false, 8>(plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-  }
-  if (es == 2) {
-    if (block_n == 256) return launch_single_term<256, 2, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-    return launch_single_term<128, 2, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-  }
-  if (block_n == 256) return launch_single_term<256, 4, 4>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
-  return launch_single_term<128, 4, 6>(loader, plan.a_mn, plan.b_mn, maps, p, grid, stream, pdl);
+  return NOVA_B200_OK;
 }
 
 }  // namespace nova

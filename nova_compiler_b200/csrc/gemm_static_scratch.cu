@@ -13,7 +13,7 @@
 #include "runtime.h"
 
 namespace nova {
-int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out, bool allow_split_k = true);
 int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream, void* const* peers = nullptr,
                     int32_t n_peers = 0);
 }  // namespace nova
@@ -96,7 +96,7 @@ int32_t static_scratch_status(int dev, uint32_t* code_out) {
 extern "C" int32_t nova_b200_gemm_f32_static(const nova_b200_gemm_args* args, void* stream, uint32_t* wait_code_out) {
   using namespace nova;
   nova_b200_gemm_plan_info info;
-  int32_t st = gemm_plan_only(args, &info);
+  int32_t st = gemm_plan_only(args, &info, /*allow_split_k=*/false);
   if (st != NOVA_B200_OK) return st;
   if (args->dtype_ab != NOVA_B200_F32 || args->f32_mode != NOVA_B200_TF32X3)
     return fail(NOVA_B200_ERR_UNSUPPORTED, "gemm_f32_static: only the f32 contraction in NOVA_B200_TF32X3 mode is offered here; 16-bit and "

@@ -11,7 +11,7 @@
 
 namespace nova {
 
-int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out);
+int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out, bool allow_split_k = true);
 int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream_t stream, void* const* peers = nullptr,
                     int32_t n_peers = 0);
 int32_t static_scratch_status(int dev, uint32_t* code_out);
@@ -167,6 +167,7 @@ const OptionEntry kOptionTable[] = {
     {"ring_stages", "NOVA_B200_RING_STAGES", &Options::ring_stages},
     {"ring_ctas", "NOVA_B200_RING_CTAS", &Options::ring_ctas},
     {"host_tiles", "NOVA_B200_HOST_TILES", &Options::host_tiles},
+    {"split_k", "NOVA_B200_SPLIT_K", &Options::split_k},
 };
 }  // namespace
 

@@ -82,6 +82,7 @@ struct Options {
   std::atomic<int64_t> plan_cache{1}; // reuse plans and tensor maps of repeated calls
   std::atomic<int64_t> pdl{1};        // launch contractions with programmatic stream serialization
   std::atomic<int64_t> ring_rows{1};  // layer_norm (forward / backward) rows of a few KB through the shared-memory ring kernels
+  std::atomic<int64_t> split_k{-1};   // K ranges of a product with few output tiles: -1 = planner, 0 = never, n >= 2 = n
   std::atomic<int64_t> host_tiles{0}; // host pipeline of one large product: 0 = built-in, -1 = row blocks only, else rows * 100 + cols
   std::atomic<int64_t> debug{0};
   std::atomic<uint32_t> epoch{0};     // bumped by every change: cached plans are keyed on it

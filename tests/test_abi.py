@@ -102,13 +102,15 @@ def test_plan_ragged_pitches_select_the_non_tma_loader(lib):
 
 def test_plan_f32_modes(lib):
     st, info = _plan(lib, _args(512, 512, 512, dt=L.F32))
-    # 16 tiles of 128 x 128 would use 16 SMs: 128 x 64 tiles, four stages of hi and lo copies of both operands
-    assert st == L.OK and info.block_n == 64 and info.block_k == 32 and info.stages == 4 and info.tiles == 32
+    # 16 tiles of 128 x 128 would use 16 SMs: 128 x 64 tiles, four stages of hi and lo copies of both operands; even
+    # those 32 tiles leave most SMs idle, so K runs as four ranges of 128 (32 x 4 work units) summed by a second kernel
+    assert st == L.OK and info.block_n == 64 and info.block_k == 32 and info.stages == 4 and info.tiles == 4 * 32
     st2, big = _plan(lib, _args(4096, 4096, 512, dt=L.F32))
-    assert st2 == L.OK and big.block_n == 128 and big.stages == 3
-    assert info.scratch_bytes == 2 * 4 * (512 * 512 + 512 * 512)  # hi and lo copies of A and B
+    assert st2 == L.OK and big.block_n == 128 and big.stages == 3 and big.tiles == 32 * 32
+    # hi and lo copies of A and B, then four fp32 partial matrices
+    assert info.scratch_bytes == 2 * 4 * (512 * 512 + 512 * 512) + 4 * 512 * 512 * 4
     st, info = _plan(lib, _args(512, 512, 512, dt=L.F32, f32_mode=L.TF32X1))
-    assert st == L.OK and info.scratch_bytes == 0
+    assert st == L.OK and info.scratch_bytes == 4 * 512 * 512 * 4   # no hi/lo copies; the K ranges' partials only
     # unaligned f32 operands are re-laid out by the split, never read through the loader
     st, info = _plan(lib, _args(100, 200, 301, dt=L.F32))
     assert st == L.OK and (info.loader_a, info.loader_b) == (0, 0)

@@ -498,6 +498,97 @@ def test_gemm_host_tiled_pipeline_writes_only_its_window(cuda, oracle, lib, N):
     assert np.all(cbuf[:M, N:] == 0x4321) and np.all(cbuf[M:] == 0x4321)
 
 
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
+def test_split_k_matches_the_unsplit_product(cuda, oracle, lib, dt, trans_a, trans_b):
+    """A product with few output tiles and a long K runs its K ranges as the batches of one launch and sums the fp32
+    partials in a second kernel that applies the epilogue once.  Forced ranges (option split_k) on every operand
+    major, every init / activation, a ragged N and a C window; against the oracle, and against the unsplit kernel
+    (same arithmetic up to the association of the fp32 additions)."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    rng = np.random.default_rng(71)
+    M, N, K = 200, 150, 1024
+    a = rand_bits(oracle, rng, (K, M) if trans_a else (M, K), dt)
+    b = rand_bits(oracle, rng, (N, K) if trans_b else (K, N), dt)
+    bias = rand_bits(oracle, rng, (N,), dt)
+    res = rand_bits(oracle, rng, (M, N), dt)
+    z = rand_bits(oracle, rng, (M, N), dt)
+    cases = [dict(), dict(bias=bias, act="relu"), dict(bias=bias, residual=res, act="gelu"), dict(residual=res),
+             dict(bias=bias, gelu_grad_of=z)]
+    try:
+        for kw in cases:
+            okw = {k: v for k, v in kw.items() if k != "act"}
+            if "act" in kw:
+                okw["act"] = {"gelu": "gelu_tanh"}.get(kw["act"], kw["act"])
+            want = oracle.gemm(a, b, dtype_in=dt, trans_a=trans_a, trans_b=trans_b, **okw)
+            got = {}
+            for ranges in (0, 4, 8):
+                L.set_option("split_k", ranges)
+                gkw = dict(kw)
+                if "residual" in gkw:
+                    gkw["residual"] = res[None]
+                if "gelu_grad_of" in gkw:
+                    gkw["gelu_grad_of"] = to_dev(torch, z, dt)[None]
+                got[ranges] = run_gpu(torch, a, b, dt, trans_a=trans_a, trans_b=trans_b, **gkw)
+                check(oracle, got[ranges], want, dt)
+            for ranges in (4, 8):
+                assert oracle.rel_fro(oracle.from_bits(got[ranges], dt), oracle.from_bits(got[0], dt)) <= (2e-5 if dt == "f32" else 4e-3)
+            if dt == "f32" and not kw:
+                # the tensor core adds into its fp32 accumulator with truncation, so the error of the 3xTF32 product
+                # grows with the length of one accumulation chain: shorter ranges are MORE accurate against float64
+                af = (a.T if trans_a else a).astype(np.float64)
+                bf = (b.T if trans_b else b).astype(np.float64)
+                truth = af @ bf
+                err = {r: oracle.rel_fro(got[r].astype(np.float64), truth) for r in (0, 4, 8)}
+                assert err[8] < err[4] < err[0] and err[8] <= 2e-6
+        # accumulate into a live C that is a window of a wider buffer; bytes outside the window survive
+        L.set_option("split_k", 4)
+        ta, tb = to_dev(torch, a, dt)[None], to_dev(torch, b, dt)[None]
+        if trans_a:
+            ta = ta.transpose(1, 2)
+        if trans_b:
+            tb = tb.transpose(1, 2)
+        buf = torch.full((1, M + 2, N + 10), 3.0, device="cuda", dtype=_tdt(torch, dt))
+        win = buf[:, :M, :N]
+        ops.gemm(ta, tb, out=win, accumulate_into_out=True)
+        torch.cuda.synchronize()
+        want = oracle.gemm(a, b, dtype_in=dt, trans_a=trans_a, trans_b=trans_b,
+                           residual=oracle.to_bits(np.full((M, N), 3.0, np.float32), dt))
+        check(oracle, to_host(torch, win, dt)[0], want, dt)
+        mask = torch.ones_like(buf, dtype=torch.bool)
+        mask[:, :M, :N] = False
+        assert torch.all(buf[mask] == 3.0)
+        assert ops.device_status() == 0
+    finally:
+        L.set_option("split_k", -1)
+
+
+def test_split_k_is_planned_for_few_tiles_only(cuda, lib):
+    """The planner's rule, read from the plan record: the 512-cubed f32 product (32 tiles of 128 x 64) runs four K
+    ranges; the headline linear layer and a batched product never split."""
+    from nova_compiler_b200 import _lib as L
+
+    def plan(dt, batch, M, N, K):
+        g = L.GemmArgs()
+        g.struct_size = C.sizeof(L.GemmArgs)
+        g.dtype_ab = g.dtype_c = dt
+        g.batch, g.M, g.N, g.K = batch, M, N, K
+        g.lda, g.ldb, g.ldc = K, N, N
+        g.batch_stride_a, g.batch_stride_b, g.batch_stride_c = M * K, K * N, M * N
+        g.A = g.B = g.C = 4096  # never dereferenced by the planner
+        info = L.GemmPlanInfo()
+        L.check(lib.nova_b200_gemm_plan(C.byref(g), C.byref(info)))
+        return info
+    small = plan(L.F32, 1, 512, 512, 512)
+    assert small.tiles == 4 * 32 and small.scratch_bytes >= 4 * 512 * 512 * 4
+    assert plan(L.BF16, 1, 8192, 11008, 4096).tiles == 32 * 43
+    assert plan(L.F16, 32, 1024, 1024, 1024).tiles == 32 * 16
+    # a weight gradient: 384 x 1536 outputs from K = 8192 tokens, bf16: 36 tiles of 128 x 128 -> four ranges
+    wg = plan(L.BF16, 1, 384, 1536, 8192)
+    assert wg.tiles % 36 == 0 and wg.tiles // 36 >= 2
+
+
 def test_nova_matmul_rank_rules(cuda, oracle):
     """nova.matmul shape rules (MatmulOp::inferReturnTypes, NovaOps.cpp:1116-1285)."""
     torch = cuda
