@@ -1721,33 +1721,46 @@ ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, con
 #pragma unroll
   for (int p = 0; p < NP; ++p) dg[p] = db[p] = make_float2(0.0f, 0.0f);
   uint32_t trip = 0;
+  // Running pointers: the row addresses of a trip are these plus k * D, and a trip advances them by one constant.  (With
+  // the addresses recomputed from the row index every trip, 64-bit multiplies and the re-reading of kernel parameters
+  // and thread ids they drag in were a third of all instructions executed: ncu opcode counts.)
+  const int tid = threadIdx.x;
   const int64_t step = static_cast<int64_t>(gridDim.x) * kRowsPer;
-  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * kRowsPer; r0 < rows; r0 += step) {
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * kRowsPer;
+  const uint4* gy_p = reinterpret_cast<const uint4*>(gy + first * D) + tid;
+  const uint4* x_p = reinterpret_cast<const uint4*>(x + first * D) + tid;
+  uint4* dx_p = reinterpret_cast<uint4*>(dx + first * D) + tid;
+  const T* ms_p = mean_sum + first;
+  const T* rs_p = rstd + first;
+  const int row_vecs = D / VEC;   // vectors from one row to the next
+  const int64_t trip_vecs = step * row_vecs;
+  const bool prefetcher = mine && (tid & 7) == 0;
+  for (int64_t r0 = first; r0 < rows; r0 += step, gy_p += trip_vecs, x_p += trip_vecs, dx_p += trip_vecs,
+               ms_p += step, rs_p += step) {
     uint4 pg[kRowsPer], px[kRowsPer];
     float rs[kRowsPer], nmr[kRowsPer];
+    const int live_rows = static_cast<int>(rows - r0 < kRowsPer ? rows - r0 : kRowsPer);   // uniform
 #pragma unroll
     for (int k = 0; k < kRowsPer; ++k) {
-      const int64_t r = r0 + k;
-      const bool live = mine && r < rows;
-      pg[k] = live ? reinterpret_cast<const uint4*>(gy + r * D)[threadIdx.x] : zero4;
-      px[k] = live ? reinterpret_cast<const uint4*>(x + r * D)[threadIdx.x] : zero4;
+      const bool live = mine && k < live_rows;
+      pg[k] = live ? gy_p[k * row_vecs] : zero4;
+      px[k] = live ? x_p[k * row_vecs] : zero4;
     }
-    if (mine && (threadIdx.x & 7) == 0) {  // the trip after this one into L2, one request per 128-byte line
+    if (prefetcher) {  // the trip after this one into L2, one request per 128-byte line
+      const int64_t ahead = rows - (r0 + step);
 #pragma unroll
       for (int k = 0; k < kRowsPer; ++k) {
-        const int64_t r = r0 + step + k;
-        if (r < rows) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(gy + r * D) + threadIdx.x));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(x + r * D) + threadIdx.x));
+        if (k < ahead) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(gy_p + trip_vecs + k * row_vecs));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x_p + trip_vecs + k * row_vecs));
         }
       }
     }
 #pragma unroll
     for (int k = 0; k < kRowsPer; ++k) {
-      const int64_t r = r0 + k;
-      const bool live = r < rows;
-      rs[k] = live ? ld_f32<T>(rstd[r]) : 0.0f;
-      nmr[k] = live ? -ld_f32<T>(mean_sum[r]) * inv_d * rs[k] : 0.0f;
+      const bool live = k < live_rows;
+      rs[k] = live ? ld_f32<T>(rs_p[k]) : 0.0f;
+      nmr[k] = live ? -ld_f32<T>(ms_p[k]) * inv_d * rs[k] : 0.0f;
     }
     float2 kxh[kRowsPer][NP], kgg[kRowsPer][NP];
     float s[NS];
@@ -1791,7 +1804,6 @@ ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, con
     for (int o = 1; o < kLanesPerSum; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
 #pragma unroll
     for (int k = 0; k < kRowsPer; ++k) {
-      const int64_t r = r0 + k;
       const float m1 = __shfl_sync(0xffffffffu, t, 2 * k * kLanesPerSum) * inv_d;
       const float m2 = __shfl_sync(0xffffffffu, t, (2 * k + 1) * kLanesPerSum) * inv_d;
       const float2 a2 = splat2(rs[k]), b2 = splat2(-m2 * rs[k]), c2 = splat2(-m1 * rs[k]);
@@ -1806,7 +1818,7 @@ ln_backward_packed_kernel(const T* __restrict__ gy, const T* __restrict__ x, con
         const float2 hi = __ffma2_rn(kxh[k][1], b2, __ffma2_rn(kgg[k][1], a2, c2));
         o = make_uint4(__float_as_uint(lo.x), __float_as_uint(lo.y), __float_as_uint(hi.x), __float_as_uint(hi.y));
       }
-      if (mine && r < rows) reinterpret_cast<uint4*>(dx + r * D)[threadIdx.x] = o;
+      if (mine && k < live_rows) dx_p[k * row_vecs] = o;
     }
   }
   if (mine) {
