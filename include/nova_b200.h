@@ -188,6 +188,16 @@ int32_t nova_b200_abi_version(void);
 int32_t nova_b200_set_option(const char* name, int64_t value);
 int32_t nova_b200_get_option(const char* name, int64_t* value_out);
 
+/* An f32 matrix that several contractions read (a gradient that feeds both the input-gradient and the weight-gradient
+ * product): splits it ONCE into the hi / lo halves of the 3xTF32 scheme, stream-ordered on `stream`, and remembers them.
+ * Until the release, every nova_b200_gemm on this device whose A or B is exactly this matrix (same pointer, stored
+ * rows, columns and pitch; not batched) uses the halves and skips its own split pass.  The caller promises that the
+ * matrix does not change in between and that those contractions run on `stream` or after it.  No counterpart in the
+ * reference (its f32 contractions are single-pass TF32, NVIDIATargetUtils.cpp:58-65). */
+int32_t nova_b200_f32_presplit(const void* x_dev, int64_t rows, int64_t cols, int64_t ld, void* stream, void** handle_out);
+/* Forgets the matrix and frees the halves in stream order (after the contractions enqueued so far on `stream`). */
+int32_t nova_b200_f32_presplit_release(void* handle, void* stream);
+
 /* Makes sure `stream` of the current device owns at least `bytes` of library scratch (see nova_b200_gemm_args), so
  * that later calls on it, e.g. under stream capture, need not allocate.  Counterpart in the reference: the
  * cudaMallocAsync calls its generated host code makes per launch (lib/Transforms/FixGpuLaunch.cpp:49-50). */

@@ -89,6 +89,8 @@ PROTOTYPES = {
                                   C.c_int32, C.c_void_p, C.c_void_p]),
     "nova_b200_sce_backward": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                            C.c_int32, C.c_void_p]),
+    "nova_b200_f32_presplit": (C.c_int32, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "nova_b200_f32_presplit_release": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "nova_b200_sce_backward_scaled": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                                   C.c_int32, C.c_float, C.c_void_p]),
     "nova_b200_scatter_add": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,

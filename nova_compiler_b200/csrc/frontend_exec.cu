@@ -5,7 +5,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cstring>
+#include <map>
+#include <string>
 #include <memory>
 #include <vector>
 
@@ -134,8 +137,45 @@ struct Exec {
   cudaStream_t stream;
   std::map<std::string, Value> vals;
   std::vector<void*> owned;
+  // f32 intermediates that more than one contraction reads (the logits gradient feeds both backward products of the
+  // vocabulary layer): split into hi / lo once and shared (nova_b200_f32_presplit), released when the run ends
+  std::map<std::string, std::string> view_root;
+  std::map<std::string, int> gemm_reads;
+  struct Shared { const void* ptr; int64_t rows, cols, ld; void* handle; };
+  std::vector<Shared> shared;
+
+  void count_gemm_reads() {
+    auto root_of = [&](const std::string& n) {
+      auto it = view_root.find(n);
+      return it == view_root.end() ? n : it->second;
+    };
+    for (const Step& s : p.steps) {
+      if ((s.kind == "alias" || s.kind == "reshape" || s.kind == "transpose") && !s.inputs.empty() && !s.outputs.empty())
+        view_root[s.outputs[0]] = root_of(s.inputs[0]);
+      else if (s.kind == "gemm" && s.inputs.size() >= 2) {
+        ++gemm_reads[root_of(s.inputs[0])];
+        ++gemm_reads[root_of(s.inputs[1])];
+      }
+    }
+  }
+  // Called with an operand of a contraction about to run: shares its split when the value has another reader.
+  void maybe_share_split(const std::string& name, const Value& v, int64_t ld, int32_t trans) {
+    auto rt = view_root.find(name);
+    const std::string& root = rt == view_root.end() ? name : rt->second;
+    auto it = gemm_reads.find(root);
+    if (it == gemm_reads.end() || it->second < 2 || v.dtype != NOVA_B200_F32 || v.shape.size() < 2) return;
+    if (std::find(owned.begin(), owned.end(), v.ptr) == owned.end()) return;  // arguments may be written during the run
+    const size_t r = v.shape.size();
+    const int64_t rows = trans ? v.shape[r - 1] : v.shape[r - 2], cols = trans ? v.shape[r - 2] : v.shape[r - 1];
+    for (const Shared& e : shared)
+      if (e.ptr == v.ptr && e.rows == rows && e.cols == cols && e.ld == ld) return;
+    void* handle = nullptr;
+    if (nova_b200_f32_presplit(v.ptr, rows, cols, ld, stream, &handle) == NOVA_B200_OK)
+      shared.push_back(Shared{v.ptr, rows, cols, ld, handle});  // on failure the contraction splits it itself
+  }
 
   ~Exec() {
+    for (const Shared& e : shared) nova_b200_f32_presplit_release(e.handle, stream);
     for (void* q : owned) cudaFreeAsync(q, stream);
   }
   std::string canon(const std::string& n) const {
@@ -255,6 +295,10 @@ struct Exec {
     if ((st = inner(a, &g.lda, &g.trans_a, &g.batch_stride_a)) != NOVA_B200_OK) return st;
     if ((st = inner(b, &g.ldb, &g.trans_b, &g.batch_stride_b)) != NOVA_B200_OK) return st;
     g.A = a.ptr; g.B = b.ptr; g.C = c.ptr;
+    if (g.batch == 1) {
+      maybe_share_split(s.inputs[0], a, g.lda, g.trans_a);
+      maybe_share_split(s.inputs[1], b, g.ldb, g.trans_b);
+    }
     g.ldc = g.N;
     g.batch_stride_c = g.M * g.N;
     g.act = s.act;
@@ -552,6 +596,7 @@ int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const 
   int32_t st = NOVA_B200_OK;
   if (!current_context(&st)) return st;
   fe::Exec ex{*f, p, static_cast<cudaStream_t>(stream), {}, {}};
+  ex.count_gemm_reads();
   for (int32_t i = 0; i < n_args; ++i) {
     if (!fe::same_shape(f->arg_types[i], args[i]))
       return fail(NOVA_B200_ERR_INVALID_ARG, "module_run: argument " + std::to_string(i) + " does not match the signature");

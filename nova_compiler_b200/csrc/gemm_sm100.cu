@@ -366,6 +366,7 @@ struct Prepared {
   const void* key_scratch = nullptr;
   uint32_t key_epoch = 0;
   bool key_allow_split = true;
+  uint32_t key_presplit = 0;
   bool valid = false;
   Plan plan;
   GemmKernelParams p{};
@@ -459,6 +460,21 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
     out->pre_kernel = 1;
     a_src[0] = a_hi; a_src[1] = a_lo; b_src[0] = b_hi; b_src[1] = b_lo;
     a_ld = a_ldo; b_ld = b_ldo; a_bs = a_rows * a_ldo; b_bs = b_rows * b_ldo;
+    // an operand the caller had split in advance: read those halves, skip its half of the split pass
+    if (a->batch == 1) {
+      std::lock_guard<std::mutex> lock(ctx->presplit_mu);
+      for (const DeviceContext::PreSplit& e : ctx->presplit) {
+        if (e.x == a->A && e.rows == a_rows && e.cols == a_cols && e.ld == a->lda) {
+          a_src[0] = e.hi; a_src[1] = e.lo; a_ld = e.ld_out; a_bs = a_rows * a_ld;
+          out->split_a.rows_total = 0;
+        }
+        if (e.x == a->B && e.rows == b_rows && e.cols == b_cols && e.ld == a->ldb) {
+          b_src[0] = e.hi; b_src[1] = e.lo; b_ld = e.ld_out; b_bs = b_rows * b_ld;
+          out->split_b.rows_total = 0;
+        }
+      }
+      if (out->split_a.rows_total == 0 && out->split_b.rows_total == 0) out->pre_kernel = 0;
+    }
   } else if (plan.repitch_a_ld > 0 || plan.repitch_b_ld > 0) {
     uint8_t* s = static_cast<uint8_t*>(scratch);
     out->rep_a = RepitchOperand{};
@@ -564,6 +580,18 @@ int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_
   return NOVA_B200_OK;
 }
 
+// hi = rna-tf32(x), lo = x - hi of one f32 matrix into [rows, ld_out] buffers (nova_b200_f32_presplit).
+int32_t split_launch(const float* x, float* hi, float* lo, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                     int sm_count, cudaStream_t stream) {
+  SplitOperand o{x, hi, lo, rows, ld_in, 0, static_cast<int32_t>(rows), static_cast<int32_t>(cols), static_cast<int32_t>(ld_out)};
+  SplitOperand none{};
+  const int64_t want = (rows * ld_out / 4 + 255) / 256;
+  const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, static_cast<int64_t>(sm_count) * 8)));
+  nova_split_tf32_kernel<<<dim3(blocks, 1), 256, 0, stream>>>(o, none);
+  NOVA_CUDA_OK(cudaGetLastError());
+  return NOVA_B200_OK;
+}
+
 int32_t gemm_plan_only(const nova_b200_gemm_args* args, nova_b200_gemm_plan_info* out, bool allow_split_k) {
   Plan plan;
   int sm = 148;  // the plan a B200 will execute; needs no device
@@ -587,11 +615,17 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   // (the push epilogue stores finished boxes of C; a K-split product finishes in the reduce kernel: never split those)
   // (nor with the fixed scratch of the no-allocation entry point, whose size is promised in terms of A and B alone)
   const bool allow_split = n_peers == 0 && ctx->fixed_scratch == nullptr;
+  uint32_t presplit_version;
+  {
+    std::lock_guard<std::mutex> lock(ctx->presplit_mu);
+    presplit_version = ctx->presplit_version;
+  }
   Prepared* hit = nullptr;
   if (use_cache) {
     for (int i = 0; i < kPlanCacheEntries; ++i) {
       Prepared& c = cache[i];
       if (c.valid && c.key_status == ctx->status_word && c.key_epoch == epoch && c.key_allow_split == allow_split &&
+          c.key_presplit == presplit_version &&
           std::memcmp(&c.key, a, sizeof(nova_b200_gemm_args)) == 0) {
         hit = &c;
         break;
@@ -631,6 +665,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
     pr->key_scratch = scratch;
     pr->key_epoch = epoch;
     pr->key_allow_split = allow_split;
+    pr->key_presplit = presplit_version;
     pr->valid = true;
     if (!hit && use_cache) next_slot = (next_slot + 1) % kPlanCacheEntries;
   }

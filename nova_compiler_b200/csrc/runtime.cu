@@ -17,6 +17,8 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
 int32_t static_scratch_status(int dev, uint32_t* code_out);
 int32_t repitch_launch(const void* src, void* dst, int es, int64_t batch, int64_t rows, int64_t cols, int64_t ld_in,
                        int64_t stride_in, int64_t ld_out, int sm_count, cudaStream_t stream);
+int32_t split_launch(const float* x, float* hi, float* lo, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                     int sm_count, cudaStream_t stream);
 
 namespace {
 thread_local std::string g_last_error;
@@ -355,6 +357,66 @@ int32_t nova_b200_operand_view(const nova_b200_operand* op, const void** data_de
   if (data_dev) *data_dev = op->data;
   if (ld) *ld = op->ld;
   if (batch_stride) *batch_stride = op->batch_stride;
+  return NOVA_B200_OK;
+}
+
+struct nova_b200_presplit_handle {
+  int device;
+  const void* x;
+  float* base;   // hi then lo, one stream-ordered allocation
+};
+
+int32_t nova_b200_f32_presplit(const void* x_dev, int64_t rows, int64_t cols, int64_t ld, void* stream, void** handle_out) {
+  if (!handle_out) return fail(NOVA_B200_ERR_INVALID_ARG, "f32_presplit: handle_out is null");
+  *handle_out = nullptr;
+  if (!x_dev || rows < 1 || cols < 1 || ld < cols) return fail(NOVA_B200_ERR_INVALID_ARG, "f32_presplit: bad extent, pitch or pointer");
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  st = check_pointer_device(ctx, x_dev, "f32_presplit: the matrix");
+  if (st != NOVA_B200_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t ldo = (cols + 3) & ~3ll;
+  const size_t half = static_cast<size_t>(rows) * ldo * sizeof(float);
+  void* base = nullptr;
+  cudaError_t e = cudaMallocAsync(&base, 2 * half, s);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NOVA_B200_ERR_CUDA, "f32_presplit: allocation of " + std::to_string(2 * half) + " bytes failed: " + cudaGetErrorString(e));
+  }
+  float* hi = static_cast<float*>(base);
+  float* lo = hi + static_cast<size_t>(rows) * ldo;
+  st = split_launch(static_cast<const float*>(x_dev), hi, lo, rows, cols, ld, ldo, ctx->sm_count, s);
+  if (st != NOVA_B200_OK) { cudaFreeAsync(base, s); return st; }
+  {
+    std::lock_guard<std::mutex> lock(ctx->presplit_mu);
+    ctx->presplit.push_back(DeviceContext::PreSplit{x_dev, rows, cols, ld, hi, lo, ldo});
+    ++ctx->presplit_version;
+  }
+  *handle_out = new nova_b200_presplit_handle{ctx->device, x_dev, hi};
+  return NOVA_B200_OK;
+}
+
+int32_t nova_b200_f32_presplit_release(void* handle, void* stream) {
+  if (!handle) return NOVA_B200_OK;
+  auto* h = static_cast<nova_b200_presplit_handle*>(handle);
+  int32_t st = NOVA_B200_OK;
+  DeviceContext* ctx = current_context(&st);
+  if (!ctx) return st;
+  if (ctx->device != h->device) return fail(NOVA_B200_ERR_INVALID_ARG, "f32_presplit_release: the handle belongs to another device");
+  {
+    std::lock_guard<std::mutex> lock(ctx->presplit_mu);
+    for (size_t i = 0; i < ctx->presplit.size(); ++i) {
+      if (ctx->presplit[i].hi == h->base) {
+        ctx->presplit.erase(ctx->presplit.begin() + static_cast<std::ptrdiff_t>(i));
+        break;
+      }
+    }
+    ++ctx->presplit_version;
+  }
+  cudaError_t e = cudaFreeAsync(h->base, static_cast<cudaStream_t>(stream));
+  delete h;
+  if (e != cudaSuccess) { cudaGetLastError(); return fail(NOVA_B200_ERR_CUDA, std::string("f32_presplit_release: ") + cudaGetErrorString(e)); }
   return NOVA_B200_OK;
 }
 

@@ -56,6 +56,12 @@ struct DeviceContext {
   cudaEvent_t ev_in[kHostEvents] = {}, ev_comp[kHostEvents] = {};
   std::mutex mu;       // guards the scratch pool
   std::mutex host_mu;  // guards staging (the *_host entry points)
+  // f32 matrices whose hi / lo halves (the 3xTF32 split) a caller asked to keep: a contraction that is given one of
+  // them as an operand reads the halves instead of splitting it again (nova_b200_f32_presplit)
+  struct PreSplit { const void* x; int64_t rows, cols, ld; float* hi; float* lo; int64_t ld_out; };
+  std::vector<PreSplit> presplit;
+  uint32_t presplit_version = 0;   // bumped by every change: cached launch descriptions are keyed on it
+  std::mutex presplit_mu;
 };
 
 void set_error(const std::string& msg);

@@ -244,6 +244,37 @@ def test_slab_interleave_kernel(cuda, lib, n, dt):
     assert torch.equal(out, full)
 
 
+def test_f32_presplit_is_shared_by_contractions(cuda, lib):
+    """An f32 matrix split into its 3xTF32 halves once (nova_b200_f32_presplit): contractions that read it as A, as B
+    or through a transposed view give the same bits as when they split it themselves, and forget it on release."""
+    torch = cuda
+    from nova_compiler_b200 import ops, _lib as L
+    g = torch.Generator(device="cuda")
+    g.manual_seed(31)
+    M, N, K = 320, 264, 1024
+    x = torch.randn(M, K, device="cuda", generator=g)          # read as A [M, K], as B [M(K'), K(N')] and transposed
+    w = torch.randn(K, N, device="cuda", generator=g)
+    u = torch.randn(96, M, device="cuda", generator=g)
+    want_a = ops.gemm(x[None], w[None])
+    want_b = ops.gemm(u[None], x[None])
+    want_t = ops.gemm(x.t()[None], u.t()[None])                # x^T [K, M] . u^T [M, 96]
+    handle = C.c_void_p()
+    L.check(lib.nova_b200_f32_presplit(x.data_ptr(), M, K, K, None, C.byref(handle)))
+    try:
+        assert torch.equal(ops.gemm(x[None], w[None]), want_a)
+        assert torch.equal(ops.gemm(u[None], x[None]), want_b)
+        assert torch.equal(ops.gemm(x.t()[None], u.t()[None]), want_t)
+        # the halves are a snapshot: a contraction reading the registered matrix does not see a later change of x
+        x2 = x.clone()
+        x.add_(1.0)
+        assert torch.equal(ops.gemm(x[None], w[None]), want_a)
+    finally:
+        L.check(lib.nova_b200_f32_presplit_release(handle, None))
+    got = ops.gemm(x[None], w[None])                           # forgotten: the new contents are split and used
+    assert torch.equal(got, ops.gemm((x2 + 1.0)[None], w[None])) and not torch.equal(got, want_a)
+    torch.cuda.synchronize()
+
+
 def test_operands_on_another_device_are_refused(cuda, lib):
     torch = cuda
     if torch.cuda.device_count() < 2:
