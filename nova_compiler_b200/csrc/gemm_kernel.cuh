@@ -62,6 +62,9 @@ struct GemmKernelParams {
   int64_t ldc, stride_c, ldr, stride_r;
   int32_t act, init, out_dtype, vec_store;
   int32_t prefetch_dist;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads (0 = none)
+  // Split K: "batch" s of the launch is the K range [s * split_k_len, (s + 1) * split_k_len) of ONE matrix product (both
+  // batch multipliers are 0 then); a range that runs past K reads zeros from the tensor maps.  0 = not split.
+  int32_t split_k_len;
   uint32_t* status;
   // multi-GPU push: every finished output box is also stored into these peers' matrices (same pitch and batch
   // stride as C), with plain 16-byte stores over NVLink
@@ -592,7 +595,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
           const uint32_t stage = smem_base + s * L::kStageBytes;
           const uint32_t bar = full_bar(s);
           mbar_arrive_expect_tx(bar, expect);
-          const int k0 = kb * kBlockK;
+          const int k0 = t.batch * p.split_k_len + kb * kBlockK;  // (a K range of a split product: see split_k_len)
 #pragma unroll
           for (int term = 0; term < kOpTerms; ++term) {
             if (!p.loader_a) {

@@ -27,6 +27,7 @@ struct Plan {
   // K split into this many equal ranges that run as the batches of one launch and are summed (in a fixed order) by a
   // second kernel that also applies the epilogue: for products with too few output tiles to fill the GPU
   int split_k = 1;
+  int64_t split_len = 0;         // K elements per range (a multiple of the k-block)
   int64_t split_ldp = 0;         // pitch of one partial matrix (floats)
   int64_t split_offset = 0;      // byte offset of the partials in the stream's scratch
 };
@@ -210,7 +211,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     const int64_t kb = (a->K + stage_k - 1) / stage_k;
     const int64_t tiles = pi.tiles;
     int64_t want = 1;
-    if (allow_split_k && opt != 0 && a->batch == 1 && !pair && both_tma && a->K % stage_k == 0 && tiles > 0) {
+    if (allow_split_k && opt != 0 && a->batch == 1 && !pair && both_tma && tiles > 0) {
       if (opt >= 2) want = opt;
       else if (tiles * 4 <= sms && kb >= 16) want = std::min<int64_t>(8, sms / tiles);
       else if (kb >= 256 && tiles < 4 * sms) {
@@ -229,9 +230,12 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
       if (opt < 0 && plan->terms == 3) want = std::max<int64_t>(want, (a->K + 1023) / 1024);
     }
     int64_t sp = std::min<int64_t>(want, 16);
-    while (sp > 1 && (kb % sp != 0 || kb / sp < 4)) --sp;
+    while (sp > 1 && (kb + sp - 1) / sp < 4) --sp;   // at least four k-blocks per range
+    int64_t kb_per = sp > 1 ? (kb + sp - 1) / sp : kb;
+    if (sp > 1) sp = (kb + kb_per - 1) / kb_per;      // ranges of kb_per k-blocks; the last may be shorter (zeros past K)
     if (sp > 1) {
       plan->split_k = static_cast<int>(sp);
+      plan->split_len = kb_per * stage_k;
       plan->split_ldp = (a->N + 3) & ~3ll;
       plan->split_offset = (pi.scratch_bytes + 255) / 256 * 256;
       pi.scratch_bytes = plan->split_offset + sp * a->M * plan->split_ldp * 4;
@@ -498,20 +502,17 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
     out->pre_kernel = 2;
   }
 
-  // Split K: range s of K becomes batch s of the launch.  A K-major operand moves along its columns (batch stride =
-  // the range length), an MN-major one along its rows; the output is the fp32 partial [s, M, ldp] in scratch, written
-  // with no init and no activation.
+  // Split K: range s of K becomes "batch" s of the launch: the producer adds s * split_len to its K coordinate, the
+  // tensor maps of A and B stay those of the whole matrices (so a last range that runs past K reads zeros); the
+  // output is the fp32 partial [s, M, ldp] in scratch, written with no init and no activation.
   int64_t a_rows_v = a_rows, a_cols_v = a_cols, b_rows_v = b_rows, b_cols_v = b_cols, a_nb_v = a_nb, b_nb_v = b_nb;
   out->splitk = SplitKReduce{};
   if (plan.split_k > 1) {
-    const int64_t sp = plan.split_k, ks = a->K / sp;
-    p.K = static_cast<int32_t>(ks);
-    p.k_blocks = static_cast<int32_t>((ks + stage_k - 1) / stage_k);
+    const int64_t sp = plan.split_k;
+    p.split_k_len = static_cast<int32_t>(plan.split_len);
+    p.k_blocks = static_cast<int32_t>(plan.split_len / stage_k);
     p.batch = static_cast<int32_t>(sp);
-    p.a_batch_mul = p.b_batch_mul = 1;
-    if (plan.a_mn) { a_rows_v = ks; a_bs = ks * a_ld; } else { a_cols_v = ks; a_bs = ks; }
-    if (plan.b_mn) { b_rows_v = ks; b_bs = ks * b_ld; } else { b_cols_v = ks; b_bs = ks; }
-    a_nb_v = b_nb_v = sp;
+    p.a_batch_mul = p.b_batch_mul = 0;
     float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + plan.split_offset);
     out->splitk = SplitKReduce{partial, a->C, a->bias, a->residual, a->M, a->N, plan.split_ldp, a->ldc, a->ldr,
                                static_cast<int32_t>(sp), a->init, a->act, a->dtype_c};
