@@ -229,7 +229,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
       // fp32 has 5e-7).  Ranges of at most 1024 keep one chain short; the partials are then added with rounding.
       if (opt < 0 && plan->terms == 3) want = std::max<int64_t>(want, (a->K + 1023) / 1024);
     }
-    int64_t sp = std::min<int64_t>(want, 16);
+    int64_t sp = std::min<int64_t>(want, 64);
     while (sp > 1 && (kb + sp - 1) / sp < 4) --sp;   // at least four k-blocks per range
     int64_t kb_per = sp > 1 ? (kb + sp - 1) / sp : kb;
     if (sp > 1) sp = (kb + kb_per - 1) / kb_per;      // ranges of kb_per k-blocks; the last may be shorter (zeros past K)

@@ -565,6 +565,23 @@ def test_split_k_matches_the_unsplit_product(cuda, oracle, lib, dt, trans_a, tra
         L.set_option("split_k", -1)
 
 
+def test_f32_error_does_not_grow_with_k(cuda):
+    """The tensor core adds into its fp32 accumulator with truncation, so one long accumulation chain drifts: the
+    unsplit 3xTF32 product is 5.7e-5 off float64 at K = 8192 and 3.5e-4 at K = 50304.  With K in ranges of at most
+    1024 the error stays under the 1e-5 the f32 path promises, for ragged and very long K alike."""
+    torch = cuda
+    from nova_compiler_b200 import ops
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77)
+    for M, N, K in [(200, 150, 1000), (256, 384, 8191), (128, 128, 50304)]:
+        a = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+        b = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
+        c = ops.gemm(a[None], b[None])[0].double()
+        truth = a.double() @ b.double()
+        err = float((c - truth).norm() / truth.norm())
+        assert err <= 1e-5, (M, N, K, err)
+
+
 def test_split_k_is_planned_for_few_tiles_only(cuda, lib):
     """The planner's rule, read from the plan record: the 512-cubed f32 product (32 tiles of 128 x 64) runs four K
     ranges; the headline linear layer and a batched product never split."""
