@@ -444,14 +444,19 @@ def run_contraction(ctx, w, steps, warmup, headline=False):
     ga.A, ga.B, ga.C = sets[0][0].data_ptr(), sets[0][1].data_ptr(), sets[0][2].data_ptr()
     info = L.GemmPlanInfo()
     L.check(lib.nova_b200_gemm_plan(C.byref(ga), C.byref(info)))
-    launches_per_step = 2 if info.scratch_bytes > 0 else 1
+    # kernels per call: the contraction, a pre-pass when an operand goes through scratch (hi/lo split of f32, re-pitch),
+    # and the reduce kernel when K runs as ranges (the plan then counts range x tile work units)
+    base_tiles = ga.batch * ((ga.M + info.block_m - 1) // info.block_m) * ((ga.N + info.block_n - 1) // info.block_n)
+    k_ranges = info.tiles // base_tiles if base_tiles and info.tiles % base_tiles == 0 else 1
+    pre_pass = dab == "f32" or info.loader_a == 2 or info.loader_b == 2
+    launches_per_step = 1 + (1 if pre_pass else 0) + (1 if k_ranges > 1 else 0)
 
     rec = {
         "workload": f"{w}: {desc}", "value": value, "unit": "TFLOP/s", "per_gpu": per_gpu, "ms_per_step": ms_step,
         "steps": steps, "dtype": dab, "roofline": roof, "clocks": clocks, "gpu_launches": launches_per_step * steps,
         "pct_of_bf16_dense_peak_nominal": 100.0 * per_gpu / NOMINAL_BF16_TFLOPS,
         "plan": {"tile": [info.block_m, info.block_n, info.block_k], "stages": info.stages, "grid": info.grid,
-                 "tiles": info.tiles, "loader_a": info.loader_a, "loader_b": info.loader_b, "store_c": info.store_c,
+                 "tiles": info.tiles, "k_ranges": k_ranges, "loader_a": info.loader_a, "loader_b": info.loader_b, "store_c": info.store_c,
                  "repitch_bytes": int(info.scratch_bytes) if info.loader_a == 2 or info.loader_b == 2 else 0},
         "l2": f"rotating {n_sets} buffer sets ({n_sets * r_bytes / 1e6:.0f} MB per rank) so operands never sit in L2",
         "launch": "direct calls" if graph is None else f"CUDA graph of {n_sets} steps, replayed",
