@@ -179,8 +179,8 @@ int32_t nova_b200_abi_version(void);
  *                  square, -1 = row blocks only, rows * 100 + cols = that many row blocks and column slabs, + 10000 = slab
  *                  by slab instead of the growing square (tuning)
  *   "split_k" (-1) K split into ranges that run as one launch and are summed by a second kernel, for products whose
- *                  output tiles fill under a quarter of the SMs (or leave the last wave mostly empty while K is very
- *                  long): -1 = planner, 0 = never, n >= 2 = n ranges where K allows.  A split product differs from
+ *                  output tiles fill at most half of the SMs (or leave the last wave mostly empty while K is very
+ *                  long) and for f32 products with K > 1024: -1 = planner, 0 = never, n >= 2 = n ranges.  A split product differs from
  *                  the unsplit one in the last bits (fp32 additions associate differently)
  *   "plan_cache" (1) reuse plans and tensor maps of repeated calls;  "debug" (0)
  * No counterpart in the reference (its schedule is fixed at compile time by lowering_config attributes,

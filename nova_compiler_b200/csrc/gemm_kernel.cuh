@@ -860,32 +860,57 @@ struct SplitKReduce {
 };
 
 template <typename OutT>
+__device__ __forceinline__ float splitk_finish(const SplitKReduce& r, float v, int64_t m, int64_t col, const OutT* bias,
+                                               const OutT* res, const OutT* c) {
+  if (r.init == NOVA_B200_INIT_LN_FOLD) {
+    // v = rstd_m * (acc - mean_m * c_n) + d_n: bias = the fp32 arrays c then d, residual = {mean, rstd} per row
+    const float* cd = static_cast<const float*>(r.bias);
+    const float2 st = static_cast<const float2*>(r.residual)[m];
+    v = fmaf(st.y, fmaf(-st.x, cd[col], v), cd[r.N + col]);
+  }
+  if (r.init == NOVA_B200_INIT_BIAS_ROW || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(bias[col]);
+  if (r.init == NOVA_B200_INIT_RESIDUAL_FULL || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(res[m * r.ldr + col]);
+  if (r.init == NOVA_B200_INIT_FROM_C) v += to_f32<OutT>(c[m * r.ldc + col]);
+  if (r.act == NOVA_B200_ACT_RELU) v = fmaxf(v, 0.0f);
+  else if (r.act == NOVA_B200_ACT_GELU_TANH) v = gelu_tanh_f32(v);
+  else if (r.act == NOVA_B200_ACT_GELU_TANH_GRAD) v *= gelu_tanh_grad_f32(to_f32<OutT>(res[m * r.ldr + col]));
+  return v;
+}
+
+// One thread finishes four consecutive columns: 16-byte loads of the partials (their pitch is a multiple of four
+// floats), four loads in flight per range step; the ragged last columns of a row fall back to single elements.
+template <typename OutT>
 __global__ void __launch_bounds__(256) nova_splitk_reduce_kernel(const SplitKReduce r) {
   griddep_wait();  // launched with programmatic serialization behind the contraction that writes the partials
-  const int64_t n = r.M * r.N;
+  const int64_t quads = r.ldp >> 2;
+  const int64_t n = r.M * quads;
   const int64_t plane = r.M * r.ldp;
   OutT* c = static_cast<OutT*>(r.C);
   const OutT* bias = static_cast<const OutT*>(r.bias);
   const OutT* res = static_cast<const OutT*>(r.residual);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t m = i / r.N, col = i - m * r.N;
-    const float* pp = r.partial + m * r.ldp + col;
-    float v = pp[0];
-    for (int32_t s = 1; s < r.ranges; ++s) v += pp[s * plane];
-    if (r.init == NOVA_B200_INIT_LN_FOLD) {
-      // v = rstd_m * (acc - mean_m * c_n) + d_n: bias = the fp32 arrays c then d, residual = {mean, rstd} per row
-      const float* cd = static_cast<const float*>(r.bias);
-      const float2 st = static_cast<const float2*>(r.residual)[m];
-      v = fmaf(st.y, fmaf(-st.x, cd[col], v), cd[r.N + col]);
+    const int64_t m = i / quads, col = (i - m * quads) << 2;
+    if (col >= r.N) continue;
+    const float4* pp = reinterpret_cast<const float4*>(r.partial + m * r.ldp + col);
+    const int64_t plane4 = plane >> 2;
+    float4 acc = pp[0];
+    int32_t s = 1;
+    for (; s + 3 < r.ranges; s += 4) {   // ascending range order, four loads in flight
+      const float4 q0 = pp[s * plane4], q1 = pp[(s + 1) * plane4], q2 = pp[(s + 2) * plane4], q3 = pp[(s + 3) * plane4];
+      acc.x = (((acc.x + q0.x) + q1.x) + q2.x) + q3.x;
+      acc.y = (((acc.y + q0.y) + q1.y) + q2.y) + q3.y;
+      acc.z = (((acc.z + q0.z) + q1.z) + q2.z) + q3.z;
+      acc.w = (((acc.w + q0.w) + q1.w) + q2.w) + q3.w;
     }
-    if (r.init == NOVA_B200_INIT_BIAS_ROW || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(bias[col]);
-    if (r.init == NOVA_B200_INIT_RESIDUAL_FULL || r.init == NOVA_B200_INIT_BIAS_AND_RESIDUAL) v += to_f32<OutT>(res[m * r.ldr + col]);
-    if (r.init == NOVA_B200_INIT_FROM_C) v += to_f32<OutT>(c[m * r.ldc + col]);
-    if (r.act == NOVA_B200_ACT_RELU) v = fmaxf(v, 0.0f);
-    else if (r.act == NOVA_B200_ACT_GELU_TANH) v = gelu_tanh_f32(v);
-    else if (r.act == NOVA_B200_ACT_GELU_TANH_GRAD) v *= gelu_tanh_grad_f32(to_f32<OutT>(res[m * r.ldr + col]));
-    c[m * r.ldc + col] = from_f32<OutT>(v);
+    for (; s < r.ranges; ++s) {
+      const float4 q = pp[s * plane4];
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (col + e < r.N) c[m * r.ldc + col + e] = from_f32<OutT>(splitk_finish<OutT>(r, v[e], m, col + e, bias, res, c));
   }
 }
 

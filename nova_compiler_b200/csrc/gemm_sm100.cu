@@ -200,7 +200,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     const int64_t pf = options().prefetch.load();
     plan->prefetch_dist = pf >= 0 ? static_cast<int>(std::min<int64_t>(pf, 64)) : 0;
   }
-  // Split K: one matrix product whose output tiles fill less than a quarter of the SMs (weight gradients: small M and
+  // Split K: one matrix product whose output tiles fill at most half of the SMs (weight gradients: small M and
   // N, K = the token count; the small f32 product), or whose last wave is mostly empty while K is very long.  The K
   // ranges run as the batches of the same kernel into fp32 partials in scratch; nova_splitk_reduce_kernel adds them in
   // range order and applies init / activation / rounding exactly once.  Results differ from the unsplit product in the
@@ -213,7 +213,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     int64_t want = 1;
     if (allow_split_k && opt != 0 && a->batch == 1 && !pair && both_tma && tiles > 0) {
       if (opt >= 2) want = opt;
-      else if (tiles * 4 <= sms && kb >= 16) want = std::min<int64_t>(8, sms / tiles);
+      else if (tiles * 2 <= sms && kb >= 16) want = std::min<int64_t>(8, sms / tiles);
       else if (kb >= 256 && tiles < 4 * sms) {
         const double eff1 = static_cast<double>(tiles) / (waves(tiles, sms) * sms);
         if (eff1 < 0.72) {
@@ -760,7 +760,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   {
     const SplitKReduce& r = pr->splitk;
     cudaLaunchConfig_t cfg = {};
-    const int64_t want = (r.M * r.N + 255) / 256;
+    const int64_t want = (r.M * (r.ldp / 4) + 255) / 256;
     cfg.gridDim = dim3(static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8))), 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = stream;
