@@ -62,9 +62,9 @@ struct GemmKernelParams {
   int64_t ldc, stride_c, ldr, stride_r;
   int32_t act, init, out_dtype, vec_store;
   int32_t prefetch_dist;  // pair kernel: ring stages the L2 prefetch cursor runs ahead of the loads (0 = none)
-  // Split K: "batch" s of the launch is the K range [s * split_k_len, (s + 1) * split_k_len) of ONE matrix product (both
-  // batch multipliers are 0 then); a range that runs past K reads zeros from the tensor maps.  0 = not split.
-  int32_t split_k_len;
+  // Split K: launch batch b * split_k_ranges + s is the K range [s * split_k_len, (s + 1) * split_k_len) of operand
+  // batch b; a range that runs past K reads zeros from the tensor maps.  split_k_ranges <= 1 = not split.
+  int32_t split_k_len, split_k_ranges;
   uint32_t* status;
   // multi-GPU push: every finished output box is also stored into these peers' matrices (same pitch and batch
   // stride as C), with plain 16-byte stores over NVLink
@@ -587,7 +587,10 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
       for (int32_t tile = blockIdx.x; ok && tile < p.tiles; tile += gridDim.x) {
         const TileCoord t = decode_tile(p, tile);
         const int m0 = t.m_blk * kBlockM, n0 = t.n_blk * kBlockN;
-        const int za = t.batch * p.a_batch_mul, zb = t.batch * p.b_batch_mul;
+        // a split product: launch batch index = operand batch * ranges + range (see split_k_len)
+        const int ob = p.split_k_ranges > 1 ? t.batch / p.split_k_ranges : t.batch;
+        const int k_first = p.split_k_ranges > 1 ? (t.batch - ob * p.split_k_ranges) * p.split_k_len : 0;
+        const int za = ob * p.a_batch_mul, zb = ob * p.b_batch_mul;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -595,7 +598,7 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
           const uint32_t stage = smem_base + s * L::kStageBytes;
           const uint32_t bar = full_bar(s);
           mbar_arrive_expect_tx(bar, expect);
-          const int k0 = t.batch * p.split_k_len + kb * kBlockK;  // (a K range of a split product: see split_k_len)
+          const int k0 = k_first + kb * kBlockK;
 #pragma unroll
           for (int term = 0; term < kOpTerms; ++term) {
             if (!p.loader_a) {
@@ -851,11 +854,11 @@ __global__ void nova_repitch_kernel(const RepitchOperand oa, const RepitchOperan
 // Second half of a K-split product: C[m, n] = round(act(init + sum over ranges of partial[s][m][n])), the ranges added in
 // ascending order, init / activation exactly as the contraction's own epilogue applies them.
 struct SplitKReduce {
-  const float* partial;   // [ranges][M][ldp]
+  const float* partial;   // [batch][ranges][M][ldp]
   void* C;
   const void* bias;
   const void* residual;
-  int64_t M, N, ldp, ldc, ldr;
+  int64_t M, N, ldp, ldc, ldr, batch, stride_c, stride_r;
   int32_t ranges, init, act, out_dtype;
 };
 
@@ -883,16 +886,20 @@ template <typename OutT>
 __global__ void __launch_bounds__(256) nova_splitk_reduce_kernel(const SplitKReduce r) {
   griddep_wait();  // launched with programmatic serialization behind the contraction that writes the partials
   const int64_t quads = r.ldp >> 2;
-  const int64_t n = r.M * quads;
+  const int64_t per_batch = r.M * quads;
+  const int64_t n = r.batch * per_batch;
   const int64_t plane = r.M * r.ldp;
-  OutT* c = static_cast<OutT*>(r.C);
   const OutT* bias = static_cast<const OutT*>(r.bias);
-  const OutT* res = static_cast<const OutT*>(r.residual);
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t m = i / quads, col = (i - m * quads) << 2;
+    const int64_t b = i / per_batch, ib = i - b * per_batch;
+    const int64_t m = ib / quads, col = (ib - m * quads) << 2;
     if (col >= r.N) continue;
-    const float4* pp = reinterpret_cast<const float4*>(r.partial + m * r.ldp + col);
+    OutT* c = static_cast<OutT*>(r.C) + b * r.stride_c;
+    // (the LN fold keeps per-row statistics, not a matrix, behind `residual`; it is never batched)
+    const OutT* res = r.init == NOVA_B200_INIT_LN_FOLD ? static_cast<const OutT*>(r.residual)
+                                                        : static_cast<const OutT*>(r.residual) + b * r.stride_r;
+    const float4* pp = reinterpret_cast<const float4*>(r.partial + b * r.ranges * plane + m * r.ldp + col);
     const int64_t plane4 = plane >> 2;
     float4 acc = pp[0];
     int32_t s = 1;

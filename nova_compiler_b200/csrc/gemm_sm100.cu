@@ -211,7 +211,8 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
     const int64_t kb = (a->K + stage_k - 1) / stage_k;
     const int64_t tiles = pi.tiles;
     int64_t want = 1;
-    if (allow_split_k && opt != 0 && a->batch == 1 && !pair && both_tma && tiles > 0) {
+    const bool batched_ok = a->batch == 1 || (a->init != NOVA_B200_INIT_LN_FOLD && a->batch_stride_c > 0);
+    if (allow_split_k && opt != 0 && batched_ok && !pair && both_tma && tiles > 0) {
       if (opt >= 2) want = opt;
       else if (tiles * 2 <= sms && kb >= 16) want = std::min<int64_t>(8, sms / tiles);
       else if (kb >= 256 && tiles < 4 * sms) {
@@ -238,7 +239,7 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
       plan->split_len = kb_per * stage_k;
       plan->split_ldp = (a->N + 3) & ~3ll;
       plan->split_offset = (pi.scratch_bytes + 255) / 256 * 256;
-      pi.scratch_bytes = plan->split_offset + sp * a->M * plan->split_ldp * 4;
+      pi.scratch_bytes = plan->split_offset + a->batch * sp * a->M * plan->split_ldp * 4;
       pi.tiles = tiles * sp;
       pi.grid = static_cast<int32_t>(pi.tiles < sms ? pi.tiles : sms);
       pi.store_c = 0;  // the kernel writes the aligned partials; the reduce kernel writes C
@@ -510,11 +511,12 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
   if (plan.split_k > 1) {
     const int64_t sp = plan.split_k;
     p.split_k_len = static_cast<int32_t>(plan.split_len);
+    p.split_k_ranges = static_cast<int32_t>(sp);
     p.k_blocks = static_cast<int32_t>(plan.split_len / stage_k);
-    p.batch = static_cast<int32_t>(sp);
-    p.a_batch_mul = p.b_batch_mul = 0;
+    p.batch = static_cast<int32_t>(a->batch * sp);
     float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + plan.split_offset);
     out->splitk = SplitKReduce{partial, a->C, a->bias, a->residual, a->M, a->N, plan.split_ldp, a->ldc, a->ldr,
+                               a->batch, a->batch_stride_c, a->batch_stride_r,
                                static_cast<int32_t>(sp), a->init, a->act, a->dtype_c};
     p.C = partial; p.ldc = plan.split_ldp; p.stride_c = a->M * plan.split_ldp;
     p.bias = nullptr; p.residual = nullptr; p.init = NOVA_B200_INIT_ZERO; p.act = NOVA_B200_ACT_NONE;
@@ -549,7 +551,7 @@ int32_t prepare(DeviceContext* ctx, const nova_b200_gemm_args* a, void* scratch,
   if (p.vec_store && plan.split_k > 1) {
     // (columns N .. ldp of a partial row may be written by the last 16-byte chunk: they are padding)
     st = encode_operand_map(ctx, &maps[4], p.C, 4, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->M, plan.split_ldp, plan.split_ldp,
-                            plan.split_k, a->M * plan.split_ldp, static_cast<uint32_t>(kSwizzleBytes / 4), 32u,
+                            a->batch * plan.split_k, a->M * plan.split_ldp, static_cast<uint32_t>(kSwizzleBytes / 4), 32u,
                             CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != NOVA_B200_OK) return st;
   } else if (p.vec_store) {
@@ -760,7 +762,7 @@ int32_t gemm_launch(DeviceContext* ctx, const nova_b200_gemm_args* a, cudaStream
   {
     const SplitKReduce& r = pr->splitk;
     cudaLaunchConfig_t cfg = {};
-    const int64_t want = (r.M * (r.ldp / 4) + 255) / 256;
+    const int64_t want = (r.batch * r.M * (r.ldp / 4) + 255) / 256;
     cfg.gridDim = dim3(static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(want, ctx->sm_count * 8))), 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = stream;

@@ -565,6 +565,30 @@ def test_split_k_matches_the_unsplit_product(cuda, oracle, lib, dt, trans_a, tra
         L.set_option("split_k", -1)
 
 
+@pytest.mark.parametrize("dt", ["f32", "f16"])
+def test_split_k_of_batched_products(cuda, oracle, dt):
+    """K ranges of a BATCHED product: launch batch b * ranges + s; bias, residual and a shared B (batch stride 0)."""
+    torch = cuda
+    from nova_compiler_b200 import _lib as L
+    rng = np.random.default_rng(73)
+    B, M, N, K = 3, 130, 200, 1500
+    a = rand_bits(oracle, rng, (B, M, K), dt)
+    bias = rand_bits(oracle, rng, (N,), dt)
+    res = rand_bits(oracle, rng, (B, M, N), dt)
+    try:
+        for b in (rand_bits(oracle, rng, (B, K, N), dt), rand_bits(oracle, rng, (K, N), dt)):
+            want = oracle.gemm(a, b, dtype_in=dt, bias=bias, residual=res, act="relu")
+            got = {}
+            for ranges in (0, 5, -1):
+                L.set_option("split_k", ranges)
+                got[ranges] = run_gpu(torch, a, b, dt, bias=bias, residual=res, act="relu")
+                # (forced to one chain of 1500, the f32 product is ~1.1e-5 off: what the ranges are for)
+                check(oracle, got[ranges], want, dt, tol=3e-5 if (dt == "f32" and ranges == 0) else None)
+            assert oracle.rel_fro(oracle.from_bits(got[5], dt), oracle.from_bits(got[0], dt)) <= (2e-5 if dt == "f32" else 2e-3)
+    finally:
+        L.set_option("split_k", -1)
+
+
 def test_f32_error_does_not_grow_with_k(cuda):
     """The tensor core adds into its fp32 accumulator with truncation, so one long accumulation chain drifts: the
     unsplit 3xTF32 product is 5.7e-5 off float64 at K = 8192 and 3.5e-4 at K = 50304.  With K in ranges of at most
@@ -573,13 +597,13 @@ def test_f32_error_does_not_grow_with_k(cuda):
     from nova_compiler_b200 import ops
     g = torch.Generator(device="cuda")
     g.manual_seed(77)
-    for M, N, K in [(200, 150, 1000), (256, 384, 8191), (128, 128, 50304)]:
-        a = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
-        b = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
-        c = ops.gemm(a[None], b[None])[0].double()
+    for Bn, M, N, K in [(1, 200, 150, 1000), (1, 256, 384, 8191), (1, 128, 128, 50304), (4, 256, 192, 8192)]:
+        a = torch.rand(Bn, M, K, device="cuda", generator=g) * 2 - 1
+        b = torch.rand(Bn, K, N, device="cuda", generator=g) * 2 - 1
+        c = ops.gemm(a, b).double()
         truth = a.double() @ b.double()
         err = float((c - truth).norm() / truth.norm())
-        assert err <= 1e-5, (M, N, K, err)
+        assert err <= 1e-5, (Bn, M, N, K, err)
 
 
 def test_split_k_is_planned_for_few_tiles_only(cuda, lib):
