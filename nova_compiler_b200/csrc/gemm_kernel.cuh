@@ -327,7 +327,7 @@ __device__ __forceinline__ void epilogue_push_box(const GemmKernelParams& p, con
 // One epilogue warp drains kCols columns of its 32 accumulator rows, one 128-byte-wide box at a time.
 // kBoxes staging boxes per warp: with two, the TMA store of one box overlaps the whole of the next; with
 // one, it overlaps only the next box's first tensor-memory load and its arithmetic.
-template <typename OutT, int kCols, int kBoxes = 2>
+template <typename OutT, int kCols, int kBoxes = 2, int kSecondAcc = 0>
 __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const CUtensorMap* tmap_c, uint32_t taddr,
                                               uint8_t* staging, uint32_t& box_iter, int lane, int32_t batch,
                                               int32_t row0, int32_t n0, long long* waits = nullptr) {
@@ -347,6 +347,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmKernelParams& p, const C
       long long t0 = 0;
       if (waits) t0 = clock64();
       tmem_ld_32x32(taddr + c * kColsPerBox + h * 32, r);
+      if (kSecondAcc > 0) {
+        // kSecondAcc columns further: the accumulator of the small 3xTF32 terms, added here with rounding
+        uint32_t r2[32];
+        tmem_ld_32x32(taddr + kSecondAcc + c * kColsPerBox + h * 32, r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+      }
       tmem_ld_wait();
       if (waits) waits[1] += clock64() - t0;
       float v[32];
@@ -527,7 +535,10 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
   constexpr int kBlockK = kElemsPerRow;
   constexpr int kUmmaK = 32 / kElemBytes;
   constexpr int kKSteps = kBlockK / kUmmaK;  // 4
-  constexpr uint32_t kTmemCols = 2 * kBlockN < 32 ? 32 : 2 * kBlockN;
+  // 3xTF32: the two small products (lo x hi, hi x lo) go to accumulators of their own, so that the big one takes a third
+  // of the additions: the tensor core adds with truncation and the drift of a sum grows with its number of additions.
+  constexpr bool kTwoAcc = kTerms == 3;
+  constexpr uint32_t kTmemCols = (kTwoAcc ? 4 : 2) * kBlockN < 32 ? 32 : (kTwoAcc ? 4 : 2) * kBlockN;
   static_assert(kBlockN % 32 == 0 && kBlockN >= 32 && kBlockN <= 256, "UMMA N / epilogue chunking");
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   static_assert(L::kDynamicBytes <= 227 * 1024, "shared memory budget");
@@ -659,9 +670,9 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
             } else {
               const uint64_t a_lo = make_smem_desc(a_stage + L::kATile + k * p.a_kstep, p.a_desc_lbo, p.a_desc_hi);
               const uint64_t b_lo = make_smem_desc(b_stage + L::kBTile + k * p.b_kstep, p.b_desc_lbo, p.b_desc_hi);
-              umma_tf32(d_tmem, a_lo, b_hi, p.idesc, first);  // small terms first
-              umma_tf32(d_tmem, a_hi, b_lo, p.idesc, 1u);
-              umma_tf32(d_tmem, a_hi, b_hi, p.idesc, 1u);
+              umma_tf32(d_tmem + 2 * kBlockN, a_lo, b_hi, p.idesc, first);  // the small terms: their own accumulator
+              umma_tf32(d_tmem + 2 * kBlockN, a_hi, b_lo, p.idesc, 1u);
+              umma_tf32(d_tmem, a_hi, b_hi, p.idesc, first);
             }
           }
           umma_commit(empty_bar(s));  // stage reusable once these MMAs have read it
@@ -689,11 +700,11 @@ nova_gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid
       const int32_t n0 = t.n_blk * kBlockN + cg * kColsPerWarp;
       const uint32_t taddr = tmem_base + acc * kBlockN + cg * kColsPerWarp + (static_cast<uint32_t>(q * 32) << 16);
       if (p.out_dtype == NOVA_B200_BF16)
-        epilogue_tile<__nv_bfloat16, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__nv_bfloat16, kColsPerWarp, 2, kTwoAcc ? 2 * kBlockN : 0>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       else if (p.out_dtype == NOVA_B200_F16)
-        epilogue_tile<__half, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<__half, kColsPerWarp, 2, kTwoAcc ? 2 * kBlockN : 0>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       else
-        epilogue_tile<float, kColsPerWarp>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
+        epilogue_tile<float, kColsPerWarp, 2, kTwoAcc ? 2 * kBlockN : 0>(p, &tmap_c, taddr, staging, box_iter, lane, t.batch, row0, n0);
       tc_fence_before_sync();
       mbar_arrive(tmem_empty_bar(acc));
     }

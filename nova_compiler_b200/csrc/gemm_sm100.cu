@@ -226,9 +226,10 @@ int32_t validate_and_plan(const nova_b200_gemm_args* a, Plan* plan, int sm_count
         }
       }
       // f32 through 3xTF32: the tensor core adds every product group into its fp32 accumulator with truncation, a bias
-      // that grows with the length of the chain (measured: relative error ~7e-9 x K, 5.7e-5 at K = 8192, where cuBLAS
-      // fp32 has 5e-7).  Ranges of at most 1024 keep one chain short; the partials are then added with rounding.
-      if (opt < 0 && plan->terms == 3) want = std::max<int64_t>(want, (a->K + 1023) / 1024);
+      // that grows with the length of the chain (measured against float64: ~2.3e-9 x K with the small terms in their
+      // own accumulator, ~7e-9 x K before that; cuBLAS fp32 stays at 3-8e-7).  Ranges of at most 2048 keep one chain
+      // under 5e-6; the partials are then added with rounding.
+      if (opt < 0 && plan->terms == 3) want = std::max<int64_t>(want, (a->K + 2047) / 2048);
     }
     int64_t sp = std::min<int64_t>(want, 64);
     while (sp > 1 && (kb + sp - 1) / sp < 4) --sp;   // at least four k-blocks per range
