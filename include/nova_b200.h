@@ -494,7 +494,9 @@ int32_t nova_b200_module_signature(const nova_b200_module* m, const char* func, 
 /* Human-readable list of the calls a run will make, after fusion.  Needs no GPU. */
 int32_t nova_b200_module_plan(const nova_b200_module* m, const char* func, char* buf, int64_t buflen);
 /* Runs @func: `args` in signature order, `results` caller-provided buffers in return order.  Intermediates
- * are allocated with cudaMallocAsync on `stream` and freed when the call returns (stream-ordered). */
+ * are allocated with cudaMallocAsync on `stream` and freed when the call returns (stream-ordered).  The first run on a
+ * device raises the release threshold of that device's default memory pool from 0 (if the application left it there)
+ * so that the freed blocks are reused by the next run instead of going back to the driver at every synchronisation. */
 int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const nova_b200_tensor* args, int32_t n_args,
                              nova_b200_tensor* results, int32_t n_results, void* stream);
 

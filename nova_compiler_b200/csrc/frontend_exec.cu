@@ -8,6 +8,7 @@
 #include <algorithm>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <memory>
 #include <vector>
@@ -595,6 +596,29 @@ int32_t nova_b200_module_run(const nova_b200_module* m, const char* func, const 
   if ((n_args && !args) || (n_results && !results)) return fail(NOVA_B200_ERR_INVALID_ARG, "module_run: null tensor list");
   int32_t st = NOVA_B200_OK;
   if (!current_context(&st)) return st;
+  {
+    // Intermediates come from the device's default stream-ordered pool.  With the pool's release threshold at its
+    // default of 0 every synchronisation hands the freed blocks back to the driver and the next run allocates them
+    // again (measured on the GPT fixture: 10.4 ms per step against 8.1 ms): keep them, unless the application has
+    // already chosen a threshold of its own.
+    static std::mutex mu;
+    static std::vector<int> done;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+      std::lock_guard<std::mutex> lock(mu);
+      if (std::find(done.begin(), done.end(), dev) == done.end()) {
+        done.push_back(dev);
+        cudaMemPool_t pool = nullptr;
+        uint64_t cur = 0;
+        if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess &&
+            cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &cur) == cudaSuccess && cur == 0) {
+          uint64_t keep = ~0ull;
+          cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+        cudaGetLastError();
+      }
+    }
+  }
   fe::Exec ex{*f, p, static_cast<cudaStream_t>(stream), {}, {}};
   ex.count_gemm_reads();
   for (int32_t i = 0; i < n_args; ++i) {
