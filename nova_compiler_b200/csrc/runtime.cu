@@ -235,6 +235,8 @@ int32_t nova_b200_shutdown(void) {
       if (sb.second.ptr) cudaFree(sb.second.ptr);
     for (void* r : c->retired_scratch) cudaFree(r);
     if (c->staging) cudaFree(c->staging);
+    for (const DeviceContext::PreSplit& e : c->presplit) cudaFree(e.hi);  // halves nobody released (hi is the allocation's base)
+    c->presplit.clear();
     if (c->s_in) {
       cudaStreamDestroy(c->s_in); cudaStreamDestroy(c->s_comp); cudaStreamDestroy(c->s_out);
       for (int i = 0; i < kHostEvents; ++i) { cudaEventDestroy(c->ev_in[i]); cudaEventDestroy(c->ev_comp[i]); }
